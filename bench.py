@@ -1,0 +1,399 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--m M]
+
+Workload (BASELINE.json configs[1], the configuration the metric is quoted on): the four
+Llama-3-8B projection shapes in Q4_K -- 4096->6144 (QKV), 4096->4096 (O), 4096->28672 (gate|up),
+14336->4096 (down) -- at decode batch M (default 1), for 32 layers with distinct weights.  One step
+is one pass over all 128 linears (3.93 GB of packed weights, far larger than the 126 MB L2, so every
+step streams from HBM).  Weights are N(0, 0.02) quantized with the package encoder, activations
+N(0, 1) bf16, all seeded and synthetic.
+
+Metric: Q4_K dequant-GEMV GB/s = algorithmic bytes (packed weights + x + y) / time.
+N > 1 (torchrun, one rank per GPU): each linear is tensor-parallel -- QKV and gate|up split by
+output rows, O and down by input columns followed by an NCCL all-reduce -- total work fixed
+("strong" scaling).
+
+`--impl reference` times the reference's CPU implementation of the same operator on the host cores:
+ATen linear on dequantized bf16 weights (what Linear.forward, linear.nim:45-57, calls), on a bounded
+sample of the workload (one layer per step).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPES = [("qkv", 4096, 6144), ("o", 4096, 4096), ("gate_up", 4096, 28672), ("down", 14336, 4096)]
+N_LAYERS = 32
+Q4K_BYTES_PER_256 = 144
+
+
+def algorithmic_bytes(m: int, k: int, n: int, x_bytes: int = 2, y_bytes: int = 2) -> int:
+    return n * (k // 256) * Q4K_BYTES_PER_256 + m * k * x_bytes + m * n * y_bytes
+
+
+class ClockSampler:
+    """Polls NVML for SM clock and throttle reasons while the timed region runs (read-only)."""
+
+    REASONS = {
+        0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+        0x80: "hw_power_brake_slowdown",
+    }
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def start(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+        med = int(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def visible_physical_index(local_index: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_index])
+        except (ValueError, IndexError):
+            pass
+    return local_index
+
+
+# --------------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: ATen linear on the host cores (and the packed-bytes CPU port)
+# --------------------------------------------------------------------------------------------------
+def cpu_layer_sample(m: int, seed: int = 2000):
+    """One layer's four linears: dequantized bf16 weights (reference path) and packed blocks (port)."""
+    import oracle  # CPU checker; used here only to decode blocks for the CPU baseline
+
+    from tattletale_b200 import quantize as Q
+
+    layers = []
+    for idx, (_, k, n) in enumerate(SHAPES):
+        g = torch.Generator().manual_seed(seed + idx)
+        w = torch.randn(n, k, generator=g) * 0.02
+        blocks = Q.quantize(Q.FMT_Q4_K, w).numpy()
+        w_deq = torch.from_numpy(oracle.dequantize(oracle.Q4_K, blocks)).to(torch.bfloat16)
+        x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+        layers.append((k, n, blocks, w_deq, x))
+    return layers
+
+
+def time_cpu_reference(m: int, steps: int, warmup: int, budget_s: float = 25.0):
+    """Returns (GB/s of the metric, ms per step, cores, port GB/s) for one-layer steps on the host."""
+    import oracle
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    layers = cpu_layer_sample(m)
+    step_bytes = sum(algorithmic_bytes(m, k, n) for k, n, *_ in layers)
+
+    def aten_step():
+        for _, _, _, w_deq, x in layers:
+            torch.nn.functional.linear(x, w_deq)
+
+    def port_step():
+        for _, _, blocks, _, x in layers:
+            oracle.linear(oracle.Q4_K, blocks, x.view(torch.int16).numpy().view(np.uint16), oracle.BF16, fast=True)
+
+    def run(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        t0 = time.perf_counter()
+        done = 0
+        for _ in range(steps):
+            fn()
+            done += 1
+            if time.perf_counter() - t0 > budget_s:
+                break
+        return (time.perf_counter() - t0) / done, done
+
+    t_aten, done = run(aten_step, steps, warmup)
+    t_port, _ = run(port_step, max(3, min(steps, 10)), 1)
+    return step_bytes / t_aten / 1e9, t_aten * 1e3, cores, step_bytes / t_port / 1e9, done
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = min(args.steps, 50)
+    gbs, ms, cores, port_gbs, done = time_cpu_reference(args.m, steps, min(args.warmup, 3))
+    sample = (f"one Llama-3-8B layer (4 linears, M={args.m}) per step, {done} steps; ATen linear on "
+              f"dequantized bf16 weights, {cores} threads")
+    line = {
+        "impl": "reference", "metric": "Q4_K dequant-GEMV GB/s", "value": round(gbs, 3), "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": done, "warmup": min(args.warmup, 3), "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args.m, args.gpus),
+        "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": "reference",
+                         "sample": sample, "port_value": round(port_gbs, 3)},
+        "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(m: int, gpus: int):
+    return {
+        "workload": f"Llama-3-8B projection shapes, Q4_K, M={m} decode GEMV, {N_LAYERS} layers x 4 linears",
+        "shapes_k_to_n": [[k, n] for _, k, n in SHAPES], "M": m, "layers": N_LAYERS,
+        "parallelism": "single GPU" if gpus == 1 else f"tp{gpus} (column/row split, NCCL all-reduce)",
+        "l2": "3.93 GB of weights per step, larger than L2: every step streams from HBM",
+    }
+
+
+# --------------------------------------------------------------------------------------------------
+# our arm
+# --------------------------------------------------------------------------------------------------
+def build_layers(ttq, ctx, dev, rank, world, m):
+    """Quantize on the device, repack through the C ABI.  Returns per-layer lists of (linear, x, y)."""
+    from tattletale_b200 import quantize as Q
+
+    layers = []
+    for layer in range(N_LAYERS):
+        entry = []
+        for idx, (name, k, n) in enumerate(SHAPES):
+            g = torch.Generator(device=dev).manual_seed(2000 + idx + 16 * layer)
+            if world == 1:
+                nl, kl = n, k
+            elif name in ("qkv", "gate_up"):
+                nl, kl = n // world, k
+            else:
+                nl, kl = n, k // world
+            # every rank draws its own slice; the full matrix is never materialised
+            w = torch.randn(nl, kl, generator=g, device=dev) * 0.02
+            blocks = Q.quantize(Q.FMT_Q4_K, w)
+            lin = ttq.QuantLinear(ctx, ttq.FMT_Q4_K, blocks, kl)
+            del w, blocks
+            x = torch.randn(m, kl, generator=g, device=dev).to(torch.bfloat16)
+            y = torch.empty(m, nl, dtype=torch.bfloat16, device=dev)
+            entry.append((name, lin, x, y))
+        layers.append(entry)
+    return layers
+
+
+def ours_arm(args):
+    import tattletale_b200 as ttq
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the quantized-linear path has no CPU implementation")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    m = args.m
+    ctx = ttq.Context(local_rank)
+    layers = build_layers(ttq, ctx, dev, rank, world, m)
+    torch.cuda.synchronize()
+
+    def step():
+        for entry in layers:
+            for name, lin, x, y in entry:
+                lin.forward(x, out=y)
+                if world > 1 and name in ("o", "down"):
+                    dist.all_reduce(y)
+
+    # launches per step, counted on an eager step
+    torch.cuda.synchronize()
+    c0 = ctx.launch_count
+    step()
+    torch.cuda.synchronize()
+    launches_per_step = ctx.launch_count - c0
+
+    graph = None
+    if not args.no_graph:
+        try:
+            stream = torch.cuda.Stream()
+            stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(stream):
+                step()
+            torch.cuda.current_stream().wait_stream(stream)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+        except Exception as exc:  # capture refused (e.g. a collective that cannot be captured): run eagerly
+            print(f"[bench] CUDA graph capture failed, running eagerly: {exc}", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
+    run_step = graph.replay if graph is not None else step
+
+    for _ in range(max(args.warmup, 3)):
+        run_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(visible_physical_index(local_rank))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.start()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        run_step()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    if world > 1:
+        dist.barrier()
+    ms_total = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    step_bytes = N_LAYERS * sum(algorithmic_bytes(m, k, n) for _, k, n in SHAPES)  # whole job, all ranks
+    value = step_bytes / (ms_step * 1e-3) / 1e9
+
+    # ---- end to end: host buffers through the C-ABI host entry point, copies inside the timed region
+    e2e = None
+    h2d = d2h = 0
+    if world == 1:
+        host = []
+        for entry in layers:
+            for name, lin, x, y in entry:
+                xh = x.cpu().pin_memory()
+                yh = torch.empty(y.shape, dtype=y.dtype).pin_memory()
+                host.append((lin, xh, yh))
+                h2d += xh.numel() * xh.element_size()
+                d2h += yh.numel() * yh.element_size()
+        e2e_steps = max(3, min(args.steps, 50))
+        for lin, xh, yh in host:
+            lin.forward_host(xh, yh)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            for lin, xh, yh in host:
+                lin.forward_host(xh, yh)
+        torch.cuda.synchronize()
+        e2e_s = (time.perf_counter() - t0) / e2e_steps
+        e2e = {"value": round(step_bytes / e2e_s / 1e9, 3), "unit": "GB/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_s * 1e3, 4), "steps": e2e_steps,
+               "api": "ttq_linear_forward_host (one call per linear: H2D, kernel, D2H, sync)"}
+
+    # ---- per-shape breakdown (device-resident, cold L2: the 32 layers' copies are rotated)
+    per_shape = {}
+    if world == 1:
+        for idx, (name, k, n) in enumerate(SHAPES):
+            items = [layers[l][idx] for l in range(N_LAYERS)]
+            for _, lin, x, y in items:
+                lin.forward(x, out=y)
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 4
+            a.record()
+            for _ in range(reps):
+                for _, lin, x, y in items:
+                    lin.forward(x, out=y)
+            b.record()
+            torch.cuda.synchronize()
+            us = a.elapsed_time(b) * 1e3 / (reps * N_LAYERS)
+            per_shape[f"{k}x{n}"] = {"us": round(us, 3), "gbs": round(algorithmic_bytes(m, k, n) / us / 1e3, 1)}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    peak_kind = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650"
+    gemv_launches = N_LAYERS * len(SHAPES)
+    roofline = {
+        "bound": "hbm", "achieved": round(value / world, 2), "peak": peak, "unit": "GB/s",
+        "frac": round(value / world / peak, 4), "traffic": None, "peak_source": peak_kind,
+        "kernel": "gemv_kernel<Q4_K, fused x-prep> (M<=2) / xprep + gemv_kernel (M>2)",
+        "avg_launch_us": round(ms_step * 1e3 / gemv_launches, 3),
+        "algorithmic_bytes_per_launch": step_bytes // gemv_launches,
+        "frac_of_nominal_8TBs": round(value / world / 8000.0, 4),
+    }
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu_baseline:
+        gbs, ms, cores, port_gbs, done = time_cpu_reference(m, 20, 2, budget_s=12.0)
+        cpu_baseline = {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": "reference",
+                        "sample": f"one layer (4 linears, M={m}) x {done} steps, ATen linear on dequantized bf16 weights",
+                        "port_value": round(port_gbs, 3), "port_kind": "oracle fused dequant-dot on packed blocks"}
+    line = {
+        "metric": "Q4_K dequant-GEMV GB/s", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 5),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "arithmetic": "u8|s8 x s8 -> s32 tensor-core dot per sub-block, fp32 scales",
+        "data": "synthetic", "config": workload_config(m, world), "roofline": roofline, "cpu_baseline": cpu_baseline,
+        "e2e": e2e, "gpu_launches": int(launches_per_step * args.steps), "launches_per_step": int(launches_per_step),
+        "cuda_graph": graph is not None, "clocks": clocks, "per_shape": per_shape,
+        "decode_linears_tokens_per_s": round(m / (ms_step * 1e-3), 1),
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=500)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=1, help="decode batch (rows of x)")
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        ours_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,159 @@
+/*
+ * ttq.h -- C ABI of the B200 (sm_100a) quantized-linear library.
+ *
+ * This is the boundary a host program binds against (Nim `{.importc, cdecl.}`, C++, ctypes).  Plain
+ * pointers and sizes only: no torch, no C++ types.  Every function returns a ttq_status (0 = OK),
+ * never throws and never aborts; a human-readable reason for the last failure on a context is
+ * available from ttq_last_error().
+ *
+ * The operator replaced is the reference's `Linear` (workspace/transformers/src/layers/linear.nim):
+ *   Linear.init(weight[out,in], bias)   -> ttq_weight_create*()      (linear.nim:29-43)
+ *   Linear.forward(x[..., in])          -> ttq_linear_forward()       (linear.nim:45-57)
+ * whose only callee is ATen's linear (workspace/libtorch/src/abi/neural_nets.nim:64-81).  Here the
+ * weight is a block-quantized matrix (GGUF-style Q8_0 / Q4_K / Q6_K) that the library repacks once,
+ * at creation, into a tiled device layout; forward never allocates.
+ *
+ * Conventions
+ *  - A ttq_ctx is bound to ONE CUDA device and is not thread-safe: one context per host thread and
+ *    device, as in the reference's single-threaded model.
+ *  - The caller owns x, y, bias and the stream.  The library owns repacked weights and its scratch.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ *  - Device-pointer entry points are asynchronous on `stream`; *_host entry points copy in, run,
+ *    copy out and synchronise before returning.
+ *  - Shapes: W is [N = out_features][K = in_features]; x is [M][ldx] (ldx >= K, in elements);
+ *    y is [M][ldy] (ldy >= N).  K must be a multiple of the format's block length.
+ */
+#ifndef TTQ_H
+#define TTQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define TTQ_API __attribute__((visibility("default")))
+#else
+#define TTQ_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ttq_ctx ttq_ctx;
+typedef struct ttq_weight ttq_weight;
+
+typedef enum ttq_status {
+    TTQ_OK = 0,
+    TTQ_ERR_INVALID_ARG = 1, /* null pointer, negative size, unknown enum value */
+    TTQ_ERR_SHAPE = 2,       /* K not a multiple of the block length, nbytes mismatch, ld too small */
+    TTQ_ERR_UNSUPPORTED = 3, /* valid request this build cannot serve */
+    TTQ_ERR_CUDA = 4,        /* a CUDA runtime call failed; see ttq_last_error */
+    TTQ_ERR_OOM = 5,         /* device or host allocation failed */
+    TTQ_ERR_DEVICE = 6,      /* no sm_100 device / wrong device current */
+    TTQ_ERR_LIMIT = 7        /* request exceeds a fixed capacity (scratch, static buffers) */
+} ttq_status;
+
+typedef enum ttq_format {
+    TTQ_FMT_Q8_0 = 0, /* 32 weights / 34 B: fp16 d, 32 x int8 */
+    TTQ_FMT_Q4_K = 1, /* 256 weights / 144 B: fp16 d, fp16 dmin, 12 B of 6-bit scales+mins, 128 B nibbles */
+    TTQ_FMT_Q6_K = 2  /* 256 weights / 210 B: 128 B low nibbles, 64 B high 2 bits, 16 x int8 scales, fp16 d */
+} ttq_format;
+
+typedef enum ttq_dtype { TTQ_DT_BF16 = 0, TTQ_DT_F16 = 1, TTQ_DT_F32 = 2 } ttq_dtype;
+
+/* Which slice of the full [N][K] matrix a rank keeps (tensor parallelism).  There is no reference
+ * counterpart (the reference has no parallelism); the split follows the usual column/row scheme:
+ *  COLUMN       rows    [rank*N/world, (rank+1)*N/world)                    -- no collective after
+ *  COLUMN_GATED as COLUMN but applied to each half of a fused gate|up weight (mlp.nim:39), so the
+ *               shard is [gate_rank ; up_rank] and silu_and_mul stays local
+ *  ROW          columns [rank*K/world, (rank+1)*K/world), K/world a multiple of the block length;
+ *               outputs of all ranks must be summed (all-reduce) by the caller */
+typedef enum ttq_shard_kind {
+    TTQ_SHARD_NONE = 0,
+    TTQ_SHARD_COLUMN = 1,
+    TTQ_SHARD_COLUMN_GATED = 2,
+    TTQ_SHARD_ROW = 3
+} ttq_shard_kind;
+
+typedef struct ttq_shard {
+    int32_t kind; /* ttq_shard_kind */
+    int32_t rank;
+    int32_t world;
+} ttq_shard;
+
+/* ---- context ------------------------------------------------------------------------------ */
+
+/* Creates a context on CUDA device `device` (made current for the call).  Allocates the fixed
+ * scratch used by forward.  Fails with TTQ_ERR_DEVICE when the device is not compute capability
+ * 10.x: there is no fallback path. */
+TTQ_API ttq_status ttq_init(int device, ttq_ctx **out);
+TTQ_API ttq_status ttq_destroy(ttq_ctx *ctx);
+/* Message of the last failure on this context ("" if none).  Valid until the next call on ctx. */
+TTQ_API const char *ttq_last_error(const ttq_ctx *ctx);
+TTQ_API const char *ttq_status_string(ttq_status s);
+/* Library version, "major.minor.patch". */
+TTQ_API const char *ttq_version(void);
+
+/* ---- format facts (host only, no device needed) --------------------------------------------- */
+
+TTQ_API int64_t ttq_block_elems(ttq_format fmt); /* weights per block, 0 for an unknown format */
+TTQ_API int64_t ttq_block_bytes(ttq_format fmt); /* bytes per block,   0 for an unknown format */
+/* Bytes of canonical blocks for an [N][K] matrix (= the algorithmic weight bytes of one forward). */
+TTQ_API int64_t ttq_packed_bytes(ttq_format fmt, int64_t N, int64_t K);
+
+/* ---- weights: Linear.init (linear.nim:29-43) ------------------------------------------------ */
+
+/* host_blocks: canonical row-major blocks, [N][K / block_elems] blocks of block_bytes each (for
+ * instance a view into an mmap'ed file, cf. safetensors.nim:256-274 getMmapView); nbytes must equal
+ * ttq_packed_bytes(fmt, N, K).  The blocks are uploaded and repacked on the device into the tiled
+ * layout; the call returns after the repack finished, the host buffer may then be released.
+ * `shard` may be NULL (whole matrix); otherwise only the rank's slice is uploaded and the
+ * resulting weight has the slice's N and K. */
+TTQ_API ttq_status ttq_weight_create(ttq_ctx *ctx, ttq_format fmt, int64_t N, int64_t K, const void *host_blocks,
+                             size_t nbytes, const ttq_shard *shard, ttq_weight **out);
+/* Same, with the canonical blocks already in device memory (whole matrix).  Repack runs on
+ * `stream`; dev_blocks may be released once the stream has passed this point. */
+TTQ_API ttq_status ttq_weight_create_device(ttq_ctx *ctx, ttq_format fmt, int64_t N, int64_t K,
+                                    const void *dev_blocks, size_t nbytes, void *stream,
+                                    ttq_weight **out);
+TTQ_API ttq_status ttq_weight_destroy(ttq_weight *w);
+TTQ_API ttq_status ttq_weight_info(const ttq_weight *w, int32_t *fmt, int64_t *N, int64_t *K);
+/* Canonical (algorithmic) byte count of this weight, ttq_packed_bytes of its own N and K. */
+TTQ_API int64_t ttq_weight_bytes(const ttq_weight *w);
+
+/* Test hook: expands the tiled device layout back to canonical order, fp32 [N][ld] in device
+ * memory.  Must reproduce a CPU dequantization of the original blocks bit for bit. */
+TTQ_API ttq_status ttq_dequantize(ttq_ctx *ctx, const ttq_weight *w, float *dev_out, int64_t ld, void *stream);
+
+/* ---- forward: Linear.forward (linear.nim:45-57) -------------------------------------------- */
+
+/* y[m][n] = sum_k x[m][k] * W[n][k] (+ bias[n]).  x: bf16 or f16 device matrix; bias: NULL or a
+ * device vector of N elements of bias_dt; y: f32, bf16 or f16 device matrix.  Any M >= 0.
+ * Integer dot products are exact and scales are applied in fp32. */
+TTQ_API ttq_status ttq_linear_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_dev, ttq_dtype x_dt,
+                              int64_t M, int64_t ldx, const void *bias_dev, ttq_dtype bias_dt,
+                              void *y_dev, ttq_dtype y_dt, int64_t ldy, void *stream);
+
+/* Host-buffer form of the same call: copies x (and bias) to the device through the context's pinned
+ * staging area, runs forward, copies y back and synchronises.  x/y limited to the staging capacity
+ * (TTQ_ERR_LIMIT beyond it). */
+TTQ_API ttq_status ttq_linear_forward_host(ttq_ctx *ctx, const ttq_weight *w, const void *x_host, ttq_dtype x_dt,
+                                   int64_t M, int64_t ldx, const void *bias_host, ttq_dtype bias_dt,
+                                   void *y_host, ttq_dtype y_dt, int64_t ldy);
+
+/* ---- adjacent step: silu_and_mul (kernels/activations.nim:14-38) ---------------------------- */
+
+/* out[m][h] = silu(in[m][h]) * in[m][H + h]; in is [M][ld_in] with 2H used columns, out [M][ld_out].
+ * Same dtype in and out (bf16, f16 or f32). */
+TTQ_API ttq_status ttq_silu_and_mul(ttq_ctx *ctx, const void *in_dev, ttq_dtype dt, int64_t M, int64_t H,
+                            int64_t ld_in, void *out_dev, int64_t ld_out, void *stream);
+
+/* ---- introspection for benchmarks ----------------------------------------------------------- */
+
+/* Number of kernels this context has launched since creation (forward, repack, dequantize ...). */
+TTQ_API int64_t ttq_launch_count(const ttq_ctx *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TTQ_H */

@@ -1,0 +1,373 @@
+// C-ABI entry points of libttq: argument validation, context and weight lifetime, dispatch.
+// Nothing here touches weights on the host beyond copying the caller's canonical blocks to the
+// device; there is no CPU compute path.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "ttq_internal.cuh"
+
+using namespace ttq;
+
+struct ttq_ctx {
+    int device;
+    char err[512];
+    int64_t launches;
+    // scratch for the activation planes of the non-fused GEMV path (M <= 16)
+    XqView xq;
+    int64_t xq_capacity_k;
+    void *xq_base;
+    // device staging for the *_host entry points
+    uint8_t *stage_x, *stage_y, *stage_b;
+    size_t stage_x_bytes, stage_y_bytes, stage_b_bytes;
+    cudaStream_t host_stream;
+};
+
+struct ttq_weight : public Weight {};
+
+namespace {
+
+constexpr int64_t XQ_CAPACITY_K = 65536;          // largest K (padded to 256) the scratch planes hold
+constexpr size_t STAGE_X_BYTES = 64u << 20;       // host-entry staging: activations
+constexpr size_t STAGE_Y_BYTES = 128u << 20;      // host-entry staging: outputs
+constexpr size_t STAGE_B_BYTES = 4u << 20;        // host-entry staging: bias
+
+ttq_status fail(ttq_ctx *ctx, ttq_status s, const char *fmt, ...) {
+    if (ctx) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(ctx->err, sizeof(ctx->err), fmt, ap);
+        va_end(ap);
+    }
+    return s;
+}
+
+ttq_status cuda_fail(ttq_ctx *ctx, cudaError_t e, const char *what) {
+    ttq_status s = (e == cudaErrorMemoryAllocation) ? TTQ_ERR_OOM : TTQ_ERR_CUDA;
+    return fail(ctx, s, "%s: %s", what, cudaGetErrorString(e));
+}
+
+#define TTQ_CUDA(ctx, call)                                       \
+    do {                                                          \
+        cudaError_t e__ = (call);                                 \
+        if (e__ != cudaSuccess) return cuda_fail(ctx, e__, #call); \
+    } while (0)
+
+bool valid_fmt(int f) { return f == TTQ_FMT_Q8_0 || f == TTQ_FMT_Q4_K || f == TTQ_FMT_Q6_K; }
+bool valid_dt(int d) { return d == TTQ_DT_BF16 || d == TTQ_DT_F16 || d == TTQ_DT_F32; }
+int dt_size(int d) { return d == TTQ_DT_F32 ? 4 : 2; }
+
+ttq_status alloc_weight(ttq_ctx *ctx, int fmt, int64_t N, int64_t K, ttq_weight **out) {
+    ttq_weight *w = new (std::nothrow) ttq_weight();
+    if (!w) return fail(ctx, TTQ_ERR_OOM, "host allocation of weight handle failed");
+    w->ctx = ctx;
+    w->fmt = fmt;
+    w->N = N;
+    w->K = K;
+    w->NT = (N + TILE_ROWS - 1) / TILE_ROWS;
+    w->SBp = (K + TILE_K - 1) / TILE_K;
+    w->tiled_bytes = (size_t)w->NT * w->SBp * tile_bytes(fmt);
+    w->tiles = nullptr;
+    cudaError_t e = cudaMalloc(&w->tiles, w->tiled_bytes);
+    if (e != cudaSuccess) {
+        delete w;
+        return cuda_fail(ctx, e, "cudaMalloc(tiled weight)");
+    }
+    *out = w;
+    return TTQ_OK;
+}
+
+ttq_status check_create_args(ttq_ctx *ctx, int fmt, int64_t N, int64_t K, const void *blocks, size_t nbytes,
+                             ttq_weight **out) {
+    if (!ctx) return TTQ_ERR_INVALID_ARG;
+    if (!out) return fail(ctx, TTQ_ERR_INVALID_ARG, "out is NULL");
+    *out = nullptr;
+    if (!blocks) return fail(ctx, TTQ_ERR_INVALID_ARG, "blocks pointer is NULL");
+    if (!valid_fmt(fmt)) return fail(ctx, TTQ_ERR_INVALID_ARG, "unknown format %d", fmt);
+    if (N <= 0 || K <= 0) return fail(ctx, TTQ_ERR_SHAPE, "N and K must be positive (N=%lld K=%lld)", (long long)N, (long long)K);
+    if (K % block_elems(fmt)) return fail(ctx, TTQ_ERR_SHAPE, "K=%lld is not a multiple of the block length %d", (long long)K, block_elems(fmt));
+    if ((int64_t)nbytes != ttq_packed_bytes((ttq_format)fmt, N, K))
+        return fail(ctx, TTQ_ERR_SHAPE, "nbytes=%zu but an [%lld][%lld] matrix of this format has %lld bytes", nbytes,
+                    (long long)N, (long long)K, (long long)ttq_packed_bytes((ttq_format)fmt, N, K));
+    return TTQ_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *ttq_version(void) { return "0.1.0"; }
+
+const char *ttq_status_string(ttq_status s) {
+    switch (s) {
+    case TTQ_OK: return "ok";
+    case TTQ_ERR_INVALID_ARG: return "invalid argument";
+    case TTQ_ERR_SHAPE: return "shape or size mismatch";
+    case TTQ_ERR_UNSUPPORTED: return "unsupported request";
+    case TTQ_ERR_CUDA: return "CUDA error";
+    case TTQ_ERR_OOM: return "out of memory";
+    case TTQ_ERR_DEVICE: return "no usable sm_100 device";
+    case TTQ_ERR_LIMIT: return "fixed capacity exceeded";
+    }
+    return "unknown status";
+}
+
+int64_t ttq_block_elems(ttq_format fmt) { return valid_fmt(fmt) ? block_elems(fmt) : 0; }
+int64_t ttq_block_bytes(ttq_format fmt) { return valid_fmt(fmt) ? block_bytes(fmt) : 0; }
+int64_t ttq_packed_bytes(ttq_format fmt, int64_t N, int64_t K) {
+    if (!valid_fmt(fmt) || N < 0 || K < 0 || K % block_elems(fmt)) return 0;
+    return N * (K / block_elems(fmt)) * block_bytes(fmt);
+}
+
+const char *ttq_last_error(const ttq_ctx *ctx) { return ctx ? ctx->err : "null context"; }
+int64_t ttq_launch_count(const ttq_ctx *ctx) { return ctx ? ctx->launches : 0; }
+
+ttq_status ttq_init(int device, ttq_ctx **out) {
+    if (!out) return TTQ_ERR_INVALID_ARG;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) {
+        cudaGetLastError();
+        return TTQ_ERR_DEVICE;
+    }
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return TTQ_ERR_DEVICE;
+    if (prop.major != 10) return TTQ_ERR_DEVICE;  // kernels are built for sm_100a only
+    if (cudaSetDevice(device) != cudaSuccess) return TTQ_ERR_DEVICE;
+    ttq_ctx *ctx = new (std::nothrow) ttq_ctx();
+    if (!ctx) return TTQ_ERR_OOM;
+    memset(ctx, 0, sizeof(*ctx));
+    ctx->device = device;
+    // scratch: planes [2*16][Kcap] int8, sum16 [16][Kcap/16], sum32 [16][Kcap/32], sx [16][Kcap/256]
+    const int64_t Kc = XQ_CAPACITY_K, MP = MAX_GEMV_M;
+    const size_t planes_b = (size_t)2 * MP * Kc, s16_b = (size_t)MP * (Kc / 16) * 4, s32_b = (size_t)MP * (Kc / 32) * 4,
+                 sx_b = (size_t)MP * (Kc / 256) * 4;
+    cudaError_t e = cudaMalloc(&ctx->xq_base, planes_b + s16_b + s32_b + sx_b);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->stage_x, STAGE_X_BYTES);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->stage_y, STAGE_Y_BYTES);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->stage_b, STAGE_B_BYTES);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->host_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = gemv_configure();
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        ttq_destroy(ctx);
+        return e == cudaErrorMemoryAllocation ? TTQ_ERR_OOM : TTQ_ERR_CUDA;
+    }
+    uint8_t *b = reinterpret_cast<uint8_t *>(ctx->xq_base);
+    ctx->xq.planes = reinterpret_cast<int8_t *>(b);
+    ctx->xq.sum16 = reinterpret_cast<float *>(b + planes_b);
+    ctx->xq.sum32 = reinterpret_cast<float *>(b + planes_b + s16_b);
+    ctx->xq.sx = reinterpret_cast<float *>(b + planes_b + s16_b + s32_b);
+    ctx->xq_capacity_k = Kc;
+    ctx->stage_x_bytes = STAGE_X_BYTES;
+    ctx->stage_y_bytes = STAGE_Y_BYTES;
+    ctx->stage_b_bytes = STAGE_B_BYTES;
+    *out = ctx;
+    return TTQ_OK;
+}
+
+ttq_status ttq_destroy(ttq_ctx *ctx) {
+    if (!ctx) return TTQ_OK;
+    cudaSetDevice(ctx->device);
+    if (ctx->host_stream) cudaStreamDestroy(ctx->host_stream);
+    cudaFree(ctx->xq_base);
+    cudaFree(ctx->stage_x);
+    cudaFree(ctx->stage_y);
+    cudaFree(ctx->stage_b);
+    delete ctx;
+    return TTQ_OK;
+}
+
+ttq_status ttq_weight_create_device(ttq_ctx *ctx, ttq_format fmt, int64_t N, int64_t K, const void *dev_blocks,
+                                    size_t nbytes, void *stream, ttq_weight **out) {
+    ttq_status s = check_create_args(ctx, fmt, N, K, dev_blocks, nbytes, out);
+    if (s != TTQ_OK) return s;
+    TTQ_CUDA(ctx, cudaSetDevice(ctx->device));
+    ttq_weight *w = nullptr;
+    if ((s = alloc_weight(ctx, fmt, N, K, &w)) != TTQ_OK) return s;
+    cudaError_t e = launch_repack(fmt, reinterpret_cast<const uint8_t *>(dev_blocks), w->tiles, N, K, w->NT, w->SBp,
+                                  (cudaStream_t)stream);
+    if (e != cudaSuccess) {
+        ttq_weight_destroy(w);
+        return cuda_fail(ctx, e, "repack launch");
+    }
+    ctx->launches++;
+    *out = w;
+    return TTQ_OK;
+}
+
+ttq_status ttq_weight_create(ttq_ctx *ctx, ttq_format fmt, int64_t N, int64_t K, const void *host_blocks,
+                             size_t nbytes, const ttq_shard *shard, ttq_weight **out) {
+    ttq_status s = check_create_args(ctx, fmt, N, K, host_blocks, nbytes, out);
+    if (s != TTQ_OK) return s;
+    TTQ_CUDA(ctx, cudaSetDevice(ctx->device));
+    const int64_t be = block_elems(fmt), bb = block_bytes(fmt);
+    const int64_t row_bytes = (K / be) * bb;
+    const uint8_t *src = reinterpret_cast<const uint8_t *>(host_blocks);
+    int64_t Nl = N, Kl = K;
+    int kind = shard ? shard->kind : TTQ_SHARD_NONE;
+    if (kind != TTQ_SHARD_NONE) {
+        if (shard->world <= 0 || shard->rank < 0 || shard->rank >= shard->world)
+            return fail(ctx, TTQ_ERR_INVALID_ARG, "bad shard rank %d of %d", shard->rank, shard->world);
+        const int64_t P = shard->world;
+        if (kind == TTQ_SHARD_COLUMN) {
+            if (N % P) return fail(ctx, TTQ_ERR_SHAPE, "N=%lld not divisible by world %lld", (long long)N, (long long)P);
+            Nl = N / P;
+        } else if (kind == TTQ_SHARD_COLUMN_GATED) {
+            if (N % (2 * P)) return fail(ctx, TTQ_ERR_SHAPE, "N=%lld not divisible by 2*world", (long long)N);
+            Nl = N / P;
+        } else if (kind == TTQ_SHARD_ROW) {
+            if (K % (P * be)) return fail(ctx, TTQ_ERR_SHAPE, "K=%lld: K/world must be a multiple of the block length %lld", (long long)K, (long long)be);
+            Kl = K / P;
+        } else {
+            return fail(ctx, TTQ_ERR_INVALID_ARG, "unknown shard kind %d", kind);
+        }
+    }
+    const size_t local_bytes = (size_t)Nl * (Kl / be) * bb;
+    uint8_t *staging = nullptr;
+    TTQ_CUDA(ctx, cudaMalloc(&staging, local_bytes));
+    cudaError_t e = cudaSuccess;
+    if (kind == TTQ_SHARD_NONE) {
+        e = cudaMemcpy(staging, src, local_bytes, cudaMemcpyHostToDevice);
+    } else if (kind == TTQ_SHARD_COLUMN) {
+        e = cudaMemcpy(staging, src + (size_t)shard->rank * Nl * row_bytes, local_bytes, cudaMemcpyHostToDevice);
+    } else if (kind == TTQ_SHARD_COLUMN_GATED) {
+        const int64_t half = N / 2, hl = Nl / 2;
+        e = cudaMemcpy(staging, src + (size_t)(shard->rank * hl) * row_bytes, (size_t)hl * row_bytes, cudaMemcpyHostToDevice);
+        if (e == cudaSuccess)
+            e = cudaMemcpy(staging + (size_t)hl * row_bytes, src + (size_t)(half + shard->rank * hl) * row_bytes,
+                           (size_t)hl * row_bytes, cudaMemcpyHostToDevice);
+    } else {
+        const size_t lrow = (size_t)(Kl / be) * bb;
+        e = cudaMemcpy2D(staging, lrow, src + (size_t)shard->rank * lrow, row_bytes, lrow, (size_t)N, cudaMemcpyHostToDevice);
+    }
+    if (e != cudaSuccess) {
+        cudaFree(staging);
+        return cuda_fail(ctx, e, "upload of canonical blocks");
+    }
+    ttq_weight *w = nullptr;
+    if ((s = alloc_weight(ctx, fmt, Nl, Kl, &w)) != TTQ_OK) {
+        cudaFree(staging);
+        return s;
+    }
+    e = launch_repack(fmt, staging, w->tiles, Nl, Kl, w->NT, w->SBp, ctx->host_stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->host_stream);
+    cudaFree(staging);
+    if (e != cudaSuccess) {
+        ttq_weight_destroy(w);
+        return cuda_fail(ctx, e, "repack");
+    }
+    ctx->launches++;
+    *out = w;
+    return TTQ_OK;
+}
+
+ttq_status ttq_weight_destroy(ttq_weight *w) {
+    if (!w) return TTQ_OK;
+    if (w->ctx) cudaSetDevice(w->ctx->device);
+    cudaFree(w->tiles);
+    delete w;
+    return TTQ_OK;
+}
+
+ttq_status ttq_weight_info(const ttq_weight *w, int32_t *fmt, int64_t *N, int64_t *K) {
+    if (!w) return TTQ_ERR_INVALID_ARG;
+    if (fmt) *fmt = w->fmt;
+    if (N) *N = w->N;
+    if (K) *K = w->K;
+    return TTQ_OK;
+}
+
+int64_t ttq_weight_bytes(const ttq_weight *w) { return w ? ttq_packed_bytes((ttq_format)w->fmt, w->N, w->K) : 0; }
+
+ttq_status ttq_dequantize(ttq_ctx *ctx, const ttq_weight *w, float *dev_out, int64_t ld, void *stream) {
+    if (!ctx) return TTQ_ERR_INVALID_ARG;
+    if (!w || !dev_out) return fail(ctx, TTQ_ERR_INVALID_ARG, "weight or output pointer is NULL");
+    if (w->ctx != ctx) return fail(ctx, TTQ_ERR_INVALID_ARG, "weight belongs to another context");
+    if (ld < w->K) return fail(ctx, TTQ_ERR_SHAPE, "ld=%lld < K=%lld", (long long)ld, (long long)w->K);
+    cudaError_t e = launch_dequant(w->fmt, w->tiles, dev_out, ld, w->N, w->K, w->SBp, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "dequantize launch");
+    ctx->launches++;
+    return TTQ_OK;
+}
+
+ttq_status ttq_linear_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_dev, ttq_dtype x_dt, int64_t M,
+                              int64_t ldx, const void *bias_dev, ttq_dtype bias_dt, void *y_dev, ttq_dtype y_dt,
+                              int64_t ldy, void *stream) {
+    if (!ctx) return TTQ_ERR_INVALID_ARG;
+    if (!w) return fail(ctx, TTQ_ERR_INVALID_ARG, "weight is NULL");
+    if (w->ctx != ctx) return fail(ctx, TTQ_ERR_INVALID_ARG, "weight belongs to another context");
+    if (M < 0) return fail(ctx, TTQ_ERR_SHAPE, "M=%lld is negative", (long long)M);
+    if (M == 0) return TTQ_OK;
+    if (!x_dev || !y_dev) return fail(ctx, TTQ_ERR_INVALID_ARG, "x or y pointer is NULL");
+    if (x_dt != TTQ_DT_BF16 && x_dt != TTQ_DT_F16) return fail(ctx, TTQ_ERR_INVALID_ARG, "x dtype must be bf16 or f16");
+    if (!valid_dt(y_dt)) return fail(ctx, TTQ_ERR_INVALID_ARG, "unknown y dtype %d", (int)y_dt);
+    if (bias_dev && !valid_dt(bias_dt)) return fail(ctx, TTQ_ERR_INVALID_ARG, "unknown bias dtype %d", (int)bias_dt);
+    if (ldx < w->K) return fail(ctx, TTQ_ERR_SHAPE, "ldx=%lld < K=%lld", (long long)ldx, (long long)w->K);
+    if (ldy < w->N) return fail(ctx, TTQ_ERR_SHAPE, "ldy=%lld < N=%lld", (long long)ldy, (long long)w->N);
+    if (w->SBp * TILE_K > ctx->xq_capacity_k && M > 2)
+        return fail(ctx, TTQ_ERR_LIMIT, "K=%lld exceeds the activation scratch capacity %lld", (long long)w->K,
+                    (long long)ctx->xq_capacity_k);
+    cudaStream_t st = (cudaStream_t)stream;
+    // Rows are processed in groups of at most MAX_GEMV_M through the decode kernel.
+    for (int64_t m0 = 0; m0 < M; m0 += MAX_GEMV_M) {
+        LinearArgs a;
+        a.tiles = w->tiles;
+        a.N = w->N; a.K = w->K; a.NT = w->NT; a.SBp = w->SBp;
+        a.x = reinterpret_cast<const uint8_t *>(x_dev) + (size_t)m0 * ldx * dt_size(x_dt);
+        a.x_dt = x_dt;
+        a.M = (M - m0) < MAX_GEMV_M ? (M - m0) : MAX_GEMV_M;
+        a.ldx = ldx;
+        a.bias = bias_dev; a.bias_dt = bias_dt;
+        a.y = reinterpret_cast<uint8_t *>(y_dev) + (size_t)m0 * ldy * dt_size(y_dt);
+        a.y_dt = y_dt; a.ldy = ldy;
+        int launches = 0;
+        cudaError_t e = launch_gemv(w->fmt, a, ctx->xq, ctx->xq_capacity_k, st, &launches);
+        ctx->launches += launches;
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "linear forward launch");
+    }
+    return TTQ_OK;
+}
+
+ttq_status ttq_linear_forward_host(ttq_ctx *ctx, const ttq_weight *w, const void *x_host, ttq_dtype x_dt, int64_t M,
+                                   int64_t ldx, const void *bias_host, ttq_dtype bias_dt, void *y_host, ttq_dtype y_dt,
+                                   int64_t ldy) {
+    if (!ctx) return TTQ_ERR_INVALID_ARG;
+    if (!w) return fail(ctx, TTQ_ERR_INVALID_ARG, "weight is NULL");
+    if (M < 0) return fail(ctx, TTQ_ERR_SHAPE, "M=%lld is negative", (long long)M);
+    if (M == 0) return TTQ_OK;
+    if (!x_host || !y_host) return fail(ctx, TTQ_ERR_INVALID_ARG, "x or y pointer is NULL");
+    if (!valid_dt(x_dt) || !valid_dt(y_dt)) return fail(ctx, TTQ_ERR_INVALID_ARG, "unknown dtype");
+    if (ldx < w->K || ldy < w->N) return fail(ctx, TTQ_ERR_SHAPE, "leading dimension smaller than the row length");
+    const size_t xb = (size_t)M * ldx * dt_size(x_dt), yb = (size_t)M * ldy * dt_size(y_dt);
+    const size_t bbytes = bias_host ? (size_t)w->N * dt_size(bias_dt) : 0;
+    if (xb > ctx->stage_x_bytes || yb > ctx->stage_y_bytes || bbytes > ctx->stage_b_bytes)
+        return fail(ctx, TTQ_ERR_LIMIT, "host-entry staging capacity exceeded (x %zu B, y %zu B)", xb, yb);
+    TTQ_CUDA(ctx, cudaSetDevice(ctx->device));
+    cudaStream_t st = ctx->host_stream;
+    TTQ_CUDA(ctx, cudaMemcpyAsync(ctx->stage_x, x_host, xb, cudaMemcpyHostToDevice, st));
+    if (bias_host) TTQ_CUDA(ctx, cudaMemcpyAsync(ctx->stage_b, bias_host, bbytes, cudaMemcpyHostToDevice, st));
+    ttq_status s = ttq_linear_forward(ctx, w, ctx->stage_x, x_dt, M, ldx, bias_host ? ctx->stage_b : nullptr, bias_dt,
+                                      ctx->stage_y, y_dt, ldy, st);
+    if (s != TTQ_OK) return s;
+    TTQ_CUDA(ctx, cudaMemcpyAsync(y_host, ctx->stage_y, yb, cudaMemcpyDeviceToHost, st));
+    TTQ_CUDA(ctx, cudaStreamSynchronize(st));
+    return TTQ_OK;
+}
+
+ttq_status ttq_silu_and_mul(ttq_ctx *ctx, const void *in_dev, ttq_dtype dt, int64_t M, int64_t H, int64_t ld_in,
+                            void *out_dev, int64_t ld_out, void *stream) {
+    if (!ctx) return TTQ_ERR_INVALID_ARG;
+    if (M < 0 || H < 0) return fail(ctx, TTQ_ERR_SHAPE, "negative size");
+    if (M == 0 || H == 0) return TTQ_OK;
+    if (!in_dev || !out_dev) return fail(ctx, TTQ_ERR_INVALID_ARG, "input or output pointer is NULL");
+    if (!valid_dt(dt)) return fail(ctx, TTQ_ERR_INVALID_ARG, "unknown dtype %d", (int)dt);
+    if (ld_in < 2 * H || ld_out < H) return fail(ctx, TTQ_ERR_SHAPE, "leading dimension smaller than the row length");
+    cudaError_t e = launch_silu_and_mul(in_dev, dt, M, H, ld_in, out_dev, ld_out, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "silu_and_mul launch");
+    ctx->launches++;
+    return TTQ_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,129 @@
+// Internal declarations shared by the translation units of libttq (not part of the public ABI).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ttq.h"
+
+namespace ttq {
+
+// ------------------------------------------------------------------------------------------------
+// Tiled device layout.
+//
+// Every format is cut into tiles of TILE_ROWS weight rows x TILE_K weights along K (one Q4_K / Q6_K
+// super-block, eight Q8_0 blocks).  Tiles of one row-tile are contiguous along K, so a warp that
+// walks K for 16 rows reads one contiguous byte stream:
+//
+//     offset(tile nt, sb) = (nt * SBp + sb) * tile_bytes(fmt),   SBp = ceil(K / 256)
+//
+// Inside a tile the quant payload is stored in the order the integer tensor-core instruction
+// wants its A operand (mma.sync m16n8k32 / m16n8k16, A row-major): lane L = 4*g + t owns rows g and
+// g+8, and one 16-byte load per lane is a complete A fragment.  `W(r, i)` below is the 32-bit word
+// holding quants 4i..4i+3 of row r within the 32-weight group at hand.
+//
+//  Q4_K (2304 B = 16 x 144):
+//     [0,2048)      4 pair-chunks p (sub-blocks 2p | 2p+1 share bytes, low | high nibble):
+//                   chunk p, lane L -> 16 B {W(g,t), W(g+8,t), W(g,t+4), W(g+8,t+4)}
+//     [2048,2304)   16 row headers x 16 B, canonical {fp16 d, fp16 dmin, 12 B 6-bit scales/mins}
+//  Q8_0 (4352 B = 16 x 8 x 34):
+//     [0,4096)      8 blocks b: block b, lane L -> 16 B {W(g,t), W(g+8,t), W(g,t+4), W(g+8,t+4)}
+//     [4096,4352)   fp16 d[r][b], row-major (16 B per row)
+//  Q6_K (3360 B = 16 x 210): sub-blocks of 16 weights, quad c = sub-blocks 4c..4c+3
+//     [0,2048)      quad c, lane L -> 16 B {QL(g,c,0), QL(g+8,c,0), QL(g,c,1), QL(g+8,c,1)}
+//                   QL(r,c,h) byte i: low nibble = low 4 bits of q[r][16(4c+2h)+4t+i],
+//                                     high nibble = low 4 bits of q[r][16(4c+2h+1)+4t+i]
+//     [2048,3072)   e in {0,1}, lane L -> 16 B {QH(g,2e), QH(g+8,2e), QH(g,2e+1), QH(g+8,2e+1)}
+//                   QH(r,c) byte i: bit pairs 0..3 = high 2 bits of q[r][16(4c+s)+4t+i], s = 0..3
+//     [3072,3328)   int8 scales[r][16]
+//     [3328,3360)   fp16 d[r]
+//  Rows >= N and Q8_0 blocks beyond K are stored as zero bytes (they dequantize to 0).
+// ------------------------------------------------------------------------------------------------
+constexpr int TILE_ROWS = 16;
+constexpr int TILE_K = 256;
+
+__host__ __device__ constexpr int tile_bytes(int fmt) {
+    return fmt == TTQ_FMT_Q8_0 ? 4352 : (fmt == TTQ_FMT_Q4_K ? 2304 : 3360);
+}
+__host__ __device__ constexpr int block_elems(int fmt) { return fmt == TTQ_FMT_Q8_0 ? 32 : 256; }
+__host__ __device__ constexpr int block_bytes(int fmt) {
+    return fmt == TTQ_FMT_Q8_0 ? 34 : (fmt == TTQ_FMT_Q4_K ? 144 : 210);
+}
+
+// Activation fixed-point: per 256-chunk scale, |xq| <= XQ_MAX so that xq = 256*hi + lo with both
+// planes in int8.
+constexpr int XQ_MAX = 32639;
+constexpr int MAX_GEMV_M = 16;
+
+struct Weight {
+    ttq_ctx *ctx;
+    int fmt;
+    int64_t N, K;
+    int64_t NT;   // row tiles
+    int64_t SBp;  // 256-wide K tiles
+    uint8_t *tiles;
+    size_t tiled_bytes;
+};
+
+// Activation planes produced by the x-prep kernel (global scratch) for the non-fused GEMV path.
+struct XqView {
+    int8_t *planes;   // [2*Mpad][Kp] : row 2m = high plane, 2m+1 = low plane
+    float *sum16;     // [Mpad][Kp/16] sum of xq over 16-weight groups
+    float *sum32;     // [Mpad][Kp/32]
+    float *sx;        // [Mpad][SBp]
+};
+
+struct LinearArgs {
+    const uint8_t *tiles;
+    int64_t N, K, NT, SBp;
+    const void *x;
+    int x_dt;
+    int64_t M, ldx;
+    const void *bias;
+    int bias_dt;
+    void *y;
+    int y_dt;
+    int64_t ldy;
+};
+
+// launchers (defined in the .cu files); each returns the number of kernels it launched or -1
+cudaError_t launch_repack(int fmt, const uint8_t *canon, uint8_t *tiled, int64_t N, int64_t K, int64_t NT,
+                          int64_t SBp, cudaStream_t st);
+cudaError_t launch_dequant(int fmt, const uint8_t *tiled, float *out, int64_t ld, int64_t N, int64_t K,
+                           int64_t SBp, cudaStream_t st);
+// GEMV for M <= MAX_GEMV_M.  `xq` is scratch for the separate x-prep pass (used when M > fused limit).
+cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t xq_capacity_k,
+                        cudaStream_t st, int *launches);
+cudaError_t launch_silu_and_mul(const void *in, int dt, int64_t M, int64_t H, int64_t ld_in, void *out,
+                                int64_t ld_out, cudaStream_t st);
+size_t gemv_max_dynamic_smem();
+cudaError_t gemv_configure();  // one-time cudaFuncSetAttribute calls
+
+// ---------------------------------------------------------------------------------------------
+// small device helpers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float load_as_float(const void *p, int dt, int64_t i) {
+    if (dt == TTQ_DT_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p)[i]);
+    if (dt == TTQ_DT_F16) return __half2float(reinterpret_cast<const __half *>(p)[i]);
+    return reinterpret_cast<const float *>(p)[i];
+}
+__device__ __forceinline__ void store_from_float(void *p, int dt, int64_t i, float v) {
+    if (dt == TTQ_DT_BF16) reinterpret_cast<__nv_bfloat16 *>(p)[i] = __float2bfloat16_rn(v);
+    else if (dt == TTQ_DT_F16) reinterpret_cast<__half *>(p)[i] = __float2half_rn(v);
+    else reinterpret_cast<float *>(p)[i] = v;
+}
+
+// Q4_K: unpack the 6-bit scale (sc) and min (m) of sub-block j from the 12 packed bytes.
+__device__ __forceinline__ void q4k_scale_min(int j, const uint8_t *s, int &sc, int &m) {
+    if (j < 4) {
+        sc = s[j] & 63;
+        m = s[j + 4] & 63;
+    } else {
+        sc = (s[j + 4] & 0x0f) | ((s[j - 4] >> 6) << 4);
+        m = (s[j + 4] >> 4) | ((s[j] >> 6) << 4);
+    }
+}
+
+}  // namespace ttq

@@ -1,0 +1,202 @@
+"""Operator objects with the reference's surface: plain objects with ``init``-style constructors
+and a ``forward`` method, no base class (workspace/transformers/src/layers/all.nim:8-15)."""
+from __future__ import annotations
+
+import ctypes
+import enum
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import Shard, TtqError, check
+from .formats import BLOCK_BYTES, BLOCK_ELEMS, packed_bytes
+
+_TORCH_DT = {torch.bfloat16: _lib.DT_BF16, torch.float16: _lib.DT_F16, torch.float32: _lib.DT_F32}
+
+
+def _dt(t: torch.dtype) -> int:
+    try:
+        return _TORCH_DT[t]
+    except KeyError:
+        raise TtqError(_lib.OK + 1, f"unsupported dtype {t}") from None
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+class Context:
+    """One per (host thread, device): owns the library's scratch.  ``ttq_init`` / ``ttq_destroy``."""
+
+    def __init__(self, device: int | torch.device = 0):
+        self._lib = _lib.load()
+        dev = torch.device(device) if not isinstance(device, int) else torch.device("cuda", device)
+        self.device = dev
+        h = ctypes.c_void_p()
+        st = self._lib.ttq_init(dev.index or 0, ctypes.byref(h))
+        check(None, st)
+        self.handle = h
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self._lib.ttq_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.ttq_launch_count(self.handle))
+
+
+class QuantLinear:
+    """Quantized ``Linear`` (linear.nim:14-57): ``y = x @ W^T + bias`` with W held as packed blocks.
+
+    ``blocks`` is a uint8 tensor of canonical row-major blocks, shape ``[out_features, bytes_per_row]``,
+    on the host (uploaded and repacked) or already on the device.  ``bias`` is an optional device
+    tensor of ``out_features`` elements.  ``forward`` accepts ``x`` of shape ``(..., in_features)`` in
+    bf16 or f16 on the context's device and returns ``(..., out_features)`` in ``out_dtype`` (the
+    input dtype by default, as ATen linear does).
+    """
+
+    def __init__(self, ctx: Context, fmt: int, blocks: torch.Tensor, in_features: int,
+                 bias: Optional[torch.Tensor] = None, shard: Optional[tuple[int, int, int]] = None):
+        if blocks.dtype != torch.uint8 or blocks.dim() != 2:
+            raise TtqError(1, "blocks must be a 2-D uint8 tensor [out_features, bytes_per_row]")
+        self.ctx, self.fmt = ctx, fmt
+        lib = ctx._lib
+        n, k = int(blocks.shape[0]), int(in_features)
+        blocks = blocks.contiguous()
+        h = ctypes.c_void_p()
+        if blocks.is_cuda:
+            if shard is not None:
+                raise TtqError(3, "sharding is applied while uploading host blocks")
+            st = lib.ttq_weight_create_device(ctx.handle, fmt, n, k, blocks.data_ptr(), blocks.numel(),
+                                              _stream_ptr(blocks.device), ctypes.byref(h))
+            check(ctx.handle, st)
+            torch.cuda.current_stream(blocks.device).synchronize()  # blocks may be freed by the caller
+        else:
+            sh = None if shard is None else ctypes.byref(Shard(*shard))
+            st = lib.ttq_weight_create(ctx.handle, fmt, n, k, blocks.data_ptr(), blocks.numel(), sh,
+                                       ctypes.byref(h))
+            check(ctx.handle, st)
+        self.handle = h
+        f, nn, kk = ctypes.c_int32(), ctypes.c_int64(), ctypes.c_int64()
+        check(ctx.handle, lib.ttq_weight_info(h, ctypes.byref(f), ctypes.byref(nn), ctypes.byref(kk)))
+        self.out_features, self.in_features = int(nn.value), int(kk.value)
+        if bias is not None and bias.numel() != self.out_features:
+            raise TtqError(2, f"bias has {bias.numel()} elements, expected {self.out_features}")
+        self.bias = None if bias is None else bias.contiguous()
+
+    @classmethod
+    def init(cls, ctx: Context, fmt: int, blocks: torch.Tensor, in_features: int,
+             bias: Optional[torch.Tensor] = None, shard=None) -> "QuantLinear":
+        """Spelling of the reference constructor (``Linear.init``, linear.nim:29)."""
+        return cls(ctx, fmt, blocks, in_features, bias, shard)
+
+    @property
+    def weight_bytes(self) -> int:
+        return int(self.ctx._lib.ttq_weight_bytes(self.handle))
+
+    def dequantize(self) -> torch.Tensor:
+        """fp32 ``[out_features, in_features]`` expansion of the device layout (test hook)."""
+        out = torch.empty((self.out_features, self.in_features), dtype=torch.float32, device=self.ctx.device)
+        st = self.ctx._lib.ttq_dequantize(self.ctx.handle, self.handle, out.data_ptr(), self.in_features,
+                                          _stream_ptr(self.ctx.device))
+        check(self.ctx.handle, st)
+        return out
+
+    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if not x.is_cuda:
+            raise TtqError(1, "x must live on the context's CUDA device (use forward_host for host buffers)")
+        if x.shape[-1] != self.in_features:
+            raise TtqError(2, f"x has {x.shape[-1]} input features, the layer has {self.in_features}")
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, self.in_features)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        m = x2.shape[0]
+        odt = out_dtype or x.dtype
+        if out is None:
+            out = torch.empty((m, self.out_features), dtype=odt, device=x.device)
+        y2 = out.reshape(-1, self.out_features)
+        b = self.bias
+        st = self.ctx._lib.ttq_linear_forward(
+            self.ctx.handle, self.handle, x2.data_ptr(), _dt(x2.dtype), m, x2.stride(0) if m > 1 else self.in_features,
+            None if b is None else b.data_ptr(), _lib.DT_F32 if b is None else _dt(b.dtype),
+            y2.data_ptr(), _dt(y2.dtype), y2.stride(0) if m > 1 else self.out_features, _stream_ptr(x.device))
+        check(self.ctx.handle, st)
+        return out.reshape(*lead, self.out_features)
+
+    __call__ = forward
+
+    def forward_host(self, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        """Host-buffer call: x and y are CPU tensors (pinned for speed); copies are part of the call."""
+        x2 = x.reshape(-1, self.in_features)
+        y2 = y.reshape(-1, self.out_features)
+        m = x2.shape[0]
+        st = self.ctx._lib.ttq_linear_forward_host(
+            self.ctx.handle, self.handle, x2.data_ptr(), _dt(x2.dtype), m, self.in_features, None, _lib.DT_F32,
+            y2.data_ptr(), _dt(y2.dtype), self.out_features)
+        check(self.ctx.handle, st)
+        return y
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self.ctx._lib.ttq_weight_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class ActivationKind(enum.IntEnum):
+    """kernels/activations.nim:10-12"""
+    kSilu = 0
+
+
+def silu_and_mul(ctx: Context, x: torch.Tensor) -> torch.Tensor:
+    """``silu(x[..., :H]) * x[..., H:]`` (kernels/activations.nim:14-38); the gate is the first half."""
+    h = x.shape[-1] // 2
+    x2 = x.reshape(-1, 2 * h)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    out = torch.empty((x2.shape[0], h), dtype=x.dtype, device=x.device)
+    st = ctx._lib.ttq_silu_and_mul(ctx.handle, x2.data_ptr(), _dt(x.dtype), x2.shape[0], h,
+                                   x2.stride(0) if x2.shape[0] > 1 else 2 * h, out.data_ptr(), h,
+                                   _stream_ptr(x.device))
+    check(ctx.handle, st)
+    return out.reshape(*x.shape[:-1], h)
+
+
+class GatedMLP:
+    """Gated MLP (mlp.nim:14-60): fused gate|up projection, silu_and_mul, down projection.
+
+    The reference concatenates dense gate and up weights along dim 0 at init (mlp.nim:39); packed
+    blocks are row-major, so the same concatenation of the two block matrices is the fused weight.
+    """
+
+    def __init__(self, ctx: Context, fmt: int, gate_blocks: torch.Tensor, up_blocks: torch.Tensor,
+                 down_blocks: torch.Tensor, hidden_size: int, intermediate_size: int,
+                 activation: ActivationKind = ActivationKind.kSilu):
+        self.ctx = ctx
+        self.gate_up_proj = QuantLinear(ctx, fmt, torch.cat([gate_blocks, up_blocks], 0), hidden_size)
+        self.down_proj = QuantLinear(ctx, fmt, down_blocks, intermediate_size)
+        self.activation = activation
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        gate_up = self.gate_up_proj.forward(x)
+        if self.activation != ActivationKind.kSilu:
+            raise TtqError(3, f"activation {self.activation} is not implemented")
+        return self.down_proj.forward(silu_and_mul(self.ctx, gate_up))
+
+    __call__ = forward
