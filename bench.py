@@ -181,7 +181,7 @@ def workload_config(m: int, gpus: int):
         "workload": f"Llama-3-8B projection shapes, Q4_K, M={m} decode GEMV, {N_LAYERS} layers x 4 linears",
         "shapes_k_to_n": [[k, n] for _, k, n in SHAPES], "M": m, "layers": N_LAYERS,
         "parallelism": "single GPU" if gpus == 1 else f"tp{gpus} (column/row split, NCCL all-reduce)",
-        "l2": "3.93 GB of weights per step, larger than L2: every step streams from HBM",
+        "l2": f"{N_LAYERS * 122683392 / 1e9:.2f} GB of weights per step, larger than L2: every step streams from HBM",
     }
 
 
@@ -296,7 +296,7 @@ def ours_arm(args):
     # ---- end to end: host buffers through the C-ABI host entry point, copies inside the timed region
     e2e = None
     h2d = d2h = 0
-    if world == 1:
+    if world == 1 and not args.no_e2e:
         host = []
         for entry in layers:
             for name, lin, x, y in entry:
@@ -321,7 +321,7 @@ def ours_arm(args):
 
     # ---- per-shape breakdown (device-resident, cold L2: the 32 layers' copies are rotated)
     per_shape = {}
-    if world == 1:
+    if world == 1 and not args.no_e2e:
         for idx, (name, k, n) in enumerate(SHAPES):
             items = [layers[l][idx] for l in range(N_LAYERS)]
             for _, lin, x, y in items:
@@ -380,6 +380,7 @@ def ours_arm(args):
 
 
 def main():
+    global N_LAYERS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=500)
@@ -388,7 +389,11 @@ def main():
     ap.add_argument("--m", type=int, default=1, help="decode batch (rows of x)")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--layers", type=int, default=32,
+                    help="layers in the pass (default 32; smaller values are for profiler captures only)")
     args = ap.parse_args()
+    N_LAYERS = args.layers
     if args.impl == "reference":
         reference_arm(args)
     else:

@@ -50,7 +50,8 @@ typedef enum ttq_status {
     TTQ_ERR_CUDA = 4,        /* a CUDA runtime call failed; see ttq_last_error */
     TTQ_ERR_OOM = 5,         /* device or host allocation failed */
     TTQ_ERR_DEVICE = 6,      /* no sm_100 device / wrong device current */
-    TTQ_ERR_LIMIT = 7        /* request exceeds a fixed capacity (scratch, static buffers) */
+    TTQ_ERR_LIMIT = 7,       /* request exceeds a fixed capacity (scratch, static buffers) */
+    TTQ_ERR_TIMEOUT = 8      /* a kernel gave up a bounded wait on its copy pipeline; results invalid */
 } ttq_status;
 
 typedef enum ttq_format {
@@ -140,6 +141,11 @@ TTQ_API ttq_status ttq_linear_forward(ttq_ctx *ctx, const ttq_weight *w, const v
 TTQ_API ttq_status ttq_linear_forward_host(ttq_ctx *ctx, const ttq_weight *w, const void *x_host, ttq_dtype x_dt,
                                    int64_t M, int64_t ldx, const void *bias_host, ttq_dtype bias_dt,
                                    void *y_host, ttq_dtype y_dt, int64_t ldy);
+
+/* Synchronises `stream` and reports whether any kernel launched through this context since the last
+ * check gave up a bounded device-side wait (TTQ_ERR_TIMEOUT; the flag is cleared).  The *_host entry
+ * points perform this check themselves. */
+TTQ_API ttq_status ttq_device_status(ttq_ctx *ctx, void *stream);
 
 /* ---- adjacent step: silu_and_mul (kernels/activations.nim:14-38) ---------------------------- */
 

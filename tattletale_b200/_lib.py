@@ -16,7 +16,8 @@ DT_BF16, DT_F16, DT_F32 = 0, 1, 2
 SHARD_NONE, SHARD_COLUMN, SHARD_COLUMN_GATED, SHARD_ROW = 0, 1, 2, 3
 OK = 0
 STATUS_NAMES = {0: "TTQ_OK", 1: "TTQ_ERR_INVALID_ARG", 2: "TTQ_ERR_SHAPE", 3: "TTQ_ERR_UNSUPPORTED",
-                4: "TTQ_ERR_CUDA", 5: "TTQ_ERR_OOM", 6: "TTQ_ERR_DEVICE", 7: "TTQ_ERR_LIMIT"}
+                4: "TTQ_ERR_CUDA", 5: "TTQ_ERR_OOM", 6: "TTQ_ERR_DEVICE", 7: "TTQ_ERR_LIMIT",
+                8: "TTQ_ERR_TIMEOUT"}
 
 # Every symbol include/ttq.h declares, with its signature.
 _i64, _vp, _ci, _sz = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
@@ -46,6 +47,7 @@ SIGNATURES = {
     "ttq_linear_forward_host": (_ci, [_vp, _vp, _vp, _ci, _i64, _i64, _vp, _ci, _vp, _ci, _i64]),
     "ttq_silu_and_mul": (_ci, [_vp, _vp, _ci, _i64, _i64, _i64, _vp, _i64, _vp]),
     "ttq_launch_count": (_i64, [_vp]),
+    "ttq_device_status": (_ci, [_vp, _vp]),
 }
 
 _lib = None

@@ -18,6 +18,8 @@ struct ttq_ctx {
     XqView xq;
     int64_t xq_capacity_k;
     void *xq_base;
+    int sms;          // multiprocessor count of the device
+    int *dev_status;  // device word the kernels OR failure bits into (bit 0: a bounded wait gave up)
     // device staging for the *_host entry points
     uint8_t *stage_x, *stage_y, *stage_b;
     size_t stage_x_bytes, stage_y_bytes, stage_b_bytes;
@@ -109,6 +111,7 @@ const char *ttq_status_string(ttq_status s) {
     case TTQ_ERR_OOM: return "out of memory";
     case TTQ_ERR_DEVICE: return "no usable sm_100 device";
     case TTQ_ERR_LIMIT: return "fixed capacity exceeded";
+    case TTQ_ERR_TIMEOUT: return "device-side wait timed out";
     }
     return "unknown status";
 }
@@ -139,11 +142,14 @@ ttq_status ttq_init(int device, ttq_ctx **out) {
     if (!ctx) return TTQ_ERR_OOM;
     memset(ctx, 0, sizeof(*ctx));
     ctx->device = device;
+    ctx->sms = prop.multiProcessorCount;
     // scratch: planes [2*16][Kcap] int8, sum16 [16][Kcap/16], sum32 [16][Kcap/32], sx [16][Kcap/256]
     const int64_t Kc = XQ_CAPACITY_K, MP = MAX_GEMV_M;
     const size_t planes_b = (size_t)2 * MP * Kc, s16_b = (size_t)MP * (Kc / 16) * 4, s32_b = (size_t)MP * (Kc / 32) * 4,
-                 sx_b = (size_t)MP * (Kc / 256) * 4;
+                 sx_b = (size_t)MP * (Kc / 256 + 4) * 4;
     cudaError_t e = cudaMalloc(&ctx->xq_base, planes_b + s16_b + s32_b + sx_b);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->dev_status, 256);
+    if (e == cudaSuccess) e = cudaMemset(ctx->dev_status, 0, 256);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->stage_x, STAGE_X_BYTES);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->stage_y, STAGE_Y_BYTES);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->stage_b, STAGE_B_BYTES);
@@ -172,6 +178,7 @@ ttq_status ttq_destroy(ttq_ctx *ctx) {
     cudaSetDevice(ctx->device);
     if (ctx->host_stream) cudaStreamDestroy(ctx->host_stream);
     cudaFree(ctx->xq_base);
+    cudaFree(ctx->dev_status);
     cudaFree(ctx->stage_x);
     cudaFree(ctx->stage_y);
     cudaFree(ctx->stage_b);
@@ -228,19 +235,23 @@ ttq_status ttq_weight_create(ttq_ctx *ctx, ttq_format fmt, int64_t N, int64_t K,
     uint8_t *staging = nullptr;
     TTQ_CUDA(ctx, cudaMalloc(&staging, local_bytes));
     cudaError_t e = cudaSuccess;
+    // All copies are ordered on the same stream as the repack kernel that consumes them.
+    cudaStream_t up = ctx->host_stream;
     if (kind == TTQ_SHARD_NONE) {
-        e = cudaMemcpy(staging, src, local_bytes, cudaMemcpyHostToDevice);
+        e = cudaMemcpyAsync(staging, src, local_bytes, cudaMemcpyHostToDevice, up);
     } else if (kind == TTQ_SHARD_COLUMN) {
-        e = cudaMemcpy(staging, src + (size_t)shard->rank * Nl * row_bytes, local_bytes, cudaMemcpyHostToDevice);
+        e = cudaMemcpyAsync(staging, src + (size_t)shard->rank * Nl * row_bytes, local_bytes, cudaMemcpyHostToDevice, up);
     } else if (kind == TTQ_SHARD_COLUMN_GATED) {
         const int64_t half = N / 2, hl = Nl / 2;
-        e = cudaMemcpy(staging, src + (size_t)(shard->rank * hl) * row_bytes, (size_t)hl * row_bytes, cudaMemcpyHostToDevice);
+        e = cudaMemcpyAsync(staging, src + (size_t)(shard->rank * hl) * row_bytes, (size_t)hl * row_bytes,
+                            cudaMemcpyHostToDevice, up);
         if (e == cudaSuccess)
-            e = cudaMemcpy(staging + (size_t)hl * row_bytes, src + (size_t)(half + shard->rank * hl) * row_bytes,
-                           (size_t)hl * row_bytes, cudaMemcpyHostToDevice);
+            e = cudaMemcpyAsync(staging + (size_t)hl * row_bytes, src + (size_t)(half + shard->rank * hl) * row_bytes,
+                                (size_t)hl * row_bytes, cudaMemcpyHostToDevice, up);
     } else {
         const size_t lrow = (size_t)(Kl / be) * bb;
-        e = cudaMemcpy2D(staging, lrow, src + (size_t)shard->rank * lrow, row_bytes, lrow, (size_t)N, cudaMemcpyHostToDevice);
+        e = cudaMemcpy2DAsync(staging, lrow, src + (size_t)shard->rank * lrow, row_bytes, lrow, (size_t)N,
+                              cudaMemcpyHostToDevice, up);
     }
     if (e != cudaSuccess) {
         cudaFree(staging);
@@ -306,7 +317,7 @@ ttq_status ttq_linear_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_d
     if (bias_dev && !valid_dt(bias_dt)) return fail(ctx, TTQ_ERR_INVALID_ARG, "unknown bias dtype %d", (int)bias_dt);
     if (ldx < w->K) return fail(ctx, TTQ_ERR_SHAPE, "ldx=%lld < K=%lld", (long long)ldx, (long long)w->K);
     if (ldy < w->N) return fail(ctx, TTQ_ERR_SHAPE, "ldy=%lld < N=%lld", (long long)ldy, (long long)w->N);
-    if (w->SBp * TILE_K > ctx->xq_capacity_k && M > 2)
+    if (w->SBp * TILE_K > ctx->xq_capacity_k)
         return fail(ctx, TTQ_ERR_LIMIT, "K=%lld exceeds the activation scratch capacity %lld", (long long)w->K,
                     (long long)ctx->xq_capacity_k);
     cudaStream_t st = (cudaStream_t)stream;
@@ -323,7 +334,7 @@ ttq_status ttq_linear_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_d
         a.y = reinterpret_cast<uint8_t *>(y_dev) + (size_t)m0 * ldy * dt_size(y_dt);
         a.y_dt = y_dt; a.ldy = ldy;
         int launches = 0;
-        cudaError_t e = launch_gemv(w->fmt, a, ctx->xq, ctx->xq_capacity_k, st, &launches);
+        cudaError_t e = launch_gemv(w->fmt, a, ctx->xq, ctx->xq_capacity_k, ctx->sms, ctx->dev_status, st, &launches);
         ctx->launches += launches;
         if (e != cudaSuccess) return cuda_fail(ctx, e, "linear forward launch");
     }
@@ -353,6 +364,18 @@ ttq_status ttq_linear_forward_host(ttq_ctx *ctx, const ttq_weight *w, const void
     if (s != TTQ_OK) return s;
     TTQ_CUDA(ctx, cudaMemcpyAsync(y_host, ctx->stage_y, yb, cudaMemcpyDeviceToHost, st));
     TTQ_CUDA(ctx, cudaStreamSynchronize(st));
+    return ttq_device_status(ctx, st);
+}
+
+ttq_status ttq_device_status(ttq_ctx *ctx, void *stream) {
+    if (!ctx) return TTQ_ERR_INVALID_ARG;
+    int host = 0;
+    TTQ_CUDA(ctx, cudaMemcpyAsync(&host, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    TTQ_CUDA(ctx, cudaStreamSynchronize((cudaStream_t)stream));
+    if (host != 0) {
+        cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), (cudaStream_t)stream);
+        return fail(ctx, TTQ_ERR_TIMEOUT, "a kernel gave up a bounded wait (status word 0x%x); results of that call are invalid", host);
+    }
     return TTQ_OK;
 }
 

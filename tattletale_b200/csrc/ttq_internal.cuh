@@ -94,11 +94,10 @@ cudaError_t launch_repack(int fmt, const uint8_t *canon, uint8_t *tiled, int64_t
 cudaError_t launch_dequant(int fmt, const uint8_t *tiled, float *out, int64_t ld, int64_t N, int64_t K,
                            int64_t SBp, cudaStream_t st);
 // GEMV for M <= MAX_GEMV_M.  `xq` is scratch for the separate x-prep pass (used when M > fused limit).
-cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t xq_capacity_k,
-                        cudaStream_t st, int *launches);
+cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t xq_capacity_k, int sms,
+                        int *status, cudaStream_t st, int *launches);
 cudaError_t launch_silu_and_mul(const void *in, int dt, int64_t M, int64_t H, int64_t ld_in, void *out,
                                 int64_t ld_out, cudaStream_t st);
-size_t gemv_max_dynamic_smem();
 cudaError_t gemv_configure();  // one-time cudaFuncSetAttribute calls
 
 // ---------------------------------------------------------------------------------------------

@@ -49,6 +49,10 @@ class Context:
         except Exception:
             pass
 
+    def check_device_status(self) -> None:
+        """Synchronises the current stream; raises TtqError(TIMEOUT) if a kernel gave up a bounded wait."""
+        check(self.handle, self._lib.ttq_device_status(self.handle, _stream_ptr(self.device)))
+
     @property
     def launch_count(self) -> int:
         return int(self._lib.ttq_launch_count(self.handle))

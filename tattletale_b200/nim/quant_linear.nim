@@ -1,0 +1,120 @@
+## QuantLinear -- drop-in for `Linear` (workspace/transformers/src/layers/linear.nim) whose weight
+## is a block-quantized matrix served by libttq (include/ttq.h).
+##
+## Same surface as the reference layer: a plain object, `init` from existing weights, `forward(x)`.
+## Compile with `nim cpp` like the rest of the workspace; link with `--passL:-lttq`.
+## This file is the whole host-side integration: every call goes through the C ABI, no libtorch call
+## is made on this path except `data_ptr` to obtain device pointers.
+
+import
+  std/options,
+  workspace/libtorch as F
+
+{.passL: "-lttq".}
+
+type
+  TtqCtx* {.importc: "ttq_ctx", header: "ttq.h", incompleteStruct.} = object
+  TtqWeight* {.importc: "ttq_weight", header: "ttq.h", incompleteStruct.} = object
+  TtqStatus* = cint
+  TtqFormat* {.size: sizeof(cint).} = enum
+    kQ8_0 = 0, kQ4_K = 1, kQ6_K = 2
+  TtqDtype* {.size: sizeof(cint).} = enum
+    kTtqBF16 = 0, kTtqF16 = 1, kTtqF32 = 2
+  TtqShard* {.importc: "ttq_shard", header: "ttq.h", bycopy.} = object
+    kind*, rank*, world*: int32
+
+proc ttq_init(device: cint, ctx: ptr ptr TtqCtx): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_destroy(ctx: ptr TtqCtx): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_last_error(ctx: ptr TtqCtx): cstring {.importc, cdecl, header: "ttq.h".}
+proc ttq_weight_create(ctx: ptr TtqCtx, fmt: TtqFormat, N, K: int64, hostBlocks: pointer, nbytes: csize_t,
+                       shard: ptr TtqShard, w: ptr ptr TtqWeight): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_weight_destroy(w: ptr TtqWeight): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_linear_forward(ctx: ptr TtqCtx, w: ptr TtqWeight, x: pointer, xDt: TtqDtype, M, ldx: int64,
+                        bias: pointer, biasDt: TtqDtype, y: pointer, yDt: TtqDtype, ldy: int64,
+                        stream: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_silu_and_mul(ctx: ptr TtqCtx, inp: pointer, dt: TtqDtype, M, H, ldIn: int64, outp: pointer,
+                      ldOut: int64, stream: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
+
+template check(ctx: ptr TtqCtx, rc: TtqStatus) =
+  ## Non-zero status -> ValueError, the exception style of the reference's own loaders
+  ## (workspace/safetensors/src/safetensors.nim:17-25).
+  if rc != 0:
+    raise newException(ValueError, "ttq: " & $ttq_last_error(ctx))
+
+type
+  TtqContext* = object
+    ## One per host thread and device (value type holding the raw handle; never a module-level global).
+    handle*: ptr TtqCtx
+
+  QuantLinear* = object
+    ## Quantized linear layer.
+    ##
+    ## Input:
+    ##   - An externally provided `x` of shape [..., in_features], bf16 or f16, on the context's device
+    ##   - A local packed weight of logical shape [out_features, in_features]
+    ##   - Optionally a local bias of shape [out_features]
+    ##
+    ## Return:
+    ##   - x @ weight^T + bias, shape [..., out_features], dtype of x
+    ctx*: ptr TtqCtx
+    weight*: ptr TtqWeight
+    bias*: Option[TorchTensor]
+    in_features*: int
+    out_features*: int
+
+proc init*(_: type TtqContext, device = 0): TtqContext =
+  check(nil, ttq_init(device.cint, addr result.handle))
+
+proc close*(c: var TtqContext) =
+  discard ttq_destroy(c.handle)
+  c.handle = nil
+
+proc init*(_: type QuantLinear, ctx: TtqContext, fmt: TtqFormat, blocks: pointer, nbytes: int,
+           out_features, in_features: int, bias = none(TorchTensor)): QuantLinear =
+  ## Creates a quantized linear layer from canonical blocks in host memory (for instance the
+  ## `MemSlice` returned by `getMmapView`, workspace/safetensors/src/safetensors.nim:256-274).
+  ## The blocks are uploaded and repacked once; the host buffer can be unmapped afterwards.
+  result = QuantLinear(ctx: ctx.handle, bias: bias, in_features: in_features, out_features: out_features)
+  check(ctx.handle, ttq_weight_create(ctx.handle, fmt, out_features.int64, in_features.int64, blocks,
+                                      nbytes.csize_t, nil, addr result.weight))
+
+proc close*(self: var QuantLinear) =
+  discard ttq_weight_destroy(self.weight)
+  self.weight = nil
+
+func ttqDtype(k: ScalarKind): TtqDtype =
+  case k
+  of kBFloat16: kTtqBF16
+  of kFloat16: kTtqF16
+  of kFloat32: kTtqF32
+  else: raise newException(ValueError, "ttq: unsupported dtype " & $k)
+
+proc forward*(self: QuantLinear, x: TorchTensor, stream: pointer = nil): TorchTensor =
+  ## Forward pass for inference.
+  ##
+  ## Args:
+  ##   x: Input tensor of shape (..., in_features), contiguous in its last dimension
+  ##
+  ## Returns:
+  ##   Output tensor of shape (..., out_features)
+  let x2 = x.reshape([-1, self.in_features]).contiguous()
+  let M = x2.size(0)
+  var outShape = x.sizes().asNimView().toSeq()
+  outShape[^1] = self.out_features
+  result = F.empty(outShape, x.options())
+  let biasPtr = if self.bias.isSome: self.bias.get().data_ptr(byte) else: nil
+  let biasDt = if self.bias.isSome: ttqDtype(self.bias.get().scalarType()) else: kTtqF32
+  check(self.ctx, ttq_linear_forward(self.ctx, self.weight, x2.data_ptr(byte), ttqDtype(x2.scalarType()),
+                                     M.int64, self.in_features.int64, biasPtr, biasDt,
+                                     result.data_ptr(byte), ttqDtype(result.scalarType()),
+                                     self.out_features.int64, stream))
+
+proc silu_and_mul*(ctx: TtqContext, x: TorchTensor, stream: pointer = nil): TorchTensor =
+  ## Fused form of workspace/transformers/src/kernels/activations.nim:14-38.
+  let H = x.size(-1) div 2
+  let x2 = x.reshape([-1, 2 * H]).contiguous()
+  var outShape = x.sizes().asNimView().toSeq()
+  outShape[^1] = H
+  result = F.empty(outShape, x.options())
+  check(ctx.handle, ttq_silu_and_mul(ctx.handle, x2.data_ptr(byte), ttqDtype(x2.scalarType()), x2.size(0).int64,
+                                     H.int64, (2 * H).int64, result.data_ptr(byte), H.int64, stream))

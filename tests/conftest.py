@@ -35,6 +35,7 @@ def ctx():
     assert torch.cuda.is_available(), "GPU tests need a CUDA device"
     c = ttq.Context(0)
     yield c
+    c.check_device_status()  # no kernel gave up a bounded wait during the session
     c.close()
 
 
