@@ -37,7 +37,23 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, defines: tuple[str, ...] = (), out: str | None = None) -> str:
+    """Compile and link.  ``defines``/``out`` build an experimental variant next to the default library
+    (select it at load time with the TTQ_LIB environment variable)."""
+    if defines or out:
+        return _build_variant(verbose, defines, out or LIB)
+    return _build_default(force, verbose)
+
+
+def _build_variant(verbose: bool, defines: tuple[str, ...], out: str) -> str:
+    nvcc = _nvcc()
+    extra = ["-Xptxas", "-v"] if verbose else []
+    srcs = [os.path.join(CSRC, s) for s in SOURCES]
+    subprocess.check_call([nvcc, *NVCC_FLAGS, *extra, *[f"-D{d}" for d in defines], "-shared", "-o", out, *srcs])
+    return out
+
+
+def _build_default(force: bool = False, verbose: bool = False) -> str:
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(ROOT, "include", "ttq.h"))
     objs = []
@@ -56,4 +72,6 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    defs = tuple(a[2:] for a in sys.argv[1:] if a.startswith("-D"))
+    outs = [a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--out=")]
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, defines=defs, out=outs[0] if outs else None))

@@ -257,7 +257,10 @@ struct GemvParams {
     int *status;  // device word: bit 0 set when a bounded wait gave up
 };
 
-constexpr int RING_STAGES = 2;
+#ifndef TTQ_RING_STAGES
+#define TTQ_RING_STAGES 2
+#endif
+constexpr int RING_STAGES = TTQ_RING_STAGES;  // stages of each warp's bulk-copy ring
 constexpr int XSRC_CONVERT = 0, XSRC_COPY = 1, XSRC_GLOBAL = 2;
 
 // Shared-memory carve-up, identical on host (size) and device (offsets).  `rows` = activation rows
@@ -269,7 +272,7 @@ __host__ __device__ inline SmemLayout smem_layout(int fmt, int MG, int rows, int
     SmemLayout L;
     const int64_t Kp = SBp * TILE_K;
     uint32_t o = 0;
-    L.bars = o; o += 256;                                  // [warps][stages] mbarriers + one for the planes
+    L.bars = o; o += 256 + 64 * (RING_STAGES > 3 ? RING_STAGES - 3 : 0);  // [warps][stages] mbarriers + one for the planes (last 8 bytes)
     L.hdr = o; o += GEMV_WARPS * 1024;                      // per-warp unpacked sub-block scales
     L.red = o; o += GEMV_WARPS * MG * 6 * 32 * 4;           // per-warp partial sums (dot part + offset part)
     L.ring = o; o += GEMV_WARPS * RING_STAGES * tile_bytes(fmt);
@@ -486,7 +489,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, XSRC == XSRC_GLOBAL ? 2 : 3) gem
     float *red_s = reinterpret_cast<float *>(smem + L.red);
     const uint32_t ring_u32 = smem0 + L.ring + warp * STAGES * TB;
     const uint32_t bar_u32 = smem0 + L.bars + warp * STAGES * 8;
-    const uint32_t xbar_u32 = smem0 + L.bars + 248;
+    const uint32_t xbar_u32 = smem0 + L.hdr - 8;  // last slot of the barrier area, past every ring barrier
 
     // group / K-slice of this warp
     const int WK = p.wk, R = GEMV_WARPS / WK;
@@ -514,7 +517,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, XSRC == XSRC_GLOBAL ? 2 : 3) gem
     const uint8_t *p_row = a.tiles + (rt0 * SBp + sb_begin) * (int64_t)TB;
     const int64_t p_row_step = rt_step * SBp * (int64_t)TB;
     auto issue_next = [&]() {
-        const int s = p_item & (STAGES - 1);
+        const int s = p_item % STAGES;
         mbar_expect_tx(bar_u32 + 8 * s, TB);
         bulk_g2s(ring_u32 + s * TB, p_row + (int64_t)p_sbi * TB, TB, bar_u32 + 8 * s);
         p_item++;
@@ -590,7 +593,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, XSRC == XSRC_GLOBAL ? 2 : 3) gem
 #pragma unroll
         for (int m = 0; m < MR; m++) oacc[m] = 0.f;
         for (int sbi = 0; sbi < nsb; sbi++, item++) {
-            const int s = item & (STAGES - 1);
+            const int s = item % STAGES;
             if (alive) alive = mbar_wait_bounded(bar_u32 + 8 * s, (uint32_t)((item / STAGES) & 1), p.status);
             compute_tile<FMT, MG, SHARED, MR>(ring_u32 + s * TB, sb_begin + sbi, lane, hdr_u32, A, yacc, oacc);
             __syncwarp();  // every lane is done reading the stage before it is refilled
