@@ -154,6 +154,16 @@ TTQ_API ttq_status ttq_device_status(ttq_ctx *ctx, void *stream);
 TTQ_API ttq_status ttq_silu_and_mul(ttq_ctx *ctx, const void *in_dev, ttq_dtype dt, int64_t M, int64_t H,
                             int64_t ld_in, void *out_dev, int64_t ld_out, void *stream);
 
+/* ---- optional device timeline (tracing) -------------------------------------------------------
+ * The reference meters host procedures (workspace/probes/src/tracer.nim:72-133, enabled by a
+ * compile-time switch); the counterpart here is a device-side timeline enabled by setting the
+ * environment variable TTQ_TRACE=1 before ttq_init.  Every kernel then records, from its first block,
+ * eight 64-bit words: kind (1 activation pass, 2 GEMV), start, after the dependency wait, activations
+ * ready, first weight tile ready, end of block 0 (all in globaltimer nanoseconds), grid size, N.
+ * ttq_trace_read synchronises the device, copies up to max_entries entries (8 words each) into `out`,
+ * stores their number in *n_entries and clears the buffer.  With tracing off it reports 0 entries. */
+TTQ_API ttq_status ttq_trace_read(ttq_ctx *ctx, uint64_t *out, int64_t max_entries, int64_t *n_entries);
+
 /* ---- introspection for benchmarks ----------------------------------------------------------- */
 
 /* Number of kernels this context has launched since creation (forward, repack, dequantize ...). */

@@ -49,6 +49,7 @@ SIGNATURES = {
     "ttq_silu_and_mul": (_ci, [_vp, _vp, _ci, _i64, _i64, _i64, _vp, _i64, _vp]),
     "ttq_launch_count": (_i64, [_vp]),
     "ttq_device_status": (_ci, [_vp, _vp]),
+    "ttq_trace_read": (_ci, [_vp, _vp, _i64, ctypes.POINTER(_i64)]),
 }
 
 _lib = None

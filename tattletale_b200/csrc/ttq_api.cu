@@ -3,6 +3,7 @@
 // device; there is no CPU compute path.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -20,6 +21,7 @@ struct ttq_ctx {
     void *xq_base;
     int sms;          // multiprocessor count of the device
     int *dev_status;  // device word the kernels OR failure bits into (bit 0: a bounded wait gave up)
+    unsigned long long *trace;  // device timeline buffer, allocated only when TTQ_TRACE=1 is set at init
     // device staging for the *_host entry points
     uint8_t *stage_x, *stage_y, *stage_b;
     size_t stage_x_bytes, stage_y_bytes, stage_b_bytes;
@@ -148,8 +150,14 @@ ttq_status ttq_init(int device, ttq_ctx **out) {
     const size_t planes_b = (size_t)2 * MP * Kc, s16_b = (size_t)MP * (Kc / 16) * 4, s32_b = (size_t)MP * (Kc / 32) * 4,
                  sx_b = (size_t)MP * (Kc / 256 + 4) * 4;
     cudaError_t e = cudaMalloc(&ctx->xq_base, planes_b + s16_b + s32_b + sx_b);
-    if (e == cudaSuccess) e = cudaMalloc(&ctx->dev_status, 256);
-    if (e == cudaSuccess) e = cudaMemset(ctx->dev_status, 0, 256);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->dev_status, 1024);  // status word, then 768 zero bytes
+    if (e == cudaSuccess) e = cudaMemset(ctx->dev_status, 0, 1024);
+    const char *tr = getenv("TTQ_TRACE");
+    if (e == cudaSuccess && tr && tr[0] == '1') {
+        const size_t tb = (size_t)(8 + 8 * TTQ_TRACE_ENTRIES) * sizeof(unsigned long long);
+        e = cudaMalloc(&ctx->trace, tb);
+        if (e == cudaSuccess) e = cudaMemset(ctx->trace, 0, tb);
+    }
     if (e == cudaSuccess) e = cudaMalloc(&ctx->stage_x, STAGE_X_BYTES);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->stage_y, STAGE_Y_BYTES);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->stage_b, STAGE_B_BYTES);
@@ -179,6 +187,7 @@ ttq_status ttq_destroy(ttq_ctx *ctx) {
     if (ctx->host_stream) cudaStreamDestroy(ctx->host_stream);
     cudaFree(ctx->xq_base);
     cudaFree(ctx->dev_status);
+    cudaFree(ctx->trace);
     cudaFree(ctx->stage_x);
     cudaFree(ctx->stage_y);
     cudaFree(ctx->stage_b);
@@ -334,7 +343,8 @@ ttq_status ttq_linear_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_d
         a.y = reinterpret_cast<uint8_t *>(y_dev) + (size_t)m0 * ldy * dt_size(y_dt);
         a.y_dt = y_dt; a.ldy = ldy;
         int launches = 0;
-        cudaError_t e = launch_gemv(w->fmt, a, ctx->xq, ctx->xq_capacity_k, ctx->sms, ctx->dev_status, st, &launches);
+        cudaError_t e = launch_gemv(w->fmt, a, ctx->xq, ctx->xq_capacity_k, reinterpret_cast<const uint8_t *>(ctx->dev_status) + 256, ctx->sms,
+                                    ctx->dev_status, ctx->trace, st, &launches);
         ctx->launches += launches;
         if (e != cudaSuccess) return cuda_fail(ctx, e, "linear forward launch");
     }
@@ -376,6 +386,21 @@ ttq_status ttq_device_status(ttq_ctx *ctx, void *stream) {
         cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), (cudaStream_t)stream);
         return fail(ctx, TTQ_ERR_TIMEOUT, "a kernel gave up a bounded wait (status word 0x%x); results of that call are invalid", host);
     }
+    return TTQ_OK;
+}
+
+ttq_status ttq_trace_read(ttq_ctx *ctx, uint64_t *out, int64_t max_entries, int64_t *n_entries) {
+    if (!ctx || !out || !n_entries) return TTQ_ERR_INVALID_ARG;
+    *n_entries = 0;
+    if (!ctx->trace) return TTQ_OK;
+    TTQ_CUDA(ctx, cudaDeviceSynchronize());
+    unsigned long long count = 0;
+    TTQ_CUDA(ctx, cudaMemcpy(&count, ctx->trace, sizeof(count), cudaMemcpyDeviceToHost));
+    int64_t n = (int64_t)(count < (unsigned long long)TTQ_TRACE_ENTRIES ? count : TTQ_TRACE_ENTRIES);
+    if (n > max_entries) n = max_entries;
+    if (n > 0) TTQ_CUDA(ctx, cudaMemcpy(out, ctx->trace + 8, (size_t)n * 8 * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+    TTQ_CUDA(ctx, cudaMemset(ctx->trace, 0, sizeof(unsigned long long)));
+    *n_entries = n;
     return TTQ_OK;
 }
 

@@ -29,32 +29,24 @@ namespace ttq {
 
 namespace {
 
-constexpr int GEMV_WARPS = 8;
+constexpr int GEMV_WARPS = 8;  // warps of the activation pass and of the small GEMV CTA; at most this many split K
 constexpr int GEMV_THREADS = GEMV_WARPS * 32;
 constexpr int PLANE_PAD = 16;  // bytes between activation planes in shared memory (bank spread)
 
-// ---- integer tensor-core wrappers ---------------------------------------------------------------
+// ---- integer tensor-core wrappers (D = A*B + D) ---------------------------------------------------
 __device__ __forceinline__ void mma_k32_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                              uint32_t b0, uint32_t b1) {
-    asm(
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%10,%10,%10,%10};\n"
-        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void mma_k32_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                              uint32_t b0, uint32_t b1) {
-    asm(
-        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%10,%10,%10,%10};\n"
-        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
-}
-__device__ __forceinline__ void mma_k16_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-    asm(
-        "mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};\n"
-        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
-        : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 // ---- bulk-copy ring primitives (all waits are bounded) ---------------------------------------------
@@ -95,6 +87,25 @@ __device__ __forceinline__ void named_barrier(int id, int nthreads) {
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+constexpr int TRACE_CAP = 8192;  // entries
+// Timeline entry of one kernel (written by thread 0 of block 0 when tracing is on):
+// [0] kind (1 = activation pass, 2 = GEMV), [1] start, [2] after the dependency wait, [3] activations ready,
+// [4] first weight tile ready, [5] end of block 0, [6] grid size, [7] N
+__device__ __forceinline__ unsigned long long *trace_open(unsigned long long *trace, unsigned long long kind) {
+    if (trace == nullptr || blockIdx.x != 0 || threadIdx.x != 0) return nullptr;
+    const unsigned long long slot = atomicAdd(trace, 1ull);
+    if (slot >= TRACE_CAP) return nullptr;
+    unsigned long long *e = trace + 8 + slot * 8;
+    e[0] = kind;
+    e[1] = global_ns();
+    return e;
+}
+
 // compile-time loop: f(std::integral_constant<int, I>) for I in [0, N)
 template <int V>
 struct IC {
@@ -119,35 +130,46 @@ struct XqRow {
 
 __host__ __device__ constexpr int sx_stride(int64_t SBp) { return (int)((SBp + 3) & ~(int64_t)3); }
 
+// Raw 8 activations of one lane (loaded early so that several chunks' loads are in flight at once).
+struct RawChunk {
+    uint4 raw;
+    bool vec;  // raw holds 8 16-bit values; otherwise the slow path reloads element by element
+};
+__device__ __forceinline__ RawChunk xprep_load(const void *xrow, int x_dt, int64_t K, int sb, int lane) {
+    const int64_t k0 = (int64_t)sb * TILE_K + 8 * lane;
+    RawChunk rc;
+    rc.raw = make_uint4(0, 0, 0, 0);
+    rc.vec = xrow != nullptr && (x_dt != TTQ_DT_F32) && (k0 + 8 <= K) &&
+             ((reinterpret_cast<uintptr_t>(xrow) + 2 * k0) & 15) == 0;
+    if (rc.vec) rc.raw = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(xrow) + k0);
+    return rc;
+}
+
 // One warp converts the 256-wide chunk `sb` of activation row `xrow` (nullptr = emit zeros):
 // xq = round(x * 32639 / amax) in [-32639, 32639], stored as two int8 planes with xq = 256*hi + lo.
-__device__ __forceinline__ void xprep_chunk(const void *xrow, int x_dt, int64_t K, int sb, int lane, const XqRow &dst) {
+__device__ __forceinline__ void xprep_convert(const RawChunk &rc, const void *xrow, int x_dt, int64_t K, int sb, int lane,
+                                              const XqRow &dst) {
     const int64_t k0 = (int64_t)sb * TILE_K + 8 * lane;
     float v[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) v[i] = 0.f;
-    if (xrow != nullptr) {
-        const bool vec = (x_dt != TTQ_DT_F32) && (k0 + 8 <= K) &&
-                         ((reinterpret_cast<uintptr_t>(xrow) + 2 * k0) & 15) == 0;
-        if (vec) {
-            uint4 raw = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(xrow) + k0);
-            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    if (rc.vec) {
+        const uint32_t w[4] = {rc.raw.x, rc.raw.y, rc.raw.z, rc.raw.w};
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                if (x_dt == TTQ_DT_BF16) {
-                    v[2 * i] = __uint_as_float(w[i] << 16);
-                    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-                } else {
-                    float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
-                    v[2 * i] = f.x;
-                    v[2 * i + 1] = f.y;
-                }
+        for (int i = 0; i < 4; i++) {
+            if (x_dt == TTQ_DT_BF16) {
+                v[2 * i] = __uint_as_float(w[i] << 16);
+                v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+            } else {
+                float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+                v[2 * i] = f.x;
+                v[2 * i + 1] = f.y;
             }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 8; i++)
-                if (k0 + i < K) v[i] = load_as_float(xrow, x_dt, k0 + i);
         }
+    } else if (xrow != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            if (k0 + i < K) v[i] = load_as_float(xrow, x_dt, k0 + i);
     }
     float amax = 0.f;
 #pragma unroll
@@ -180,13 +202,18 @@ __device__ __forceinline__ void xprep_chunk(const void *xrow, int x_dt, int64_t 
     if ((lane & 3) == 0) dst.sum32[sb * 8 + (lane >> 2)] = (float)s32;
     if (lane == 0) dst.sx[sb] = amax > 1e-20f ? amax * (1.0f / (float)XQ_MAX) : 0.f;
 }
+__device__ __forceinline__ void xprep_chunk(const void *xrow, int x_dt, int64_t K, int sb, int lane, const XqRow &dst) {
+    xprep_convert(xprep_load(xrow, x_dt, K, sb, lane), xrow, x_dt, K, sb, lane, dst);
+}
 
 // Separate conversion pass: (Mpad x SBp) chunks, one warp each; rows >= M are written as zeros.
 __global__ void __launch_bounds__(GEMV_THREADS) xprep_kernel(const void *__restrict__ x, int x_dt, int64_t M,
                                                              int64_t Mpad, int64_t K, int64_t ldx, int64_t SBp,
-                                                             XqView xq) {
+                                                             XqView xq, unsigned long long *trace) {
+    unsigned long long *te = trace_open(trace, 1);
     grid_launch_dependents();
     grid_dependency_wait();  // the scratch planes may still be read by the preceding kernel
+    if (te) te[2] = global_ns();
     const int lane = threadIdx.x & 31;
     const int64_t Kp = SBp * TILE_K;
     const int64_t unit = (int64_t)blockIdx.x * GEMV_WARPS + (threadIdx.x >> 5);
@@ -201,6 +228,10 @@ __global__ void __launch_bounds__(GEMV_THREADS) xprep_kernel(const void *__restr
         xrow = reinterpret_cast<const uint8_t *>(x) + m * ldx * esz;
     }
     xprep_chunk(xrow, x_dt, K, sb, lane, dst);
+    if (te) {
+        te[5] = global_ns();
+        te[6] = gridDim.x;
+    }
 }
 
 // ---- shared-memory access with 32-bit addresses and immediate offsets ----------------------------
@@ -249,12 +280,19 @@ __device__ __forceinline__ void stsf(uint32_t addr, float v) {
     asm volatile("st.shared.f32 [%0+%1], %2;" ::"r"(addr), "n"(OFF), "f"(v) : "memory");
 }
 
+template <int OFF>
+__device__ __forceinline__ void sts128f(uint32_t addr, float a, float b, float c, float d) {
+    asm volatile("st.shared.v4.f32 [%0+%1], {%2,%3,%4,%5};" ::"r"(addr), "n"(OFF), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 // ---- the GEMV --------------------------------------------------------------------------------
 struct GemvParams {
     LinearArgs a;
-    XqView xq;    // activation planes in scratch (XSRC 1 and 2)
-    int wk;       // warps that split K of one row tile (1, 2, 4 or 8)
-    int *status;  // device word: bit 0 set when a bounded wait gave up
+    XqView xq;             // activation planes in scratch
+    const uint8_t *zeros;  // >= 512 zero bytes in global memory (operand of lanes outside the block diagonal)
+    int wk;                // warps that split K of one row tile (1, 2, 4 or 8)
+    int *status;           // device word: bit 0 set when a bounded wait gave up
+    unsigned long long *trace;  // optional timeline buffer (nullptr = off): [0] = entry counter, entries of 8 words from [8]
 };
 
 #ifndef TTQ_RING_STAGES
@@ -262,20 +300,26 @@ struct GemvParams {
 #endif
 constexpr int RING_STAGES = TTQ_RING_STAGES;  // stages of each warp's bulk-copy ring
 constexpr int XSRC_CONVERT = 0, XSRC_COPY = 1, XSRC_GLOBAL = 2;
+constexpr int ZERO_BYTES = 512;
+
+// K distance between the sub-blocks that share one MMA (groups u = 0..3), in weights = plane bytes
+__host__ __device__ constexpr int group_stride(int fmt) { return fmt == TTQ_FMT_Q4_K ? 64 : (fmt == TTQ_FMT_Q8_0 ? 32 : 16); }
 
 // Shared-memory carve-up, identical on host (size) and device (offsets).  `rows` = activation rows
 // held in shared memory (0 when they stay in scratch).
 struct SmemLayout {
-    uint32_t bars, hdr, red, ring, sx, sum32, sum16, planes, total;
+    uint32_t bars, zero, hdr, red, ring, sx, sum32, sum16, planes, total;
 };
-__host__ __device__ inline SmemLayout smem_layout(int fmt, int MG, int rows, int64_t SBp) {
+__host__ __device__ inline SmemLayout smem_layout(int fmt, int MP, int rows, int64_t SBp, int nw) {
     SmemLayout L;
     const int64_t Kp = SBp * TILE_K;
     uint32_t o = 0;
-    L.bars = o; o += 256 + 64 * (RING_STAGES > 3 ? RING_STAGES - 3 : 0);  // [warps][stages] mbarriers + one for the planes (last 8 bytes)
-    L.hdr = o; o += GEMV_WARPS * 1024;                      // per-warp unpacked sub-block scales
-    L.red = o; o += GEMV_WARPS * MG * 6 * 32 * 4;           // per-warp partial sums (dot part + offset part)
-    L.ring = o; o += GEMV_WARPS * RING_STAGES * tile_bytes(fmt);
+    L.bars = o; o += nw * 8 * RING_STAGES + 64;              // [warps][stages] mbarriers, then one for the planes
+    o = (o + 127u) & ~127u;
+    L.zero = o; o += ZERO_BYTES;
+    L.hdr = o; o += nw * 1024;                        // per-warp unpacked sub-block scales
+    L.red = o; o += nw * 2 * TILE_ROWS * MP * 4;      // per-warp partial sums: dot part, offset part
+    L.ring = o; o += nw * RING_STAGES * tile_bytes(fmt);
     L.sx = L.sum32 = L.sum16 = L.planes = o;
     if (rows > 0) {
         L.sx = o; o += (uint32_t)(rows * sx_stride(SBp) * 4);
@@ -288,19 +332,29 @@ __host__ __device__ inline SmemLayout smem_layout(int fmt, int MG, int rows, int
 }
 
 // Per-lane view of the activation side, set up once per kernel.
-template <int MG, bool SHARED>
+// Operand B of one MMA is block diagonal: column c = 2u + plane is non-zero only in K group u.  A
+// lane (g, t) supplies column g in groups t>>1 (register b0) and 2 + (t>>1) (register b1), so at
+// most one of its two registers is non-zero; the other one (or both) is read from a zero region.
+// b0/b1 addresses of activation row m, tile sb: base + mul * (sb*256 + m*row_step), mul = 0 for zeros.
+template <bool SHARED>
 struct ActView {
-    uint32_t bfrag_s;            // SHARED: address of this lane's B word stream (column g, byte 4t)
-    const uint8_t *bfrag_g[MG];  // !SHARED: pointers, one per activation group (column 8q+g)
+    uint32_t b0_s, b1_s;          // SHARED: shared-memory addresses
+    const uint8_t *b0_g, *b1_g;   // !SHARED: global pointers
+    uint32_t mul0, mul1;          // 1 if the register is on the diagonal, else 0
+    uint32_t row_step;            // bytes between the plane pairs of consecutive activation rows
     uint32_t sx_s, sum32_s, sum16_s;        // SHARED: addresses of row 0
     const float *sx_g, *sum32_g, *sum16_g;  // !SHARED
     int SBs, Kp;
-    int rows;  // activation rows that exist in the side arrays
 
     template <int OFF>
-    __device__ __forceinline__ uint32_t bword(int q, uint32_t tile_off) const {
-        if constexpr (SHARED) return lds32<OFF>(bfrag_s + tile_off);
-        else return __ldg(reinterpret_cast<const uint32_t *>(bfrag_g[q] + tile_off + OFF));
+    __device__ __forceinline__ uint32_t b0(uint32_t off) const {
+        if constexpr (SHARED) return lds32<OFF>(b0_s + off);
+        else return __ldg(reinterpret_cast<const uint32_t *>(b0_g + off + OFF));
+    }
+    template <int OFF>
+    __device__ __forceinline__ uint32_t b1(uint32_t off) const {
+        if constexpr (SHARED) return lds32<OFF>(b1_s + off);
+        else return __ldg(reinterpret_cast<const uint32_t *>(b1_g + off + OFF));
     }
     __device__ __forceinline__ float sx(int m, int sb) const {
         if constexpr (SHARED) return ldsf<0>(sx_s + (uint32_t)(m * SBs + sb) * 4);
@@ -318,29 +372,31 @@ struct ActView {
 };
 
 __device__ __forceinline__ float byte_to_float(uint32_t w, int i) { return (float)((w >> (8 * i)) & 0xffu); }
+__device__ __forceinline__ float combine(const int (&c)[4], int i) { return (float)(c[2 * i] * 256 + c[2 * i + 1]); }
 
-// One tile (16 rows x 256 weights) from a shared-memory stage.
-//  Main role, lane (g,t): integer dot products of rows g and g+8 with activation row 4q+t, scaled
-//  by the sub-block scale, accumulated into yacc[q][0..1].
+// One tile (16 rows x 256 weights) from a shared-memory stage, for MR activation rows m0..m0+MR-1.
+//  Main role, lane (g,t): after the windows of a set are accumulated it owns the integer dot
+//  products of sub-block t of the set for rows g and g+8; it scales them and adds them to
+//  yacc[m][0..1] (the four t lanes of a row hold different sub-blocks: summed at flush time).
 //  Header role, lane (r = lane&15, h = lane>>4): unpacks the scales of row r (half h of the
 //  sub-blocks) into shared memory for the main role, and accumulates the part of the result that
 //  does not depend on the quants (Q4_K: dmin*m_j * sum of activations; Q6_K: the -32 offset) into
-//  oacc[m], m < MR.  Output = sum over K tiles of (yacc part) - (oacc parts of both halves).
-template <int FMT, int MG, bool SHARED, int MR>
-__device__ __forceinline__ void compute_tile(uint32_t stage, int sb, int lane, uint32_t hdr,
-                                             const ActView<MG, SHARED> &A, float (&yacc)[MG][2], float (&oacc)[MR]) {
+//  oacc[m].  Output = sum over K tiles of (yacc parts) - (oacc parts of both halves).
+template <int FMT, bool SHARED, int MR>
+__device__ __forceinline__ void compute_tile(uint32_t stage, int sb, int m0, int lane, uint32_t hdr,
+                                             const ActView<SHARED> &A, float (&yacc)[MR][2], float (&oacc)[MR]) {
     const int g = lane >> 2, t = lane & 3;
     const int r = lane & 15, h = lane >> 4;
-    const uint32_t hr = hdr + (uint32_t)g * 8;  // reader base: {scale(row g), scale(row g+8)} of sub-block 0
     const uint32_t sa = stage + (uint32_t)lane * 16;
-    const uint32_t toff = (uint32_t)sb * TILE_K;
-    float tmp[MG][2];
+    const uint32_t toff = (uint32_t)sb * TILE_K + (uint32_t)m0 * A.row_step;
+    const uint32_t off0 = A.mul0 * toff, off1 = A.mul1 * toff;
+    const uint32_t rs0 = A.mul0 * A.row_step, rs1 = A.mul1 * A.row_step;
+    float tmp[MR][2];
 #pragma unroll
-    for (int q = 0; q < MG; q++) tmp[q][0] = tmp[q][1] = 0.f;
+    for (int m = 0; m < MR; m++) tmp[m][0] = tmp[m][1] = 0.f;
 
     if constexpr (FMT == TTQ_FMT_Q4_K) {
         {
-            const uint32_t hw = hdr + (uint32_t)((h * 4 * 8 + (r & 7)) * 2 + (r >> 3)) * 4;
             const uint4 hv = lds128<2048>(stage + (uint32_t)r * 16);
             const __half2 dd = *reinterpret_cast<const __half2 *>(&hv.x);
             const float d = __low2float(dd), dmin = __high2float(dd), d16 = d * 0.0625f;
@@ -354,62 +410,74 @@ __device__ __forceinline__ void compute_tile(uint32_t stage, int sb, int lane, u
             }
             __syncwarp();  // main-role reads of the previous tile's scales are done
             // odd sub-blocks are fed to the MMA as 16*q (high nibble left in place): scale by d/16
-            stsf<0 * 64>(hw, d * byte_to_float(scw, 0));
-            stsf<1 * 64>(hw, d16 * byte_to_float(scw, 1));
-            stsf<2 * 64>(hw, d * byte_to_float(scw, 2));
-            stsf<3 * 64>(hw, d16 * byte_to_float(scw, 3));
-            const float m0 = byte_to_float(mw, 0), m1 = byte_to_float(mw, 1), m2 = byte_to_float(mw, 2),
-                        m3 = byte_to_float(mw, 3);
+            sts128f<0>(hdr + (uint32_t)(r * 8 + 4 * h) * 4, d * byte_to_float(scw, 0), d16 * byte_to_float(scw, 1),
+                       d * byte_to_float(scw, 2), d16 * byte_to_float(scw, 3));
+            const float mn0 = byte_to_float(mw, 0), mn1 = byte_to_float(mw, 1), mn2 = byte_to_float(mw, 2),
+                        mn3 = byte_to_float(mw, 3);
 #pragma unroll
             for (int m = 0; m < MR; m++) {
-                const float4 s4 = A.sum32x4(m, sb * 8 + h * 4);
-                const float part = fmaf(m0, s4.x, fmaf(m1, s4.y, fmaf(m2, s4.z, m3 * s4.w)));
-                oacc[m] = fmaf(A.sx(m, sb) * dmin, part, oacc[m]);
+                const float4 s4 = A.sum32x4(m0 + m, sb * 8 + h * 4);
+                const float part = fmaf(mn0, s4.x, fmaf(mn1, s4.y, fmaf(mn2, s4.z, mn3 * s4.w)));
+                oacc[m] = fmaf(A.sx(m0 + m, sb) * dmin, part, oacc[m]);
             }
             __syncwarp();
         }
-        static_for<0, 4>([&](auto pp_) {
-            constexpr int pp = decltype(pp_)::value;
-            const uint4 w = lds128<pp * 512>(sa);
-            static_for<0, 2>([&](auto hn_) {
-                constexpr int hn = decltype(hn_)::value;
-                constexpr int j = 2 * pp + hn;
-                constexpr uint32_t msk = hn ? 0xf0f0f0f0u : 0x0f0f0f0fu;
-                const float2 sc = lds64f<j * 64>(hr);
+        int cx[MR][4], cy[MR][4];
 #pragma unroll
-                for (int q = 0; q < MG; q++) {
-                    int c[4];
-                    mma_k32_u8s8(c, w.x & msk, w.y & msk, w.z & msk, w.w & msk, A.template bword<j * 32>(q, toff),
-                                 A.template bword<j * 32 + 16>(q, toff));
-                    tmp[q][0] = fmaf(sc.x, (float)(c[0] * 256 + c[1]), tmp[q][0]);
-                    tmp[q][1] = fmaf(sc.y, (float)(c[2] * 256 + c[3]), tmp[q][1]);
-                }
-            });
+        for (int m = 0; m < MR; m++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) cx[m][i] = cy[m][i] = 0;
+        static_for<0, 4>([&](auto n_) {
+            constexpr int n = decltype(n_)::value;
+            const uint4 w = lds128<n * 512>(sa);
+            const uint32_t l0 = w.x & 0x0f0f0f0fu, l1 = w.y & 0x0f0f0f0fu, l2 = w.z & 0x0f0f0f0fu, l3 = w.w & 0x0f0f0f0fu;
+            const uint32_t h0 = w.x & 0xf0f0f0f0u, h1 = w.y & 0xf0f0f0f0u, h2 = w.z & 0xf0f0f0f0u, h3 = w.w & 0xf0f0f0f0u;
+#pragma unroll
+            for (int m = 0; m < MR; m++) {
+                const uint32_t o0 = off0 + m * rs0, o1 = off1 + m * rs1;
+                mma_k32_u8s8(cx[m], l0, l1, l2, l3, A.template b0<8 * n>(o0), A.template b1<8 * n>(o1));
+                mma_k32_u8s8(cy[m], h0, h1, h2, h3, A.template b0<32 + 8 * n>(o0), A.template b1<32 + 8 * n>(o1));
+            }
         });
+        // lane (g,t): set X holds sub-block 2t, set Y sub-block 2t+1
+        const uint32_t hr = hdr + (uint32_t)(g * 8 + 2 * t) * 4;
+        const float2 sg = lds64f<0>(hr), sg8 = lds64f<256>(hr);
+#pragma unroll
+        for (int m = 0; m < MR; m++) {
+            tmp[m][0] = fmaf(sg.x, combine(cx[m], 0), sg.y * combine(cy[m], 0));
+            tmp[m][1] = fmaf(sg8.x, combine(cx[m], 1), sg8.y * combine(cy[m], 1));
+        }
     } else if constexpr (FMT == TTQ_FMT_Q8_0) {
         {
             // fp16 d[r][b]: header lane (r, h) converts blocks 4h..4h+3 of row r
-            const uint32_t hw = hdr + (uint32_t)((h * 4 * 8 + (r & 7)) * 2 + (r >> 3)) * 4;
             const uint2 dv = lds64<4096>(stage + (uint32_t)r * 16 + (uint32_t)h * 8);
             const float2 f01 = __half22float2(*reinterpret_cast<const __half2 *>(&dv.x));
             const float2 f23 = __half22float2(*reinterpret_cast<const __half2 *>(&dv.y));
             __syncwarp();
-            stsf<0 * 64>(hw, f01.x);
-            stsf<1 * 64>(hw, f01.y);
-            stsf<2 * 64>(hw, f23.x);
-            stsf<3 * 64>(hw, f23.y);
+            sts128f<0>(hdr + (uint32_t)(r * 8 + 4 * h) * 4, f01.x, f01.y, f23.x, f23.y);
             __syncwarp();
         }
-        static_for<0, 8>([&](auto b_) {
-            constexpr int b = decltype(b_)::value;
-            const uint4 w = lds128<b * 512>(sa);
-            const float2 sc = lds64f<b * 64>(hr);
+        const uint32_t hr = hdr + (uint32_t)(g * 8 + t) * 4;
+        static_for<0, 2>([&](auto s_) {
+            constexpr int s = decltype(s_)::value;
+            int cs[MR][4];
 #pragma unroll
-            for (int q = 0; q < MG; q++) {
-                int c[4];
-                mma_k32_s8s8(c, w.x, w.y, w.z, w.w, A.template bword<b * 32>(q, toff), A.template bword<b * 32 + 16>(q, toff));
-                tmp[q][0] = fmaf(sc.x, (float)(c[0] * 256 + c[1]), tmp[q][0]);
-                tmp[q][1] = fmaf(sc.y, (float)(c[2] * 256 + c[3]), tmp[q][1]);
+            for (int m = 0; m < MR; m++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) cs[m][i] = 0;
+            static_for<0, 4>([&](auto n_) {
+                constexpr int n = decltype(n_)::value;
+                const uint4 w = lds128<(4 * s + n) * 512>(sa);
+#pragma unroll
+                for (int m = 0; m < MR; m++)
+                    mma_k32_s8s8(cs[m], w.x, w.y, w.z, w.w, A.template b0<128 * s + 8 * n>(off0 + m * rs0),
+                                 A.template b1<128 * s + 8 * n>(off1 + m * rs1));
+            });
+            const float dg = ldsf<16 * s>(hr), dg8 = ldsf<256 + 16 * s>(hr);  // block 4s+t of rows g, g+8
+#pragma unroll
+            for (int m = 0; m < MR; m++) {
+                tmp[m][0] = fmaf(dg, combine(cs[m], 0), tmp[m][0]);
+                tmp[m][1] = fmaf(dg8, combine(cs[m], 1), tmp[m][1]);
             }
         });
     } else {
@@ -418,7 +486,6 @@ __device__ __forceinline__ void compute_tile(uint32_t stage, int sb, int lane, u
             const uint2 scw = lds64<3072>(stage + (uint32_t)r * 16 + (uint32_t)h * 8);
             const float d = __half2float(
                 __ushort_as_half((unsigned short)(lds32<3328>(stage + (uint32_t)(r >> 1) * 4) >> (16 * (r & 1)))));
-            const uint32_t hw6 = hdr + (uint32_t)((h * 8 * 8 + (r & 7)) * 2 + (r >> 3)) * 4;
             float ds[8];
 #pragma unroll
             for (int i = 0; i < 8; i++) {
@@ -426,73 +493,85 @@ __device__ __forceinline__ void compute_tile(uint32_t stage, int sb, int lane, u
                 ds[i] = d * (float)(int)(int8_t)((word >> (8 * (i & 3))) & 0xff);
             }
             __syncwarp();
-            stsf<0 * 64>(hw6, ds[0]); stsf<1 * 64>(hw6, ds[1]); stsf<2 * 64>(hw6, ds[2]); stsf<3 * 64>(hw6, ds[3]);
-            stsf<4 * 64>(hw6, ds[4]); stsf<5 * 64>(hw6, ds[5]); stsf<6 * 64>(hw6, ds[6]); stsf<7 * 64>(hw6, ds[7]);
+            const uint32_t hw = hdr + (uint32_t)(r * 16 + 8 * h) * 4;
+            sts128f<0>(hw, ds[0], ds[1], ds[2], ds[3]);
+            sts128f<16>(hw, ds[4], ds[5], ds[6], ds[7]);
 #pragma unroll
             for (int m = 0; m < MR; m++) {
-                const float4 sA = A.sum16x4(m, sb * 16 + h * 8), sB = A.sum16x4(m, sb * 16 + h * 8 + 4);
+                const float4 sA = A.sum16x4(m0 + m, sb * 16 + h * 8), sB = A.sum16x4(m0 + m, sb * 16 + h * 8 + 4);
                 float part = fmaf(ds[0], sA.x, fmaf(ds[1], sA.y, fmaf(ds[2], sA.z, ds[3] * sA.w)));
                 part = fmaf(ds[4], sB.x, fmaf(ds[5], sB.y, fmaf(ds[6], sB.z, fmaf(ds[7], sB.w, part))));
-                oacc[m] = fmaf(A.sx(m, sb) * 32.f, part, oacc[m]);  // quants are stored with a +32 offset
+                oacc[m] = fmaf(A.sx(m0 + m, sb) * 32.f, part, oacc[m]);  // quants are stored with a +32 offset
             }
             __syncwarp();
         }
-        static_for<0, 4>([&](auto c4_) {
-            constexpr int c4 = decltype(c4_)::value;
-            const uint4 w = lds128<c4 * 512>(sa);
-            const uint2 hq = lds64<2048 + (c4 >> 1) * 512 + (c4 & 1) * 8>(sa);
-            static_for<0, 4>([&](auto s_) {
-                constexpr int s = decltype(s_)::value;
-                constexpr int j = 4 * c4 + s;
-                const uint32_t l0 = (s & 2) ? w.z : w.x, l1 = (s & 2) ? w.w : w.y;
-                uint32_t a0 = (s & 1) ? (l0 >> 4) : l0, a1 = (s & 1) ? (l1 >> 4) : l1;
-                // high 2 bits of sub-block s sit at bit pair s of each byte: move them to bits 4..5
-                const uint32_t h0 = s == 0 ? (hq.x << 4) : s == 1 ? (hq.x << 2) : s == 2 ? hq.x : (hq.x >> 2);
-                const uint32_t h1 = s == 0 ? (hq.y << 4) : s == 1 ? (hq.y << 2) : s == 2 ? hq.y : (hq.y >> 2);
-                a0 = (a0 & 0x0f0f0f0fu) | (h0 & 0x30303030u);
-                a1 = (a1 & 0x0f0f0f0fu) | (h1 & 0x30303030u);
-                const float2 sc = lds64f<j * 64>(hr);
+        const uint32_t hr = hdr + (uint32_t)(g * 16 + t) * 4;
+        static_for<0, 4>([&](auto s_) {
+            constexpr int s = decltype(s_)::value;
+            int cs[MR][4];
 #pragma unroll
-                for (int q = 0; q < MG; q++) {
-                    int c[4];
-                    mma_k16_u8s8(c, a0, a1, A.template bword<j * 16>(q, toff));
-                    tmp[q][0] = fmaf(sc.x, (float)(c[0] * 256 + c[1]), tmp[q][0]);
-                    tmp[q][1] = fmaf(sc.y, (float)(c[2] * 256 + c[3]), tmp[q][1]);
+            for (int m = 0; m < MR; m++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) cs[m][i] = 0;
+            static_for<0, 2>([&](auto n_) {
+                constexpr int n = decltype(n_)::value;
+                const uint4 ql = lds128<(2 * (s & 1) + n) * 512>(sa);
+                const uint4 qh = lds128<2048 + n * 512>(sa);
+                const uint32_t qlw[4] = {ql.x, ql.y, ql.z, ql.w}, qhw[4] = {qh.x, qh.y, qh.z, qh.w};
+                uint32_t a[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const uint32_t lo = (s >> 1) ? (qlw[i] >> 4) : qlw[i];
+                    // high 2 bits of set s sit at bit pair s of each byte: move them to bits 4..5
+                    const uint32_t hb = s == 0 ? (qhw[i] << 4) : s == 1 ? (qhw[i] << 2) : s == 2 ? qhw[i] : (qhw[i] >> 2);
+                    a[i] = (lo & 0x0f0f0f0fu) | (hb & 0x30303030u);
                 }
+#pragma unroll
+                for (int m = 0; m < MR; m++)
+                    mma_k32_u8s8(cs[m], a[0], a[1], a[2], a[3], A.template b0<64 * s + 8 * n>(off0 + m * rs0),
+                                 A.template b1<64 * s + 8 * n>(off1 + m * rs1));
             });
+            const float dg = ldsf<16 * s>(hr), dg8 = ldsf<512 + 16 * s>(hr);  // sub-block 4s+t of rows g, g+8
+#pragma unroll
+            for (int m = 0; m < MR; m++) {
+                tmp[m][0] = fmaf(dg, combine(cs[m], 0), tmp[m][0]);
+                tmp[m][1] = fmaf(dg8, combine(cs[m], 1), tmp[m][1]);
+            }
         });
     }
 #pragma unroll
-    for (int q = 0; q < MG; q++) {
-        const int mrow = (4 * q + t) < A.rows ? (4 * q + t) : A.rows - 1;
-        const float sx = A.sx(mrow, sb);
-        yacc[q][0] = fmaf(sx, tmp[q][0], yacc[q][0]);
-        yacc[q][1] = fmaf(sx, tmp[q][1], yacc[q][1]);
+    for (int m = 0; m < MR; m++) {
+        const float sx = A.sx(m0 + m, sb);
+        yacc[m][0] = fmaf(sx, tmp[m][0], yacc[m][0]);
+        yacc[m][1] = fmaf(sx, tmp[m][1], yacc[m][1]);
     }
 }
 
-template <int FMT, int MG, int XSRC, int MR>
-__global__ void __launch_bounds__(GEMV_THREADS, XSRC == XSRC_GLOBAL ? 2 : 3) gemv_kernel(GemvParams p) {
+// NPASS passes of MR activation rows each are made over every tile (NPASS > 1 only with scratch planes).
+// NW warps per CTA: 8 (two or three CTAs per SM) or 16 / 24 (one CTA per SM, so that the activation
+// conversion of XSRC_CONVERT is done once per SM instead of once per small CTA).
+template <int FMT, int XSRC, int MR, int NPASS, int NW>
+__global__ void __launch_bounds__(NW * 32, NW > 8 ? 1 : (XSRC == XSRC_GLOBAL ? 2 : 3)) gemv_kernel(GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr bool SHARED = XSRC != XSRC_GLOBAL;
     constexpr int TB = tile_bytes(FMT);
     constexpr int STAGES = RING_STAGES;
-    constexpr int MP = 4 * MG;
+    constexpr int MP = MR * NPASS;
     const LinearArgs &a = p.a;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int SBp = (int)a.SBp, Kp = SBp * TILE_K, SBs = sx_stride(a.SBp);
     const int M = (int)a.M;
-    const SmemLayout L = smem_layout(FMT, MG, SHARED ? MR : 0, a.SBp);
+    const SmemLayout L = smem_layout(FMT, MP, SHARED ? MR : 0, a.SBp, NW);
     const uint32_t smem0 = smem_u32(smem);
 
     const uint32_t hdr_u32 = smem0 + L.hdr + warp * 1024;
     float *red_s = reinterpret_cast<float *>(smem + L.red);
     const uint32_t ring_u32 = smem0 + L.ring + warp * STAGES * TB;
     const uint32_t bar_u32 = smem0 + L.bars + warp * STAGES * 8;
-    const uint32_t xbar_u32 = smem0 + L.hdr - 8;  // last slot of the barrier area, past every ring barrier
+    const uint32_t xbar_u32 = smem0 + L.bars + NW * STAGES * 8;
 
     // group / K-slice of this warp
-    const int WK = p.wk, R = GEMV_WARPS / WK;
+    const int WK = p.wk, R = NW / WK;
     const int grp = warp / WK, ks = warp % WK;
     const int sb_begin = (ks * SBp) / WK, sb_end = ((ks + 1) * SBp) / WK;
     const int nsb = sb_end - sb_begin;
@@ -501,6 +580,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, XSRC == XSRC_GLOBAL ? 2 : 3) gem
     const int n_iters = rt0 < a.NT ? (int)((a.NT - rt0 + rt_step - 1) / rt_step) : 0;
     const int total_items = n_iters * nsb;
 
+    unsigned long long *te = trace_open(p.trace, 2);
     grid_launch_dependents();  // the next kernel may start its own weight copies as soon as it fits
 
     // ---- ring set-up and first copies (weights do not depend on the activations)
@@ -511,6 +591,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, XSRC == XSRC_GLOBAL ? 2 : 3) gem
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    if (SHARED && threadIdx.x < ZERO_BYTES / 4) reinterpret_cast<uint32_t *>(smem + L.zero)[threadIdx.x] = 0u;
     __syncwarp();
     // producer state (lane 0): next item to issue, walking (iteration, K tile) without divisions
     int p_item = 0, p_sbi = 0;
@@ -532,29 +613,53 @@ __global__ void __launch_bounds__(GEMV_THREADS, XSRC == XSRC_GLOBAL ? 2 : 3) gem
 
     // ---- activations: everything below may depend on the preceding kernel
     grid_dependency_wait();
-    ActView<MG, SHARED> A;
+    if (te) te[2] = global_ns();
+    ActView<SHARED> A;
     A.SBs = SBs;
     A.Kp = Kp;
     const int g = lane >> 2, t = lane & 3;
+    // block-diagonal operand: this lane's column g belongs to K group g>>1
+    const bool act0 = (g >> 1) == (t >> 1), act1 = (g >> 1) == 2 + (t >> 1);
+    const uint32_t lane_off = (uint32_t)(group_stride(FMT) * (g >> 1) + 4 * (t & 1));
+    A.mul0 = act0 ? 1u : 0u;
+    A.mul1 = act1 ? 1u : 0u;
     bool alive = true;  // false once a bounded wait gave up: skip further waits, keep the barriers
     if constexpr (SHARED) {
         if constexpr (XSRC == XSRC_CONVERT) {
+            // every CTA converts the activations itself: no second kernel on the dependency chain
             float *sx_s = reinterpret_cast<float *>(smem + L.sx);
             float *sum32_s = reinterpret_cast<float *>(smem + L.sum32);
             float *sum16_s = reinterpret_cast<float *>(smem + L.sum16);
             int8_t *planes_s = reinterpret_cast<int8_t *>(smem + L.planes);
             const int esz = a.x_dt == TTQ_DT_F32 ? 4 : 2;
             const int units = MR * SBp;
-            for (int u = warp; u < units; u += GEMV_WARPS) {
-                const int m = u / SBp, sb = u - m * SBp;
-                XqRow dst{planes_s + (2 * m) * (Kp + PLANE_PAD), planes_s + (2 * m + 1) * (Kp + PLANE_PAD),
-                          sum16_s + m * (Kp / 16), sum32_s + m * (Kp / 32), sx_s + m * SBs};
-                xprep_chunk(reinterpret_cast<const uint8_t *>(a.x) + (int64_t)m * a.ldx * esz, a.x_dt, a.K, sb, lane, dst);
+            constexpr int BATCH = NW > 8 ? 4 : 8;  // chunks whose loads one warp keeps in flight together
+            for (int u0 = warp; u0 < units; u0 += BATCH * NW) {
+                RawChunk rc[BATCH];
+#pragma unroll
+                for (int i = 0; i < BATCH; i++) {
+                    const int u = u0 + i * NW;
+                    if (u < units) {
+                        const int m = u / SBp, sb = u - m * SBp;
+                        rc[i] = xprep_load(reinterpret_cast<const uint8_t *>(a.x) + (int64_t)m * a.ldx * esz, a.x_dt, a.K, sb, lane);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < BATCH; i++) {
+                    const int u = u0 + i * NW;
+                    if (u < units) {
+                        const int m = u / SBp, sb = u - m * SBp;
+                        XqRow dst{planes_s + (2 * m) * (Kp + PLANE_PAD), planes_s + (2 * m + 1) * (Kp + PLANE_PAD),
+                                  sum16_s + m * (Kp / 16), sum32_s + m * (Kp / 32), sx_s + m * SBs};
+                        xprep_convert(rc[i], reinterpret_cast<const uint8_t *>(a.x) + (int64_t)m * a.ldx * esz, a.x_dt, a.K, sb,
+                                      lane, dst);
+                    }
+                }
             }
-            __syncthreads();
+            __syncthreads();  // planes complete, zero region written
         } else {
             // planes and side arrays were produced by the conversion pass: bulk-copy them in
-            __syncthreads();  // the plane barrier is initialised
+            __syncthreads();  // the plane barrier is initialised, the zero region is written
             if (threadIdx.x == 0) {
                 const uint32_t bytes = (uint32_t)(MR * SBs * 4 + MR * (Kp / 32) * 4 + MR * (Kp / 16) * 4 + 2 * MR * Kp);
                 mbar_expect_tx(xbar_u32, bytes);
@@ -566,80 +671,112 @@ __global__ void __launch_bounds__(GEMV_THREADS, XSRC == XSRC_GLOBAL ? 2 : 3) gem
             }
             alive = mbar_wait_bounded(xbar_u32, 0, p.status);
         }
-        // columns beyond 2*MR do not exist: such lanes read an existing column, their outputs are never stored
-        const int col = g % (2 * MR);
-        A.bfrag_s = smem0 + L.planes + (uint32_t)col * (Kp + PLANE_PAD) + 4 * t;
+        const uint32_t col_base = smem0 + L.planes + (uint32_t)(g & 1) * (Kp + PLANE_PAD) + lane_off;
+        // +32: keeps the broadcast zero word off the banks the diagonal lanes read
+        A.b0_s = act0 ? col_base : smem0 + L.zero + 32;
+        A.b1_s = act1 ? col_base : smem0 + L.zero + 32;
+        A.row_step = 2u * (Kp + PLANE_PAD);
         A.sx_s = smem0 + L.sx;
         A.sum32_s = smem0 + L.sum32;
         A.sum16_s = smem0 + L.sum16;
-        A.rows = MR;
     } else {
-#pragma unroll
-        for (int q = 0; q < MG; q++)
-            A.bfrag_g[q] = reinterpret_cast<const uint8_t *>(p.xq.planes) + (int64_t)(8 * q + g) * Kp + 4 * t;
+        const uint8_t *col_base = reinterpret_cast<const uint8_t *>(p.xq.planes) + (int64_t)(g & 1) * Kp + lane_off;
+        A.b0_g = act0 ? col_base : p.zeros;
+        A.b1_g = act1 ? col_base : p.zeros;
+        A.row_step = 2u * Kp;
         A.sx_g = p.xq.sx;
         A.sum32_g = p.xq.sum32;
         A.sum16_g = p.xq.sum16;
-        A.rows = MP;
     }
 
+    if (te) te[3] = global_ns();
     // ---- main loop over this warp's items
     int item = 0;
-    float *red_w = red_s + warp * (MG * 6 * 32);
+    float *redy = red_s + warp * (2 * MP * TILE_ROWS), *redo = redy + MP * TILE_ROWS;
     for (int it = 0; it < n_iters; it++) {
-        float yacc[MG][2], oacc[MR];
+        float yacc[NPASS][MR][2], oacc[NPASS][MR];
 #pragma unroll
-        for (int q = 0; q < MG; q++) yacc[q][0] = yacc[q][1] = 0.f;
+        for (int ps = 0; ps < NPASS; ps++)
 #pragma unroll
-        for (int m = 0; m < MR; m++) oacc[m] = 0.f;
+            for (int m = 0; m < MR; m++) yacc[ps][m][0] = yacc[ps][m][1] = oacc[ps][m] = 0.f;
         for (int sbi = 0; sbi < nsb; sbi++, item++) {
             const int s = item % STAGES;
             if (alive) alive = mbar_wait_bounded(bar_u32 + 8 * s, (uint32_t)((item / STAGES) & 1), p.status);
-            compute_tile<FMT, MG, SHARED, MR>(ring_u32 + s * TB, sb_begin + sbi, lane, hdr_u32, A, yacc, oacc);
+            if (te && item == 0) te[4] = global_ns();
+#pragma unroll
+            for (int ps = 0; ps < NPASS; ps++)
+                compute_tile<FMT, SHARED, MR>(ring_u32 + s * TB, sb_begin + sbi, ps * MR, lane, hdr_u32, A, yacc[ps], oacc[ps]);
             __syncwarp();  // every lane is done reading the stage before it is refilled
             if (lane == 0 && alive && p_item < total_items) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 issue_next();
             }
         }
-        // ---- flush the row tile of this iteration: partial sums of the group's warps meet in shared memory
-        const int64_t rt = rt0 + it * rt_step;
+        // ---- flush the row tile of this iteration
+        // the four t lanes of a row hold different sub-blocks, the two header halves different scales
 #pragma unroll
-        for (int q = 0; q < MG; q++) {
-            red_w[(q * 2 + 0) * 32 + lane] = yacc[q][0];
-            red_w[(q * 2 + 1) * 32 + lane] = yacc[q][1];
-        }
+        for (int ps = 0; ps < NPASS; ps++)
 #pragma unroll
-        for (int m = 0; m < MR; m++) red_w[(MG * 2 + m) * 32 + lane] = oacc[m];
-        named_barrier(1 + grp, WK * 32);
+            for (int m = 0; m < MR; m++) {
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    float v = yacc[ps][m][i];
+                    v += __shfl_xor_sync(0xffffffffu, v, 1);
+                    v += __shfl_xor_sync(0xffffffffu, v, 2);
+                    if (t == 0) redy[(ps * MR + m) * TILE_ROWS + g + 8 * i] = v;
+                }
+                float o = oacc[ps][m];
+                o += __shfl_xor_sync(0xffffffffu, o, 16);
+                if (lane < 16) redo[(ps * MR + m) * TILE_ROWS + lane] = o;
+            }
+        if (WK > 1) named_barrier(1 + grp, WK * 32);
+        else __syncwarp();
         if (ks == 0) {
-            for (int o = lane; o < MR * TILE_ROWS; o += 32) {
-                const int row = o & 15, m = o >> 4;
+            const int64_t rt = rt0 + it * rt_step;
+            for (int o = lane; o < MP * TILE_ROWS; o += 32) {
+                const int row = o & 15, mm = o >> 4;
                 const int64_t n = rt * TILE_ROWS + row;
-                if (m < M && n < a.N) {
-                    const int q = m >> 2, src_lane = (row & 7) * 4 + (m & 3), i = row >> 3;
+                if (mm < M && n < a.N) {
                     float acc = 0.f;
                     for (int w = 0; w < WK; w++) {
-                        const float *rw = red_s + (grp * WK + w) * (MG * 6 * 32);
-                        acc += rw[(q * 2 + i) * 32 + src_lane] - rw[(MG * 2 + m) * 32 + row] -
-                               rw[(MG * 2 + m) * 32 + row + 16];
+                        const float *rw = red_s + (grp * WK + w) * (2 * MP * TILE_ROWS);
+                        acc += rw[o] - rw[MP * TILE_ROWS + o];
                     }
                     if (a.bias != nullptr) acc += load_as_float(a.bias, a.bias_dt, n);
-                    store_from_float(a.y, a.y_dt, m * a.ldy + n, acc);
+                    store_from_float(a.y, a.y_dt, mm * a.ldy + n, acc);
                 }
             }
         }
-        named_barrier(1 + grp, WK * 32);  // the partial-sum area is free again
+        if (WK > 1) named_barrier(1 + grp, WK * 32);  // the partial-sum area is free again
+        else __syncwarp();
+    }
+    if (te) {
+        te[5] = global_ns();
+        te[6] = gridDim.x;
+        te[7] = (unsigned long long)a.N;
     }
 }
 
 constexpr size_t GEMV_SMEM_LIMIT = 112 * 1024;  // at least two CTAs per SM
 
-int pick_wk(int64_t NT, int64_t SBp, int64_t resident_warps) {
-    // enough (row tile, K slice) units to give every resident warp work, never more slices than K tiles
-    int wk = 1;
-    while (wk < GEMV_WARPS && NT * wk < resident_warps && 2 * wk <= SBp) wk *= 2;
-    return wk;
+// K-split factor: the one that minimises the longest CTA's work, measured in row tiles of full K
+// (ties: fewer slices, less reduction).  cap = resident CTAs.
+int pick_wk(int64_t NT, int64_t SBp, int64_t cap, int nw) {
+    int best = 1;
+    int64_t best_cost = -1;
+    for (int wk = 1; wk <= GEMV_WARPS; wk *= 2) {
+        if (wk > 1 && wk > SBp) break;
+        const int R = nw / wk;
+        const int64_t cta_iters = (NT + R - 1) / R;
+        const int64_t rounds = (cta_iters + cap - 1) / cap;
+        // a round costs R row tiles spread over 8 warps; compare in units of 1/8 row tile per warp
+        const int64_t cost = rounds * (8 / wk);  // each round: a warp walks 1/wk of K for one row tile
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best = wk;
+        }
+    }
+    return best;
 }
 
 bool env_flag(const char *name, bool dflt) {
@@ -665,78 +802,100 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
-template <int FMT, int MG, int XSRC, int MR>
+constexpr size_t GEMV_SMEM_BIG = 200 * 1024;  // one CTA per SM
+
+template <int FMT, int XSRC, int MR, int NPASS, int NW>
 cudaError_t launch_one(GemvParams &p, int sms, cudaStream_t st) {
-    auto kernel = gemv_kernel<FMT, MG, XSRC, MR>;
-    const size_t smem = smem_layout(FMT, MG, XSRC == XSRC_GLOBAL ? 0 : MR, p.a.SBp).total;
+    auto kernel = gemv_kernel<FMT, XSRC, MR, NPASS, NW>;
+    const size_t smem = smem_layout(FMT, MR * NPASS, XSRC == XSRC_GLOBAL ? 0 : MR, p.a.SBp, NW).total;
     static bool configured = false;  // per instantiation; contexts on several devices share the setting
     static int occ_cache_smem = -1, occ_cache = 0;
     cudaError_t e;
     if (!configured) {
-        if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMV_SMEM_LIMIT))) return e;
+        const int lim = (int)(NW > 8 ? GEMV_SMEM_BIG : GEMV_SMEM_LIMIT);
+        if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, lim))) return e;
         configured = true;
     }
     if (occ_cache_smem != (int)smem) {
-        if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ_cache, kernel, GEMV_THREADS, smem))) return e;
+        if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ_cache, kernel, NW * 32, smem))) return e;
         occ_cache_smem = (int)smem;
     }
     if (occ_cache < 1) return cudaErrorLaunchOutOfResources;
     const int64_t cap = (int64_t)sms * occ_cache;
-    p.wk = pick_wk(p.a.NT, p.a.SBp, cap * GEMV_WARPS);
-    const int R = GEMV_WARPS / p.wk;
+    p.wk = pick_wk(p.a.NT, p.a.SBp, cap, NW);
+    const int R = NW / p.wk;
     const int64_t cta_iters = (p.a.NT + R - 1) / R;
     const unsigned grid = (unsigned)(cta_iters < cap ? cta_iters : cap);
-    return launch_pdl(kernel, dim3(grid), dim3(GEMV_THREADS), smem, st, p);
+    return launch_pdl(kernel, dim3(grid), dim3(NW * 32), smem, st, p);
 }
 
-template <int FMT, int XSRC>
-cudaError_t dispatch_shared(GemvParams &p, int sms, cudaStream_t st) {
+template <int FMT, int XSRC, int NW>
+cudaError_t dispatch_rows(GemvParams &p, int sms, cudaStream_t st) {
     switch (p.a.M) {
-    case 1: return launch_one<FMT, 1, XSRC, 1>(p, sms, st);
-    case 2: return launch_one<FMT, 1, XSRC, 2>(p, sms, st);
-    case 3: return launch_one<FMT, 1, XSRC, 3>(p, sms, st);
-    default: return launch_one<FMT, 1, XSRC, 4>(p, sms, st);
+    case 1: return launch_one<FMT, XSRC, 1, 1, NW>(p, sms, st);
+    case 2: return launch_one<FMT, XSRC, 2, 1, NW>(p, sms, st);
+    case 3: return launch_one<FMT, XSRC, 3, 1, NW>(p, sms, st);
+    default: return launch_one<FMT, XSRC, 4, 1, NW>(p, sms, st);
     }
 }
 
+// warps per CTA for the modes that keep the activations in shared memory; 0 = they do not fit
+int pick_nw(int fmt, int mode, int64_t M, int64_t SBp) {
+    if (mode == XSRC_CONVERT) {
+        if (smem_layout(fmt, (int)M, (int)M, SBp, 24).total <= GEMV_SMEM_BIG) return 24;
+        if (smem_layout(fmt, (int)M, (int)M, SBp, 16).total <= GEMV_SMEM_BIG) return 16;
+    }
+    if (smem_layout(fmt, (int)M, (int)M, SBp, 8).total <= GEMV_SMEM_LIMIT) return 8;
+    return 0;
+}
+
 template <int FMT>
-cudaError_t dispatch(GemvParams &p, int mode, int MG, int sms, cudaStream_t st) {
-    if (mode == XSRC_CONVERT) return dispatch_shared<FMT, XSRC_CONVERT>(p, sms, st);
-    if (mode == XSRC_COPY) return dispatch_shared<FMT, XSRC_COPY>(p, sms, st);
-    if (MG == 1) return launch_one<FMT, 1, XSRC_GLOBAL, 4>(p, sms, st);
-    if (MG == 2) return launch_one<FMT, 2, XSRC_GLOBAL, 8>(p, sms, st);
-    return launch_one<FMT, 4, XSRC_GLOBAL, 16>(p, sms, st);
+cudaError_t dispatch(GemvParams &p, int mode, int nw, int sms, cudaStream_t st) {
+    if (mode == XSRC_CONVERT) {
+        if (nw == 24) return dispatch_rows<FMT, XSRC_CONVERT, 24>(p, sms, st);
+        if (nw == 16) return dispatch_rows<FMT, XSRC_CONVERT, 16>(p, sms, st);
+        return dispatch_rows<FMT, XSRC_CONVERT, 8>(p, sms, st);
+    }
+    if (mode == XSRC_COPY) return dispatch_rows<FMT, XSRC_COPY, 8>(p, sms, st);
+    if (p.a.M <= 4) return launch_one<FMT, XSRC_GLOBAL, 4, 1, 8>(p, sms, st);
+    if (p.a.M <= 8) return launch_one<FMT, XSRC_GLOBAL, 4, 2, 8>(p, sms, st);
+    return launch_one<FMT, XSRC_GLOBAL, 4, 4, 8>(p, sms, st);
 }
 
 }  // namespace
 
 cudaError_t gemv_configure() { return cudaSuccess; }
 
-cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t xq_capacity_k, int sms, int *status,
-                        cudaStream_t st, int *launches) {
-    // TTQ_XPREP=fused converts activations inside every CTA (no second launch); default: one separate pass
-    static const bool prefer_convert = []() {
-        const char *v = getenv("TTQ_XPREP");
-        return v && v[0] == 'f';
-    }();
-    GemvParams p{a, xq, 1, status};
+cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t xq_capacity_k, const uint8_t *zeros,
+                        int sms, int *status, unsigned long long *trace, cudaStream_t st, int *launches) {
+    GemvParams p{a, xq, zeros, 1, status, trace};
     *launches = 0;
     const int64_t Kp = a.SBp * TILE_K;
-    const bool fits = a.M <= 4 && smem_layout(fmt, 1, (int)a.M, a.SBp).total <= GEMV_SMEM_LIMIT;
-    const int MG = a.M <= 4 ? 1 : (a.M <= 8 ? 2 : 4);
-    const int mode = !fits ? XSRC_GLOBAL : (prefer_convert ? XSRC_CONVERT : XSRC_COPY);
+    if (Kp > xq_capacity_k) return cudaErrorInvalidValue;
+    // Activation conversion: by default one separate pass whose planes every CTA bulk-copies into shared
+    // memory (measured fastest on decode chains); TTQ_XPREP=fused converts inside every CTA instead.
+    static const int pref = []() {
+        const char *v = getenv("TTQ_XPREP");
+        if (v && v[0] == 'f') return XSRC_CONVERT;  // "fused"
+        if (v && v[0] == 'g') return XSRC_GLOBAL;   // "global": separate pass, fragments read from scratch
+        return XSRC_COPY;                           // "separate" (default)
+    }();
+    int mode = pref;
+    const int nw = (a.M <= 4 && mode != XSRC_GLOBAL) ? pick_nw(fmt, mode, a.M, a.SBp) : 0;
+    if (nw == 0) mode = XSRC_GLOBAL;
+    const bool shared = mode != XSRC_GLOBAL;
+    cudaError_t e = cudaSuccess;
     if (mode != XSRC_CONVERT) {
-        if (Kp > xq_capacity_k) return cudaErrorInvalidValue;
-        const int64_t Mpad = 4 * MG, units = Mpad * a.SBp;
-        cudaError_t e = launch_pdl(xprep_kernel, dim3((unsigned)((units + GEMV_WARPS - 1) / GEMV_WARPS)), dim3(GEMV_THREADS),
-                                   0, st, a.x, a.x_dt, a.M, Mpad, a.K, a.ldx, a.SBp, xq);
+        const int64_t Mpad = shared ? a.M : (a.M <= 4 ? 4 : (a.M <= 8 ? 8 : 16));
+        const int64_t units = Mpad * a.SBp;
+        e = launch_pdl(xprep_kernel, dim3((unsigned)((units + GEMV_WARPS - 1) / GEMV_WARPS)), dim3(GEMV_THREADS), 0, st, a.x,
+                       a.x_dt, a.M, Mpad, a.K, a.ldx, a.SBp, xq, trace);
         if (e != cudaSuccess) return e;
         ++*launches;
     }
-    cudaError_t e;
-    if (fmt == TTQ_FMT_Q4_K) e = dispatch<TTQ_FMT_Q4_K>(p, mode, MG, sms, st);
-    else if (fmt == TTQ_FMT_Q8_0) e = dispatch<TTQ_FMT_Q8_0>(p, mode, MG, sms, st);
-    else e = dispatch<TTQ_FMT_Q6_K>(p, mode, MG, sms, st);
+    if (fmt == TTQ_FMT_Q4_K) e = dispatch<TTQ_FMT_Q4_K>(p, mode, nw, sms, st);
+    else if (fmt == TTQ_FMT_Q8_0) e = dispatch<TTQ_FMT_Q8_0>(p, mode, nw, sms, st);
+    else e = dispatch<TTQ_FMT_Q6_K>(p, mode, nw, sms, st);
     if (e == cudaSuccess) ++*launches;
     return e;
 }

@@ -20,23 +20,28 @@ namespace ttq {
 //     offset(tile nt, sb) = (nt * SBp + sb) * tile_bytes(fmt),   SBp = ceil(K / 256)
 //
 // Inside a tile the quant payload is stored in the order the integer tensor-core instruction
-// wants its A operand (mma.sync m16n8k32 / m16n8k16, A row-major): lane L = 4*g + t owns rows g and
-// g+8, and one 16-byte load per lane is a complete A fragment.  `W(r, i)` below is the 32-bit word
-// holding quants 4i..4i+3 of row r within the 32-weight group at hand.
+// (mma.sync m16n8k32, A row-major, u8|s8) wants its A operand, so that one 16-byte load per lane is a
+// complete A fragment.  One instruction multiplies FOUR sub-blocks at once: its 32 K slots are four
+// groups of 8, group u holding an 8-weight window of sub-block u of the current set; the activation
+// operand is block-diagonal (columns 2u, 2u+1 = high/low activation plane, non-zero only in group
+// u), so after the windows of a set have been accumulated, lane (g, t) holds the complete integer
+// dot products of sub-block t for rows g and g+8 -- every lane owns a different (row, sub-block)
+// pair when the per-sub-block scales are applied.
 //
-//  Q4_K (2304 B = 16 x 144):
-//     [0,2048)      4 pair-chunks p (sub-blocks 2p | 2p+1 share bytes, low | high nibble):
-//                   chunk p, lane L -> 16 B {W(g,t), W(g+8,t), W(g,t+4), W(g+8,t+4)}
+//  A chunk is 512 bytes, lane L = 4g + t owns 16 bytes = registers a0..a3; register `sl` covers
+//     row = g + 8*(sl & 1),  group u = (t >> 1) + 2*(sl >> 1),  weights 4*(t & 1) .. +3 of the window.
+//
+//  Q4_K (2304 B = 16 x 144): set X = sub-blocks 0,2,4,6 (low nibbles), set Y = 1,3,5,7 (high nibbles)
+//     [0,2048)      4 chunks, chunk n = window n (weights 8n..8n+7 of each sub-block); the byte of
+//                   group u is the canonical qs byte of pair u (low nibble: sub-block 2u, high: 2u+1)
 //     [2048,2304)   16 row headers x 16 B, canonical {fp16 d, fp16 dmin, 12 B 6-bit scales/mins}
-//  Q8_0 (4352 B = 16 x 8 x 34):
-//     [0,4096)      8 blocks b: block b, lane L -> 16 B {W(g,t), W(g+8,t), W(g,t+4), W(g+8,t+4)}
+//  Q8_0 (4352 B = 16 x 8 x 34): set s = blocks 4s..4s+3
+//     [0,4096)      8 chunks, chunk 4s+n = window n of set s
 //     [4096,4352)   fp16 d[r][b], row-major (16 B per row)
-//  Q6_K (3360 B = 16 x 210): sub-blocks of 16 weights, quad c = sub-blocks 4c..4c+3
-//     [0,2048)      quad c, lane L -> 16 B {QL(g,c,0), QL(g+8,c,0), QL(g,c,1), QL(g+8,c,1)}
-//                   QL(r,c,h) byte i: low nibble = low 4 bits of q[r][16(4c+2h)+4t+i],
-//                                     high nibble = low 4 bits of q[r][16(4c+2h+1)+4t+i]
-//     [2048,3072)   e in {0,1}, lane L -> 16 B {QH(g,2e), QH(g+8,2e), QH(g,2e+1), QH(g+8,2e+1)}
-//                   QH(r,c) byte i: bit pairs 0..3 = high 2 bits of q[r][16(4c+s)+4t+i], s = 0..3
+//  Q6_K (3360 B = 16 x 210): sub-blocks of 16 weights, set s = sub-blocks 4s..4s+3, windows n = 0,1
+//     [0,2048)      4 chunks, chunk 2s'+n: low nibble = low 4 bits of the quant of set s', high nibble
+//                   = low 4 bits of the quant at the same position of set s'+2
+//     [2048,3072)   2 chunks, chunk n: bit pair s of a byte = high 2 bits of the quant of set s
 //     [3072,3328)   int8 scales[r][16]
 //     [3328,3360)   fp16 d[r]
 //  Rows >= N and Q8_0 blocks beyond K are stored as zero bytes (they dequantize to 0).
@@ -94,8 +99,9 @@ cudaError_t launch_repack(int fmt, const uint8_t *canon, uint8_t *tiled, int64_t
 cudaError_t launch_dequant(int fmt, const uint8_t *tiled, float *out, int64_t ld, int64_t N, int64_t K,
                            int64_t SBp, cudaStream_t st);
 // GEMV for M <= MAX_GEMV_M.  `xq` is scratch for the separate x-prep pass (used when M > fused limit).
-cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t xq_capacity_k, int sms,
-                        int *status, cudaStream_t st, int *launches);
+cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t xq_capacity_k, const uint8_t *zeros,
+                        int sms, int *status, unsigned long long *trace, cudaStream_t st, int *launches);
+constexpr int TTQ_TRACE_ENTRIES = 8192;
 cudaError_t launch_silu_and_mul(const void *in, int dt, int64_t M, int64_t H, int64_t ld_in, void *out,
                                 int64_t ld_out, cudaStream_t st);
 cudaError_t gemv_configure();  // one-time cudaFuncSetAttribute calls

@@ -34,58 +34,67 @@ __device__ __forceinline__ void q6k_parts(const uint8_t *blk, int kk, int &lo4, 
     hi2 = (blk[128 + half * 32 + l] >> (2 * grp)) & 3;
 }
 
-// Decompose a payload offset (inside a 512-byte lane-ordered chunk) into the A-fragment coordinates.
-__device__ __forceinline__ void frag_coords(int o512, int &r, int &word_hi, int &t, int &bi) {
-    int L = o512 >> 4, slot = (o512 >> 2) & 3;
-    bi = o512 & 3;
-    t = L & 3;
-    r = (L >> 2) + ((slot & 1) ? 8 : 0);
-    word_hi = slot >> 1;  // second half of the K group (words t+4) or second QL/QH word
+// Decompose a payload offset inside a 512-byte lane-ordered chunk into A-fragment coordinates:
+// lane L = 4g + t, slot sl = register a0..a3 of mma.m16n8k32, byte i.  The register covers
+//   row    = g + 8 * (sl & 1)
+//   group  = (t >> 1) + 2 * (sl >> 1)       one of the 4 sub-blocks that share the instruction
+//   kpos   = 4 * (t & 1) + i                position inside the group's 8-weight window
+__device__ __forceinline__ void frag_coords(int o512, int &row, int &group, int &kpos) {
+    const int L = o512 >> 4, sl = (o512 >> 2) & 3, i = o512 & 3;
+    const int g = L >> 2, t = L & 3;
+    row = g + 8 * (sl & 1);
+    group = (t >> 1) + 2 * (sl >> 1);
+    kpos = 4 * (t & 1) + i;
+}
+// Inverse: byte offset inside a 512-byte chunk of (row, group, kpos).
+__device__ __forceinline__ int frag_offset(int row, int group, int kpos) {
+    const int g = row & 7, t = 2 * (group & 1) + (kpos >> 2), sl = (row >> 3) + 2 * (group >> 1);
+    return ((g * 4 + t) << 4) + (sl << 2) + (kpos & 3);
 }
 
 template <int FMT>
 __device__ uint8_t tiled_byte(const CanonTile &ct, int o) {
-    int r, wh, t, bi;
+    int r, u, kpos;
     if (FMT == TTQ_FMT_Q4_K) {
         if (o < 2048) {
-            int p = o >> 9;
-            frag_coords(o & 511, r, wh, t, bi);
+            const int n = o >> 9;  // window n: weights 8n..8n+7 of each sub-block
+            frag_coords(o & 511, r, u, kpos);
             const uint8_t *blk = ct.block256(r, 144);
-            return blk ? blk[16 + 32 * p + 4 * (t + 4 * wh) + bi] : 0;
+            return blk ? blk[16 + 32 * u + 8 * n + kpos] : 0;  // pair u: low nibble sub-block 2u, high 2u+1
         }
         int h = o - 2048;
         const uint8_t *blk = ct.block256(h >> 4, 144);
         return blk ? blk[h & 15] : 0;
     } else if (FMT == TTQ_FMT_Q8_0) {
         if (o < 4096) {
-            int b = o >> 9;
-            frag_coords(o & 511, r, wh, t, bi);
-            const uint8_t *blk = ct.block32(r, b);
-            return blk ? blk[2 + 4 * (t + 4 * wh) + bi] : 0;
+            const int c = o >> 9, s = c >> 2, n = c & 3;  // set s: blocks 4s..4s+3
+            frag_coords(o & 511, r, u, kpos);
+            const uint8_t *blk = ct.block32(r, 4 * s + u);
+            return blk ? blk[2 + 8 * n + kpos] : 0;
         }
         int h = o - 4096;
         const uint8_t *blk = ct.block32(h >> 4, (h & 15) >> 1);
         return blk ? blk[h & 1] : 0;
     } else {
         if (o < 2048) {
-            int c = o >> 9;
-            frag_coords(o & 511, r, wh, t, bi);
+            const int c = o >> 9, sp = c >> 1, n = c & 1;  // low nibbles: set sp, high nibbles: set sp+2
+            frag_coords(o & 511, r, u, kpos);
             const uint8_t *blk = ct.block256(r, 210);
             if (!blk) return 0;
-            int jlo = 4 * c + 2 * wh, a, b2, dummy;
-            q6k_parts(blk, 16 * jlo + 4 * t + bi, a, dummy);
-            q6k_parts(blk, 16 * (jlo + 1) + 4 * t + bi, b2, dummy);
+            int a, b2, dummy;
+            q6k_parts(blk, 16 * (4 * sp + u) + 8 * n + kpos, a, dummy);
+            q6k_parts(blk, 16 * (4 * (sp + 2) + u) + 8 * n + kpos, b2, dummy);
             return (uint8_t)(a | (b2 << 4));
         }
         if (o < 3072) {
-            int o2 = o - 2048, e = o2 >> 9;
-            frag_coords(o2 & 511, r, wh, t, bi);
+            const int o2 = o - 2048, n = o2 >> 9;
+            frag_coords(o2 & 511, r, u, kpos);
             const uint8_t *blk = ct.block256(r, 210);
             if (!blk) return 0;
-            int c = 2 * e + wh, v = 0;
+            int v = 0;
             for (int s = 0; s < 4; s++) {
                 int lo, hi;
-                q6k_parts(blk, 16 * (4 * c + s) + 4 * t + bi, lo, hi);
+                q6k_parts(blk, 16 * (4 * s + u) + 8 * n + kpos, lo, hi);
                 v |= hi << (2 * s);
             }
             return (uint8_t)v;
@@ -121,11 +130,10 @@ __global__ void __launch_bounds__(128) repack_kernel(const uint8_t *__restrict__
 // ---- inverse: tiled -> fp32 [N][ld], canonical element order ----------------------------------
 template <int FMT>
 __device__ float dequant_elem(const uint8_t *tile, int r, int kk) {
-    const int g = r & 7, rh = r >> 3;
     if (FMT == TTQ_FMT_Q4_K) {
-        int j = kk >> 5, l = kk & 31, p = j >> 1, i = l >> 2, bi = l & 3;
-        int o = p * 512 + ((g * 4 + (i & 3)) << 4) + ((rh + 2 * (i >> 2)) << 2) + bi;
-        int q = (j & 1) ? (tile[o] >> 4) : (tile[o] & 15);
+        const int j = kk >> 5, l = kk & 31;
+        const uint8_t b = tile[(l >> 3) * 512 + frag_offset(r, j >> 1, l & 7)];
+        const int q = (j & 1) ? (b >> 4) : (b & 15);
         const uint8_t *hdr = tile + 2048 + r * 16;
         float d = __half2float(*reinterpret_cast<const __half *>(hdr));
         float dmin = __half2float(*reinterpret_cast<const __half *>(hdr + 2));
@@ -133,16 +141,17 @@ __device__ float dequant_elem(const uint8_t *tile, int r, int kk) {
         q4k_scale_min(j, hdr + 4, sc, m);
         return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)q), __fmul_rn(dmin, (float)m));
     } else if (FMT == TTQ_FMT_Q8_0) {
-        int b = kk >> 5, l = kk & 31, i = l >> 2, bi = l & 3;
-        int o = b * 512 + ((g * 4 + (i & 3)) << 4) + ((rh + 2 * (i >> 2)) << 2) + bi;
+        const int b = kk >> 5, l = kk & 31;
+        const int o = (4 * (b >> 2) + (l >> 3)) * 512 + frag_offset(r, b & 3, l & 7);
         float d = __half2float(*reinterpret_cast<const __half *>(tile + 4096 + r * 16 + b * 2));
         return __fmul_rn(d, (float)(int8_t)tile[o]);
     } else {
-        int j = kk >> 4, c = j >> 2, s = j & 3, idx = kk & 15, t = idx >> 2, bi = idx & 3;
-        int o = c * 512 + ((g * 4 + t) << 4) + ((rh + 2 * (s >> 1)) << 2) + bi;
-        int nib = (s & 1) ? (tile[o] >> 4) : (tile[o] & 15);
-        int o2 = 2048 + (c >> 1) * 512 + ((g * 4 + t) << 4) + ((rh + 2 * (c & 1)) << 2) + bi;
-        int q = (nib | (((tile[o2] >> (2 * s)) & 3) << 4)) - 32;
+        const int j = kk >> 4, s = j >> 2, u = j & 3, l = kk & 15, n = l >> 3;
+        const int fo = frag_offset(r, u, l & 7);
+        const uint8_t qlb = tile[(2 * (s & 1) + n) * 512 + fo];
+        const int nib = (s >> 1) ? (qlb >> 4) : (qlb & 15);
+        const int hi2 = (tile[2048 + n * 512 + fo] >> (2 * s)) & 3;
+        const int q = (nib | (hi2 << 4)) - 32;
         float sc = (float)(int8_t)tile[3072 + r * 16 + j];
         float d = __half2float(*reinterpret_cast<const __half *>(tile + 3328 + 2 * r));
         return __fmul_rn(__fmul_rn(d, sc), (float)q);

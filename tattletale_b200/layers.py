@@ -53,6 +53,13 @@ class Context:
         """Synchronises the current stream; raises TtqError(TIMEOUT) if a kernel gave up a bounded wait."""
         check(self.handle, self._lib.ttq_device_status(self.handle, _stream_ptr(self.device)))
 
+    def read_trace(self, max_entries: int = 8192):
+        """Device timeline entries recorded since the last read (needs TTQ_TRACE=1 at creation): int64 [n, 8]."""
+        buf = torch.zeros((max_entries, 8), dtype=torch.int64)
+        n = ctypes.c_int64()
+        check(self.handle, self._lib.ttq_trace_read(self.handle, buf.data_ptr(), max_entries, ctypes.byref(n)))
+        return buf[: n.value]
+
     @property
     def launch_count(self) -> int:
         return int(self._lib.ttq_launch_count(self.handle))
