@@ -147,6 +147,26 @@ TTQ_API ttq_status ttq_linear_forward_host(ttq_ctx *ctx, const ttq_weight *w, co
  * points perform this check themselves. */
 TTQ_API ttq_status ttq_device_status(ttq_ctx *ctx, void *stream);
 
+/* The decode linear for hosts that cannot allocate device memory.  No counterpart in the reference.
+ * Some hosts are not allowed to call cudaMalloc at all: a server that has given every byte of device
+ * memory to its own pool, or a plug-in under a framework that forbids allocation after start-up.  Such
+ * a host cannot create a ttq_ctx (ttq_init allocates scratch and staging buffers).  This call needs no
+ * context and allocates nothing: its activation scratch is a fixed 173,120-byte array inside the
+ * library image, present on every GPU that loads the library until the process exits.
+ *   Limits: M <= 4 and K <= 16384; larger requests return TTQ_ERR_LIMIT (message in errbuf).
+ *   The weight's device must be the current device.  x, bias, y and the weight (created elsewhere,
+ *   e.g. while loading, by code that may allocate) are passed as for ttq_linear_forward.
+ *   The first call on a device looks up the array's device address (cudaGetSymbolAddress, checked)
+ *   and the SM count; make that first call before starting any stream capture.
+ *   All calls share the one array, which keeps the previous call's contents; every call rewrites what
+ *   it reads and clears its status word.  Calls that overlap on the GPU (two streams, two threads)
+ *   race on it: keep them on one stream.  Not thread-safe on the host either.
+ *   errbuf (optional) receives a message when the status is not TTQ_OK. */
+TTQ_API ttq_status ttq_linear_forward_static(const ttq_weight *w, const void *x_dev, ttq_dtype x_dt, int64_t M,
+                                             int64_t ldx, const void *bias_dev, ttq_dtype bias_dt, void *y_dev,
+                                             ttq_dtype y_dt, int64_t ldy, void *stream, char *errbuf,
+                                             size_t errbuf_len);
+
 /* ---- adjacent step: silu_and_mul (kernels/activations.nim:14-38) ---------------------------- */
 
 /* out[m][h] = silu(in[m][h]) * in[m][H + h]; in is [M][ld_in] with 2H used columns, out [M][ld_out].

@@ -46,6 +46,7 @@ SIGNATURES = {
     "ttq_dequantize": (_ci, [_vp, _vp, _vp, _i64, _vp]),
     "ttq_linear_forward": (_ci, [_vp, _vp, _vp, _ci, _i64, _i64, _vp, _ci, _vp, _ci, _i64, _vp]),
     "ttq_linear_forward_host": (_ci, [_vp, _vp, _vp, _ci, _i64, _i64, _vp, _ci, _vp, _ci, _i64]),
+    "ttq_linear_forward_static": (_ci, [_vp, _vp, _ci, _i64, _i64, _vp, _ci, _vp, _ci, _i64, _vp, ctypes.c_char_p, _sz]),
     "ttq_silu_and_mul": (_ci, [_vp, _vp, _ci, _i64, _i64, _i64, _vp, _i64, _vp]),
     "ttq_launch_count": (_i64, [_vp]),
     "ttq_device_status": (_ci, [_vp, _vp]),

@@ -28,8 +28,6 @@ struct ttq_ctx {
     cudaStream_t host_stream;
 };
 
-struct ttq_weight : public Weight {};
-
 namespace {
 
 constexpr int64_t XQ_CAPACITY_K = 65536;          // largest K (padded to 256) the scratch planes hold
@@ -66,6 +64,7 @@ ttq_status alloc_weight(ttq_ctx *ctx, int fmt, int64_t N, int64_t K, ttq_weight 
     ttq_weight *w = new (std::nothrow) ttq_weight();
     if (!w) return fail(ctx, TTQ_ERR_OOM, "host allocation of weight handle failed");
     w->ctx = ctx;
+    w->device = ctx->device;
     w->fmt = fmt;
     w->N = N;
     w->K = K;

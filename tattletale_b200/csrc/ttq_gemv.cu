@@ -901,3 +901,120 @@ cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t 
 }
 
 }  // namespace ttq
+
+// ================================================================================================
+// ttq_linear_forward_static: the same decode linear with NO allocation anywhere on its path.
+//
+// Who needs it: a host that may not (or cannot) call the CUDA allocator -- an inference server that
+// has handed every byte of device memory to its own pool, or a plug-in running under a framework that
+// forbids cudaMalloc after start-up.  ttq_init allocates scratch and staging buffers, so such a host
+// cannot create a context; this entry point needs none.  The activation planes that the context
+// normally keeps in allocated scratch live here in a fixed array inside the library image.  The array
+// is part of the module: every GPU that loads the library reserves it until the process exits.
+//
+// Limits: M <= TTQ_STATIC_MAX_M rows, K <= TTQ_STATIC_MAX_K (after rounding K up to 256).
+// The array is shared by all calls and keeps whatever the last call left in it; each call rewrites
+// every byte it will read (padding rows are written as zeros by the conversion pass) and clears the
+// status word, and the zero page at its start is never written.  Two calls that overlap on the GPU
+// (different streams, or different host threads) race on the array: issue them on one stream.
+// ================================================================================================
+namespace ttq {
+namespace {
+
+constexpr int64_t TTQ_STATIC_MAX_M = 4;
+constexpr int64_t TTQ_STATIC_MAX_K = 16384;
+constexpr size_t ST_ZERO = 1024;                                             // zero page + status word at byte 768
+constexpr size_t ST_PLANES = (size_t)2 * TTQ_STATIC_MAX_M * TTQ_STATIC_MAX_K;  // int8 planes
+constexpr size_t ST_SUM16 = (size_t)TTQ_STATIC_MAX_M * (TTQ_STATIC_MAX_K / 16) * 4;
+constexpr size_t ST_SUM32 = (size_t)TTQ_STATIC_MAX_M * (TTQ_STATIC_MAX_K / 32) * 4;
+constexpr size_t ST_SX = (size_t)TTQ_STATIC_MAX_M * (TTQ_STATIC_MAX_K / 256 + 4) * 4;
+constexpr size_t ST_TOTAL = ST_ZERO + ST_PLANES + ST_SUM16 + ST_SUM32 + ST_SX;  // 173,120 bytes
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char g_static_scratch[ST_TOTAL];
+
+struct StaticDevice {
+    bool ready;
+    unsigned char *base;  // device address of g_static_scratch on this device
+    int sms;
+};
+StaticDevice g_static_dev[64];
+
+void set_msg(char *buf, size_t len, const char *msg) {
+    if (buf && len) {
+        size_t i = 0;
+        for (; i + 1 < len && msg[i]; i++) buf[i] = msg[i];
+        buf[i] = 0;
+    }
+}
+
+}  // namespace
+}  // namespace ttq
+
+extern "C" TTQ_API ttq_status ttq_linear_forward_static(const ttq_weight *w, const void *x_dev, ttq_dtype x_dt, int64_t M,
+                                                        int64_t ldx, const void *bias_dev, ttq_dtype bias_dt, void *y_dev,
+                                                        ttq_dtype y_dt, int64_t ldy, void *stream, char *errbuf,
+                                                        size_t errbuf_len) {
+    using namespace ttq;
+    set_msg(errbuf, errbuf_len, "");
+    if (!w || !x_dev || !y_dev) {
+        set_msg(errbuf, errbuf_len, "weight, x or y pointer is NULL");
+        return TTQ_ERR_INVALID_ARG;
+    }
+    if (M < 0 || ldx < w->K || ldy < w->N) {
+        set_msg(errbuf, errbuf_len, "negative M or leading dimension smaller than the row length");
+        return TTQ_ERR_SHAPE;
+    }
+    if (M == 0) return TTQ_OK;
+    if ((x_dt != TTQ_DT_BF16 && x_dt != TTQ_DT_F16) || y_dt < TTQ_DT_BF16 || y_dt > TTQ_DT_F32 ||
+        (bias_dev && (bias_dt < TTQ_DT_BF16 || bias_dt > TTQ_DT_F32))) {
+        set_msg(errbuf, errbuf_len, "unsupported dtype (x: bf16|f16; y, bias: bf16|f16|f32)");
+        return TTQ_ERR_INVALID_ARG;
+    }
+    if (M > TTQ_STATIC_MAX_M || w->SBp * TILE_K > TTQ_STATIC_MAX_K) {
+        set_msg(errbuf, errbuf_len, "ttq_linear_forward_static is limited to M <= 4 and K <= 16384 (fixed scratch array)");
+        return TTQ_ERR_LIMIT;
+    }
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev != w->device || dev < 0 || dev >= 64) {
+        set_msg(errbuf, errbuf_len, "the weight's device must be the current CUDA device");
+        return TTQ_ERR_DEVICE;
+    }
+    StaticDevice &sd = g_static_dev[dev];
+    if (!sd.ready) {
+        // one-time set-up on this device: resolve the device address of the array (no allocation)
+        void *ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sd.sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess || ptr == nullptr) {
+            set_msg(errbuf, errbuf_len, cudaGetErrorString(e));
+            return TTQ_ERR_CUDA;
+        }
+        sd.base = reinterpret_cast<unsigned char *>(ptr);
+        sd.ready = true;
+    }
+    XqView xq;
+    xq.planes = reinterpret_cast<int8_t *>(sd.base + ST_ZERO);
+    xq.sum16 = reinterpret_cast<float *>(sd.base + ST_ZERO + ST_PLANES);
+    xq.sum32 = reinterpret_cast<float *>(sd.base + ST_ZERO + ST_PLANES + ST_SUM16);
+    xq.sx = reinterpret_cast<float *>(sd.base + ST_ZERO + ST_PLANES + ST_SUM16 + ST_SUM32);
+    int *status = reinterpret_cast<int *>(sd.base + 768);
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int), st);  // must start at zero; the rest is rewritten below
+    if (e == cudaSuccess) {
+        LinearArgs a;
+        a.tiles = w->tiles;
+        a.N = w->N; a.K = w->K; a.NT = w->NT; a.SBp = w->SBp;
+        a.x = x_dev; a.x_dt = x_dt; a.M = M; a.ldx = ldx;
+        a.bias = bias_dev; a.bias_dt = bias_dt;
+        a.y = y_dev; a.y_dt = y_dt; a.ldy = ldy;
+        int launches = 0;
+        e = launch_gemv(w->fmt, a, xq, TTQ_STATIC_MAX_K, sd.base, sd.sms, status, nullptr, st, &launches);
+    }
+    if (e != cudaSuccess) {
+        set_msg(errbuf, errbuf_len, cudaGetErrorString(e));
+        return TTQ_ERR_CUDA;
+    }
+    return TTQ_OK;
+}
+

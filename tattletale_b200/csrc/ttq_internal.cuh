@@ -64,6 +64,7 @@ constexpr int MAX_GEMV_M = 16;
 
 struct Weight {
     ttq_ctx *ctx;
+    int device;  // CUDA device that holds `tiles`
     int fmt;
     int64_t N, K;
     int64_t NT;   // row tiles
@@ -71,6 +72,12 @@ struct Weight {
     uint8_t *tiles;
     size_t tiled_bytes;
 };
+
+}  // namespace ttq
+
+struct ttq_weight : public ttq::Weight {};
+
+namespace ttq {
 
 // Activation planes produced by the x-prep kernel (global scratch) for the non-fused GEMV path.
 struct XqView {
