@@ -22,6 +22,8 @@ struct ttq_ctx {
     int sms;          // multiprocessor count of the device
     int *dev_status;  // device word the kernels OR failure bits into (bit 0: a bounded wait gave up)
     unsigned long long *trace;  // device timeline buffer, allocated only when TTQ_TRACE=1 is set at init
+    __half *xh;                 // fp16 activation scratch of the tcgen05 GEMM path
+    int64_t xh_capacity;        // in halves
     // device staging for the *_host entry points
     uint8_t *stage_x, *stage_y, *stage_b;
     size_t stage_x_bytes, stage_y_bytes, stage_b_bytes;
@@ -34,6 +36,7 @@ constexpr int64_t XQ_CAPACITY_K = 65536;          // largest K (padded to 256) t
 constexpr size_t STAGE_X_BYTES = 64u << 20;       // host-entry staging: activations
 constexpr size_t STAGE_Y_BYTES = 128u << 20;      // host-entry staging: outputs
 constexpr size_t STAGE_B_BYTES = 4u << 20;        // host-entry staging: bias
+constexpr int64_t XH_CAPACITY = 32ll << 20;       // halves (64 MB): fp16 activations of one GEMM slab
 
 ttq_status fail(ttq_ctx *ctx, ttq_status s, const char *fmt, ...) {
     if (ctx) {
@@ -157,6 +160,7 @@ ttq_status ttq_init(int device, ttq_ctx **out) {
         e = cudaMalloc(&ctx->trace, tb);
         if (e == cudaSuccess) e = cudaMemset(ctx->trace, 0, tb);
     }
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->xh, (size_t)XH_CAPACITY * sizeof(__half));
     if (e == cudaSuccess) e = cudaMalloc(&ctx->stage_x, STAGE_X_BYTES);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->stage_y, STAGE_Y_BYTES);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->stage_b, STAGE_B_BYTES);
@@ -173,6 +177,7 @@ ttq_status ttq_init(int device, ttq_ctx **out) {
     ctx->xq.sum32 = reinterpret_cast<float *>(b + planes_b + s16_b);
     ctx->xq.sx = reinterpret_cast<float *>(b + planes_b + s16_b + s32_b);
     ctx->xq_capacity_k = Kc;
+    ctx->xh_capacity = XH_CAPACITY;
     ctx->stage_x_bytes = STAGE_X_BYTES;
     ctx->stage_y_bytes = STAGE_Y_BYTES;
     ctx->stage_b_bytes = STAGE_B_BYTES;
@@ -187,6 +192,7 @@ ttq_status ttq_destroy(ttq_ctx *ctx) {
     cudaFree(ctx->xq_base);
     cudaFree(ctx->dev_status);
     cudaFree(ctx->trace);
+    cudaFree(ctx->xh);
     cudaFree(ctx->stage_x);
     cudaFree(ctx->stage_y);
     cudaFree(ctx->stage_b);
@@ -329,18 +335,30 @@ ttq_status ttq_linear_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_d
         return fail(ctx, TTQ_ERR_LIMIT, "K=%lld exceeds the activation scratch capacity %lld", (long long)w->K,
                     (long long)ctx->xq_capacity_k);
     cudaStream_t st = (cudaStream_t)stream;
-    // Rows are processed in groups of at most MAX_GEMV_M through the decode kernel.
+    LinearArgs a;
+    a.tiles = w->tiles;
+    a.N = w->N; a.K = w->K; a.NT = w->NT; a.SBp = w->SBp;
+    a.x_dt = x_dt; a.ldx = ldx;
+    a.bias = bias_dev; a.bias_dt = bias_dt;
+    a.y_dt = y_dt; a.ldy = ldy;
+    static const bool use_gemm = []() {
+        const char *v = getenv("TTQ_GEMM");
+        return !(v && v[0] == '0');
+    }();
+    if (M > MAX_GEMV_M && use_gemm && gemm_supported(w->fmt)) {
+        // prefill / large batch: tensor-core path
+        a.x = x_dev; a.M = M; a.y = y_dev;
+        int launches = 0;
+        cudaError_t e = launch_gemm(w->fmt, a, ctx->xh, ctx->xh_capacity, ctx->dev_status, st, &launches);
+        ctx->launches += launches;
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "linear forward (GEMM) launch");
+        return TTQ_OK;
+    }
+    // decode path; more rows than one pass holds are processed in groups of MAX_GEMV_M
     for (int64_t m0 = 0; m0 < M; m0 += MAX_GEMV_M) {
-        LinearArgs a;
-        a.tiles = w->tiles;
-        a.N = w->N; a.K = w->K; a.NT = w->NT; a.SBp = w->SBp;
         a.x = reinterpret_cast<const uint8_t *>(x_dev) + (size_t)m0 * ldx * dt_size(x_dt);
-        a.x_dt = x_dt;
         a.M = (M - m0) < MAX_GEMV_M ? (M - m0) : MAX_GEMV_M;
-        a.ldx = ldx;
-        a.bias = bias_dev; a.bias_dt = bias_dt;
         a.y = reinterpret_cast<uint8_t *>(y_dev) + (size_t)m0 * ldy * dt_size(y_dt);
-        a.y_dt = y_dt; a.ldy = ldy;
         int launches = 0;
         cudaError_t e = launch_gemv(w->fmt, a, ctx->xq, ctx->xq_capacity_k, reinterpret_cast<const uint8_t *>(ctx->dev_status) + 256, ctx->sms,
                                     ctx->dev_status, ctx->trace, st, &launches);

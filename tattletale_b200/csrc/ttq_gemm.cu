@@ -1,0 +1,403 @@
+// Prefill / batched side: y[M][N] = x . W^T for M > 16 on the 5th-generation tensor cores.
+//
+// The contraction is issued as tcgen05.mma (kind::f16, cta_group::1) with the accumulator in tensor
+// memory.  Operand roles are swapped with respect to the GEMM's names: the 128 rows of the MMA are
+// 128 weight rows (n), its N dimension is a tile of BM activation rows (m), so that any batch from 17
+// rows up maps onto a legal instruction shape (N = 64, 128 or 256).
+//
+// Per CTA (one 128 x BM output tile), 11 warps:
+//   warps 0-7   dequantize: each owns 16 weight rows (one row tile of the packed layout), reads one
+//               512-byte chunk per stage straight from global memory (16 bytes per lane, prefetched
+//               one stage ahead), expands nibbles to fp16 with the 1024-offset bit trick, applies the
+//               sub-block scale and offset with one HFMA2 per pair, and writes the 128-byte-swizzled
+//               K-major A tile.  Afterwards the same warps run the epilogue (tcgen05.ld -> bias -> y).
+//   warps 8-9   copy the activation tile (already fp16 and permuted by xh_prep_kernel) into the
+//               swizzled B tile.
+//   warp 10     allocates tensor memory, issues the MMAs (one elected lane) and commits them to the
+//               stage barriers.
+// A stage is one window of one 256-weight super-block: 64 K values (8 from each sub-block), in the
+// order the packed chunk delivers them; the activation pass applies the same K permutation, so the
+// dequant warps never shuffle.  Every mbarrier wait is bounded; tensor memory is always released.
+#include <cstdlib>
+
+#include "ttq_internal.cuh"
+
+namespace ttq {
+
+namespace {
+
+constexpr int GEMM_DEQ_WARPS = 8, GEMM_B_WARPS = 2;
+constexpr int GEMM_WARPS = GEMM_DEQ_WARPS + GEMM_B_WARPS + 1;
+constexpr int GEMM_THREADS = GEMM_WARPS * 32;
+constexpr int GEMM_STAGES = 4;
+constexpr int GEMM_BN = 128;                     // weight rows per CTA = MMA M
+constexpr int A_STAGE_BYTES = GEMM_BN * 128;     // 128 rows x 64 fp16
+constexpr int GEMM_WAIT_LIMIT = 1 << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: after GEMM_WAIT_LIMIT polls the failure is recorded and the caller carries on (with
+// garbage data) so that every role still finishes and tensor memory is released.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int *status) {
+    for (int i = 0; i < GEMM_WAIT_LIMIT; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicOr(status, 2);
+    return false;
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
+// 8-row atoms of 1024 bytes stacked contiguously (stride byte offset 1024), descriptor version 1.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    const uint32_t lo = ((addr & 0x3ffffu) >> 4) | (1u << 16);          // start address, leading byte offset (unused) = 1
+    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);         // stride byte offset, version = 1, SWIZZLE_128B
+    return ((uint64_t)hi << 32) | lo;
+}
+// Instruction descriptor, kind::f16: D = f32, A = B = f16, both K-major, M = 128, N = bm.
+__host__ __device__ constexpr uint32_t idesc_f16(int bm) { return (1u << 4) | ((uint32_t)(bm >> 3) << 17) | ((128u >> 4) << 24); }
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---- activation pass: x [M][K] (bf16 | f16) -> xh [Mp][Kp] fp16 in stage order ------------------------
+// Row layout of xh: [super-block sb][window s][sub-block j][pos 0..7]; pos = 4*half + p holds the
+// activation of K index sb*256 + 32*j + 8*s + 4*half + perm[p], perm = {0, 2, 1, 3} -- the order in
+// which the nibble expansion of the dequant warps emits a register's four weights.
+__global__ void __launch_bounds__(256) xh_prep_kernel(const void *__restrict__ x, int x_dt, int64_t M, int64_t Mp, int64_t K,
+                                                      int64_t Kp, int64_t ldx, __half *__restrict__ xh) {
+    const int64_t chunks_per_row = Kp / 8;
+    const int64_t total = Mp * chunks_per_row;
+    for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < total; c += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = c / chunks_per_row, cc = c % chunks_per_row;
+        const int64_t sb = cc >> 5;
+        const int s = (int)((cc >> 3) & 3), j = (int)(cc & 7);
+        const int64_t k0 = sb * 256 + 32 * j + 8 * s;
+        __half out[8];
+#pragma unroll
+        for (int p = 0; p < 8; p++) {
+            const int i = (p & 4) + ((p & 1) << 1) + ((p & 2) >> 1);  // swap the middle two of each group of four
+            const int64_t k = k0 + i;
+            float v = 0.f;
+            if (m < M && k < K) v = load_as_float(x, x_dt, m * ldx + k);
+            out[p] = __float2half_rn(v);
+        }
+        *reinterpret_cast<uint4 *>(xh + m * Kp + cc * 8) = *reinterpret_cast<const uint4 *>(out);
+    }
+}
+
+struct GemmParams {
+    const uint8_t *tiles;  // Q4_K tiled layout
+    int64_t N, NT, SBp;
+    const __half *xh;      // [Mp][Kp]
+    int64_t M, Kp;
+    const void *bias;
+    int bias_dt;
+    void *y;
+    int y_dt;
+    int64_t ldy;
+    int *status;
+};
+
+template <int BM>
+struct GemmSmem {
+    static constexpr int B_STAGE_BYTES = BM * 128;
+    static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    static constexpr int HDR_BYTES = GEMM_DEQ_WARPS * 1024;
+    static constexpr int BAR_BYTES = 128;
+    // + 1024 slack to align the first stage to the swizzle atom
+    static constexpr int TOTAL = 1024 + GEMM_STAGES * STAGE_BYTES + HDR_BYTES + BAR_BYTES;
+};
+
+template <int BM>
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_q4k_kernel(GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    using SM = GemmSmem<BM>;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t stages_u32 = base;
+    const uint32_t hdr_u32 = base + GEMM_STAGES * SM::STAGE_BYTES;
+    const uint32_t bars_u32 = hdr_u32 + SM::HDR_BYTES;
+    const uint32_t full_bar = bars_u32, empty_bar = bars_u32 + 8 * GEMM_STAGES, accum_bar = bars_u32 + 16 * GEMM_STAGES;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + GEMM_STAGES * SM::STAGE_BYTES + SM::HDR_BYTES +
+                                                                         16 * GEMM_STAGES + 8);
+    const int64_t n_tile = blockIdx.x, m_tile = blockIdx.y;
+    const int64_t n0 = n_tile * GEMM_BN, m0 = m_tile * BM;
+    const int iters = (int)p.SBp * 4;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < GEMM_STAGES; s++) {
+            mbar_init(full_bar + 8 * s, GEMM_DEQ_WARPS + GEMM_B_WARPS);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+    }
+    if (warp == GEMM_WARPS - 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_slot)),
+                     "r"((uint32_t)BM)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < GEMM_DEQ_WARPS) {
+        // ------------------------------------------------------------------ dequantize A
+        const int g = lane >> 2, t = lane & 3;
+        const int r = lane & 15, h = lane >> 4;
+        const int64_t nt = n_tile * (GEMM_BN / TILE_ROWS) + warp;
+        const bool have = nt < p.NT;
+        const uint8_t *tile0 = p.tiles + (have ? nt : 0) * p.SBp * 2304;
+        const uint32_t my_hdr = hdr_u32 + warp * 1024;
+        // smem row offsets of this lane's two rows inside an A stage, and its chunk swizzle keys
+        const int row0 = warp * 16 + g, row1 = row0 + 8;
+        const uint32_t rowoff0 = (uint32_t)row0 * 128, rowoff1 = (uint32_t)row1 * 128;
+        const uint32_t key0 = (uint32_t)(row0 & 7), key1 = (uint32_t)(row1 & 7);
+        const int u0 = t >> 1, u1 = 2 + (t >> 1);
+        const uint32_t half_off = (uint32_t)(t & 1) * 8;
+        bool alive = true;
+        uint4 next = make_uint4(0, 0, 0, 0);
+        if (have) next = *reinterpret_cast<const uint4 *>(tile0 + lane * 16);
+        for (int it = 0; it < iters; it++) {
+            const int sb = it >> 2, s = it & 3;
+            const int stage = it % GEMM_STAGES;
+            const uint4 w = next;
+            if (have && it + 1 < iters) {
+                const int sb2 = (it + 1) >> 2, s2 = (it + 1) & 3;
+                next = *reinterpret_cast<const uint4 *>(tile0 + (int64_t)sb2 * 2304 + s2 * 512 + lane * 16);
+            }
+            if (s == 0) {
+                // header of (row tile, super-block): lane (r, h) unpacks sub-blocks 4h..4h+3 of row r into
+                // {scale, scale, offset, offset} halves: w = scale*(q-8) + offset (high nibbles arrive as 16*(q-8))
+                uint4 hv = make_uint4(0, 0, 0, 0);
+                if (have) hv = *reinterpret_cast<const uint4 *>(tile0 + (int64_t)sb * 2304 + 2048 + r * 16);
+                const __half2 dd = *reinterpret_cast<const __half2 *>(&hv.x);
+                const float d = __low2float(dd), dmin = __high2float(dd);
+                uint32_t scw, mw;
+                if (h == 0) {
+                    scw = hv.y & 0x3f3f3f3fu;
+                    mw = hv.z & 0x3f3f3f3fu;
+                } else {
+                    scw = (hv.w & 0x0f0f0f0fu) | ((hv.y >> 2) & 0x30303030u);
+                    mw = ((hv.w >> 4) & 0x0f0f0f0fu) | ((hv.z >> 2) & 0x30303030u);
+                }
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float sc = d * (float)((scw >> (8 * i)) & 0xff);
+                    const float off = fmaf(8.f, sc, -dmin * (float)((mw >> (8 * i)) & 0xff));
+                    const __half2 s2 = __float2half2_rn((i & 1) ? sc * 0.0625f : sc);
+                    const __half2 o2 = __float2half2_rn(off);
+                    uint2 pk;
+                    pk.x = *reinterpret_cast<const uint32_t *>(&s2);
+                    pk.y = *reinterpret_cast<const uint32_t *>(&o2);
+                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(my_hdr + (uint32_t)((r * 8 + 4 * h + i) * 8)), "r"(pk.x),
+                                 "r"(pk.y)
+                                 : "memory");
+                }
+                __syncwarp();
+            }
+            if (it >= GEMM_STAGES && alive)
+                alive = mbar_wait_bounded(empty_bar + 8 * stage, (uint32_t)(((it / GEMM_STAGES) - 1) & 1), p.status);
+            const uint32_t a_stage = stages_u32 + stage * SM::STAGE_BYTES;
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int sl = 0; sl < 4; sl++) {
+                const int u = (sl >> 1) ? u1 : u0;
+                const int row = (sl & 1) ? (g + 8) : g;
+                const uint32_t rowoff = (sl & 1) ? rowoff1 : rowoff0, key = (sl & 1) ? key1 : key0;
+                // {scale2, offset2} of sub-blocks 2u (low nibbles) and 2u+1 (high nibbles)
+                uint4 so;
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(so.x), "=r"(so.y), "=r"(so.z), "=r"(so.w)
+                             : "r"(my_hdr + (uint32_t)((row * 8 + 2 * u) * 8)));
+                const __half2 sc_lo = *reinterpret_cast<const __half2 *>(&so.x), of_lo = *reinterpret_cast<const __half2 *>(&so.y);
+                const __half2 sc_hi = *reinterpret_cast<const __half2 *>(&so.z), of_hi = *reinterpret_cast<const __half2 *>(&so.w);
+                const uint32_t x = ww[sl], x8 = x >> 8;
+                uint32_t v0 = (x & 0x000f000fu) | 0x64006400u, v1 = (x8 & 0x000f000fu) | 0x64006400u;  // 1024 + q
+                uint32_t v2 = (x & 0x00f000f0u) | 0x64006400u, v3 = (x8 & 0x00f000f0u) | 0x64006400u;  // 1024 + 16 q
+                const __half2 k1032 = __float2half2_rn(1032.f), k1152 = __float2half2_rn(1152.f);
+                const __half2 a0 = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v0), k1032), sc_lo, of_lo);
+                const __half2 a1 = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v1), k1032), sc_lo, of_lo);
+                const __half2 b0 = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v2), k1152), sc_hi, of_hi);
+                const __half2 b1 = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v3), k1152), sc_hi, of_hi);
+                // chunk 2u (low) and 2u+1 (high) of this row, 8 bytes at half_off, swizzled by the row's key
+                const uint32_t dlo = a_stage + rowoff + ((((uint32_t)(2 * u)) ^ key) << 4) + half_off;
+                const uint32_t dhi = a_stage + rowoff + ((((uint32_t)(2 * u + 1)) ^ key) << 4) + half_off;
+                asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(dlo), "r"(*reinterpret_cast<const uint32_t *>(&a0)),
+                             "r"(*reinterpret_cast<const uint32_t *>(&a1))
+                             : "memory");
+                asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(dhi), "r"(*reinterpret_cast<const uint32_t *>(&b0)),
+                             "r"(*reinterpret_cast<const uint32_t *>(&b1))
+                             : "memory");
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full_bar + 8 * stage);
+        }
+        // ------------------------------------------------------------------ epilogue
+        if (alive) alive = mbar_wait_bounded(accum_bar, 0, p.status);
+        tc_fence_after();
+        const int q = warp & 3, ch = warp >> 2;
+        const int64_t n = n0 + q * 32 + lane;
+        float bias_v = 0.f;
+        if (p.bias != nullptr && n < p.N) bias_v = load_as_float(p.bias, p.bias_dt, n);
+#pragma unroll 1
+        for (int c0 = ch * (BM / 2); c0 < (ch + 1) * (BM / 2); c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+                const int64_t m = m0 + c0 + i;
+                if (m < p.M && n < p.N) store_from_float(p.y, p.y_dt, m * p.ldy + n, __uint_as_float(v[i]) + bias_v);
+            }
+        }
+        tc_fence_before();
+    } else if (warp < GEMM_DEQ_WARPS + GEMM_B_WARPS) {
+        // ------------------------------------------------------------------ activation tile copy
+        const int bw = warp - GEMM_DEQ_WARPS;
+        const int tid = bw * 32 + lane;
+        bool alive = true;
+        for (int it = 0; it < iters; it++) {
+            const int stage = it % GEMM_STAGES;
+            if (it >= GEMM_STAGES && alive)
+                alive = mbar_wait_bounded(empty_bar + 8 * stage, (uint32_t)(((it / GEMM_STAGES) - 1) & 1), p.status);
+            const uint32_t b_stage = stages_u32 + stage * SM::STAGE_BYTES + A_STAGE_BYTES;
+            const __half *src = p.xh + m0 * p.Kp + (int64_t)it * 64;
+#pragma unroll 4
+            for (int c = tid; c < BM * 8; c += GEMM_B_WARPS * 32) {
+                const int m = c >> 3, j = c & 7;
+                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(src + (int64_t)m * p.Kp + j * 8));
+                const uint32_t dst = b_stage + (uint32_t)m * 128 + ((uint32_t)(j ^ (m & 7)) << 4);
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full_bar + 8 * stage);
+        }
+    } else {
+        // ------------------------------------------------------------------ MMA issue
+        if (lane == 0) {
+            bool alive = true;
+            const uint32_t idesc = idesc_f16(BM);
+            for (int it = 0; it < iters; it++) {
+                const int stage = it % GEMM_STAGES;
+                if (alive) alive = mbar_wait_bounded(full_bar + 8 * stage, (uint32_t)((it / GEMM_STAGES) & 1), p.status);
+                tc_fence_after();
+                const uint32_t a_stage = stages_u32 + stage * SM::STAGE_BYTES;
+                const uint64_t adesc = smem_desc_sw128(a_stage), bdesc = smem_desc_sw128(a_stage + A_STAGE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < 4; kk++)  // 16 K values = 32 bytes along the swizzled row per instruction
+                    umma_f16(tmem_base, adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), idesc, (it > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(empty_bar + 8 * stage);
+            }
+            umma_commit(accum_bar);
+        }
+        __syncwarp();
+    }
+    __syncthreads();
+    if (warp == GEMM_WARPS - 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BM) : "memory");
+    }
+}
+
+template <int BM>
+cudaError_t launch_bm(const GemmParams &p, int64_t m_tiles, cudaStream_t st) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_q4k_kernel<BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BM>::TOTAL);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    const dim3 grid((unsigned)((p.N + GEMM_BN - 1) / GEMM_BN), (unsigned)m_tiles);
+    gemm_q4k_kernel<BM><<<grid, GEMM_THREADS, GemmSmem<BM>::TOTAL, st>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool gemm_supported(int fmt) { return fmt == TTQ_FMT_Q4_K; }
+
+// x rows are processed in slabs that fit the fp16 activation scratch (capacity in halves).
+cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_capacity, int *status, cudaStream_t st,
+                        int *launches) {
+    *launches = 0;
+    if (fmt != TTQ_FMT_Q4_K) return cudaErrorNotSupported;
+    const int64_t Kp = a.SBp * TILE_K;
+    const int BM = a.M <= 64 ? 64 : (a.M <= 128 ? 128 : 256);
+    int64_t slab = (xh_capacity / Kp) / BM * BM;  // rows per pass
+    if (slab < BM) return cudaErrorInvalidValue;
+    const int esz_x = a.x_dt == TTQ_DT_F32 ? 4 : 2, esz_y = a.y_dt == TTQ_DT_F32 ? 4 : 2;
+    for (int64_t m0 = 0; m0 < a.M; m0 += slab) {
+        const int64_t Ms = (a.M - m0) < slab ? (a.M - m0) : slab;
+        const int64_t m_tiles = (Ms + BM - 1) / BM, Mp = m_tiles * BM;
+        const uint8_t *xs = reinterpret_cast<const uint8_t *>(a.x) + (size_t)m0 * a.ldx * esz_x;
+        const int64_t chunks = Mp * (Kp / 8);
+        const unsigned grid = (unsigned)((chunks + 255) / 256 < 148 * 16 ? (chunks + 255) / 256 : 148 * 16);
+        xh_prep_kernel<<<grid, 256, 0, st>>>(xs, a.x_dt, Ms, Mp, a.K, Kp, a.ldx, xh);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        ++*launches;
+        GemmParams p;
+        p.tiles = a.tiles;
+        p.N = a.N; p.NT = a.NT; p.SBp = a.SBp;
+        p.xh = xh;
+        p.M = Ms; p.Kp = Kp;
+        p.bias = a.bias; p.bias_dt = a.bias_dt;
+        p.y = reinterpret_cast<uint8_t *>(a.y) + (size_t)m0 * a.ldy * esz_y;
+        p.y_dt = a.y_dt; p.ldy = a.ldy;
+        p.status = status;
+        if (BM == 64) e = launch_bm<64>(p, m_tiles, st);
+        else if (BM == 128) e = launch_bm<128>(p, m_tiles, st);
+        else e = launch_bm<256>(p, m_tiles, st);
+        if (e != cudaSuccess) return e;
+        ++*launches;
+    }
+    return cudaSuccess;
+}
+
+}  // namespace ttq
