@@ -5,15 +5,18 @@
 // 128 weight rows (n), its N dimension is a tile of BM activation rows (m), so that any batch from 17
 // rows up maps onto a legal instruction shape (N = 64, 128 or 256).
 //
-// Per CTA (one 128 x BM output tile), 11 warps:
-//   warps 0-7   dequantize: each owns 16 weight rows (one row tile of the packed layout), reads one
+// Persistent CTAs (one per SM) walk the 128 x BM output tiles; 13 warps per CTA:
+//   warps 0-3   epilogue: tcgen05.ld of their 32 accumulator lanes -> bias -> y.  Two accumulators
+//               in tensor memory alternate, so the epilogue of a tile overlaps the next tile's MMAs.
+//   warps 4-11  dequantize: each owns 16 weight rows (one row tile of the packed layout), reads one
 //               512-byte chunk per stage straight from global memory (16 bytes per lane, prefetched
 //               one stage ahead), expands nibbles to fp16 with the 1024-offset bit trick, applies the
 //               sub-block scale and offset with one HFMA2 per pair, and writes the 128-byte-swizzled
-//               K-major A tile.  Afterwards the same warps run the epilogue (tcgen05.ld -> bias -> y).
-//   warps 8-9   copy the activation tile (already fp16 and permuted by xh_prep_kernel) into the
-//               swizzled B tile.
-//   warp 10     allocates tensor memory, issues the MMAs (one elected lane) and commits them to the
+//               K-major A tile.
+//               Lane 0 of the first of them also brings the activation tile in with a single bulk
+//               async copy per stage (xh_prep_kernel stores fp16 activations as ready-made swizzled
+//               tile images).
+//   warp 12     allocates tensor memory, issues the MMAs (one elected lane) and commits them to the
 //               stage barriers.
 // A stage is one window of one 256-weight super-block: 64 K values (8 from each sub-block), in the
 // order the packed chunk delivers them; the activation pass applies the same K permutation, so the
@@ -26,8 +29,8 @@ namespace ttq {
 
 namespace {
 
-constexpr int GEMM_DEQ_WARPS = 8, GEMM_B_WARPS = 2;
-constexpr int GEMM_WARPS = GEMM_DEQ_WARPS + GEMM_B_WARPS + 1;
+constexpr int GEMM_EPI_WARPS = 4, GEMM_DEQ_WARPS = 8;
+constexpr int GEMM_WARPS = GEMM_EPI_WARPS + GEMM_DEQ_WARPS + 1;  // + MMA warp
 constexpr int GEMM_THREADS = GEMM_WARPS * 32;
 constexpr int GEMM_STAGES = 4;
 constexpr int GEMM_BN = 128;                     // weight rows per CTA = MMA M
@@ -57,6 +60,14 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
         if (mbar_try_wait(bar, parity)) return true;
     atomicOr(status, 2);
     return false;
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -98,37 +109,61 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// ---- activation pass: x [M][K] (bf16 | f16) -> xh [Mp][Kp] fp16 in stage order ------------------------
-// Row layout of xh: [super-block sb][window s][sub-block j][pos 0..7]; pos = 4*half + p holds the
-// activation of K index sb*256 + 32*j + 8*s + 4*half + perm[p], perm = {0, 2, 1, 3} -- the order in
-// which the nibble expansion of the dequant warps emits a register's four weights.
+// ---- activation pass: x [M][K] (bf16 | f16) -> fp16 tile images ------------------------------------
+// Output layout: [stage it = 4*sb + s][row atom m/8][1024 bytes]: the 8 rows x 128 bytes of one
+// swizzle atom exactly as they must sit in shared memory, so that the B tile of a stage (BM rows) is
+// ONE contiguous run of BM*128 bytes.  Inside a row, 16-byte chunk j (sub-block j) sits at position
+// j ^ (m & 7) and holds, at pos = 4*half + p, the activation of K index
+// sb*256 + 32*j + 8*s + 4*half + perm[p], perm = {0, 2, 1, 3} -- the order in which the nibble
+// expansion of the dequant warps emits a register's four weights.
 __global__ void __launch_bounds__(256) xh_prep_kernel(const void *__restrict__ x, int x_dt, int64_t M, int64_t Mp, int64_t K,
                                                       int64_t Kp, int64_t ldx, __half *__restrict__ xh) {
     const int64_t chunks_per_row = Kp / 8;
     const int64_t total = Mp * chunks_per_row;
     for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < total; c += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t m = c / chunks_per_row, cc = c % chunks_per_row;
-        const int64_t sb = cc >> 5;
-        const int s = (int)((cc >> 3) & 3), j = (int)(cc & 7);
+        // consecutive threads: consecutive j, then rows, then stages (coalesced 16-byte stores per atom)
+        const int j = (int)(c & 7);
+        const int64_t m = (c >> 3) % Mp, it = (c >> 3) / Mp;
+        const int64_t sb = it >> 2;
+        const int s = (int)(it & 3);
         const int64_t k0 = sb * 256 + 32 * j + 8 * s;
+        // the 8 source values are contiguous in K: one 16-byte load when the row is aligned
+        __half src[8];
+        const bool vec = x_dt != TTQ_DT_F32 && m < M && k0 + 8 <= K &&
+                         ((reinterpret_cast<uintptr_t>(x) + (size_t)(m * ldx + k0) * 2) & 15) == 0;
+        if (vec) {
+            const uint4 raw = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(x) + m * ldx + k0);
+            if (x_dt == TTQ_DT_F16) {
+                *reinterpret_cast<uint4 *>(src) = raw;
+            } else {
+                const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    src[2 * q] = __float2half_rn(__uint_as_float(w[q] << 16));
+                    src[2 * q + 1] = __float2half_rn(__uint_as_float(w[q] & 0xffff0000u));
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                float v = 0.f;
+                if (m < M && k0 + i < K) v = load_as_float(x, x_dt, m * ldx + k0 + i);
+                src[i] = __float2half_rn(v);
+            }
+        }
         __half out[8];
 #pragma unroll
-        for (int p = 0; p < 8; p++) {
-            const int i = (p & 4) + ((p & 1) << 1) + ((p & 2) >> 1);  // swap the middle two of each group of four
-            const int64_t k = k0 + i;
-            float v = 0.f;
-            if (m < M && k < K) v = load_as_float(x, x_dt, m * ldx + k);
-            out[p] = __float2half_rn(v);
-        }
-        *reinterpret_cast<uint4 *>(xh + m * Kp + cc * 8) = *reinterpret_cast<const uint4 *>(out);
+        for (int p = 0; p < 8; p++) out[p] = src[(p & 4) + ((p & 1) << 1) + ((p & 2) >> 1)];  // swap the middle two of each four
+        const int64_t dst = ((it * (Mp >> 3) + (m >> 3)) << 10) + ((m & 7) << 7) + ((int64_t)(j ^ (int)(m & 7)) << 4);
+        *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(xh) + dst) = *reinterpret_cast<const uint4 *>(out);
     }
 }
 
 struct GemmParams {
     const uint8_t *tiles;  // Q4_K tiled layout
     int64_t N, NT, SBp;
-    const __half *xh;      // [Mp][Kp]
-    int64_t M, Kp;
+    const __half *xh;      // tile images, see xh_prep_kernel
+    int64_t M, Mp, Kp;
     const void *bias;
     int bias_dt;
     void *y;
@@ -141,7 +176,7 @@ template <int BM>
 struct GemmSmem {
     static constexpr int B_STAGE_BYTES = BM * 128;
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-    static constexpr int HDR_BYTES = GEMM_DEQ_WARPS * 1024;
+    static constexpr int HDR_BYTES = GEMM_DEQ_WARPS * 1280;  // 16 rows x 80 bytes (padded against bank conflicts)
     static constexpr int BAR_BYTES = 128;
     // + 1024 slack to align the first stage to the swizzle atom
     static constexpr int TOTAL = 1024 + GEMM_STAGES * STAGE_BYTES + HDR_BYTES + BAR_BYTES;
@@ -157,25 +192,29 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_q4k_kernel(GemmParams p)
     const uint32_t stages_u32 = base;
     const uint32_t hdr_u32 = base + GEMM_STAGES * SM::STAGE_BYTES;
     const uint32_t bars_u32 = hdr_u32 + SM::HDR_BYTES;
-    const uint32_t full_bar = bars_u32, empty_bar = bars_u32 + 8 * GEMM_STAGES, accum_bar = bars_u32 + 16 * GEMM_STAGES;
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + GEMM_STAGES * SM::STAGE_BYTES + SM::HDR_BYTES +
-                                                                         16 * GEMM_STAGES + 8);
-    const int64_t n_tile = blockIdx.x, m_tile = blockIdx.y;
-    const int64_t n0 = n_tile * GEMM_BN, m0 = m_tile * BM;
-    const int iters = (int)p.SBp * 4;
+    // barriers: full[S], empty[S], accum_full[2], accum_empty[2]; then the tensor-memory address slot
+    const uint32_t full_bar = bars_u32, empty_bar = bars_u32 + 8 * GEMM_STAGES;
+    const uint32_t accf_bar = bars_u32 + 16 * GEMM_STAGES, acce_bar = accf_bar + 16;
+    volatile uint32_t *tmem_slot =
+        reinterpret_cast<volatile uint32_t *>(base_ptr + GEMM_STAGES * SM::STAGE_BYTES + SM::HDR_BYTES + 16 * GEMM_STAGES + 32);
+    const int iters = (int)p.SBp * 4;  // stages per tile
+    const int64_t n_tiles = (p.N + GEMM_BN - 1) / GEMM_BN, m_tiles = p.Mp / BM, total_tiles = n_tiles * m_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < GEMM_STAGES; s++) {
-            mbar_init(full_bar + 8 * s, GEMM_DEQ_WARPS + GEMM_B_WARPS);
+            mbar_init(full_bar + 8 * s, GEMM_DEQ_WARPS + 1);
             mbar_init(empty_bar + 8 * s, 1);
         }
-        mbar_init(accum_bar, 1);
+        for (int b = 0; b < 2; b++) {
+            mbar_init(accf_bar + 8 * b, 1);
+            mbar_init(acce_bar + 8 * b, GEMM_EPI_WARPS);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
     }
     if (warp == GEMM_WARPS - 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_slot)),
-                     "r"((uint32_t)BM)
+                     "r"((uint32_t)(2 * BM))
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -184,176 +223,201 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_q4k_kernel(GemmParams p)
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp < GEMM_DEQ_WARPS) {
+    if (warp < GEMM_EPI_WARPS) {
+        // ------------------------------------------------------------------ epilogue
+        bool alive = true;
+        int tcount = 0;
+        for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, tcount++) {
+            const int64_t n_tile = tile / m_tiles, m_tile = tile % m_tiles;
+            const int buf = tcount & 1;
+            if (alive) alive = mbar_wait_bounded(accf_bar + 8 * buf, (uint32_t)((tcount >> 1) & 1), p.status);
+            tc_fence_after();
+            const int64_t n = n_tile * GEMM_BN + warp * 32 + lane, m0 = m_tile * BM;
+            float bias_v = 0.f;
+            if (p.bias != nullptr && n < p.N) bias_v = load_as_float(p.bias, p.bias_dt, n);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BM; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * BM + c0), v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    const int64_t m = m0 + c0 + i;
+                    if (m < p.M && n < p.N) store_from_float(p.y, p.y_dt, m * p.ldy + n, __uint_as_float(v[i]) + bias_v);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acce_bar + 8 * buf);
+        }
+    } else if (warp < GEMM_EPI_WARPS + GEMM_DEQ_WARPS) {
         // ------------------------------------------------------------------ dequantize A
+        const int dw = warp - GEMM_EPI_WARPS;
         const int g = lane >> 2, t = lane & 3;
         const int r = lane & 15, h = lane >> 4;
-        const int64_t nt = n_tile * (GEMM_BN / TILE_ROWS) + warp;
-        const bool have = nt < p.NT;
-        const uint8_t *tile0 = p.tiles + (have ? nt : 0) * p.SBp * 2304;
-        const uint32_t my_hdr = hdr_u32 + warp * 1024;
-        // smem row offsets of this lane's two rows inside an A stage, and its chunk swizzle keys
-        const int row0 = warp * 16 + g, row1 = row0 + 8;
+        const uint32_t my_hdr = hdr_u32 + dw * 1280;
+        // smem row offsets of this lane's two rows inside an A stage, and their chunk swizzle keys
+        const int row0 = dw * 16 + g, row1 = row0 + 8;
         const uint32_t rowoff0 = (uint32_t)row0 * 128, rowoff1 = (uint32_t)row1 * 128;
         const uint32_t key0 = (uint32_t)(row0 & 7), key1 = (uint32_t)(row1 & 7);
         const int u0 = t >> 1, u1 = 2 + (t >> 1);
         const uint32_t half_off = (uint32_t)(t & 1) * 8;
-        bool alive = true;
-        uint4 next = make_uint4(0, 0, 0, 0);
-        if (have) next = *reinterpret_cast<const uint4 *>(tile0 + lane * 16);
-        for (int it = 0; it < iters; it++) {
-            const int sb = it >> 2, s = it & 3;
-            const int stage = it % GEMM_STAGES;
-            const uint4 w = next;
-            if (have && it + 1 < iters) {
-                const int sb2 = (it + 1) >> 2, s2 = (it + 1) & 3;
-                next = *reinterpret_cast<const uint4 *>(tile0 + (int64_t)sb2 * 2304 + s2 * 512 + lane * 16);
-            }
-            if (s == 0) {
-                // header of (row tile, super-block): lane (r, h) unpacks sub-blocks 4h..4h+3 of row r into
-                // {scale, scale, offset, offset} halves: w = scale*(q-8) + offset (high nibbles arrive as 16*(q-8))
-                uint4 hv = make_uint4(0, 0, 0, 0);
-                if (have) hv = *reinterpret_cast<const uint4 *>(tile0 + (int64_t)sb * 2304 + 2048 + r * 16);
-                const __half2 dd = *reinterpret_cast<const __half2 *>(&hv.x);
-                const float d = __low2float(dd), dmin = __high2float(dd);
-                uint32_t scw, mw;
-                if (h == 0) {
-                    scw = hv.y & 0x3f3f3f3fu;
-                    mw = hv.z & 0x3f3f3f3fu;
-                } else {
-                    scw = (hv.w & 0x0f0f0f0fu) | ((hv.y >> 2) & 0x30303030u);
-                    mw = ((hv.w >> 4) & 0x0f0f0f0fu) | ((hv.z >> 2) & 0x30303030u);
-                }
-                __syncwarp();
+        // byte offsets (inside an A stage) of the 8 stores of this lane: slot sl, low | high nibble chunk
+        uint32_t dst_off[4][2];
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const float sc = d * (float)((scw >> (8 * i)) & 0xff);
-                    const float off = fmaf(8.f, sc, -dmin * (float)((mw >> (8 * i)) & 0xff));
-                    const __half2 s2 = __float2half2_rn((i & 1) ? sc * 0.0625f : sc);
-                    const __half2 o2 = __float2half2_rn(off);
-                    uint2 pk;
-                    pk.x = *reinterpret_cast<const uint32_t *>(&s2);
-                    pk.y = *reinterpret_cast<const uint32_t *>(&o2);
-                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(my_hdr + (uint32_t)((r * 8 + 4 * h + i) * 8)), "r"(pk.x),
-                                 "r"(pk.y)
+        for (int sl = 0; sl < 4; sl++) {
+            const int u = (sl >> 1) ? u1 : u0;
+            const uint32_t rowoff = (sl & 1) ? rowoff1 : rowoff0, key = (sl & 1) ? key1 : key0;
+            dst_off[sl][0] = rowoff + ((((uint32_t)(2 * u)) ^ key) << 4) + half_off;
+            dst_off[sl][1] = rowoff + ((((uint32_t)(2 * u + 1)) ^ key) << 4) + half_off;
+        }
+        uint4 so[4];  // {scale2, offset2} x {low, high nibble sub-block} of the lane's 4 slots, per super-block
+        bool alive = true;
+        int git = 0;  // stage counter across tiles
+        const int64_t b_it_stride = (p.Mp >> 3) << 10;
+        // chunk prefetched for the upcoming stage
+        auto tile_ptr = [&](int64_t tile, bool &have) {
+            const int64_t nt = (tile / m_tiles) * (GEMM_BN / TILE_ROWS) + dw;
+            have = tile < total_tiles && nt < p.NT;
+            return p.tiles + (have ? nt : 0) * p.SBp * 2304;
+        };
+        bool have = false;
+        const uint8_t *tile0 = tile_ptr(blockIdx.x, have);
+        // chunks of the next two stages are kept in flight (global latency exceeds one stage)
+        auto chunk_at = [&](const uint8_t *t0, bool ok, int it) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (ok) v = *reinterpret_cast<const uint4 *>(t0 + (int64_t)(it >> 2) * 2304 + (it & 3) * 512 + lane * 16);
+            return v;
+        };
+        uint4 next = chunk_at(tile0, have, 0), next2 = chunk_at(tile0, have && iters > 1, 1);
+        for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            bool have_next = false;
+            const uint8_t *tile0_next = tile_ptr(tile + gridDim.x, have_next);
+            const uint8_t *bsrc0 = reinterpret_cast<const uint8_t *>(p.xh) + ((((tile % m_tiles) * BM) >> 3) << 10);
+            for (int it = 0; it < iters; it++, git++) {
+                const int sb = it >> 2;
+                const int stage = git % GEMM_STAGES;
+                const uint4 w = next;
+                next = next2;
+                if (it + 2 < iters) next2 = chunk_at(tile0, have, it + 2);
+                else next2 = chunk_at(tile0_next, have_next && (it + 2 - iters) < iters, it + 2 - iters);
+                if ((it & 3) == 0) {
+                    // header of (row tile, super-block): lane (r, h) unpacks sub-blocks 4h..4h+3 of row r into
+                    // {scale, scale, offset, offset} halves: w = scale*(q-8) + offset (high nibbles arrive as 16*(q-8))
+                    uint4 hv = make_uint4(0, 0, 0, 0);
+                    if (have) hv = *reinterpret_cast<const uint4 *>(tile0 + (int64_t)sb * 2304 + 2048 + r * 16);
+                    const __half2 dd = *reinterpret_cast<const __half2 *>(&hv.x);
+                    const float d = __low2float(dd), dmin = __high2float(dd);
+                    uint32_t scw, mw;
+                    if (h == 0) {
+                        scw = hv.y & 0x3f3f3f3fu;
+                        mw = hv.z & 0x3f3f3f3fu;
+                    } else {
+                        scw = (hv.w & 0x0f0f0f0fu) | ((hv.y >> 2) & 0x30303030u);
+                        mw = ((hv.w >> 4) & 0x0f0f0f0fu) | ((hv.z >> 2) & 0x30303030u);
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float sc = d * (float)((scw >> (8 * i)) & 0xff);
+                        const float off = fmaf(8.f, sc, -dmin * (float)((mw >> (8 * i)) & 0xff));
+                        const __half2 s2 = __float2half2_rn((i & 1) ? sc * 0.0625f : sc);
+                        const __half2 o2 = __float2half2_rn(off);
+                        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(my_hdr + (uint32_t)(r * 80 + (4 * h + i) * 8)),
+                                     "r"(*reinterpret_cast<const uint32_t *>(&s2)), "r"(*reinterpret_cast<const uint32_t *>(&o2))
+                                     : "memory");
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int sl = 0; sl < 4; sl++) {
+                        const int u = (sl >> 1) ? u1 : u0;
+                        const int row = (sl & 1) ? (g + 8) : g;
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(so[sl].x), "=r"(so[sl].y), "=r"(so[sl].z), "=r"(so[sl].w)
+                                     : "r"(my_hdr + (uint32_t)(row * 80 + 2 * u * 8)));
+                    }
+                }
+                if (git >= GEMM_STAGES && alive)
+                    alive = mbar_wait_bounded(empty_bar + 8 * stage, (uint32_t)(((git / GEMM_STAGES) - 1) & 1), p.status);
+                const uint32_t a_stage = stages_u32 + stage * SM::STAGE_BYTES;
+                if (dw == 0 && lane == 0) {
+                    // the activation tile of this stage: one bulk copy, counted on the same full barrier
+                    mbar_expect_tx(full_bar + 8 * stage, SM::B_STAGE_BYTES);
+                    bulk_g2s(a_stage + A_STAGE_BYTES, bsrc0 + it * b_it_stride, SM::B_STAGE_BYTES, full_bar + 8 * stage);
+                }
+                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+                const __half2 k1032 = __float2half2_rn(1032.f), k1152 = __float2half2_rn(1152.f);
+#pragma unroll
+                for (int sl = 0; sl < 4; sl++) {
+                    const __half2 sc_lo = *reinterpret_cast<const __half2 *>(&so[sl].x), of_lo = *reinterpret_cast<const __half2 *>(&so[sl].y);
+                    const __half2 sc_hi = *reinterpret_cast<const __half2 *>(&so[sl].z), of_hi = *reinterpret_cast<const __half2 *>(&so[sl].w);
+                    const uint32_t x = ww[sl], x8 = x >> 8;
+                    uint32_t v0 = (x & 0x000f000fu) | 0x64006400u, v1 = (x8 & 0x000f000fu) | 0x64006400u;  // 1024 + q
+                    uint32_t v2 = (x & 0x00f000f0u) | 0x64006400u, v3 = (x8 & 0x00f000f0u) | 0x64006400u;  // 1024 + 16 q
+                    const __half2 a0 = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v0), k1032), sc_lo, of_lo);
+                    const __half2 a1 = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v1), k1032), sc_lo, of_lo);
+                    const __half2 b0 = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v2), k1152), sc_hi, of_hi);
+                    const __half2 b1 = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v3), k1152), sc_hi, of_hi);
+                    const uint32_t dlo = a_stage + dst_off[sl][0], dhi = a_stage + dst_off[sl][1];
+                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(dlo), "r"(*reinterpret_cast<const uint32_t *>(&a0)),
+                                 "r"(*reinterpret_cast<const uint32_t *>(&a1))
+                                 : "memory");
+                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(dhi), "r"(*reinterpret_cast<const uint32_t *>(&b0)),
+                                 "r"(*reinterpret_cast<const uint32_t *>(&b1))
                                  : "memory");
                 }
+                fence_async_smem();
                 __syncwarp();
+                if (lane == 0) mbar_arrive(full_bar + 8 * stage);
             }
-            if (it >= GEMM_STAGES && alive)
-                alive = mbar_wait_bounded(empty_bar + 8 * stage, (uint32_t)(((it / GEMM_STAGES) - 1) & 1), p.status);
-            const uint32_t a_stage = stages_u32 + stage * SM::STAGE_BYTES;
-            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-            for (int sl = 0; sl < 4; sl++) {
-                const int u = (sl >> 1) ? u1 : u0;
-                const int row = (sl & 1) ? (g + 8) : g;
-                const uint32_t rowoff = (sl & 1) ? rowoff1 : rowoff0, key = (sl & 1) ? key1 : key0;
-                // {scale2, offset2} of sub-blocks 2u (low nibbles) and 2u+1 (high nibbles)
-                uint4 so;
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(so.x), "=r"(so.y), "=r"(so.z), "=r"(so.w)
-                             : "r"(my_hdr + (uint32_t)((row * 8 + 2 * u) * 8)));
-                const __half2 sc_lo = *reinterpret_cast<const __half2 *>(&so.x), of_lo = *reinterpret_cast<const __half2 *>(&so.y);
-                const __half2 sc_hi = *reinterpret_cast<const __half2 *>(&so.z), of_hi = *reinterpret_cast<const __half2 *>(&so.w);
-                const uint32_t x = ww[sl], x8 = x >> 8;
-                uint32_t v0 = (x & 0x000f000fu) | 0x64006400u, v1 = (x8 & 0x000f000fu) | 0x64006400u;  // 1024 + q
-                uint32_t v2 = (x & 0x00f000f0u) | 0x64006400u, v3 = (x8 & 0x00f000f0u) | 0x64006400u;  // 1024 + 16 q
-                const __half2 k1032 = __float2half2_rn(1032.f), k1152 = __float2half2_rn(1152.f);
-                const __half2 a0 = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v0), k1032), sc_lo, of_lo);
-                const __half2 a1 = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v1), k1032), sc_lo, of_lo);
-                const __half2 b0 = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v2), k1152), sc_hi, of_hi);
-                const __half2 b1 = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v3), k1152), sc_hi, of_hi);
-                // chunk 2u (low) and 2u+1 (high) of this row, 8 bytes at half_off, swizzled by the row's key
-                const uint32_t dlo = a_stage + rowoff + ((((uint32_t)(2 * u)) ^ key) << 4) + half_off;
-                const uint32_t dhi = a_stage + rowoff + ((((uint32_t)(2 * u + 1)) ^ key) << 4) + half_off;
-                asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(dlo), "r"(*reinterpret_cast<const uint32_t *>(&a0)),
-                             "r"(*reinterpret_cast<const uint32_t *>(&a1))
-                             : "memory");
-                asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(dhi), "r"(*reinterpret_cast<const uint32_t *>(&b0)),
-                             "r"(*reinterpret_cast<const uint32_t *>(&b1))
-                             : "memory");
-            }
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(full_bar + 8 * stage);
-        }
-        // ------------------------------------------------------------------ epilogue
-        if (alive) alive = mbar_wait_bounded(accum_bar, 0, p.status);
-        tc_fence_after();
-        const int q = warp & 3, ch = warp >> 2;
-        const int64_t n = n0 + q * 32 + lane;
-        float bias_v = 0.f;
-        if (p.bias != nullptr && n < p.N) bias_v = load_as_float(p.bias, p.bias_dt, n);
-#pragma unroll 1
-        for (int c0 = ch * (BM / 2); c0 < (ch + 1) * (BM / 2); c0 += 32) {
-            uint32_t v[32];
-            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
-#pragma unroll
-            for (int i = 0; i < 32; i++) {
-                const int64_t m = m0 + c0 + i;
-                if (m < p.M && n < p.N) store_from_float(p.y, p.y_dt, m * p.ldy + n, __uint_as_float(v[i]) + bias_v);
-            }
-        }
-        tc_fence_before();
-    } else if (warp < GEMM_DEQ_WARPS + GEMM_B_WARPS) {
-        // ------------------------------------------------------------------ activation tile copy
-        const int bw = warp - GEMM_DEQ_WARPS;
-        const int tid = bw * 32 + lane;
-        bool alive = true;
-        for (int it = 0; it < iters; it++) {
-            const int stage = it % GEMM_STAGES;
-            if (it >= GEMM_STAGES && alive)
-                alive = mbar_wait_bounded(empty_bar + 8 * stage, (uint32_t)(((it / GEMM_STAGES) - 1) & 1), p.status);
-            const uint32_t b_stage = stages_u32 + stage * SM::STAGE_BYTES + A_STAGE_BYTES;
-            const __half *src = p.xh + m0 * p.Kp + (int64_t)it * 64;
-#pragma unroll 4
-            for (int c = tid; c < BM * 8; c += GEMM_B_WARPS * 32) {
-                const int m = c >> 3, j = c & 7;
-                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(src + (int64_t)m * p.Kp + j * 8));
-                const uint32_t dst = b_stage + (uint32_t)m * 128 + ((uint32_t)(j ^ (m & 7)) << 4);
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-            }
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(full_bar + 8 * stage);
+            tile0 = tile0_next;
+            have = have_next;
         }
     } else {
         // ------------------------------------------------------------------ MMA issue
         if (lane == 0) {
             bool alive = true;
             const uint32_t idesc = idesc_f16(BM);
-            for (int it = 0; it < iters; it++) {
-                const int stage = it % GEMM_STAGES;
-                if (alive) alive = mbar_wait_bounded(full_bar + 8 * stage, (uint32_t)((it / GEMM_STAGES) & 1), p.status);
+            int git = 0, tcount = 0;
+            for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, tcount++) {
+                const int buf = tcount & 1;
+                // the epilogue must have drained this accumulator (used two tiles ago)
+                if (tcount >= 2 && alive) alive = mbar_wait_bounded(acce_bar + 8 * buf, (uint32_t)(((tcount >> 1) - 1) & 1), p.status);
                 tc_fence_after();
-                const uint32_t a_stage = stages_u32 + stage * SM::STAGE_BYTES;
-                const uint64_t adesc = smem_desc_sw128(a_stage), bdesc = smem_desc_sw128(a_stage + A_STAGE_BYTES);
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BM);
+                for (int it = 0; it < iters; it++, git++) {
+                    const int stage = git % GEMM_STAGES;
+                    if (alive) alive = mbar_wait_bounded(full_bar + 8 * stage, (uint32_t)((git / GEMM_STAGES) & 1), p.status);
+                    tc_fence_after();
+                    const uint32_t a_stage = stages_u32 + stage * SM::STAGE_BYTES;
+                    const uint64_t adesc = smem_desc_sw128(a_stage), bdesc = smem_desc_sw128(a_stage + A_STAGE_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < 4; kk++)  // 16 K values = 32 bytes along the swizzled row per instruction
-                    umma_f16(tmem_base, adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), idesc, (it > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(empty_bar + 8 * stage);
+                    for (int kk = 0; kk < 4; kk++)  // 16 K values = 32 bytes along the swizzled row per instruction
+                        umma_f16(tmem_d, adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), idesc, (it > 0 || kk > 0) ? 1u : 0u);
+                    umma_commit(empty_bar + 8 * stage);
+                }
+                umma_commit(accf_bar + 8 * buf);
             }
-            umma_commit(accum_bar);
         }
         __syncwarp();
     }
+    tc_fence_before();
     __syncthreads();
     if (warp == GEMM_WARPS - 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BM) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BM)) : "memory");
     }
 }
 
 template <int BM>
-cudaError_t launch_bm(const GemmParams &p, int64_t m_tiles, cudaStream_t st) {
+cudaError_t launch_bm(const GemmParams &p, int sms, cudaStream_t st) {
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_q4k_kernel<BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BM>::TOTAL);
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    const dim3 grid((unsigned)((p.N + GEMM_BN - 1) / GEMM_BN), (unsigned)m_tiles);
+    const int64_t tiles = ((p.N + GEMM_BN - 1) / GEMM_BN) * (p.Mp / BM);
+    const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
     gemm_q4k_kernel<BM><<<grid, GEMM_THREADS, GemmSmem<BM>::TOTAL, st>>>(p);
     return cudaGetLastError();
 }
@@ -363,7 +427,7 @@ cudaError_t launch_bm(const GemmParams &p, int64_t m_tiles, cudaStream_t st) {
 bool gemm_supported(int fmt) { return fmt == TTQ_FMT_Q4_K; }
 
 // x rows are processed in slabs that fit the fp16 activation scratch (capacity in halves).
-cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_capacity, int *status, cudaStream_t st,
+cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_capacity, int sms, int *status, cudaStream_t st,
                         int *launches) {
     *launches = 0;
     if (fmt != TTQ_FMT_Q4_K) return cudaErrorNotSupported;
@@ -386,14 +450,14 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
         p.tiles = a.tiles;
         p.N = a.N; p.NT = a.NT; p.SBp = a.SBp;
         p.xh = xh;
-        p.M = Ms; p.Kp = Kp;
+        p.M = Ms; p.Mp = Mp; p.Kp = Kp;
         p.bias = a.bias; p.bias_dt = a.bias_dt;
         p.y = reinterpret_cast<uint8_t *>(a.y) + (size_t)m0 * a.ldy * esz_y;
         p.y_dt = a.y_dt; p.ldy = a.ldy;
         p.status = status;
-        if (BM == 64) e = launch_bm<64>(p, m_tiles, st);
-        else if (BM == 128) e = launch_bm<128>(p, m_tiles, st);
-        else e = launch_bm<256>(p, m_tiles, st);
+        if (BM == 64) e = launch_bm<64>(p, sms, st);
+        else if (BM == 128) e = launch_bm<128>(p, sms, st);
+        else e = launch_bm<256>(p, sms, st);
         if (e != cudaSuccess) return e;
         ++*launches;
     }
