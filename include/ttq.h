@@ -180,6 +180,8 @@ TTQ_API ttq_status ttq_silu_and_mul(ttq_ctx *ctx, const void *in_dev, ttq_dtype 
  * environment variable TTQ_TRACE=1 before ttq_init.  Every kernel then records, from its first block,
  * eight 64-bit words: kind (1 activation pass, 2 GEMV), start, after the dependency wait, activations
  * ready, first weight tile ready, end of block 0 (all in globaltimer nanoseconds), grid size, N.
+ * The tensor-core GEMM records kind 3: start, ns its MMA lane waited for operands, ns it waited for the
+ * epilogue, stages issued, end, grid size, N.
  * ttq_trace_read synchronises the device, copies up to max_entries entries (8 words each) into `out`,
  * stores their number in *n_entries and clears the buffer.  With tracing off it reports 0 entries. */
 TTQ_API ttq_status ttq_trace_read(ttq_ctx *ctx, uint64_t *out, int64_t max_entries, int64_t *n_entries);

@@ -349,7 +349,7 @@ ttq_status ttq_linear_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_d
         // prefill / large batch: tensor-core path
         a.x = x_dev; a.M = M; a.y = y_dev;
         int launches = 0;
-        cudaError_t e = launch_gemm(w->fmt, a, ctx->xh, ctx->xh_capacity, ctx->sms, ctx->dev_status, st, &launches);
+        cudaError_t e = launch_gemm(w->fmt, a, ctx->xh, ctx->xh_capacity, ctx->sms, ctx->dev_status, ctx->trace, st, &launches);
         ctx->launches += launches;
         if (e != cudaSuccess) return cuda_fail(ctx, e, "linear forward (GEMM) launch");
         return TTQ_OK;

@@ -5,7 +5,9 @@
 // 128 weight rows (n), its N dimension is a tile of BM activation rows (m), so that any batch from 17
 // rows up maps onto a legal instruction shape (N = 64, 128 or 256).
 //
-// Persistent CTAs (one per SM) walk the 128 x BM output tiles; 13 warps per CTA:
+// Persistent CTAs (one per SM) walk output tiles of (128*NSUB weight rows) x (BM activation rows);
+// with NSUB = 2 one activation stage feeds two MMAs, which halves the L2 -> shared-memory traffic of
+// the activation operand (the first bound this kernel met).  13 warps per CTA:
 //   warps 0-3   epilogue: tcgen05.ld of their 32 accumulator lanes -> bias -> y.  Two accumulators
 //               in tensor memory alternate, so the epilogue of a tile overlaps the next tile's MMAs.
 //   warps 4-11  dequantize: each owns 16 weight rows (one row tile of the packed layout), reads one
@@ -29,10 +31,10 @@ namespace ttq {
 
 namespace {
 
-constexpr int GEMM_EPI_WARPS = 4, GEMM_DEQ_WARPS = 8;
-constexpr int GEMM_WARPS = GEMM_EPI_WARPS + GEMM_DEQ_WARPS + 1;  // + MMA warp
-constexpr int GEMM_THREADS = GEMM_WARPS * 32;
-constexpr int GEMM_STAGES = 4;
+constexpr int GEMM_EPI_WARPS = 4;
+// dequant warps: one per packed row tile of the CTA's weight rows (8 per 128-row sub-tile); + 1 MMA warp
+__host__ __device__ constexpr int gemm_deq_warps(int nsub) { return 8 * nsub; }
+__host__ __device__ constexpr int gemm_warps(int nsub) { return GEMM_EPI_WARPS + gemm_deq_warps(nsub) + 1; }
 constexpr int GEMM_BN = 128;                     // weight rows per CTA = MMA M
 constexpr int A_STAGE_BYTES = GEMM_BN * 128;     // 128 rows x 64 fp16
 constexpr int GEMM_WAIT_LIMIT = 1 << 22;
@@ -44,10 +46,13 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+#ifndef TTQ_GEMM_WAIT_OP
+#define TTQ_GEMM_WAIT_OP "mbarrier.try_wait"
+#endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        "{\n .reg .pred p;\n " TTQ_GEMM_WAIT_OP ".parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
         : "=r"(ok)
         : "r"(bar), "r"(parity)
         : "memory");
@@ -68,6 +73,11 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -96,15 +106,12 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(taddr));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -170,39 +177,51 @@ struct GemmParams {
     int y_dt;
     int64_t ldy;
     int *status;
+    unsigned long long *trace;  // optional: [0] entry counter, entries of 8 words from [8] (see ttq.h)
 };
 
-template <int BM>
-struct GemmSmem {
-    static constexpr int B_STAGE_BYTES = BM * 128;
-    static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-    static constexpr int HDR_BYTES = GEMM_DEQ_WARPS * 1280;  // 16 rows x 80 bytes (padded against bank conflicts)
+template <int BM, int NSUB>
+struct GemmCfg {
+    static constexpr int A_BYTES = NSUB * A_STAGE_BYTES;
+    static constexpr int B_BYTES = BM * 128;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = STAGE_BYTES > 48 * 1024 ? 3 : 4;
+    static constexpr int NACC = (2 * NSUB * BM <= 512) ? 2 : 1;  // accumulator sets in tensor memory
+    static constexpr int TMEM_COLS = NACC * NSUB * BM;            // 128 .. 512, a power of two
+    static constexpr int DEQ_WARPS = gemm_deq_warps(NSUB), WARPS = gemm_warps(NSUB), THREADS = WARPS * 32;
+    static constexpr int HDR_BYTES = DEQ_WARPS * 1280;  // per dequant warp: 16 rows x 80 bytes
     static constexpr int BAR_BYTES = 128;
     // + 1024 slack to align the first stage to the swizzle atom
-    static constexpr int TOTAL = 1024 + GEMM_STAGES * STAGE_BYTES + HDR_BYTES + BAR_BYTES;
+    static constexpr int TOTAL = 1024 + STAGES * STAGE_BYTES + HDR_BYTES + BAR_BYTES;
 };
 
-template <int BM>
-__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_q4k_kernel(GemmParams p) {
+template <int BM, int NSUB>
+__global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel(GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
-    using SM = GemmSmem<BM>;
+    using C = GemmCfg<BM, NSUB>;
+    constexpr int STAGES = C::STAGES;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *base_ptr = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t stages_u32 = base;
-    const uint32_t hdr_u32 = base + GEMM_STAGES * SM::STAGE_BYTES;
-    const uint32_t bars_u32 = hdr_u32 + SM::HDR_BYTES;
-    // barriers: full[S], empty[S], accum_full[2], accum_empty[2]; then the tensor-memory address slot
-    const uint32_t full_bar = bars_u32, empty_bar = bars_u32 + 8 * GEMM_STAGES;
-    const uint32_t accf_bar = bars_u32 + 16 * GEMM_STAGES, acce_bar = accf_bar + 16;
+    const uint32_t hdr_u32 = base + STAGES * C::STAGE_BYTES;
+    const uint32_t bars_u32 = hdr_u32 + C::HDR_BYTES;
+    // barriers: full[STAGES], empty[STAGES], accum_full[2], accum_empty[2]; then the tensor-memory address slot
+    const uint32_t full_bar = bars_u32, empty_bar = bars_u32 + 8 * STAGES;
+    const uint32_t accf_bar = bars_u32 + 16 * STAGES, acce_bar = accf_bar + 16;
     volatile uint32_t *tmem_slot =
-        reinterpret_cast<volatile uint32_t *>(base_ptr + GEMM_STAGES * SM::STAGE_BYTES + SM::HDR_BYTES + 16 * GEMM_STAGES + 32);
+        reinterpret_cast<volatile uint32_t *>(base_ptr + STAGES * C::STAGE_BYTES + C::HDR_BYTES + 16 * STAGES + 32);
     const int iters = (int)p.SBp * 4;  // stages per tile
-    const int64_t n_tiles = (p.N + GEMM_BN - 1) / GEMM_BN, m_tiles = p.Mp / BM, total_tiles = n_tiles * m_tiles;
+    constexpr int TILE_N = GEMM_BN * NSUB;
+    const int64_t n_tiles = (p.N + TILE_N - 1) / TILE_N, m_tiles = p.Mp / BM, total_tiles = n_tiles * m_tiles;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < GEMM_STAGES; s++) {
-            mbar_init(full_bar + 8 * s, GEMM_DEQ_WARPS + 1);
+        for (int s = 0; s < STAGES; s++) {
+#ifdef TTQ_DIAG_NO_B
+            mbar_init(full_bar + 8 * s, C::DEQ_WARPS);
+#else
+            mbar_init(full_bar + 8 * s, C::DEQ_WARPS + 1);
+#endif
             mbar_init(empty_bar + 8 * s, 1);
         }
         for (int b = 0; b < 2; b++) {
@@ -212,9 +231,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_q4k_kernel(GemmParams p)
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
     }
-    if (warp == GEMM_WARPS - 1) {
+    if (warp == C::WARPS - 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_slot)),
-                     "r"((uint32_t)(2 * BM))
+                     "r"((uint32_t)C::TMEM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -229,148 +248,188 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_q4k_kernel(GemmParams p)
         int tcount = 0;
         for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, tcount++) {
             const int64_t n_tile = tile / m_tiles, m_tile = tile % m_tiles;
-            const int buf = tcount & 1;
-            if (alive) alive = mbar_wait_bounded(accf_bar + 8 * buf, (uint32_t)((tcount >> 1) & 1), p.status);
+            const int buf = tcount % C::NACC, use = tcount / C::NACC;
+            if (alive) alive = mbar_wait_bounded(accf_bar + 8 * buf, (uint32_t)(use & 1), p.status);
             tc_fence_after();
-            const int64_t n = n_tile * GEMM_BN + warp * 32 + lane, m0 = m_tile * BM;
-            float bias_v = 0.f;
-            if (p.bias != nullptr && n < p.N) bias_v = load_as_float(p.bias, p.bias_dt, n);
+            const int64_t m0 = m_tile * BM;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BM; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * BM + c0), v);
+            for (int sub = 0; sub < NSUB; sub++) {
+                const int64_t n = n_tile * TILE_N + sub * GEMM_BN + warp * 32 + lane;
+                float bias_v = 0.f;
+                if (p.bias != nullptr && n < p.N) bias_v = load_as_float(p.bias, p.bias_dt, n);
+#pragma unroll 1
+                for (int c0 = 0; c0 < BM; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)((buf * NSUB + sub) * BM + c0), v);
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    const int64_t m = m0 + c0 + i;
-                    if (m < p.M && n < p.N) store_from_float(p.y, p.y_dt, m * p.ldy + n, __uint_as_float(v[i]) + bias_v);
+                    for (int i = 0; i < 16; i++) {
+                        const int64_t m = m0 + c0 + i;
+                        if (m < p.M && n < p.N) store_from_float(p.y, p.y_dt, m * p.ldy + n, __uint_as_float(v[i]) + bias_v);
+                    }
                 }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acce_bar + 8 * buf);
         }
-    } else if (warp < GEMM_EPI_WARPS + GEMM_DEQ_WARPS) {
+    } else if (warp < GEMM_EPI_WARPS + C::DEQ_WARPS) {
         // ------------------------------------------------------------------ dequantize A
-        const int dw = warp - GEMM_EPI_WARPS;
+        const int dwa = warp - GEMM_EPI_WARPS;  // dequant warp index
+        const int dw = dwa & 7, my_sub = dwa >> 3;  // row tile inside the 128-row sub-tile, sub-tile
         const int g = lane >> 2, t = lane & 3;
         const int r = lane & 15, h = lane >> 4;
-        const uint32_t my_hdr = hdr_u32 + dw * 1280;
-        // smem row offsets of this lane's two rows inside an A stage, and their chunk swizzle keys
-        const int row0 = dw * 16 + g, row1 = row0 + 8;
-        const uint32_t rowoff0 = (uint32_t)row0 * 128, rowoff1 = (uint32_t)row1 * 128;
-        const uint32_t key0 = (uint32_t)(row0 & 7), key1 = (uint32_t)(row1 & 7);
+        const uint32_t my_hdr = hdr_u32 + dwa * 1280;
+        // byte offsets (inside a 128-row A sub-tile) of the 8 stores of this lane: slot sl, low | high nibble chunk
         const int u0 = t >> 1, u1 = 2 + (t >> 1);
-        const uint32_t half_off = (uint32_t)(t & 1) * 8;
-        // byte offsets (inside an A stage) of the 8 stores of this lane: slot sl, low | high nibble chunk
-        uint32_t dst_off[4][2];
+        uint32_t dst_off[4][2], hdr_off[4];
 #pragma unroll
         for (int sl = 0; sl < 4; sl++) {
             const int u = (sl >> 1) ? u1 : u0;
-            const uint32_t rowoff = (sl & 1) ? rowoff1 : rowoff0, key = (sl & 1) ? key1 : key0;
-            dst_off[sl][0] = rowoff + ((((uint32_t)(2 * u)) ^ key) << 4) + half_off;
-            dst_off[sl][1] = rowoff + ((((uint32_t)(2 * u + 1)) ^ key) << 4) + half_off;
+            const int row = dw * 16 + g + 8 * (sl & 1);
+            const uint32_t key = (uint32_t)(row & 7);
+            dst_off[sl][0] = (uint32_t)row * 128 + ((((uint32_t)(2 * u)) ^ key) << 4) + (uint32_t)(t & 1) * 8;
+            dst_off[sl][1] = (uint32_t)row * 128 + ((((uint32_t)(2 * u + 1)) ^ key) << 4) + (uint32_t)(t & 1) * 8;
+            hdr_off[sl] = (uint32_t)((g + 8 * (sl & 1)) * 80 + 2 * u * 8);
         }
-        uint4 so[4];  // {scale2, offset2} x {low, high nibble sub-block} of the lane's 4 slots, per super-block
         bool alive = true;
         int git = 0;  // stage counter across tiles
         const int64_t b_it_stride = (p.Mp >> 3) << 10;
-        // chunk prefetched for the upcoming stage
-        auto tile_ptr = [&](int64_t tile, bool &have) {
-            const int64_t nt = (tile / m_tiles) * (GEMM_BN / TILE_ROWS) + dw;
+        // packed row tiles of this warp in a tile: sub s -> row tile (n_tile*NSUB + s)*8 + dw
+        auto tile_ptr = [&](int64_t tile, int sub, bool &have) {
+            const int64_t nt = ((tile / m_tiles) * NSUB + my_sub + sub) * (GEMM_BN / TILE_ROWS) + dw;
             have = tile < total_tiles && nt < p.NT;
             return p.tiles + (have ? nt : 0) * p.SBp * 2304;
         };
-        bool have = false;
-        const uint8_t *tile0 = tile_ptr(blockIdx.x, have);
-        // chunks of the next two stages are kept in flight (global latency exceeds one stage)
         auto chunk_at = [&](const uint8_t *t0, bool ok, int it) {
             uint4 v = make_uint4(0, 0, 0, 0);
             if (ok) v = *reinterpret_cast<const uint4 *>(t0 + (int64_t)(it >> 2) * 2304 + (it & 3) * 512 + lane * 16);
             return v;
         };
-        uint4 next = chunk_at(tile0, have, 0), next2 = chunk_at(tile0, have && iters > 1, 1);
+        bool have[1];
+        const uint8_t *tile0[1];
+        uint4 next[1], next2[1];  // chunks of the next two stages stay in flight
+        uint4 hv_next[1];               // row header of the next super-block (loaded one super-block ahead)
+        auto header_at = [&](const uint8_t *t0, bool ok, int sb) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (ok) v = *reinterpret_cast<const uint4 *>(t0 + (int64_t)sb * 2304 + 2048 + r * 16);
+            return v;
+        };
+#pragma unroll
+        for (int sub = 0; sub < 1; sub++) {
+            tile0[sub] = tile_ptr(blockIdx.x, sub, have[sub]);
+            next[sub] = chunk_at(tile0[sub], have[sub], 0);
+            next2[sub] = chunk_at(tile0[sub], have[sub] && iters > 1, 1);
+            hv_next[sub] = header_at(tile0[sub], have[sub], 0);
+        }
+        const __half2 k1032 = __float2half2_rn(1032.f), k1152 = __float2half2_rn(1152.f);
         for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-            bool have_next = false;
-            const uint8_t *tile0_next = tile_ptr(tile + gridDim.x, have_next);
+            bool have_n[1];
+            const uint8_t *tile0_n[1];
+#pragma unroll
+            for (int sub = 0; sub < 1; sub++) tile0_n[sub] = tile_ptr(tile + gridDim.x, sub, have_n[sub]);
             const uint8_t *bsrc0 = reinterpret_cast<const uint8_t *>(p.xh) + ((((tile % m_tiles) * BM) >> 3) << 10);
             for (int it = 0; it < iters; it++, git++) {
+#ifdef TTQ_DIAG_MMA_ONLY
+                continue;
+#endif
                 const int sb = it >> 2;
-                const int stage = git % GEMM_STAGES;
-                const uint4 w = next;
-                next = next2;
-                if (it + 2 < iters) next2 = chunk_at(tile0, have, it + 2);
-                else next2 = chunk_at(tile0_next, have_next && (it + 2 - iters) < iters, it + 2 - iters);
+                const int stage = git % STAGES;
+                uint4 w[1];
+#pragma unroll
+                for (int sub = 0; sub < 1; sub++) {
+                    w[sub] = next[sub];
+                    next[sub] = next2[sub];
+                    if (it + 2 < iters) next2[sub] = chunk_at(tile0[sub], have[sub], it + 2);
+                    else next2[sub] = chunk_at(tile0_n[sub], have_n[sub] && (it + 2 - iters) < iters, it + 2 - iters);
+                }
                 if ((it & 3) == 0) {
-                    // header of (row tile, super-block): lane (r, h) unpacks sub-blocks 4h..4h+3 of row r into
+                    // headers of (row tile, super-block): lane (r, h) unpacks sub-blocks 4h..4h+3 of row r into
                     // {scale, scale, offset, offset} halves: w = scale*(q-8) + offset (high nibbles arrive as 16*(q-8))
-                    uint4 hv = make_uint4(0, 0, 0, 0);
-                    if (have) hv = *reinterpret_cast<const uint4 *>(tile0 + (int64_t)sb * 2304 + 2048 + r * 16);
-                    const __half2 dd = *reinterpret_cast<const __half2 *>(&hv.x);
-                    const float d = __low2float(dd), dmin = __high2float(dd);
-                    uint32_t scw, mw;
-                    if (h == 0) {
-                        scw = hv.y & 0x3f3f3f3fu;
-                        mw = hv.z & 0x3f3f3f3fu;
-                    } else {
-                        scw = (hv.w & 0x0f0f0f0fu) | ((hv.y >> 2) & 0x30303030u);
-                        mw = ((hv.w >> 4) & 0x0f0f0f0fu) | ((hv.z >> 2) & 0x30303030u);
-                    }
                     __syncwarp();
 #pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const float sc = d * (float)((scw >> (8 * i)) & 0xff);
-                        const float off = fmaf(8.f, sc, -dmin * (float)((mw >> (8 * i)) & 0xff));
-                        const __half2 s2 = __float2half2_rn((i & 1) ? sc * 0.0625f : sc);
-                        const __half2 o2 = __float2half2_rn(off);
-                        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(my_hdr + (uint32_t)(r * 80 + (4 * h + i) * 8)),
-                                     "r"(*reinterpret_cast<const uint32_t *>(&s2)), "r"(*reinterpret_cast<const uint32_t *>(&o2))
-                                     : "memory");
+                    for (int sub = 0; sub < 1; sub++) {
+                        const uint4 hv = hv_next[sub];
+                        if (sb + 1 < (int)p.SBp) hv_next[sub] = header_at(tile0[sub], have[sub], sb + 1);
+                        else hv_next[sub] = header_at(tile0_n[sub], have_n[sub], 0);
+                        const __half2 dd = *reinterpret_cast<const __half2 *>(&hv.x);
+                        const float d = __low2float(dd), dmin = __high2float(dd);
+                        uint32_t scw, mw;
+                        if (h == 0) {
+                            scw = hv.y & 0x3f3f3f3fu;
+                            mw = hv.z & 0x3f3f3f3fu;
+                        } else {
+                            scw = (hv.w & 0x0f0f0f0fu) | ((hv.y >> 2) & 0x30303030u);
+                            mw = ((hv.w >> 4) & 0x0f0f0f0fu) | ((hv.z >> 2) & 0x30303030u);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const float sc = d * (float)((scw >> (8 * i)) & 0xff);
+                            const float off = fmaf(8.f, sc, -dmin * (float)((mw >> (8 * i)) & 0xff));
+                            const __half2 s2 = __float2half2_rn((i & 1) ? sc * 0.0625f : sc);
+                            const __half2 o2 = __float2half2_rn(off);
+                            asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(my_hdr + (uint32_t)(r * 80 + (4 * h + i) * 8)),
+                                         "r"(*reinterpret_cast<const uint32_t *>(&s2)), "r"(*reinterpret_cast<const uint32_t *>(&o2))
+                                         : "memory");
+                        }
                     }
                     __syncwarp();
+                }
+                if (git >= STAGES && alive)
+                    alive = mbar_wait_bounded(empty_bar + 8 * stage, (uint32_t)(((git / STAGES) - 1) & 1), p.status);
+                const uint32_t a_stage = stages_u32 + stage * C::STAGE_BYTES;
+#ifndef TTQ_DIAG_NO_B
+                if (dwa == 0 && lane == 0) {
+                    // the activation tile of this stage: one bulk copy, counted on the same full barrier
+                    mbar_expect_tx(full_bar + 8 * stage, C::B_BYTES);
+                    bulk_g2s(a_stage + C::A_BYTES, bsrc0 + it * b_it_stride, C::B_BYTES, full_bar + 8 * stage);
+                }
+#endif
+#ifdef TTQ_DIAG_NO_CONVERT
+                if (git < 0)
+#endif
 #pragma unroll
-                    for (int sl = 0; sl < 4; sl++) {
-                        const int u = (sl >> 1) ? u1 : u0;
-                        const int row = (sl & 1) ? (g + 8) : g;
+                for (int sub = 0; sub < 1; sub++) {
+                    const uint32_t ww[4] = {w[sub].x, w[sub].y, w[sub].z, w[sub].w};
+                    const uint32_t a_sub = a_stage + my_sub * A_STAGE_BYTES;
+                    // three phases (loads, arithmetic, stores) so that the shared-memory latencies overlap
+                    uint4 so[4];  // {scale2, offset2} of sub-blocks 2u (low nibbles) and 2u+1 (high nibbles) per slot
+#pragma unroll
+                    for (int sl = 0; sl < 4; sl++)
                         asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                                      : "=r"(so[sl].x), "=r"(so[sl].y), "=r"(so[sl].z), "=r"(so[sl].w)
-                                     : "r"(my_hdr + (uint32_t)(row * 80 + 2 * u * 8)));
-                    }
-                }
-                if (git >= GEMM_STAGES && alive)
-                    alive = mbar_wait_bounded(empty_bar + 8 * stage, (uint32_t)(((git / GEMM_STAGES) - 1) & 1), p.status);
-                const uint32_t a_stage = stages_u32 + stage * SM::STAGE_BYTES;
-                if (dw == 0 && lane == 0) {
-                    // the activation tile of this stage: one bulk copy, counted on the same full barrier
-                    mbar_expect_tx(full_bar + 8 * stage, SM::B_STAGE_BYTES);
-                    bulk_g2s(a_stage + A_STAGE_BYTES, bsrc0 + it * b_it_stride, SM::B_STAGE_BYTES, full_bar + 8 * stage);
-                }
-                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-                const __half2 k1032 = __float2half2_rn(1032.f), k1152 = __float2half2_rn(1152.f);
+                                     : "r"(my_hdr + hdr_off[sl]));
+                    __half2 res[4][4];
 #pragma unroll
-                for (int sl = 0; sl < 4; sl++) {
-                    const __half2 sc_lo = *reinterpret_cast<const __half2 *>(&so[sl].x), of_lo = *reinterpret_cast<const __half2 *>(&so[sl].y);
-                    const __half2 sc_hi = *reinterpret_cast<const __half2 *>(&so[sl].z), of_hi = *reinterpret_cast<const __half2 *>(&so[sl].w);
-                    const uint32_t x = ww[sl], x8 = x >> 8;
-                    uint32_t v0 = (x & 0x000f000fu) | 0x64006400u, v1 = (x8 & 0x000f000fu) | 0x64006400u;  // 1024 + q
-                    uint32_t v2 = (x & 0x00f000f0u) | 0x64006400u, v3 = (x8 & 0x00f000f0u) | 0x64006400u;  // 1024 + 16 q
-                    const __half2 a0 = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v0), k1032), sc_lo, of_lo);
-                    const __half2 a1 = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v1), k1032), sc_lo, of_lo);
-                    const __half2 b0 = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v2), k1152), sc_hi, of_hi);
-                    const __half2 b1 = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v3), k1152), sc_hi, of_hi);
-                    const uint32_t dlo = a_stage + dst_off[sl][0], dhi = a_stage + dst_off[sl][1];
-                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(dlo), "r"(*reinterpret_cast<const uint32_t *>(&a0)),
-                                 "r"(*reinterpret_cast<const uint32_t *>(&a1))
-                                 : "memory");
-                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(dhi), "r"(*reinterpret_cast<const uint32_t *>(&b0)),
-                                 "r"(*reinterpret_cast<const uint32_t *>(&b1))
-                                 : "memory");
+                    for (int sl = 0; sl < 4; sl++) {
+                        const __half2 sc_lo = *reinterpret_cast<const __half2 *>(&so[sl].x), of_lo = *reinterpret_cast<const __half2 *>(&so[sl].y);
+                        const __half2 sc_hi = *reinterpret_cast<const __half2 *>(&so[sl].z), of_hi = *reinterpret_cast<const __half2 *>(&so[sl].w);
+                        const uint32_t x = ww[sl], x8 = x >> 8;
+                        uint32_t v0 = (x & 0x000f000fu) | 0x64006400u, v1 = (x8 & 0x000f000fu) | 0x64006400u;  // 1024 + q
+                        uint32_t v2 = (x & 0x00f000f0u) | 0x64006400u, v3 = (x8 & 0x00f000f0u) | 0x64006400u;  // 1024 + 16 q
+                        res[sl][0] = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v0), k1032), sc_lo, of_lo);
+                        res[sl][1] = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v1), k1032), sc_lo, of_lo);
+                        res[sl][2] = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v2), k1152), sc_hi, of_hi);
+                        res[sl][3] = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v3), k1152), sc_hi, of_hi);
+                    }
+#pragma unroll
+                    for (int sl = 0; sl < 4; sl++) {
+                        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a_sub + dst_off[sl][0]),
+                                     "r"(*reinterpret_cast<const uint32_t *>(&res[sl][0])), "r"(*reinterpret_cast<const uint32_t *>(&res[sl][1]))
+                                     : "memory");
+                        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a_sub + dst_off[sl][1]),
+                                     "r"(*reinterpret_cast<const uint32_t *>(&res[sl][2])), "r"(*reinterpret_cast<const uint32_t *>(&res[sl][3]))
+                                     : "memory");
+                    }
                 }
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full_bar + 8 * stage);
             }
-            tile0 = tile0_next;
-            have = have_next;
+#pragma unroll
+            for (int sub = 0; sub < 1; sub++) {
+                tile0[sub] = tile0_n[sub];
+                have[sub] = have_n[sub];
+            }
         }
     } else {
         // ------------------------------------------------------------------ MMA issue
@@ -378,47 +437,70 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_q4k_kernel(GemmParams p)
             bool alive = true;
             const uint32_t idesc = idesc_f16(BM);
             int git = 0, tcount = 0;
+            const bool tr = p.trace != nullptr && blockIdx.x == 0;
+            unsigned long long t_start = tr ? global_ns() : 0, t_full = 0, t_acc = 0;
             for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, tcount++) {
-                const int buf = tcount & 1;
-                // the epilogue must have drained this accumulator (used two tiles ago)
-                if (tcount >= 2 && alive) alive = mbar_wait_bounded(acce_bar + 8 * buf, (uint32_t)(((tcount >> 1) - 1) & 1), p.status);
+                const int buf = tcount % C::NACC, use = tcount / C::NACC;
+                // the epilogue must have drained this accumulator set (its previous use)
+                unsigned long long t0 = tr ? global_ns() : 0;
+                if (use >= 1 && alive) alive = mbar_wait_bounded(acce_bar + 8 * buf, (uint32_t)((use - 1) & 1), p.status);
+                if (tr) t_acc += global_ns() - t0;
                 tc_fence_after();
-                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BM);
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * NSUB * BM);
                 for (int it = 0; it < iters; it++, git++) {
-                    const int stage = git % GEMM_STAGES;
-                    if (alive) alive = mbar_wait_bounded(full_bar + 8 * stage, (uint32_t)((git / GEMM_STAGES) & 1), p.status);
+                    const int stage = git % STAGES;
+                    if (tr) t0 = global_ns();
+#ifndef TTQ_DIAG_MMA_ONLY
+                    if (alive) alive = mbar_wait_bounded(full_bar + 8 * stage, (uint32_t)((git / STAGES) & 1), p.status);
+#endif
+                    if (tr) t_full += global_ns() - t0;
                     tc_fence_after();
-                    const uint32_t a_stage = stages_u32 + stage * SM::STAGE_BYTES;
-                    const uint64_t adesc = smem_desc_sw128(a_stage), bdesc = smem_desc_sw128(a_stage + A_STAGE_BYTES);
+                    const uint32_t a_stage = stages_u32 + stage * C::STAGE_BYTES;
+                    const uint64_t bdesc = smem_desc_sw128(a_stage + C::A_BYTES);
 #pragma unroll
-                    for (int kk = 0; kk < 4; kk++)  // 16 K values = 32 bytes along the swizzled row per instruction
-                        umma_f16(tmem_d, adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), idesc, (it > 0 || kk > 0) ? 1u : 0u);
+                    for (int sub = 0; sub < NSUB; sub++) {
+                        const uint64_t adesc = smem_desc_sw128(a_stage + sub * A_STAGE_BYTES);
+#pragma unroll
+                        for (int kk = 0; kk < 4; kk++)  // 16 K values = 32 bytes along the swizzled row per instruction
+                            umma_f16(tmem_d + (uint32_t)(sub * BM), adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), idesc,
+                                     (it > 0 || kk > 0) ? 1u : 0u);
+                    }
                     umma_commit(empty_bar + 8 * stage);
                 }
                 umma_commit(accf_bar + 8 * buf);
+            }
+            if (tr) {
+                // timeline entry of kind 3: start, end, time the MMA lane waited for operands / for the epilogue, stages issued
+                const unsigned long long slot = atomicAdd(p.trace, 1ull);
+                if (slot < 8192) {
+                    unsigned long long *e = p.trace + 8 + slot * 8;
+                    e[0] = 3; e[1] = t_start; e[2] = t_full; e[3] = t_acc; e[4] = (unsigned long long)git; e[5] = global_ns();
+                    e[6] = gridDim.x; e[7] = (unsigned long long)p.N;
+                }
             }
         }
         __syncwarp();
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == GEMM_WARPS - 1) {
+    if (warp == C::WARPS - 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BM)) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::TMEM_COLS) : "memory");
     }
 }
 
-template <int BM>
-cudaError_t launch_bm(const GemmParams &p, int sms, cudaStream_t st) {
+template <int BM, int NSUB>
+cudaError_t launch_cfg(const GemmParams &p, int sms, cudaStream_t st) {
+    using C = GemmCfg<BM, NSUB>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_q4k_kernel<BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BM>::TOTAL);
+        cudaError_t e = cudaFuncSetAttribute(gemm_q4k_kernel<BM, NSUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL);
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    const int64_t tiles = ((p.N + GEMM_BN - 1) / GEMM_BN) * (p.Mp / BM);
+    const int64_t tiles = ((p.N + GEMM_BN * NSUB - 1) / (GEMM_BN * NSUB)) * (p.Mp / BM);
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-    gemm_q4k_kernel<BM><<<grid, GEMM_THREADS, GemmSmem<BM>::TOTAL, st>>>(p);
+    gemm_q4k_kernel<BM, NSUB><<<grid, C::THREADS, C::TOTAL, st>>>(p);
     return cudaGetLastError();
 }
 
@@ -427,12 +509,23 @@ cudaError_t launch_bm(const GemmParams &p, int sms, cudaStream_t st) {
 bool gemm_supported(int fmt) { return fmt == TTQ_FMT_Q4_K; }
 
 // x rows are processed in slabs that fit the fp16 activation scratch (capacity in halves).
-cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_capacity, int sms, int *status, cudaStream_t st,
-                        int *launches) {
+cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_capacity, int sms, int *status,
+                        unsigned long long *trace, cudaStream_t st, int *launches) {
     *launches = 0;
     if (fmt != TTQ_FMT_Q4_K) return cudaErrorNotSupported;
     const int64_t Kp = a.SBp * TILE_K;
     const int BM = a.M <= 64 ? 64 : (a.M <= 128 ? 128 : 256);
+    // two 128-row sub-tiles per CTA once there are enough tiles to keep every SM busy with them
+    static const int force_nsub = []() {
+        const char *v = getenv("TTQ_GEMM_NSUB");
+        return v ? atoi(v) : 0;
+    }();
+    // a CTA with two sub-tiles does twice the work per activation stage in about 1.6x the time of one (measured)
+    const int64_t mt = (a.M + BM - 1) / BM;
+    const int64_t tiles1 = ((a.N + 127) / 128) * mt, tiles2 = ((a.N + 255) / 256) * mt;
+    const double cost1 = (double)((tiles1 + sms - 1) / sms), cost2 = 1.6 * (double)((tiles2 + sms - 1) / sms);
+    int nsub = (a.N > 128 && cost2 < cost1) ? 2 : 1;
+    if (force_nsub == 1 || force_nsub == 2) nsub = force_nsub;
     int64_t slab = (xh_capacity / Kp) / BM * BM;  // rows per pass
     if (slab < BM) return cudaErrorInvalidValue;
     const int esz_x = a.x_dt == TTQ_DT_F32 ? 4 : 2, esz_y = a.y_dt == TTQ_DT_F32 ? 4 : 2;
@@ -455,9 +548,16 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
         p.y = reinterpret_cast<uint8_t *>(a.y) + (size_t)m0 * a.ldy * esz_y;
         p.y_dt = a.y_dt; p.ldy = a.ldy;
         p.status = status;
-        if (BM == 64) e = launch_bm<64>(p, sms, st);
-        else if (BM == 128) e = launch_bm<128>(p, sms, st);
-        else e = launch_bm<256>(p, sms, st);
+        p.trace = trace;
+        if (nsub == 2) {
+            if (BM == 64) e = launch_cfg<64, 2>(p, sms, st);
+            else if (BM == 128) e = launch_cfg<128, 2>(p, sms, st);
+            else e = launch_cfg<256, 2>(p, sms, st);
+        } else {
+            if (BM == 64) e = launch_cfg<64, 1>(p, sms, st);
+            else if (BM == 128) e = launch_cfg<128, 1>(p, sms, st);
+            else e = launch_cfg<256, 1>(p, sms, st);
+        }
         if (e != cudaSuccess) return e;
         ++*launches;
     }

@@ -111,8 +111,8 @@ cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t 
 constexpr int TTQ_TRACE_ENTRIES = 8192;
 // tcgen05 dequant-GEMM for M > MAX_GEMV_M (formats for which gemm_supported() is true)
 bool gemm_supported(int fmt);
-cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_capacity, int sms, int *status, cudaStream_t st,
-                        int *launches);
+cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_capacity, int sms, int *status,
+                        unsigned long long *trace, cudaStream_t st, int *launches);
 cudaError_t launch_silu_and_mul(const void *in, int dt, int64_t M, int64_t H, int64_t ld_in, void *out,
                                 int64_t ld_out, cudaStream_t st);
 cudaError_t gemv_configure();  // one-time cudaFuncSetAttribute calls
