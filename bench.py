@@ -338,9 +338,33 @@ def ours_arm(args):
             us = a.elapsed_time(b) * 1e3 / (reps * N_LAYERS)
             per_shape[f"{k}x{n}"] = {"us": round(us, 3), "gbs": round(algorithmic_bytes(m, k, n) / us / 1e3, 1)}
 
+    # ---- batched rows on the same weights: M = 4, 16 (decode kernel) and 64, 256, 2048 (tcgen05 GEMM), layer 0
+    sweep = {}
+    if world == 1 and not args.no_e2e and not args.no_sweep:
+        for ms in (4, 16, 64, 256, 2048):
+            for idx, (name, k, n) in enumerate(SHAPES):
+                lin = layers[0][idx][1]
+                g = torch.Generator(device=dev).manual_seed(2100 + ms)
+                xs = torch.randn(ms, k, generator=g, device=dev).to(torch.bfloat16)
+                ys = torch.empty(ms, n, dtype=torch.bfloat16, device=dev)
+                for _ in range(2):
+                    lin.forward(xs, out=ys)
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = 10
+                a.record()
+                for _ in range(reps):
+                    lin.forward(xs, out=ys)
+                b.record()
+                torch.cuda.synchronize()
+                us = a.elapsed_time(b) * 1e3 / reps
+                sweep[f"M{ms}_{k}x{n}"] = {"us": round(us, 2), "tflops": round(2.0 * ms * n * k / us / 1e6, 1),
+                                            "gbs": round(algorithmic_bytes(ms, k, n) / us / 1e3, 1)}
+                del xs, ys
+        ctx.check_device_status()
+
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        _finish_distributed(dist, world)
         return
 
     peaks = {}
@@ -374,9 +398,26 @@ def ours_arm(args):
         "cuda_graph": graph is not None, "clocks": clocks, "per_shape": per_shape,
         "decode_linears_tokens_per_s": round(m / (ms_step * 1e-3), 1),
     }
+    if sweep:
+        best = max(v["tflops"] for key, v in sweep.items() if key.startswith("M2048_"))
+        tpeak = float(peaks.get("bf16_tflops", 1590.0))
+        line["sweep"] = sweep
+        line["roofline_gemm"] = {"bound": "tensor", "achieved": best, "peak": tpeak, "unit": "TFLOP/s",
+                                 "frac": round(best / tpeak, 4), "kernel": "gemm_q4k_kernel (tcgen05, fp16 operands, fp32 accumulate)",
+                                 "workload": "best of the four Q4_K shapes at M=2048 (hot L2, includes the activation pass)",
+                                 "peak_source": "MEASURED_PEAKS.json bf16_tflops (burst)" if "bf16_tflops" in peaks else "fallback 1590"}
     print(json.dumps(line), flush=True)
+    _finish_distributed(dist, world)
+
+
+def _finish_distributed(dist, world):
+    """Leave a multi-rank run without tearing NCCL down: a captured graph still references the communicator,
+    and destroying the process group under it has been seen to block; the process simply exits."""
     if world > 1:
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():
@@ -390,6 +431,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the M = 4..2048 sweep on layer 0")
     ap.add_argument("--layers", type=int, default=32,
                     help="layers in the pass (default 32; smaller values are for profiler captures only)")
     args = ap.parse_args()
