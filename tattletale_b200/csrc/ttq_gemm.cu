@@ -178,6 +178,8 @@ struct GemmParams {
     int64_t ldy;
     int *status;
     unsigned long long *trace;  // optional: [0] entry counter, entries of 8 words from [8] (see ttq.h)
+    int splits;   // K is cut in `splits` equal runs of super-blocks, one work unit each (1 = no split)
+    float *ws;    // splits > 1: fp32 partial outputs [split][Mp][N], summed by splitk_reduce_kernel
 };
 
 template <int BM, int NSUB>
@@ -211,9 +213,10 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
     const uint32_t accf_bar = bars_u32 + 16 * STAGES, acce_bar = accf_bar + 16;
     volatile uint32_t *tmem_slot =
         reinterpret_cast<volatile uint32_t *>(base_ptr + STAGES * C::STAGE_BYTES + C::HDR_BYTES + 16 * STAGES + 32);
-    const int iters = (int)p.SBp * 4;  // stages per tile
+    const int splits = p.splits, sb_per_unit = (int)p.SBp / splits;
+    const int iters = sb_per_unit * 4;  // stages per work unit (tile x K split)
     constexpr int TILE_N = GEMM_BN * NSUB;
-    const int64_t n_tiles = (p.N + TILE_N - 1) / TILE_N, m_tiles = p.Mp / BM, total_tiles = n_tiles * m_tiles;
+    const int64_t n_tiles = (p.N + TILE_N - 1) / TILE_N, m_tiles = p.Mp / BM, total_tiles = n_tiles * m_tiles * splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -247,7 +250,8 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
         bool alive = true;
         int tcount = 0;
         for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, tcount++) {
-            const int64_t n_tile = tile / m_tiles, m_tile = tile % m_tiles;
+            const int64_t otile = tile / splits, split = tile % splits;
+            const int64_t n_tile = otile / m_tiles, m_tile = otile % m_tiles;
             const int buf = tcount % C::NACC, use = tcount / C::NACC;
             if (alive) alive = mbar_wait_bounded(accf_bar + 8 * buf, (uint32_t)(use & 1), p.status);
             tc_fence_after();
@@ -256,7 +260,8 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
             for (int sub = 0; sub < NSUB; sub++) {
                 const int64_t n = n_tile * TILE_N + sub * GEMM_BN + warp * 32 + lane;
                 float bias_v = 0.f;
-                if (p.bias != nullptr && n < p.N) bias_v = load_as_float(p.bias, p.bias_dt, n);
+                if (splits == 1 && p.bias != nullptr && n < p.N) bias_v = load_as_float(p.bias, p.bias_dt, n);
+                float *wsp = p.ws + (size_t)split * p.Mp * p.N;
 #pragma unroll 1
                 for (int c0 = 0; c0 < BM; c0 += 16) {
                     uint32_t v[16];
@@ -264,7 +269,10 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
 #pragma unroll
                     for (int i = 0; i < 16; i++) {
                         const int64_t m = m0 + c0 + i;
-                        if (m < p.M && n < p.N) store_from_float(p.y, p.y_dt, m * p.ldy + n, __uint_as_float(v[i]) + bias_v);
+                        if (m < p.M && n < p.N) {
+                            if (splits == 1) store_from_float(p.y, p.y_dt, m * p.ldy + n, __uint_as_float(v[i]) + bias_v);
+                            else wsp[m * p.N + n] = __uint_as_float(v[i]);
+                        }
                     }
                 }
             }
@@ -296,9 +304,9 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
         const int64_t b_it_stride = (p.Mp >> 3) << 10;
         // packed row tiles of this warp in a tile: sub s -> row tile (n_tile*NSUB + s)*8 + dw
         auto tile_ptr = [&](int64_t tile, int sub, bool &have) {
-            const int64_t nt = ((tile / m_tiles) * NSUB + my_sub + sub) * (GEMM_BN / TILE_ROWS) + dw;
+            const int64_t nt = (((tile / splits) / m_tiles) * NSUB + my_sub + sub) * (GEMM_BN / TILE_ROWS) + dw;
             have = tile < total_tiles && nt < p.NT;
-            return p.tiles + (have ? nt : 0) * p.SBp * 2304;
+            return p.tiles + ((have ? nt : 0) * p.SBp + (tile % splits) * sb_per_unit) * 2304;
         };
         auto chunk_at = [&](const uint8_t *t0, bool ok, int it) {
             uint4 v = make_uint4(0, 0, 0, 0);
@@ -327,7 +335,8 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
             const uint8_t *tile0_n[1];
 #pragma unroll
             for (int sub = 0; sub < 1; sub++) tile0_n[sub] = tile_ptr(tile + gridDim.x, sub, have_n[sub]);
-            const uint8_t *bsrc0 = reinterpret_cast<const uint8_t *>(p.xh) + ((((tile % m_tiles) * BM) >> 3) << 10);
+            const uint8_t *bsrc0 = reinterpret_cast<const uint8_t *>(p.xh) + (((((tile / splits) % m_tiles) * BM) >> 3) << 10) +
+                                   (tile % splits) * iters * b_it_stride;
             for (int it = 0; it < iters; it++, git++) {
 #ifdef TTQ_DIAG_MMA_ONLY
                 continue;
@@ -349,7 +358,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
 #pragma unroll
                     for (int sub = 0; sub < 1; sub++) {
                         const uint4 hv = hv_next[sub];
-                        if (sb + 1 < (int)p.SBp) hv_next[sub] = header_at(tile0[sub], have[sub], sb + 1);
+                        if (sb + 1 < sb_per_unit) hv_next[sub] = header_at(tile0[sub], have[sub], sb + 1);
                         else hv_next[sub] = header_at(tile0_n[sub], have_n[sub], 0);
                         const __half2 dd = *reinterpret_cast<const __half2 *>(&hv.x);
                         const float d = __low2float(dd), dmin = __high2float(dd);
@@ -489,6 +498,19 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
     }
 }
 
+// Sum of the split-K partials (+ bias) into y.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ ws, int splits, int64_t M, int64_t Mp, int64_t N,
+                                                            const void *bias, int bias_dt, void *y, int y_dt, int64_t ldy) {
+    const int64_t total = M * N;
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = e / N, n = e % N;
+        float acc = 0.f;
+        for (int s = 0; s < splits; s++) acc += ws[((size_t)s * Mp + m) * N + n];
+        if (bias != nullptr) acc += load_as_float(bias, bias_dt, n);
+        store_from_float(y, y_dt, m * ldy + n, acc);
+    }
+}
+
 template <int BM, int NSUB>
 cudaError_t launch_cfg(const GemmParams &p, int sms, cudaStream_t st) {
     using C = GemmCfg<BM, NSUB>;
@@ -498,7 +520,7 @@ cudaError_t launch_cfg(const GemmParams &p, int sms, cudaStream_t st) {
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    const int64_t tiles = ((p.N + GEMM_BN * NSUB - 1) / (GEMM_BN * NSUB)) * (p.Mp / BM);
+    const int64_t tiles = ((p.N + GEMM_BN * NSUB - 1) / (GEMM_BN * NSUB)) * (p.Mp / BM) * p.splits;
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
     gemm_q4k_kernel<BM, NSUB><<<grid, C::THREADS, C::TOTAL, st>>>(p);
     return cudaGetLastError();
@@ -549,6 +571,22 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
         p.y_dt = a.y_dt; p.ldy = a.ldy;
         p.status = status;
         p.trace = trace;
+        // K split: when the output tiles alone cannot fill the SMs, cut K into equal runs of super-blocks;
+        // partials go to the tail of the activation scratch
+        int splits = 1;
+        {
+            const int64_t tiles = ((a.N + 128 * nsub - 1) / (128 * nsub)) * m_tiles;
+            const size_t xh_bytes = (size_t)Mp * Kp * sizeof(__half);
+            const size_t ws_cap = (size_t)xh_capacity * sizeof(__half) > xh_bytes ? (size_t)xh_capacity * sizeof(__half) - xh_bytes : 0;
+            for (int cand = 2; cand <= 8; cand++) {
+                if (a.SBp % cand || a.SBp / cand < 2) continue;
+                if (tiles * cand > sms) break;
+                if ((size_t)cand * Mp * a.N * sizeof(float) > ws_cap) break;
+                splits = cand;
+            }
+            p.splits = splits;
+            p.ws = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(xh) + ((xh_bytes + 255) & ~(size_t)255));
+        }
         if (nsub == 2) {
             if (BM == 64) e = launch_cfg<64, 2>(p, sms, st);
             else if (BM == 128) e = launch_cfg<128, 2>(p, sms, st);
@@ -560,6 +598,14 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
         }
         if (e != cudaSuccess) return e;
         ++*launches;
+        if (splits > 1) {
+            const int64_t total = Ms * a.N;
+            const unsigned rg = (unsigned)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+            splitk_reduce_kernel<<<rg, 256, 0, st>>>(p.ws, splits, Ms, Mp, a.N, a.bias, a.bias_dt, p.y, a.y_dt, a.ldy);
+            e = cudaGetLastError();
+            if (e != cudaSuccess) return e;
+            ++*launches;
+        }
     }
     return cudaSuccess;
 }

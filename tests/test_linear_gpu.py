@@ -209,4 +209,6 @@ def test_launch_counter_moves(ctx):
     assert ctx.launch_count == before + 2  # activation conversion pass + GEMV
     lin.forward(torch.zeros(8, 256, dtype=torch.bfloat16, device="cuda"))
     assert ctx.launch_count == before + 4
+    lin.forward(torch.zeros(64, 256, dtype=torch.bfloat16, device="cuda"))
+    assert ctx.launch_count == before + 6  # activation pass + tensor-core GEMM
     lin.close()
