@@ -410,6 +410,99 @@ def ours_arm(args):
     _finish_distributed(dist, world)
 
 
+def decode_arm(args):
+    """BASELINE configs[2]: full Llama-3-8B decoder stack (random init), one decode step at context 2048."""
+    import tattletale_b200 as ttq
+    from tattletale_b200.decoder import DecoderConfig, DecoderStack
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = DecoderConfig(n_layers=args.layers)
+    ctx = ttq.Context(local_rank)
+    torch.manual_seed(3000 + rank)
+    stack = DecoderStack(ctx, cfg, args.batch, rank, world)
+    g = torch.Generator(device=dev).manual_seed(3100)
+    ids = torch.randint(0, cfg.vocab, (args.batch,), generator=g, device=dev)
+    out = stack.step(ids)
+    torch.cuda.synchronize()
+    c0 = ctx.launch_count
+    out = stack.step(ids)
+    torch.cuda.synchronize()
+    launches_per_step = ctx.launch_count - c0
+    graph = None
+    if not args.no_graph:
+        try:
+            st = torch.cuda.Stream()
+            st.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(st):
+                stack.step(ids)
+            torch.cuda.current_stream().wait_stream(st)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = stack.step(ids)
+        except Exception as exc:
+            print(f"[bench] CUDA graph capture failed, running eagerly: {exc}", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
+    run = graph.replay if graph is not None else (lambda: stack.step(ids))
+    for _ in range(max(args.warmup, 3)):
+        run()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(visible_physical_index(local_rank))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.start()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms_total = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    ctx.check_device_status()
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        kv_bytes = 2 * cfg.n_layers * args.batch * cfg.n_kv_heads * cfg.context * cfg.head_dim * 2
+        w_bytes = stack.weight_bytes * world
+        gbs = (w_bytes + kv_bytes) / (ms_step * 1e-3) / 1e9
+        line = {
+            "metric": "decode tokens/s", "value": round(args.batch / (ms_step * 1e-3), 1), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": f"Llama-3-8B decoder stack, {cfg.n_layers} layers, Q4_K linears + Q6_K lm_head, decode batch "
+                                   f"{args.batch} at context {cfg.context}", "batch": args.batch, "context": cfg.context,
+                       "parallelism": "single GPU" if world == 1 else f"tp{world}",
+                       "glue": "RMSNorm, RoPE, KV cache and attention are torch ops (not part of the quantized-linear path)"},
+            "roofline": {"bound": "hbm", "achieved": round(gbs / world, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / world / peak, 4),
+                         "traffic": None, "bytes_per_step": {"weights": int(w_bytes), "kv_cache": int(kv_bytes)}},
+            "gpu_launches": int(launches_per_step * args.steps), "launches_per_step": int(launches_per_step),
+            "cuda_graph": graph is not None, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    _finish_distributed(dist, world)
+
+
 def _finish_distributed(dist, world):
     """Leave a multi-rank run without tearing NCCL down: a captured graph still references the communicator,
     and destroying the process group under it has been seen to block; the process simply exits."""
@@ -428,6 +521,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=1, help="decode batch (rows of x)")
+    ap.add_argument("--workload", default="linears", choices=["linears", "decode"],
+                    help="linears: the headline Q4_K GEMV pass (default); decode: full decoder stack, tokens/s")
+    ap.add_argument("--batch", type=int, default=1, help="decode workload: sequences decoded together")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
@@ -438,6 +534,8 @@ def main():
     N_LAYERS = args.layers
     if args.impl == "reference":
         reference_arm(args)
+    elif args.workload == "decode":
+        decode_arm(args)
     else:
         ours_arm(args)
 
