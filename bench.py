@@ -180,7 +180,8 @@ def workload_config(m: int, gpus: int):
     return {
         "workload": f"Llama-3-8B projection shapes, Q4_K, M={m} decode GEMV, {N_LAYERS} layers x 4 linears",
         "shapes_k_to_n": [[k, n] for _, k, n in SHAPES], "M": m, "layers": N_LAYERS,
-        "parallelism": "single GPU" if gpus == 1 else f"tp{gpus} (column/row split, NCCL all-reduce)",
+        "parallelism": "single GPU" if gpus == 1 else f"tp{gpus} (column/row split; row-parallel sum fused into the GEMV "
+                       "over NVLink peer memory for M <= 4, NCCL all-reduce otherwise)",
         "l2": f"{N_LAYERS * 122683392 / 1e9:.2f} GB of weights per step, larger than L2: every step streams from HBM",
     }
 
@@ -234,13 +235,23 @@ def ours_arm(args):
     ctx = ttq.Context(local_rank)
     layers = build_layers(ttq, ctx, dev, rank, world, m)
     torch.cuda.synchronize()
+    comm = None
+    if world > 1 and not args.nccl_allreduce:
+        from tattletale_b200 import tp
+
+        comm = tp.Communicator(ctx, n_cap=4096, m_cap=4)  # row-parallel outputs are [M, 4096]
 
     def step():
         for entry in layers:
             for name, lin, x, y in entry:
-                lin.forward(x, out=y)
                 if world > 1 and name in ("o", "down"):
-                    dist.all_reduce(y)
+                    if comm is not None:
+                        lin.forward_allreduce(x, comm, out=y)  # all-reduce fused into the linear (peer memory)
+                    else:
+                        lin.forward(x, out=y)
+                        dist.all_reduce(y)
+                else:
+                    lin.forward(x, out=y)
 
     # launches per step, counted on an eager step
     torch.cuda.synchronize()
@@ -428,7 +439,12 @@ def decode_arm(args):
     cfg = DecoderConfig(n_layers=args.layers)
     ctx = ttq.Context(local_rank)
     torch.manual_seed(3000 + rank)
-    stack = DecoderStack(ctx, cfg, args.batch, rank, world)
+    comm = None
+    if world > 1 and not args.nccl_allreduce:
+        from tattletale_b200 import tp
+
+        comm = tp.Communicator(ctx, n_cap=cfg.hidden, m_cap=4)
+    stack = DecoderStack(ctx, cfg, args.batch, rank, world, comm=comm)
     g = torch.Generator(device=dev).manual_seed(3100)
     ids = torch.randint(0, cfg.vocab, (args.batch,), generator=g, device=dev)
     out = stack.step(ids)
@@ -526,6 +542,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1, help="decode workload: sequences decoded together")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--nccl-allreduce", action="store_true", help="N > 1: use NCCL for the row-parallel sums instead of the fused exchange")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-sweep", action="store_true", help="skip the M = 4..2048 sweep on layer 0")
     ap.add_argument("--layers", type=int, default=32,

@@ -41,6 +41,7 @@ extern "C" {
 
 typedef struct ttq_ctx ttq_ctx;
 typedef struct ttq_weight ttq_weight;
+typedef struct ttq_comm ttq_comm;
 
 typedef enum ttq_status {
     TTQ_OK = 0,
@@ -146,6 +147,31 @@ TTQ_API ttq_status ttq_linear_forward_host(ttq_ctx *ctx, const ttq_weight *w, co
  * check gave up a bounded device-side wait (TTQ_ERR_TIMEOUT; the flag is cleared).  The *_host entry
  * points perform this check themselves. */
 TTQ_API ttq_status ttq_device_status(ttq_ctx *ctx, void *stream);
+
+/* ---- row-parallel linear with the all-reduce fused in (tensor parallelism) --------------------
+ * No reference counterpart (the reference has no parallelism).  One process per GPU.  For a ROW shard
+ * the outputs of all ranks must be summed; for decode-size batches the sum is done inside the linear's
+ * own kernel: every warp that finishes a 16-row tile pushes its partial sums into all ranks' exchange
+ * buffers over NVLink (plain peer stores on CUDA-IPC mappings, no multicast), raises a per-tile counter
+ * in the peers' memory, waits -- bounded -- for the peers' counters and adds the partials in rank
+ * order, so every rank ends with the same full result in y.
+ *   ttq_comm_create   allocates this rank's exchange buffer (sized for N <= n_cap, M <= m_cap <= 16) and
+ *                     returns its 64-byte CUDA IPC handle in ipc_handle_out;
+ *   ttq_comm_connect  takes the handles of ALL ranks (world x 64 bytes, in rank order; exchanged by the
+ *                     host, e.g. with an all-gather) and maps the peers' buffers.  All ranks must pass a
+ *                     host barrier after connecting and before the first forward;
+ *   ttq_linear_forward_allreduce  as ttq_linear_forward on the rank's ROW shard, y = sum over ranks
+ *                     (+ bias, added once).  Every rank must issue the same sequence of calls.  Returns
+ *                     TTQ_ERR_UNSUPPORTED when M or N exceed the buffer: fall back to ttq_linear_forward
+ *                     plus a library all-reduce.  A peer that never arrives ends the wait after a fixed
+ *                     number of polls and is reported as TTQ_ERR_TIMEOUT by ttq_device_status. */
+TTQ_API ttq_status ttq_comm_create(ttq_ctx *ctx, int rank, int world, int64_t n_cap, int m_cap, ttq_comm **out,
+                                   void *ipc_handle_out);
+TTQ_API ttq_status ttq_comm_connect(ttq_comm *comm, const void *all_handles);
+TTQ_API ttq_status ttq_comm_destroy(ttq_comm *comm);
+TTQ_API ttq_status ttq_linear_forward_allreduce(ttq_ctx *ctx, const ttq_weight *w, const void *x_dev, ttq_dtype x_dt,
+                                                int64_t M, int64_t ldx, const void *bias_dev, ttq_dtype bias_dt,
+                                                void *y_dev, ttq_dtype y_dt, int64_t ldy, ttq_comm *comm, void *stream);
 
 /* The decode linear for hosts that cannot allocate device memory.  No counterpart in the reference.
  * Some hosts are not allowed to call cudaMalloc at all: a server that has given every byte of device

@@ -30,6 +30,15 @@ struct ttq_ctx {
     cudaStream_t host_stream;
 };
 
+// Exchange area of one tensor-parallel group member (see CommView).
+struct ttq_comm {
+    ttq_ctx *ctx;
+    CommView view;
+    void *local;    // this rank's buffer (flags + data), exported through CUDA IPC
+    size_t bytes, flag_bytes;
+    void *peer_map[TTQ_MAX_RANKS];  // IPC mappings of the peers' buffers (nullptr for the own rank)
+};
+
 namespace {
 
 constexpr int64_t XQ_CAPACITY_K = 65536;          // largest K (padded to 256) the scratch planes hold
@@ -405,6 +414,103 @@ ttq_status ttq_device_status(ttq_ctx *ctx, void *stream) {
         cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), (cudaStream_t)stream);
         return fail(ctx, TTQ_ERR_TIMEOUT, "a kernel gave up a bounded wait (status word 0x%x); results of that call are invalid", host);
     }
+    return TTQ_OK;
+}
+
+ttq_status ttq_comm_create(ttq_ctx *ctx, int rank, int world, int64_t n_cap, int m_cap, ttq_comm **out, void *ipc_handle_out) {
+    if (!ctx) return TTQ_ERR_INVALID_ARG;
+    if (!out || !ipc_handle_out) return fail(ctx, TTQ_ERR_INVALID_ARG, "out or handle pointer is NULL");
+    *out = nullptr;
+    if (world < 2 || world > TTQ_MAX_RANKS || rank < 0 || rank >= world)
+        return fail(ctx, TTQ_ERR_INVALID_ARG, "rank %d of %d: world must be 2..%d", rank, world, TTQ_MAX_RANKS);
+    if (n_cap <= 0 || m_cap <= 0 || m_cap > MAX_GEMV_M) return fail(ctx, TTQ_ERR_SHAPE, "bad capacity (n_cap=%lld m_cap=%d)", (long long)n_cap, m_cap);
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    TTQ_CUDA(ctx, cudaSetDevice(ctx->device));
+    ttq_comm *c = new (std::nothrow) ttq_comm();
+    if (!c) return fail(ctx, TTQ_ERR_OOM, "host allocation failed");
+    memset(c, 0, sizeof(*c));
+    c->ctx = ctx;
+    const int64_t nt_cap = (n_cap + TILE_ROWS - 1) / TILE_ROWS;
+    n_cap = nt_cap * TILE_ROWS;
+    c->flag_bytes = ((size_t)world * nt_cap * sizeof(uint32_t) + 255) & ~(size_t)255;
+    c->bytes = c->flag_bytes + (size_t)2 * world * m_cap * n_cap * sizeof(float);
+    cudaError_t e = cudaMalloc(&c->local, c->bytes);
+    if (e == cudaSuccess) e = cudaMemset(c->local, 0, c->bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&c->view.sent, (size_t)nt_cap * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(c->view.sent, 0, (size_t)nt_cap * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(reinterpret_cast<cudaIpcMemHandle_t *>(ipc_handle_out), c->local);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        cudaFree(c->local);
+        cudaFree(c->view.sent);
+        delete c;
+        return cuda_fail(ctx, e, "exchange buffer set-up");
+    }
+    c->view.rank = rank;
+    c->view.world = world;
+    c->view.nt_cap = (int)nt_cap;
+    c->view.m_cap = m_cap;
+    c->view.n_cap = n_cap;
+    *out = c;
+    return TTQ_OK;
+}
+
+ttq_status ttq_comm_connect(ttq_comm *c, const void *all_handles) {
+    if (!c || !all_handles) return TTQ_ERR_INVALID_ARG;
+    ttq_ctx *ctx = c->ctx;
+    TTQ_CUDA(ctx, cudaSetDevice(ctx->device));
+    const cudaIpcMemHandle_t *h = reinterpret_cast<const cudaIpcMemHandle_t *>(all_handles);
+    for (int r = 0; r < c->view.world; r++) {
+        void *base = c->local;
+        if (r != c->view.rank) {
+            TTQ_CUDA(ctx, cudaIpcOpenMemHandle(&c->peer_map[r], h[r], cudaIpcMemLazyEnablePeerAccess));
+            base = c->peer_map[r];
+        }
+        c->view.flags[r] = reinterpret_cast<uint32_t *>(base);
+        c->view.data[r] = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(base) + c->flag_bytes);
+    }
+    return TTQ_OK;
+}
+
+ttq_status ttq_comm_destroy(ttq_comm *c) {
+    if (!c) return TTQ_OK;
+    cudaSetDevice(c->ctx->device);
+    cudaDeviceSynchronize();
+    for (int r = 0; r < TTQ_MAX_RANKS; r++)
+        if (c->peer_map[r]) cudaIpcCloseMemHandle(c->peer_map[r]);
+    cudaFree(c->local);
+    cudaFree(c->view.sent);
+    delete c;
+    return TTQ_OK;
+}
+
+ttq_status ttq_linear_forward_allreduce(ttq_ctx *ctx, const ttq_weight *w, const void *x_dev, ttq_dtype x_dt, int64_t M, int64_t ldx,
+                                        const void *bias_dev, ttq_dtype bias_dt, void *y_dev, ttq_dtype y_dt, int64_t ldy,
+                                        ttq_comm *comm, void *stream) {
+    if (!ctx) return TTQ_ERR_INVALID_ARG;
+    if (!w || !comm) return fail(ctx, TTQ_ERR_INVALID_ARG, "weight or communicator is NULL");
+    if (w->ctx != ctx || comm->ctx != ctx) return fail(ctx, TTQ_ERR_INVALID_ARG, "weight or communicator belongs to another context");
+    if (comm->view.flags[comm->view.world - 1] == nullptr) return fail(ctx, TTQ_ERR_INVALID_ARG, "communicator is not connected");
+    if (M < 0) return fail(ctx, TTQ_ERR_SHAPE, "M=%lld is negative", (long long)M);
+    if (M == 0) return TTQ_OK;
+    if (!x_dev || !y_dev) return fail(ctx, TTQ_ERR_INVALID_ARG, "x or y pointer is NULL");
+    if (x_dt != TTQ_DT_BF16 && x_dt != TTQ_DT_F16) return fail(ctx, TTQ_ERR_INVALID_ARG, "x dtype must be bf16 or f16");
+    if (!valid_dt(y_dt) || (bias_dev && !valid_dt(bias_dt))) return fail(ctx, TTQ_ERR_INVALID_ARG, "unknown dtype");
+    if (ldx < w->K || ldy < w->N) return fail(ctx, TTQ_ERR_SHAPE, "leading dimension smaller than the row length");
+    if (M > comm->view.m_cap || w->N > comm->view.n_cap)
+        return fail(ctx, TTQ_ERR_UNSUPPORTED, "M=%lld / N=%lld exceed the exchange buffer (m_cap=%d, n_cap=%lld): use ttq_linear_forward and a library all-reduce",
+                    (long long)M, (long long)w->N, comm->view.m_cap, (long long)comm->view.n_cap);
+    LinearArgs a;
+    a.tiles = w->tiles;
+    a.N = w->N; a.K = w->K; a.NT = w->NT; a.SBp = w->SBp;
+    a.x = x_dev; a.x_dt = x_dt; a.M = M; a.ldx = ldx;
+    a.bias = bias_dev; a.bias_dt = bias_dt;
+    a.y = y_dev; a.y_dt = y_dt; a.ldy = ldy;
+    int launches = 0;
+    cudaError_t e = launch_gemv(w->fmt, a, ctx->xq, ctx->xq_capacity_k, reinterpret_cast<const uint8_t *>(ctx->dev_status) + 256, ctx->sms,
+                                ctx->dev_status, ctx->trace, (cudaStream_t)stream, &launches, &comm->view);
+    ctx->launches += launches;
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "row-parallel linear launch");
     return TTQ_OK;
 }
 

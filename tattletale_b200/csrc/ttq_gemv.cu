@@ -293,6 +293,7 @@ struct GemvParams {
     int wk;                // warps that split K of one row tile (1, 2, 4 or 8)
     int *status;           // device word: bit 0 set when a bounded wait gave up
     unsigned long long *trace;  // optional timeline buffer (nullptr = off): [0] = entry counter, entries of 8 words from [8]
+    CommView comm;         // row-parallel exchange over peer memory (world <= 1: none)
 };
 
 #ifndef TTQ_RING_STAGES
@@ -733,18 +734,75 @@ __global__ void __launch_bounds__(NW * 32, NW > 8 ? 1 : (XSRC == XSRC_GLOBAL ? 2
         else __syncwarp();
         if (ks == 0) {
             const int64_t rt = rt0 + it * rt_step;
-            for (int o = lane; o < MP * TILE_ROWS; o += 32) {
-                const int row = o & 15, mm = o >> 4;
-                const int64_t n = rt * TILE_ROWS + row;
-                if (mm < M && n < a.N) {
-                    float acc = 0.f;
-                    for (int w = 0; w < WK; w++) {
-                        const float *rw = red_s + (grp * WK + w) * (2 * MP * TILE_ROWS);
-                        acc += rw[o] - rw[MP * TILE_ROWS + o];
+            const CommView &cm = p.comm;
+            if (cm.world <= 1) {
+                for (int o = lane; o < MP * TILE_ROWS; o += 32) {
+                    const int row = o & 15, mm = o >> 4;
+                    const int64_t n = rt * TILE_ROWS + row;
+                    if (mm < M && n < a.N) {
+                        float acc = 0.f;
+                        for (int w = 0; w < WK; w++) {
+                            const float *rw = red_s + (grp * WK + w) * (2 * MP * TILE_ROWS);
+                            acc += rw[o] - rw[MP * TILE_ROWS + o];
+                        }
+                        if (a.bias != nullptr) acc += load_as_float(a.bias, a.bias_dt, n);
+                        store_from_float(a.y, a.y_dt, mm * a.ldy + n, acc);
                     }
-                    if (a.bias != nullptr) acc += load_as_float(a.bias, a.bias_dt, n);
-                    store_from_float(a.y, a.y_dt, mm * a.ldy + n, acc);
                 }
+            } else {
+                // Row-parallel linear: the partial sums of this row tile are pushed into every rank's buffer over
+                // NVLink (plain peer stores), a per-row-tile counter tells the peers they have landed, and every
+                // rank adds the partials of all ranks in rank order -- the all-reduce happens here, tile by tile,
+                // while other warps are still streaming weights.
+                const uint32_t epoch = cm.sent[rt] + 1u;  // exchanges are counted per row tile; all ranks agree
+                const size_t slab = (size_t)cm.m_cap * cm.n_cap;
+                const size_t par_off = (size_t)(epoch & 1u) * cm.world * slab;
+                for (int o = lane; o < MP * TILE_ROWS; o += 32) {
+                    const int row = o & 15, mm = o >> 4;
+                    const int64_t n = rt * TILE_ROWS + row;
+                    if (mm < M && n < a.N) {
+                        float acc = 0.f;
+                        for (int w = 0; w < WK; w++) {
+                            const float *rw = red_s + (grp * WK + w) * (2 * MP * TILE_ROWS);
+                            acc += rw[o] - rw[MP * TILE_ROWS + o];
+                        }
+                        const size_t off = par_off + (size_t)cm.rank * slab + (size_t)mm * cm.n_cap + n;
+                        for (int q = 0; q < cm.world; q++) __stcg(cm.data[q] + off, acc);
+                    }
+                }
+                // the warp barrier orders every lane's pushes before the release stores of the counter lanes
+                __syncwarp();
+                if (lane < cm.world) {
+                    uint32_t *peer_flag = cm.flags[lane] + (size_t)cm.rank * cm.nt_cap + rt;
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_flag), "r"(epoch) : "memory");
+                }
+                bool ok = true;
+                if (lane < cm.world) {
+                    const uint32_t *my_flag = cm.flags[cm.rank] + (size_t)lane * cm.nt_cap + rt;
+                    int spins = 0;
+                    uint32_t seen;
+                    do {
+                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(my_flag) : "memory");
+                        if (++spins > (1 << 22)) {  // bounded: give up, flag the failure, keep going
+                            ok = false;
+                            break;
+                        }
+                    } while ((int32_t)(seen - epoch) < 0);
+                }
+                if (!__all_sync(0xffffffffu, ok) && lane == 0) atomicOr(p.status, 4);
+                const float *mine = cm.data[cm.rank] + par_off;
+                for (int o = lane; o < MP * TILE_ROWS; o += 32) {
+                    const int row = o & 15, mm = o >> 4;
+                    const int64_t n = rt * TILE_ROWS + row;
+                    if (mm < M && n < a.N) {
+                        float acc = 0.f;
+                        for (int q = 0; q < cm.world; q++) acc += __ldcv(mine + (size_t)q * slab + (size_t)mm * cm.n_cap + n);
+                        if (a.bias != nullptr) acc += load_as_float(a.bias, a.bias_dt, n);
+                        store_from_float(a.y, a.y_dt, mm * a.ldy + n, acc);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) cm.sent[rt] = epoch;
             }
         }
         if (WK > 1) named_barrier(1 + grp, WK * 32);  // the partial-sum area is free again
@@ -867,8 +925,10 @@ cudaError_t dispatch(GemvParams &p, int mode, int nw, int sms, cudaStream_t st) 
 cudaError_t gemv_configure() { return cudaSuccess; }
 
 cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t xq_capacity_k, const uint8_t *zeros,
-                        int sms, int *status, unsigned long long *trace, cudaStream_t st, int *launches) {
-    GemvParams p{a, xq, zeros, 1, status, trace};
+                        int sms, int *status, unsigned long long *trace, cudaStream_t st, int *launches, const CommView *comm) {
+    GemvParams p{a, xq, zeros, 1, status, trace, {}};
+    if (comm != nullptr) p.comm = *comm;
+    else p.comm.world = 0;
     *launches = 0;
     const int64_t Kp = a.SBp * TILE_K;
     if (Kp > xq_capacity_k) return cudaErrorInvalidValue;

@@ -87,6 +87,21 @@ struct XqView {
     float *sx;        // [Mpad][SBp]
 };
 
+// Peer-memory exchange area of a row-parallel linear (tensor parallelism).  Passed by value to the
+// decode kernel; world <= 1 means "no exchange".  Every rank owns one buffer holding
+//   flags [world][nt_cap] u32   slot [src][rt]: how many exchanges rank src has completed for row tile rt
+//   data  [2][world][m_cap][n_cap] f32   partial outputs pushed by rank src, double-buffered by exchange parity
+// and knows the base addresses of all ranks' buffers (its own and the peers' IPC mappings).
+constexpr int TTQ_MAX_RANKS = 8;
+struct CommView {
+    int rank, world;
+    int nt_cap, m_cap;
+    int64_t n_cap;
+    uint32_t *sent;                  // local [nt_cap]: exchanges this rank has completed per row tile
+    uint32_t *flags[TTQ_MAX_RANKS];  // flag array of every rank
+    float *data[TTQ_MAX_RANKS];      // partial-output buffer of every rank
+};
+
 struct LinearArgs {
     const uint8_t *tiles;
     int64_t N, K, NT, SBp;
@@ -107,7 +122,8 @@ cudaError_t launch_dequant(int fmt, const uint8_t *tiled, float *out, int64_t ld
                            int64_t SBp, cudaStream_t st);
 // GEMV for M <= MAX_GEMV_M.  `xq` is scratch for the separate x-prep pass (used when M > fused limit).
 cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t xq_capacity_k, const uint8_t *zeros,
-                        int sms, int *status, unsigned long long *trace, cudaStream_t st, int *launches);
+                        int sms, int *status, unsigned long long *trace, cudaStream_t st, int *launches,
+                        const CommView *comm = nullptr);
 constexpr int TTQ_TRACE_ENTRIES = 8192;
 // tcgen05 dequant-GEMM for M > MAX_GEMV_M (formats for which gemm_supported() is true)
 bool gemm_supported(int fmt);

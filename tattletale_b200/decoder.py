@@ -43,9 +43,10 @@ def _qlinear(ctx, fmt, n, k, seed, dev):
 
 
 class DecoderStack:
-    def __init__(self, ctx: Context, cfg: DecoderConfig, batch: int, rank: int = 0, world: int = 1, seed: int = 3000):
+    def __init__(self, ctx: Context, cfg: DecoderConfig, batch: int, rank: int = 0, world: int = 1, seed: int = 3000, comm=None):
         assert cfg.n_q_heads % world == 0 and cfg.n_kv_heads % world == 0 and cfg.ffn % (256 * world) == 0
         self.ctx, self.cfg, self.batch, self.rank, self.world = ctx, cfg, batch, rank, world
+        self.comm = comm  # tp.Communicator: row-parallel sums fused into the linears when the batch fits
         dev = ctx.device
         self.dev = dev
         hq, hkv, d = cfg.n_q_heads // world, cfg.n_kv_heads // world, cfg.head_dim
@@ -88,12 +89,16 @@ class DecoderStack:
         rot = torch.cat([-t[..., d // 2:], t[..., :d // 2]], dim=-1)
         return t * self.cos + rot * self.sin
 
-    def _all_reduce(self, t):
-        if self.world > 1:
-            import torch.distributed as dist
+    def _row_parallel(self, lin, x):
+        if self.world == 1:
+            return lin.forward(x)
+        if self.comm is not None:
+            return lin.forward_allreduce(x, self.comm)
+        import torch.distributed as dist
 
-            dist.all_reduce(t)
-        return t
+        y = lin.forward(x)
+        dist.all_reduce(y)
+        return y
 
     def step(self, token_ids: torch.Tensor) -> torch.Tensor:
         """One decode step for `batch` sequences at position context-1; returns next token ids."""
@@ -109,12 +114,12 @@ class DecoderStack:
             L["k"][:, :, self.pos:self.pos + 1] = k
             L["v"][:, :, self.pos:self.pos + 1] = v
             att = torch.nn.functional.scaled_dot_product_attention(q, L["k"], L["v"], enable_gqa=True)
-            o = self._all_reduce(L["o"].forward(att.reshape(B, self.hq * d)))
+            o = self._row_parallel(L["o"], att.reshape(B, self.hq * d))
             h = h + o
             x = self._rms(h, L["mlp_norm"])
             gu = L["gate_up"].forward(x)
             act = silu_and_mul(self.ctx, gu)
-            h = h + self._all_reduce(L["down"].forward(act))
+            h = h + self._row_parallel(L["down"], act)
         logits = self.lm_head.forward(self._rms(h, self.final_norm), out_dtype=torch.float32)
         if self.world > 1:
             import torch.distributed as dist

@@ -147,6 +147,32 @@ class QuantLinear:
 
     __call__ = forward
 
+    def forward_allreduce(self, x: torch.Tensor, comm, out_dtype: Optional[torch.dtype] = None,
+                          out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Row-parallel forward: this rank's K shard, summed over all ranks.  Decode-size batches go through the
+        fused peer-memory all-reduce of the library; anything larger falls back to forward + NCCL all-reduce."""
+        x2 = x.reshape(-1, self.in_features)
+        m = x2.shape[0]
+        odt = out_dtype or x.dtype
+        if out is None:
+            out = torch.empty((m, self.out_features), dtype=odt, device=x.device)
+        if m > comm.m_cap or self.out_features > comm.n_cap:
+            import torch.distributed as dist
+
+            self.forward(x, out=out)
+            dist.all_reduce(out)
+            return out.reshape(*x.shape[:-1], self.out_features)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        y2 = out.reshape(-1, self.out_features)
+        b = self.bias
+        st = self.ctx._lib.ttq_linear_forward_allreduce(
+            self.ctx.handle, self.handle, x2.data_ptr(), _dt(x2.dtype), m, x2.stride(0) if m > 1 else self.in_features,
+            None if b is None else b.data_ptr(), _lib.DT_F32 if b is None else _dt(b.dtype),
+            y2.data_ptr(), _dt(y2.dtype), y2.stride(0) if m > 1 else self.out_features, comm.handle, _stream_ptr(x.device))
+        check(self.ctx.handle, st)
+        return out.reshape(*x.shape[:-1], self.out_features)
+
     def forward_host(self, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
         """Host-buffer call: x and y are CPU tensors (pinned for speed); copies are part of the call."""
         x2 = x.reshape(-1, self.in_features)

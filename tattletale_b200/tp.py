@@ -44,3 +44,38 @@ def all_reduce_sum(y: torch.Tensor) -> torch.Tensor:
     if dist.is_initialized() and dist.get_world_size() > 1:
         dist.all_reduce(y)
     return y
+
+
+class Communicator:
+    """Exchange buffers of a tensor-parallel group for ``QuantLinear.forward_allreduce`` (one process per GPU).
+
+    Built on the C ABI (``ttq_comm_create`` / ``ttq_comm_connect``): each rank allocates its buffer, the
+    64-byte CUDA IPC handles are all-gathered with ``torch.distributed`` and every rank maps its peers.
+    """
+
+    def __init__(self, ctx, n_cap: int, m_cap: int = 4, group=None):
+        import ctypes
+
+        import torch.distributed as dist
+
+        from ._lib import check
+
+        self.ctx = ctx
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.m_cap, self.n_cap = m_cap, n_cap
+        lib = ctx._lib
+        h = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        check(ctx.handle, lib.ttq_comm_create(ctx.handle, self.rank, self.world, n_cap, m_cap, ctypes.byref(h), handle))
+        self.handle = h
+        mine = torch.frombuffer(bytearray(handle.raw), dtype=torch.uint8).to(ctx.device)
+        gathered = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(gathered, mine, group=group)
+        blob = b"".join(bytes(t.cpu().numpy().tobytes()) for t in gathered)
+        check(ctx.handle, lib.ttq_comm_connect(h, blob))
+        dist.barrier(group=group)  # every buffer is zeroed and mapped before anyone writes into it
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.ctx._lib.ttq_comm_destroy(self.handle)
+            self.handle = None
