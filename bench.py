@@ -389,7 +389,7 @@ def ours_arm(args):
     roofline = {
         "bound": "hbm", "achieved": round(value / world, 2), "peak": peak, "unit": "GB/s",
         "frac": round(value / world / peak, 4), "traffic": None, "peak_source": peak_kind,
-        "kernel": "gemv_kernel<Q4_K, fused x-prep> (M<=2) / xprep + gemv_kernel (M>2)",
+        "kernel": "xprep_kernel + gemv_kernel<Q4_K> (activation planes bulk-copied from scratch)",
         "avg_launch_us": round(ms_step * 1e3 / gemv_launches, 3),
         "algorithmic_bytes_per_launch": step_bytes // gemv_launches,
         "frac_of_nominal_8TBs": round(value / world / 8000.0, 4),

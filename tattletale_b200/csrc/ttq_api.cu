@@ -21,6 +21,7 @@ struct ttq_ctx {
     void *xq_base;
     int sms;          // multiprocessor count of the device
     int *dev_status;  // device word the kernels OR failure bits into (bit 0: a bounded wait gave up)
+    int *host_status; // pinned host copy of it, filled by the host entry points
     unsigned long long *trace;  // device timeline buffer, allocated only when TTQ_TRACE=1 is set at init
     __half *xh;                 // fp16 activation scratch of the tcgen05 GEMM path
     int64_t xh_capacity;        // in halves
@@ -163,6 +164,7 @@ ttq_status ttq_init(int device, ttq_ctx **out) {
     cudaError_t e = cudaMalloc(&ctx->xq_base, planes_b + s16_b + s32_b + sx_b);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->dev_status, 1024);  // status word, then 768 zero bytes
     if (e == cudaSuccess) e = cudaMemset(ctx->dev_status, 0, 1024);
+    if (e == cudaSuccess) e = cudaMallocHost(&ctx->host_status, sizeof(int));
     const char *tr = getenv("TTQ_TRACE");
     if (e == cudaSuccess && tr && tr[0] == '1') {
         const size_t tb = (size_t)(8 + 8 * TTQ_TRACE_ENTRIES) * sizeof(unsigned long long);
@@ -200,6 +202,7 @@ ttq_status ttq_destroy(ttq_ctx *ctx) {
     if (ctx->host_stream) cudaStreamDestroy(ctx->host_stream);
     cudaFree(ctx->xq_base);
     cudaFree(ctx->dev_status);
+    cudaFreeHost(ctx->host_status);
     cudaFree(ctx->trace);
     cudaFree(ctx->xh);
     cudaFree(ctx->stage_x);
@@ -401,8 +404,15 @@ ttq_status ttq_linear_forward_host(ttq_ctx *ctx, const ttq_weight *w, const void
                                       ctx->stage_y, y_dt, ldy, st);
     if (s != TTQ_OK) return s;
     TTQ_CUDA(ctx, cudaMemcpyAsync(y_host, ctx->stage_y, yb, cudaMemcpyDeviceToHost, st));
+    // the status word rides along with the result: one synchronisation per call
+    TTQ_CUDA(ctx, cudaMemcpyAsync(ctx->host_status, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, st));
     TTQ_CUDA(ctx, cudaStreamSynchronize(st));
-    return ttq_device_status(ctx, st);
+    if (*ctx->host_status != 0) {
+        const int seen = *ctx->host_status;
+        cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), st);
+        return fail(ctx, TTQ_ERR_TIMEOUT, "a kernel gave up a bounded wait (status word 0x%x); results of that call are invalid", seen);
+    }
+    return TTQ_OK;
 }
 
 ttq_status ttq_device_status(ttq_ctx *ctx, void *stream) {
