@@ -42,6 +42,7 @@ extern "C" {
 typedef struct ttq_ctx ttq_ctx;
 typedef struct ttq_weight ttq_weight;
 typedef struct ttq_comm ttq_comm;
+typedef struct ttq_moe ttq_moe;
 
 typedef enum ttq_status {
     TTQ_OK = 0,
@@ -199,6 +200,27 @@ TTQ_API ttq_status ttq_linear_forward_static(const ttq_weight *w, const void *x_
  * Same dtype in and out (bf16, f16 or f32). */
 TTQ_API ttq_status ttq_silu_and_mul(ttq_ctx *ctx, const void *in_dev, ttq_dtype dt, int64_t M, int64_t H,
                             int64_t ld_in, void *out_dev, int64_t ld_out, void *stream);
+
+/* ---- mixture-of-experts layer (grouped quantized GEMM) -----------------------------------------
+ * No reference counterpart: the reference has dense gated MLPs only
+ * (workspace/transformers/src/layers/mlp.nim:31-60).  The layer applies that gated MLP per expert:
+ *     y[t] = sum_j w[t][j] * down_e( silu(gate_e x[t]) * up_e x[t] ),  e = topk_ids[t][j]
+ * with E experts of identical shape, gate|up fused as one [2I][H] matrix (gate rows first) and down
+ * [H][I], all Q4_K.  Router, softmax and top-k selection stay with the caller, who passes the chosen
+ * expert ids and their weights.  Routing tables, the routed activation images and the intermediates
+ * live in a workspace allocated by ttq_moe_create for up to max_tokens tokens; the forward call
+ * allocates nothing, copies nothing to the host and is asynchronous on `stream`.  The handle keeps
+ * the experts' device pointers: destroy it before the weights. */
+TTQ_API ttq_status ttq_moe_create(ttq_ctx *ctx, int32_t n_experts, const ttq_weight *const *gate_up,
+                                  const ttq_weight *const *down, int64_t max_tokens, int32_t top_k, ttq_moe **out);
+TTQ_API ttq_status ttq_moe_destroy(ttq_moe *moe);
+
+/* x: [T][ldx] bf16|f16 device rows of H values; topk_ids: [T][top_k] int32 (an id outside 0..E-1
+ * drops that choice, which is how an expert-parallel rank skips experts it does not hold);
+ * topk_weights: [T][top_k] f32; y: [T][ldy] of H values.  TTQ_ERR_LIMIT when T > max_tokens. */
+TTQ_API ttq_status ttq_moe_forward(ttq_ctx *ctx, ttq_moe *moe, const void *x_dev, ttq_dtype x_dt, int64_t T,
+                                   int64_t ldx, const int32_t *topk_ids_dev, const float *topk_weights_dev,
+                                   void *y_dev, ttq_dtype y_dt, int64_t ldy, void *stream);
 
 /* ---- optional device timeline (tracing) -------------------------------------------------------
  * The reference meters host procedures (workspace/probes/src/tracer.nim:72-133, enabled by a

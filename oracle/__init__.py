@@ -125,6 +125,34 @@ def silu_and_mul(x: np.ndarray) -> np.ndarray:
     return out
 
 
+def moe(fmt: int, gate_up_blocks, down_blocks, x: np.ndarray, x_dtype: int, topk_ids: np.ndarray,
+        topk_weights: np.ndarray, f16_intermediates: bool = True) -> np.ndarray:
+    """Mixture of gated-MLP experts: y[t] = sum_j w[t, j] * down_e(silu(gate_e x[t]) * up_e x[t]), e = ids[t, j].
+
+    The per-expert MLP is the dataflow of the reference's GatedMLP (workspace/transformers/src/layers/mlp.nim:56-60)
+    built from this module's own linear and silu_and_mul.  With ``f16_intermediates`` the two intermediate
+    tensors are rounded to fp16 where the device path stores them (after gate|up, after down); without, everything
+    between the projections stays fp32.  ids outside 0..E-1 contribute nothing.  Sum over j in fp64, ascending j.
+    """
+    t, k = topk_ids.shape
+    n_exp = len(gate_up_blocks)
+    hidden = down_blocks[0].shape[0]
+    y = np.zeros((t, hidden), dtype=np.float64)
+    for e in range(n_exp):
+        tok, j = np.nonzero(topk_ids == e)
+        if tok.size == 0:
+            continue
+        h = linear(fmt, gate_up_blocks[e], np.ascontiguousarray(x[tok]), x_dtype)
+        if f16_intermediates:
+            h = h.astype(np.float16).astype(np.float32)
+        a = silu_and_mul(h)
+        o = linear(fmt, down_blocks[e], to_f16_bits(a), F16)
+        if f16_intermediates:
+            o = o.astype(np.float16).astype(np.float32)
+        np.add.at(y, tok, o.astype(np.float64) * topk_weights[tok, j].astype(np.float64)[:, None])
+    return y.astype(np.float32)
+
+
 def to_bf16_bits(x: np.ndarray) -> np.ndarray:
     """fp32 -> bf16 bit patterns (round to nearest even)."""
     u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)

@@ -7,6 +7,8 @@
 #include <cstring>
 #include <new>
 
+#include <vector>
+
 #include "ttq_internal.cuh"
 
 using namespace ttq;
@@ -38,6 +40,19 @@ struct ttq_comm {
     void *local;    // this rank's buffer (flags + data), exported through CUDA IPC
     size_t bytes, flag_bytes;
     void *peer_map[TTQ_MAX_RANKS];  // IPC mappings of the peers' buffers (nullptr for the own rank)
+};
+
+// Mixture-of-experts layer: expert weight tables and the workspace of one call (sized at creation).
+struct ttq_moe {
+    ttq_ctx *ctx;
+    int E, top_k;
+    int64_t H, I, max_tokens;
+    int64_t NT1, SBp1, NT2, SBp2;  // gate|up: [2I][H], down: [H][I]
+    int64_t rows_cap;              // routed row capacity: max_tokens * top_k + E * 256
+    const uint8_t **d_gate_up, **d_down;  // device arrays of the experts' tiled matrices
+    MoeRouting route;
+    void *ws;                      // one allocation: routing tables, activation images, intermediates
+    __half *xh1, *h1, *xh2, *o2;
 };
 
 namespace {
@@ -549,6 +564,137 @@ ttq_status ttq_silu_and_mul(ttq_ctx *ctx, const void *in_dev, ttq_dtype dt, int6
     if (ld_in < 2 * H || ld_out < H) return fail(ctx, TTQ_ERR_SHAPE, "leading dimension smaller than the row length");
     cudaError_t e = launch_silu_and_mul(in_dev, dt, M, H, ld_in, out_dev, ld_out, (cudaStream_t)stream);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "silu_and_mul launch");
+    ctx->launches++;
+    return TTQ_OK;
+}
+
+ttq_status ttq_moe_create(ttq_ctx *ctx, int32_t n_experts, const ttq_weight *const *gate_up, const ttq_weight *const *down,
+                          int64_t max_tokens, int32_t top_k, ttq_moe **out) {
+    if (!ctx) return TTQ_ERR_INVALID_ARG;
+    if (!out) return fail(ctx, TTQ_ERR_INVALID_ARG, "out is NULL");
+    *out = nullptr;
+    if (!gate_up || !down) return fail(ctx, TTQ_ERR_INVALID_ARG, "expert weight table is NULL");
+    if (n_experts <= 0 || n_experts > 4096) return fail(ctx, TTQ_ERR_SHAPE, "n_experts=%d out of range 1..4096", n_experts);
+    if (top_k <= 0 || top_k > n_experts) return fail(ctx, TTQ_ERR_SHAPE, "top_k=%d out of range 1..%d", top_k, n_experts);
+    if (max_tokens <= 0) return fail(ctx, TTQ_ERR_SHAPE, "max_tokens must be positive");
+    for (int e = 0; e < n_experts; e++) {
+        const ttq_weight *a = gate_up[e], *b = down[e];
+        if (!a || !b) return fail(ctx, TTQ_ERR_INVALID_ARG, "expert %d: weight is NULL", e);
+        if (a->ctx != ctx || b->ctx != ctx) return fail(ctx, TTQ_ERR_INVALID_ARG, "expert %d: weight belongs to another context", e);
+        if (a->fmt != TTQ_FMT_Q4_K || b->fmt != TTQ_FMT_Q4_K)
+            return fail(ctx, TTQ_ERR_UNSUPPORTED, "expert %d: the grouped path takes Q4_K weights", e);
+        if (a->N != gate_up[0]->N || a->K != gate_up[0]->K || b->N != down[0]->N || b->K != down[0]->K)
+            return fail(ctx, TTQ_ERR_SHAPE, "expert %d: shape differs from expert 0", e);
+    }
+    const int64_t H = gate_up[0]->K, I = down[0]->K;
+    if (gate_up[0]->N != 2 * I || down[0]->N != H)
+        return fail(ctx, TTQ_ERR_SHAPE, "gate|up must be [2I][H] and down [H][I] (got [%lld][%lld] and [%lld][%lld])",
+                    (long long)gate_up[0]->N, (long long)H, (long long)down[0]->N, (long long)I);
+    if (H % 8 || I % 8) return fail(ctx, TTQ_ERR_SHAPE, "H and I must be multiples of 8");
+    if (max_tokens * top_k + (int64_t)n_experts * 256 > (1ll << 30)) return fail(ctx, TTQ_ERR_LIMIT, "routed row capacity too large");
+    ttq_moe *m = new (std::nothrow) ttq_moe();
+    if (!m) return fail(ctx, TTQ_ERR_OOM, "host allocation failed");
+    m->ctx = ctx; m->E = n_experts; m->top_k = top_k; m->H = H; m->I = I; m->max_tokens = max_tokens;
+    m->NT1 = gate_up[0]->NT; m->SBp1 = gate_up[0]->SBp; m->NT2 = down[0]->NT; m->SBp2 = down[0]->SBp;
+    m->rows_cap = ((max_tokens * top_k + (int64_t)n_experts * 256 + 255) / 256) * 256;
+    const int64_t pairs = max_tokens * top_k;
+    auto up256 = [](size_t b) { return (b + 255) & ~(size_t)255; };
+    const size_t b_tab = up256(sizeof(void *) * (size_t)n_experts);
+    const size_t b_e = up256(sizeof(int) * (size_t)n_experts);
+    const size_t b_mt = up256(sizeof(int) * (size_t)(m->rows_cap / 64));
+    const size_t b_rows = up256(sizeof(int) * (size_t)m->rows_cap);
+    const size_t b_pairs = up256(sizeof(int) * (size_t)pairs);
+    const size_t b_xh1 = up256(sizeof(__half) * (size_t)m->rows_cap * (size_t)(m->SBp1 * TILE_K));
+    const size_t b_o2 = up256(sizeof(__half) * (size_t)m->rows_cap * (size_t)H);
+    const size_t b_a = b_xh1 > b_o2 ? b_xh1 : b_o2;  // the routed input images and the routed outputs are never live together
+    const size_t b_h1 = up256(sizeof(__half) * (size_t)m->rows_cap * (size_t)(2 * I));
+    const size_t b_xh2 = up256(sizeof(__half) * (size_t)m->rows_cap * (size_t)(m->SBp2 * TILE_K));
+    const size_t total = 2 * b_tab + 3 * b_e + 256 + b_mt + b_rows + b_pairs + b_a + b_h1 + b_xh2;
+    cudaError_t e = cudaMalloc(&m->ws, total);
+    if (e != cudaSuccess) {
+        delete m;
+        return cuda_fail(ctx, e, "cudaMalloc(mixture-of-experts workspace)");
+    }
+    uint8_t *q = reinterpret_cast<uint8_t *>(m->ws);
+    m->d_gate_up = reinterpret_cast<const uint8_t **>(q); q += b_tab;
+    m->d_down = reinterpret_cast<const uint8_t **>(q); q += b_tab;
+    m->route.counts = reinterpret_cast<int *>(q); q += b_e;
+    m->route.row_start = reinterpret_cast<int *>(q); q += b_e;
+    m->route.cursor = reinterpret_cast<int *>(q); q += b_e;
+    m->route.n_mt = reinterpret_cast<int *>(q); q += 256;
+    m->route.mt_group = reinterpret_cast<int *>(q); q += b_mt;
+    m->route.row_src = reinterpret_cast<int *>(q); q += b_rows;
+    m->route.slot_of = reinterpret_cast<int *>(q); q += b_pairs;
+    m->xh1 = reinterpret_cast<__half *>(q); m->o2 = m->xh1; q += b_a;
+    m->h1 = reinterpret_cast<__half *>(q); q += b_h1;
+    m->xh2 = reinterpret_cast<__half *>(q);
+    std::vector<const uint8_t *> tab((size_t)2 * n_experts);
+    for (int x = 0; x < n_experts; x++) {
+        tab[x] = gate_up[x]->tiles;
+        tab[(size_t)n_experts + x] = down[x]->tiles;
+    }
+    e = cudaMemcpy(m->d_gate_up, tab.data(), sizeof(void *) * (size_t)n_experts, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(m->d_down, tab.data() + n_experts, sizeof(void *) * (size_t)n_experts, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        cudaFree(m->ws);
+        delete m;
+        return cuda_fail(ctx, e, "upload of the expert tables");
+    }
+    *out = m;
+    return TTQ_OK;
+}
+
+ttq_status ttq_moe_destroy(ttq_moe *m) {
+    if (!m) return TTQ_OK;
+    cudaFree(m->ws);
+    delete m;
+    return TTQ_OK;
+}
+
+ttq_status ttq_moe_forward(ttq_ctx *ctx, ttq_moe *m, const void *x_dev, ttq_dtype x_dt, int64_t T, int64_t ldx,
+                           const int32_t *topk_ids_dev, const float *topk_weights_dev, void *y_dev, ttq_dtype y_dt, int64_t ldy,
+                           void *stream) {
+    if (!ctx) return TTQ_ERR_INVALID_ARG;
+    if (!m) return fail(ctx, TTQ_ERR_INVALID_ARG, "layer handle is NULL");
+    if (m->ctx != ctx) return fail(ctx, TTQ_ERR_INVALID_ARG, "layer belongs to another context");
+    if (T < 0) return fail(ctx, TTQ_ERR_SHAPE, "T=%lld is negative", (long long)T);
+    if (T == 0) return TTQ_OK;
+    if (T > m->max_tokens) return fail(ctx, TTQ_ERR_LIMIT, "T=%lld exceeds max_tokens=%lld of the layer", (long long)T, (long long)m->max_tokens);
+    if (!x_dev || !y_dev || !topk_ids_dev || !topk_weights_dev) return fail(ctx, TTQ_ERR_INVALID_ARG, "a device pointer is NULL");
+    if (x_dt != TTQ_DT_BF16 && x_dt != TTQ_DT_F16) return fail(ctx, TTQ_ERR_INVALID_ARG, "x dtype must be bf16 or f16");
+    if (!valid_dt(y_dt)) return fail(ctx, TTQ_ERR_INVALID_ARG, "unknown y dtype %d", (int)y_dt);
+    if (ldx < m->H || ldy < m->H) return fail(ctx, TTQ_ERR_SHAPE, "leading dimension smaller than the hidden size %lld", (long long)m->H);
+    cudaStream_t st = (cudaStream_t)stream;
+    // row-tile height from the mean number of rows per expert; capacity of this call in rows
+    const int64_t pairs = T * m->top_k, mean = pairs / m->E;
+    const int BM = mean <= 64 ? 64 : (mean <= 128 ? 128 : 256);
+    int64_t Mp = ((pairs + (int64_t)m->E * BM + BM - 1) / BM) * BM;
+    if (Mp > m->rows_cap) Mp = m->rows_cap / BM * BM;
+    int n = 0;
+    cudaError_t e = launch_moe_route(m->route, topk_ids_dev, T, m->top_k, m->E, BM, Mp, st, &n);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "routing launch");
+    ctx->launches += n;
+    GroupedArgs g;
+    g.group_tiles = m->d_gate_up;
+    g.N = 2 * m->I; g.K = m->H; g.NT = m->NT1; g.SBp = m->SBp1;
+    g.x = x_dev; g.x_dt = x_dt; g.x_rows = T; g.ldx = ldx;
+    g.row_src = m->route.row_src; g.gated = false;
+    g.Mp = Mp; g.BM = BM;
+    g.mt_group = m->route.mt_group; g.n_mt = m->route.n_mt;
+    g.y = m->h1; g.y_dt = TTQ_DT_F16; g.ldy = 2 * m->I;
+    e = launch_gemm_grouped(g, m->xh1, ctx->sms, ctx->dev_status, st, &n);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "grouped gate|up launch");
+    ctx->launches += n;
+    g.group_tiles = m->d_down;
+    g.N = m->H; g.K = m->I; g.NT = m->NT2; g.SBp = m->SBp2;
+    g.x = m->h1; g.x_dt = TTQ_DT_F16; g.x_rows = Mp; g.ldx = 2 * m->I;
+    g.row_src = nullptr; g.gated = true;
+    g.y = m->o2; g.y_dt = TTQ_DT_F16; g.ldy = m->H;
+    e = launch_gemm_grouped(g, m->xh2, ctx->sms, ctx->dev_status, st, &n);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "grouped down launch");
+    ctx->launches += n;
+    e = launch_moe_combine(m->route, m->o2, TTQ_DT_F16, m->H, topk_weights_dev, T, m->top_k, m->H, y_dev, y_dt, ldy, st);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "combine launch");
     ctx->launches++;
     return TTQ_OK;
 }

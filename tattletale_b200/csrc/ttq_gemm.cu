@@ -123,22 +123,60 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 // j ^ (m & 7) and holds, at pos = 4*half + p, the activation of K index
 // sb*256 + 32*j + 8*s + 4*half + perm[p], perm = {0, 2, 1, 3} -- the order in which the nibble
 // expansion of the dequant warps emits a register's four weights.
+//
+// Grouped (mixture-of-experts) use: `row_src` (optional) names the source row of every image row
+// (-1 = a padding row of zeros), `rows_used` (optional, device scalar in units of `rows_unit` rows)
+// bounds the rows worth converting, and GATED = true reads a row of 2K values and emits
+// silu(x[k]) * x[K + k] (the gated-MLP activation, fused into the conversion).
+template <bool GATED>
 __global__ void __launch_bounds__(256) xh_prep_kernel(const void *__restrict__ x, int x_dt, int64_t M, int64_t Mp, int64_t K,
-                                                      int64_t Kp, int64_t ldx, __half *__restrict__ xh) {
+                                                      int64_t Kp, int64_t ldx, __half *__restrict__ xh,
+                                                      const int *__restrict__ row_src, const int *__restrict__ rows_used,
+                                                      int rows_unit) {
     const int64_t chunks_per_row = Kp / 8;
     const int64_t total = Mp * chunks_per_row;
+    const int64_t m_used = rows_used != nullptr ? (int64_t)(*rows_used) * rows_unit : Mp;
     for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < total; c += (int64_t)gridDim.x * blockDim.x) {
         // consecutive threads: consecutive j, then rows, then stages (coalesced 16-byte stores per atom)
         const int j = (int)(c & 7);
-        const int64_t m = (c >> 3) % Mp, it = (c >> 3) / Mp;
+        const int64_t mi = (c >> 3) % Mp, it = (c >> 3) / Mp;
+        if (mi >= m_used) continue;
         const int64_t sb = it >> 2;
         const int s = (int)(it & 3);
         const int64_t k0 = sb * 256 + 32 * j + 8 * s;
+        // source row: the image row itself, or the row the routing table names (negative = padding)
+        int64_t m = mi;
+        if (row_src != nullptr) {
+            const int r = row_src[mi];
+            m = r < 0 ? M : (int64_t)r;
+        }
         // the 8 source values are contiguous in K: one 16-byte load when the row is aligned
         __half src[8];
         const bool vec = x_dt != TTQ_DT_F32 && m < M && k0 + 8 <= K &&
-                         ((reinterpret_cast<uintptr_t>(x) + (size_t)(m * ldx + k0) * 2) & 15) == 0;
-        if (vec) {
+                         ((reinterpret_cast<uintptr_t>(x) + (size_t)(m * ldx + k0) * 2) & 15) == 0 && (!GATED || ((K * 2) & 15) == 0);
+        if (GATED) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) src[i] = __float2half_rn(0.f);
+            if (vec && x_dt == TTQ_DT_F16) {
+                const __half *row = reinterpret_cast<const __half *>(x) + m * ldx + k0;
+                const uint4 ga = *reinterpret_cast<const uint4 *>(row), ua = *reinterpret_cast<const uint4 *>(row + K);
+                const __half2 *g2 = reinterpret_cast<const __half2 *>(&ga), *u2 = reinterpret_cast<const __half2 *>(&ua);
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const float2 gv = __half22float2(g2[q]), uv = __half22float2(u2[q]);
+                    src[2 * q] = __float2half_rn(gv.x / (1.f + expf(-gv.x)) * uv.x);
+                    src[2 * q + 1] = __float2half_rn(gv.y / (1.f + expf(-gv.y)) * uv.y);
+                }
+            } else if (m < M) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    if (k0 + i < K) {
+                        const float gv = load_as_float(x, x_dt, m * ldx + k0 + i), uv = load_as_float(x, x_dt, m * ldx + K + k0 + i);
+                        src[i] = __float2half_rn(gv / (1.f + expf(-gv)) * uv);
+                    }
+                }
+            }
+        } else if (vec) {
             const uint4 raw = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(x) + m * ldx + k0);
             if (x_dt == TTQ_DT_F16) {
                 *reinterpret_cast<uint4 *>(src) = raw;
@@ -161,7 +199,7 @@ __global__ void __launch_bounds__(256) xh_prep_kernel(const void *__restrict__ x
         __half out[8];
 #pragma unroll
         for (int p = 0; p < 8; p++) out[p] = src[(p & 4) + ((p & 1) << 1) + ((p & 2) >> 1)];  // swap the middle two of each four
-        const int64_t dst = ((it * (Mp >> 3) + (m >> 3)) << 10) + ((m & 7) << 7) + ((int64_t)(j ^ (int)(m & 7)) << 4);
+        const int64_t dst = ((it * (Mp >> 3) + (mi >> 3)) << 10) + ((mi & 7) << 7) + ((int64_t)(j ^ (int)(mi & 7)) << 4);
         *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(xh) + dst) = *reinterpret_cast<const uint4 *>(out);
     }
 }
@@ -180,6 +218,11 @@ struct GemmParams {
     unsigned long long *trace;  // optional: [0] entry counter, entries of 8 words from [8] (see ttq.h)
     int splits;   // K is cut in `splits` equal runs of super-blocks, one work unit each (1 = no split)
     float *ws;    // splits > 1: fp32 partial outputs [split][Mp][N], summed by splitk_reduce_kernel
+    // grouped (mixture-of-experts) mode, group_tiles != nullptr: every BM-row tile of x belongs to one
+    // weight matrix (all of one shape); the number of row tiles in use is a device scalar
+    const uint8_t *const *group_tiles;  // per group: Q4_K tiled layout
+    const int *mt_group;                // group of row tile mt
+    const int *n_mt;                    // row tiles in use (<= Mp / BM)
 };
 
 template <int BM, int NSUB>
@@ -216,7 +259,13 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
     const int splits = p.splits, sb_per_unit = (int)p.SBp / splits;
     const int iters = sb_per_unit * 4;  // stages per work unit (tile x K split)
     constexpr int TILE_N = GEMM_BN * NSUB;
-    const int64_t n_tiles = (p.N + TILE_N - 1) / TILE_N, m_tiles = p.Mp / BM, total_tiles = n_tiles * m_tiles * splits;
+    const bool grouped = p.group_tiles != nullptr;
+    int64_t m_tiles = p.Mp / BM;
+    if (grouped) {
+        const int64_t used = *p.n_mt;
+        m_tiles = used < m_tiles ? used : m_tiles;
+    }
+    const int64_t n_tiles = (p.N + TILE_N - 1) / TILE_N, total_tiles = n_tiles * m_tiles * splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -306,7 +355,9 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
         auto tile_ptr = [&](int64_t tile, int sub, bool &have) {
             const int64_t nt = (((tile / splits) / m_tiles) * NSUB + my_sub + sub) * (GEMM_BN / TILE_ROWS) + dw;
             have = tile < total_tiles && nt < p.NT;
-            return p.tiles + ((have ? nt : 0) * p.SBp + (tile % splits) * sb_per_unit) * 2304;
+            const uint8_t *wbase = p.tiles;
+            if (grouped && have) wbase = p.group_tiles[p.mt_group[(tile / splits) % m_tiles]];
+            return wbase + ((have ? nt : 0) * p.SBp + (tile % splits) * sb_per_unit) * 2304;
         };
         auto chunk_at = [&](const uint8_t *t0, bool ok, int it) {
             uint4 v = make_uint4(0, 0, 0, 0);
@@ -557,12 +608,13 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
         const uint8_t *xs = reinterpret_cast<const uint8_t *>(a.x) + (size_t)m0 * a.ldx * esz_x;
         const int64_t chunks = Mp * (Kp / 8);
         const unsigned grid = (unsigned)((chunks + 255) / 256 < 148 * 16 ? (chunks + 255) / 256 : 148 * 16);
-        xh_prep_kernel<<<grid, 256, 0, st>>>(xs, a.x_dt, Ms, Mp, a.K, Kp, a.ldx, xh);
+        xh_prep_kernel<false><<<grid, 256, 0, st>>>(xs, a.x_dt, Ms, Mp, a.K, Kp, a.ldx, xh, nullptr, nullptr, 0);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
         ++*launches;
         GemmParams p;
         p.tiles = a.tiles;
+        p.group_tiles = nullptr; p.mt_group = nullptr; p.n_mt = nullptr;
         p.N = a.N; p.NT = a.NT; p.SBp = a.SBp;
         p.xh = xh;
         p.M = Ms; p.Mp = Mp; p.Kp = Kp;
@@ -607,6 +659,51 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
             ++*launches;
         }
     }
+    return cudaSuccess;
+}
+
+// Grouped GEMM: row tile mt of the (routed, padded) activation rows multiplies weight matrix
+// mt_group[mt]; the tile count is read on the device, so the grid is sized for the capacity.
+cudaError_t launch_gemm_grouped(const GroupedArgs &g, __half *xh, int sms, int *status, cudaStream_t st, int *launches) {
+    *launches = 0;
+    const int64_t Kp = g.SBp * TILE_K;
+    if (g.BM != 64 && g.BM != 128 && g.BM != 256) return cudaErrorInvalidValue;
+    if (g.Mp % g.BM) return cudaErrorInvalidValue;
+    const int64_t chunks = g.Mp * (Kp / 8);
+    const unsigned grid = (unsigned)((chunks + 255) / 256 < 148 * 16 ? (chunks + 255) / 256 : 148 * 16);
+    if (g.gated)
+        xh_prep_kernel<true><<<grid, 256, 0, st>>>(g.x, g.x_dt, g.x_rows, g.Mp, g.K, Kp, g.ldx, xh, g.row_src, g.n_mt, g.BM);
+    else
+        xh_prep_kernel<false><<<grid, 256, 0, st>>>(g.x, g.x_dt, g.x_rows, g.Mp, g.K, Kp, g.ldx, xh, g.row_src, g.n_mt, g.BM);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    ++*launches;
+    GemmParams p;
+    p.tiles = nullptr;
+    p.group_tiles = g.group_tiles; p.mt_group = g.mt_group; p.n_mt = g.n_mt;
+    p.N = g.N; p.NT = g.NT; p.SBp = g.SBp;
+    p.xh = xh;
+    p.M = g.Mp; p.Mp = g.Mp; p.Kp = Kp;
+    p.bias = nullptr; p.bias_dt = TTQ_DT_F32;
+    p.y = g.y; p.y_dt = g.y_dt; p.ldy = g.ldy;
+    p.status = status;
+    p.trace = nullptr;
+    p.splits = 1;
+    p.ws = nullptr;
+    // two sub-tiles per CTA when the expected tile count still covers the SMs
+    const int64_t mt_cap = g.Mp / g.BM;
+    const int nsub = (g.N >= 256 && ((g.N + 255) / 256) * mt_cap >= 2 * (int64_t)sms) ? 2 : 1;
+    if (nsub == 2) {
+        if (g.BM == 64) e = launch_cfg<64, 2>(p, sms, st);
+        else if (g.BM == 128) e = launch_cfg<128, 2>(p, sms, st);
+        else e = launch_cfg<256, 2>(p, sms, st);
+    } else {
+        if (g.BM == 64) e = launch_cfg<64, 1>(p, sms, st);
+        else if (g.BM == 128) e = launch_cfg<128, 1>(p, sms, st);
+        else e = launch_cfg<256, 1>(p, sms, st);
+    }
+    if (e != cudaSuccess) return e;
+    ++*launches;
     return cudaSuccess;
 }
 

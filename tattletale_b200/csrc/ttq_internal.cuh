@@ -115,6 +115,38 @@ struct LinearArgs {
     int64_t ldy;
 };
 
+// Grouped (mixture-of-experts) GEMM on the tensor-core path: activation rows are routed into BM-row
+// tiles, each owned by one weight matrix; all matrices share N x K.
+struct GroupedArgs {
+    const uint8_t *const *group_tiles;  // device array: Q4_K tiled layout of every group
+    int64_t N, K, NT, SBp;
+    const void *x;                      // source rows
+    int x_dt;
+    int64_t x_rows, ldx;
+    const int *row_src;                 // device [Mp]: source row of each routed row (-1 = padding) or nullptr (identity)
+    bool gated;                         // source rows hold 2K values, the operand is silu(x[k]) * x[K + k]
+    int64_t Mp;                         // capacity in routed rows, a multiple of BM
+    int BM;                             // row-tile height: 64, 128 or 256
+    const int *mt_group, *n_mt;         // device: group of each row tile, number of row tiles in use
+    void *y;                            // [Mp][ldy] routed output rows
+    int y_dt;
+    int64_t ldy;
+};
+cudaError_t launch_gemm_grouped(const GroupedArgs &g, __half *xh, int sms, int *status, cudaStream_t st, int *launches);
+
+// Routing and combination of a mixture-of-experts layer (ttq_moe.cu).
+struct MoeRouting {
+    int *counts, *row_start, *cursor;  // [E]
+    int *n_mt;                         // [1]
+    int *mt_group;                     // [Mp / 64]
+    int *row_src;                      // [Mp]
+    int *slot_of;                      // [T * top_k]
+};
+cudaError_t launch_moe_route(const MoeRouting &r, const int *topk_ids, int64_t T, int top_k, int E, int BM, int64_t Mp,
+                             cudaStream_t st, int *launches);
+cudaError_t launch_moe_combine(const MoeRouting &r, const void *o, int o_dt, int64_t ldo, const float *topk_w, int64_t T,
+                               int top_k, int64_t H, void *y, int y_dt, int64_t ldy, cudaStream_t st);
+
 // launchers (defined in the .cu files); each returns the number of kernels it launched or -1
 cudaError_t launch_repack(int fmt, const uint8_t *canon, uint8_t *tiled, int64_t N, int64_t K, int64_t NT,
                           int64_t SBp, cudaStream_t st);

@@ -237,3 +237,68 @@ class GatedMLP:
         return self.down_proj.forward(silu_and_mul(self.ctx, gate_up))
 
     __call__ = forward
+
+
+class MoELayer:
+    """Mixture of gated-MLP experts on the grouped Q4_K GEMM (``ttq_moe_*``).
+
+    ``gate_up_blocks[e]`` is expert e's fused gate|up block matrix ``[2 * intermediate, bytes_per_row]``
+    (gate rows first, as GatedMLP fuses them), ``down_blocks[e]`` its ``[hidden, bytes_per_row]`` down
+    projection.  ``forward(x, topk_ids, topk_weights)`` computes, for every token t,
+    ``sum_j topk_weights[t, j] * mlp_{topk_ids[t, j]}(x[t])``; router and top-k selection are the caller's.
+    An id outside ``0..E-1`` drops that choice.
+    """
+
+    def __init__(self, ctx: Context, fmt: int, gate_up_blocks, down_blocks, hidden_size: int, intermediate_size: int,
+                 top_k: int, max_tokens: int):
+        if len(gate_up_blocks) != len(down_blocks) or not gate_up_blocks:
+            raise TtqError(2, "gate_up_blocks and down_blocks must be equally long, non-empty lists")
+        self.ctx, self.hidden, self.inter, self.top_k, self.max_tokens = ctx, hidden_size, intermediate_size, top_k, max_tokens
+        self.gate_up = [QuantLinear(ctx, fmt, b, hidden_size) for b in gate_up_blocks]
+        self.down = [QuantLinear(ctx, fmt, b, intermediate_size) for b in down_blocks]
+        n = len(self.gate_up)
+        self.n_experts = n
+        arr_t = ctypes.c_void_p * n
+        gu = arr_t(*[w.handle.value for w in self.gate_up])
+        dn = arr_t(*[w.handle.value for w in self.down])
+        h = ctypes.c_void_p()
+        check(ctx.handle, ctx._lib.ttq_moe_create(ctx.handle, n, gu, dn, max_tokens, top_k, ctypes.byref(h)))
+        self.handle = h
+
+    @property
+    def weight_bytes(self) -> int:
+        return sum(w.weight_bytes for w in self.gate_up) + sum(w.weight_bytes for w in self.down)
+
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if not x.is_cuda:
+            raise TtqError(1, "x must live on the context's CUDA device")
+        x2 = x.reshape(-1, self.hidden)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        t = x2.shape[0]
+        ids = topk_ids.reshape(t, self.top_k).to(torch.int32).contiguous()
+        wts = topk_weights.reshape(t, self.top_k).to(torch.float32).contiguous()
+        if out is None:
+            out = torch.empty((t, self.hidden), dtype=x.dtype, device=x.device)
+        st = self.ctx._lib.ttq_moe_forward(
+            self.ctx.handle, self.handle, x2.data_ptr(), _dt(x2.dtype), t, x2.stride(0) if t > 1 else self.hidden,
+            ids.data_ptr(), wts.data_ptr(), out.data_ptr(), _dt(out.dtype), out.stride(0) if t > 1 else self.hidden,
+            _stream_ptr(x.device))
+        check(self.ctx.handle, st)
+        return out.reshape(x.shape)
+
+    __call__ = forward
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self.ctx._lib.ttq_moe_destroy(self.handle)
+            self.handle = None
+            for w in self.gate_up + self.down:
+                w.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
