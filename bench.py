@@ -519,6 +519,105 @@ def decode_arm(args):
     _finish_distributed(dist, world)
 
 
+def moe_arm(args):
+    """Mixture-of-experts layer of BASELINE.json configs[4]: hidden 2048, 128 experts of FFN 768 (gated), top-8
+    routing from N(0,1) router logits, 4096 tokens, Q4_K experts ~N(0, 0.02).  N > 1: expert parallel (each rank
+    holds E/N experts and T/N tokens; NCCL all-to-all dispatch and combine around the local grouped GEMM)."""
+    import torch.distributed as dist
+
+    import tattletale_b200 as ttq
+    from tattletale_b200 import quantize as Q
+    from tattletale_b200 import tp
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    H, I, E, K, T = 2048, 768, 128, 8, args.tokens
+    assert E % world == 0 and T % world == 0
+    epr, tl = E // world, T // world
+    ctx = ttq.Context(local_rank)
+    gu, dn = [], []
+    for e in range(rank * epr, (rank + 1) * epr):
+        g = torch.Generator(device=dev).manual_seed(5000 + e)
+        gu.append(Q.quantize(ttq.FMT_Q4_K, torch.randn(2 * I, H, generator=g, device=dev) * 0.02))
+        dn.append(Q.quantize(ttq.FMT_Q4_K, torch.randn(H, I, generator=g, device=dev) * 0.02))
+    g = torch.Generator(device=dev).manual_seed(6000 + rank)
+    x = torch.randn(tl, H, generator=g, device=dev).to(torch.bfloat16)
+    logits = torch.randn(tl, E, generator=g, device=dev)
+    wts, ids = torch.softmax(logits, dim=-1).topk(K, dim=-1)
+    wts = (wts / wts.sum(dim=-1, keepdim=True)).float().contiguous()
+    ids = ids.to(torch.int32).contiguous()
+    if world == 1:
+        layer = ttq.MoELayer(ctx, ttq.FMT_Q4_K, gu, dn, H, I, top_k=K, max_tokens=T)
+        y = torch.empty_like(x)
+        step = lambda: layer.forward(x, ids, wts, out=y)
+    else:
+        local = ttq.MoELayer(ctx, ttq.FMT_Q4_K, gu, dn, H, I, top_k=1, max_tokens=3 * tl * K)
+        ep = tp.ExpertParallelMoE.from_layer(local)
+        step = lambda: ep.forward(x, ids, wts)
+    del gu, dn
+    step()
+    torch.cuda.synchronize()
+    c0 = ctx.launch_count
+    step()
+    torch.cuda.synchronize()
+    launches_per_step = ctx.launch_count - c0
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    steps = min(args.steps, 200)
+    sampler = ClockSampler(visible_physical_index(local_rank))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.start()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms_total = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / steps
+    ctx.check_device_status()
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak = float(peaks.get("bf16_tflops", 1590.0))
+        flops = 2.0 * T * K * (2 * I * H + H * I)
+        tf = flops / (ms_step * 1e-3) / 1e12
+        w_bytes = E * ((2 * I) * (H // 256) + H * (I // 256)) * Q4K_BYTES_PER_256
+        line = {
+            "metric": "MoE expert-GEMM TFLOP/s", "value": round(tf, 1), "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16", "arithmetic": "Q4_K expanded to fp16 in shared memory, tcgen05 f16 MMA, fp32 accumulation",
+            "data": "synthetic",
+            "config": {"workload": f"Qwen3-30B-A3B-like MoE layer: hidden {H}, {E} experts of FFN {I} (gated), top-{K}, {T} tokens, Q4_K",
+                       "tokens": T, "parallelism": "single GPU" if world == 1 else f"ep{world} (NCCL all-to-all dispatch / combine)",
+                       "l2": f"{w_bytes / 1e6:.0f} MB of expert weights + {T * K * (H + 2 * I + I + H) * 2 / 1e6:.0f} MB of routed "
+                             "intermediates per step, larger than L2",
+                       "includes": "routing, activation conversion, both grouped GEMMs, silu*up, weighted combine"},
+            "tokens_per_s": round(T / (ms_step * 1e-3), 1),
+            "roofline": {"bound": "tensor", "achieved": round(tf / world, 1), "peak": peak, "unit": "TFLOP/s",
+                         "frac": round(tf / world / peak, 4), "traffic": None,
+                         "peak_source": "measured (MEASURED_PEAKS.json bf16_tflops)" if "bf16_tflops" in peaks else "fallback"},
+            "gpu_launches": int(launches_per_step * steps), "launches_per_step": int(launches_per_step), "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    _finish_distributed(dist, world)
+
+
 def _finish_distributed(dist, world):
     """Leave a multi-rank run without tearing NCCL down: a captured graph still references the communicator,
     and destroying the process group under it has been seen to block; the process simply exits."""
@@ -537,8 +636,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=1, help="decode batch (rows of x)")
-    ap.add_argument("--workload", default="linears", choices=["linears", "decode"],
-                    help="linears: the headline Q4_K GEMV pass (default); decode: full decoder stack, tokens/s")
+    ap.add_argument("--workload", default="linears", choices=["linears", "decode", "moe"],
+                    help="linears: the headline Q4_K GEMV pass (default); decode: full decoder stack, tokens/s; "
+                         "moe: one mixture-of-experts layer, TFLOP/s")
+    ap.add_argument("--tokens", type=int, default=4096, help="moe workload: tokens per step (all ranks together)")
     ap.add_argument("--batch", type=int, default=1, help="decode workload: sequences decoded together")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -553,6 +654,8 @@ def main():
         reference_arm(args)
     elif args.workload == "decode":
         decode_arm(args)
+    elif args.workload == "moe":
+        moe_arm(args)
     else:
         ours_arm(args)
 

@@ -667,7 +667,12 @@ ttq_status ttq_moe_forward(ttq_ctx *ctx, ttq_moe *m, const void *x_dev, ttq_dtyp
     cudaStream_t st = (cudaStream_t)stream;
     // row-tile height from the mean number of rows per expert; capacity of this call in rows
     const int64_t pairs = T * m->top_k, mean = pairs / m->E;
-    const int BM = mean <= 64 ? 64 : (mean <= 128 ? 128 : 256);
+    int BM = mean <= 64 ? 64 : (mean <= 128 ? 128 : 256);
+    static const int force_bm = []() {
+        const char *v = getenv("TTQ_MOE_BM");
+        return v ? atoi(v) : 0;
+    }();
+    if (force_bm == 64 || force_bm == 128 || force_bm == 256) BM = force_bm;
     int64_t Mp = ((pairs + (int64_t)m->E * BM + BM - 1) / BM) * BM;
     if (Mp > m->rows_cap) Mp = m->rows_cap / BM * BM;
     int n = 0;

@@ -66,6 +66,14 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     atomicOr(status, 2);
     return false;
 }
+// Warp-wide form: lane 0 polls, the others park at the warp barrier (fewer shared-memory polls next to the
+// tensor core's operand reads).
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int *status, int lane) {
+    bool ok = true;
+    if (lane == 0) ok = mbar_wait_bounded(bar, parity, status);
+    __syncwarp();
+    return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+}
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
@@ -90,8 +98,8 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);         // stride byte offset, version = 1, SWIZZLE_128B
     return ((uint64_t)hi << 32) | lo;
 }
-// Instruction descriptor, kind::f16: D = f32, A = B = f16, both K-major, M = 128, N = bm.
-__host__ __device__ constexpr uint32_t idesc_f16(int bm) { return (1u << 4) | ((uint32_t)(bm >> 3) << 17) | ((128u >> 4) << 24); }
+// Instruction descriptor, kind::f16: D = f32, A = B = f16, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t idesc_f16(int n) { return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24); }
 
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -231,8 +239,12 @@ struct GemmCfg {
     static constexpr int B_BYTES = BM * 128;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = STAGE_BYTES > 48 * 1024 ? 3 : 4;
-    static constexpr int NACC = (2 * NSUB * BM <= 512) ? 2 : 1;  // accumulator sets in tensor memory
-    static constexpr int TMEM_COLS = NACC * NSUB * BM;            // 128 .. 512, a power of two
+    // The MMA's M side is a run of 128 activation rows (tensor-memory lanes), its N side the CTA's 128 * NSUB
+    // weight rows (columns): an accumulator set is MH row blocks of 128 * NSUB columns.
+    static constexpr int MH = BM > 128 ? BM / 128 : 1;
+    static constexpr int ACC_COLS = MH * 128 * NSUB;
+    static constexpr int NACC = (2 * ACC_COLS <= 512) ? 2 : 1;   // accumulator sets in tensor memory
+    static constexpr int TMEM_COLS = NACC * ACC_COLS;             // 128 .. 512, a power of two
     static constexpr int DEQ_WARPS = gemm_deq_warps(NSUB), WARPS = gemm_warps(NSUB), THREADS = WARPS * 32;
     static constexpr int HDR_BYTES = DEQ_WARPS * 1280;  // per dequant warp: 16 rows x 80 bytes
     static constexpr int BAR_BYTES = 128;
@@ -302,26 +314,69 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
             const int64_t otile = tile / splits, split = tile % splits;
             const int64_t n_tile = otile / m_tiles, m_tile = otile % m_tiles;
             const int buf = tcount % C::NACC, use = tcount / C::NACC;
-            if (alive) alive = mbar_wait_bounded(accf_bar + 8 * buf, (uint32_t)(use & 1), p.status);
+            if (alive) alive = mbar_wait_warp(accf_bar + 8 * buf, (uint32_t)(use & 1), p.status, lane);
             tc_fence_after();
             const int64_t m0 = m_tile * BM;
+            float *wsp = p.ws + (size_t)split * p.Mp * p.N;
+            const int esz = p.y_dt == TTQ_DT_F32 ? 4 : 2;
 #pragma unroll 1
-            for (int sub = 0; sub < NSUB; sub++) {
-                const int64_t n = n_tile * TILE_N + sub * GEMM_BN + warp * 32 + lane;
-                float bias_v = 0.f;
-                if (splits == 1 && p.bias != nullptr && n < p.N) bias_v = load_as_float(p.bias, p.bias_dt, n);
-                float *wsp = p.ws + (size_t)split * p.Mp * p.N;
+            for (int hb = 0; hb < C::MH; hb++) {
+                // lane = activation row, columns = consecutive output features: 16 of them per load, stored as one run
+                const int64_t m = m0 + hb * 128 + warp * 32 + lane;
+                const bool row_ok = m < p.M && hb * 128 + warp * 32 + lane < BM;  // a 64-row tile fills lanes 0..63 only
 #pragma unroll 1
-                for (int c0 = 0; c0 < BM; c0 += 16) {
+                for (int c0 = 0; c0 < 128 * NSUB; c0 += 16) {
                     uint32_t v[16];
-                    tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)((buf * NSUB + sub) * BM + c0), v);
+                    tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * C::ACC_COLS + hb * 128 * NSUB + c0), v);
+                    const int64_t n0 = n_tile * TILE_N + c0;
+                    if (!row_ok || n0 >= p.N) continue;
+                    if (splits > 1) {
+                        float *dst = wsp + m * p.N + n0;
+                        if (n0 + 16 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        const int64_t m = m0 + c0 + i;
-                        if (m < p.M && n < p.N) {
-                            if (splits == 1) store_from_float(p.y, p.y_dt, m * p.ldy + n, __uint_as_float(v[i]) + bias_v);
-                            else wsp[m * p.N + n] = __uint_as_float(v[i]);
+                            for (int q = 0; q < 4; q++)
+                                reinterpret_cast<float4 *>(dst)[q] = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                                                                                 __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; i++)
+                                if (n0 + i < p.N) dst[i] = __uint_as_float(v[i]);
                         }
+                        continue;
+                    }
+                    float f[16];
+#pragma unroll
+                    for (int i = 0; i < 16; i++) f[i] = __uint_as_float(v[i]);
+                    if (p.bias != nullptr) {
+#pragma unroll
+                        for (int i = 0; i < 16; i++)
+                            if (n0 + i < p.N) f[i] += load_as_float(p.bias, p.bias_dt, n0 + i);
+                    }
+                    uint8_t *dst = reinterpret_cast<uint8_t *>(p.y) + (size_t)(m * p.ldy + n0) * esz;
+                    if (n0 + 16 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                        if (p.y_dt == TTQ_DT_F32) {
+#pragma unroll
+                            for (int q = 0; q < 4; q++)
+                                reinterpret_cast<float4 *>(dst)[q] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+                        } else {
+                            uint32_t w[8];
+#pragma unroll
+                            for (int q = 0; q < 8; q++) {
+                                if (p.y_dt == TTQ_DT_BF16) {
+                                    const __nv_bfloat162 t2 = __floats2bfloat162_rn(f[2 * q], f[2 * q + 1]);
+                                    w[q] = *reinterpret_cast<const uint32_t *>(&t2);
+                                } else {
+                                    const __half2 t2 = __floats2half2_rn(f[2 * q], f[2 * q + 1]);
+                                    w[q] = *reinterpret_cast<const uint32_t *>(&t2);
+                                }
+                            }
+                            reinterpret_cast<uint4 *>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                            reinterpret_cast<uint4 *>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; i++)
+                            if (n0 + i < p.N) store_from_float(p.y, p.y_dt, m * p.ldy + n0 + i, f[i]);
                     }
                 }
             }
@@ -381,6 +436,8 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
             hv_next[sub] = header_at(tile0[sub], have[sub], 0);
         }
         const __half2 k1032 = __float2half2_rn(1032.f), k1152 = __float2half2_rn(1152.f);
+        const bool trd = p.trace != nullptr && blockIdx.x == 0 && dwa == 0;
+        unsigned long long t_empty = 0, t_begin = trd ? global_ns() : 0;
         for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             bool have_n[1];
             const uint8_t *tile0_n[1];
@@ -434,8 +491,10 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
                     }
                     __syncwarp();
                 }
+                unsigned long long tw0 = trd ? global_ns() : 0;
                 if (git >= STAGES && alive)
-                    alive = mbar_wait_bounded(empty_bar + 8 * stage, (uint32_t)(((git / STAGES) - 1) & 1), p.status);
+                    alive = mbar_wait_warp(empty_bar + 8 * stage, (uint32_t)(((git / STAGES) - 1) & 1), p.status, lane);
+                if (trd) t_empty += global_ns() - tw0;
                 const uint32_t a_stage = stages_u32 + stage * C::STAGE_BYTES;
 #ifndef TTQ_DIAG_NO_B
                 if (dwa == 0 && lane == 0) {
@@ -471,6 +530,9 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
                         res[sl][2] = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v2), k1152), sc_hi, of_hi);
                         res[sl][3] = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v3), k1152), sc_hi, of_hi);
                     }
+#ifdef TTQ_DIAG_NO_STS
+                    if (p.Kp < 0)
+#endif
 #pragma unroll
                     for (int sl = 0; sl < 4; sl++) {
                         asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a_sub + dst_off[sl][0]),
@@ -481,7 +543,9 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
                                      : "memory");
                     }
                 }
+#ifndef TTQ_DIAG_NO_FENCE
                 fence_async_smem();
+#endif
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full_bar + 8 * stage);
             }
@@ -491,11 +555,20 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
                 have[sub] = have_n[sub];
             }
         }
+        if (trd && lane == 0) {
+            // timeline entry of kind 4: dequant warp 0 -- start, time spent waiting for free stages, stages, end
+            const unsigned long long slot = atomicAdd(p.trace, 1ull);
+            if (slot < 8192) {
+                unsigned long long *e = p.trace + 8 + slot * 8;
+                e[0] = 4; e[1] = t_begin; e[2] = t_empty; e[3] = 0; e[4] = (unsigned long long)git; e[5] = global_ns();
+                e[6] = gridDim.x; e[7] = (unsigned long long)p.N;
+            }
+        }
     } else {
         // ------------------------------------------------------------------ MMA issue
         if (lane == 0) {
             bool alive = true;
-            const uint32_t idesc = idesc_f16(BM);
+            const uint32_t idesc = idesc_f16(128 * NSUB);
             int git = 0, tcount = 0;
             const bool tr = p.trace != nullptr && blockIdx.x == 0;
             unsigned long long t_start = tr ? global_ns() : 0, t_full = 0, t_acc = 0;
@@ -506,7 +579,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
                 if (use >= 1 && alive) alive = mbar_wait_bounded(acce_bar + 8 * buf, (uint32_t)((use - 1) & 1), p.status);
                 if (tr) t_acc += global_ns() - t0;
                 tc_fence_after();
-                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * NSUB * BM);
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * C::ACC_COLS);
                 for (int it = 0; it < iters; it++, git++) {
                     const int stage = git % STAGES;
                     if (tr) t0 = global_ns();
@@ -516,13 +589,15 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
                     if (tr) t_full += global_ns() - t0;
                     tc_fence_after();
                     const uint32_t a_stage = stages_u32 + stage * C::STAGE_BYTES;
-                    const uint64_t bdesc = smem_desc_sw128(a_stage + C::A_BYTES);
+                    // N side: the 128 * NSUB expanded weight rows of the stage (sub-tiles are contiguous 8-row atoms)
+                    const uint64_t wdesc = smem_desc_sw128(a_stage);
 #pragma unroll
-                    for (int sub = 0; sub < NSUB; sub++) {
-                        const uint64_t adesc = smem_desc_sw128(a_stage + sub * A_STAGE_BYTES);
+                    for (int hb = 0; hb < C::MH; hb++) {
+                        // M side: 128 activation rows (a 64-row tile leaves lanes 64..127 unused)
+                        const uint64_t xdesc = smem_desc_sw128(a_stage + C::A_BYTES + hb * (128 * 128));
 #pragma unroll
                         for (int kk = 0; kk < 4; kk++)  // 16 K values = 32 bytes along the swizzled row per instruction
-                            umma_f16(tmem_d + (uint32_t)(sub * BM), adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), idesc,
+                            umma_f16(tmem_d + (uint32_t)(hb * 128 * NSUB), xdesc + (uint64_t)(2 * kk), wdesc + (uint64_t)(2 * kk), idesc,
                                      (it > 0 || kk > 0) ? 1u : 0u);
                     }
                     umma_commit(empty_bar + 8 * stage);
@@ -692,7 +767,12 @@ cudaError_t launch_gemm_grouped(const GroupedArgs &g, __half *xh, int sms, int *
     p.ws = nullptr;
     // two sub-tiles per CTA when the expected tile count still covers the SMs
     const int64_t mt_cap = g.Mp / g.BM;
-    const int nsub = (g.N >= 256 && ((g.N + 255) / 256) * mt_cap >= 2 * (int64_t)sms) ? 2 : 1;
+    int nsub = (g.N >= 256 && ((g.N + 255) / 256) * mt_cap >= 2 * (int64_t)sms) ? 2 : 1;
+    static const int force_nsub = []() {
+        const char *v = getenv("TTQ_MOE_NSUB");
+        return v ? atoi(v) : 0;
+    }();
+    if (force_nsub == 1 || force_nsub == 2) nsub = force_nsub;
     if (nsub == 2) {
         if (g.BM == 64) e = launch_cfg<64, 2>(p, sms, st);
         else if (g.BM == 128) e = launch_cfg<128, 2>(p, sms, st);

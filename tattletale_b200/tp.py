@@ -79,3 +79,75 @@ class Communicator:
         if getattr(self, "handle", None):
             self.ctx._lib.ttq_comm_destroy(self.handle)
             self.handle = None
+
+
+def plan_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int):
+    """Send order of the (token, choice) pairs of one rank for expert-parallel dispatch.
+
+    Pairs go to the rank that holds their expert (``id // experts_per_rank``), grouped by destination in
+    ascending rank, original order kept inside a group.  Returns ``(order, send_counts)``: ``order[i]`` is the
+    flat pair index (``token * top_k + choice``) sent at position i; pairs with an id outside the global
+    expert range are not sent.  Pure tensor code: runs on CPU or GPU.
+    """
+    flat = topk_ids.reshape(-1).to(torch.int64)
+    valid = (flat >= 0) & (flat < experts_per_rank * world)
+    dest = torch.where(valid, flat // experts_per_rank, torch.full_like(flat, world))
+    order = torch.sort(dest, stable=True).indices
+    counts = torch.bincount(dest, minlength=world + 1)
+    order = order[: int(counts[:world].sum())]
+    return order, counts[:world]
+
+
+class ExpertParallelMoE:
+    """Expert-parallel mixture-of-experts layer: rank r holds experts ``[r * E/P, (r + 1) * E/P)`` and its own
+    slice of the tokens.  One forward is dispatch (all-to-all of the routed rows to the ranks that own their
+    experts), the local grouped GEMM layer with one choice per received row, and combine (all-to-all back,
+    weighted sum at the source in fp32, ascending choice order).
+
+    ``local_forward(rows, local_ids)`` is the layer that runs the received rows through local expert
+    ``local_ids[i]`` -- ``MoELayer`` on the GPU (``from_layer``), any callable in host-side tests.  The
+    all-to-alls are ``torch.distributed.all_to_all_single`` (NCCL over NVLink on GPUs, gloo on CPU); the
+    split sizes travel first, which costs one host synchronisation per forward.
+    """
+
+    def __init__(self, local_forward, experts_per_rank: int, top_k: int, group=None):
+        import torch.distributed as dist
+
+        self.dist, self.group = dist, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.local_forward, self.epr, self.top_k = local_forward, experts_per_rank, top_k
+
+    @classmethod
+    def from_layer(cls, layer, group=None):
+        """``layer``: a MoELayer built with top_k = 1 over this rank's experts, sized for the rows it may receive."""
+        if layer.top_k != 1:
+            raise ValueError("the local layer of an expert-parallel group takes one expert per received row")
+
+        def run(rows, local_ids):
+            ones = torch.ones((rows.shape[0], 1), dtype=torch.float32, device=rows.device)
+            return layer.forward(rows, local_ids.reshape(-1, 1), ones)
+
+        return cls(run, layer.n_experts, 1, group)
+
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
+        dist, P = self.dist, self.world
+        t, k = topk_ids.shape
+        order, send_counts = plan_dispatch(topk_ids, self.epr, P)
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        send_splits, recv_splits = send_counts.tolist(), recv_counts.tolist()
+        n_recv = sum(recv_splits)
+        send_rows = x.reshape(t, -1)[order // k].contiguous()
+        send_ids = (topk_ids.reshape(-1)[order].to(torch.int64) % self.epr).to(torch.int32).contiguous()
+        recv_rows = torch.empty((n_recv, send_rows.shape[1]), dtype=x.dtype, device=x.device)
+        recv_ids = torch.empty((n_recv,), dtype=torch.int32, device=x.device)
+        dist.all_to_all_single(recv_rows, send_rows, recv_splits, send_splits, group=self.group)
+        dist.all_to_all_single(recv_ids, send_ids, recv_splits, send_splits, group=self.group)
+        out_rows = self.local_forward(recv_rows, recv_ids) if n_recv else recv_rows
+        back = torch.empty_like(send_rows)
+        dist.all_to_all_single(back, out_rows.contiguous(), send_splits, recv_splits, group=self.group)
+        # place every returned row at its (token, choice) slot, then the weighted sum over the choices
+        slots = torch.zeros((t * k, back.shape[1]), dtype=torch.float32, device=x.device)
+        slots[order] = back.float()
+        y = (slots.view(t, k, -1) * topk_weights.reshape(t, k, 1).float()).sum(dim=1)
+        return y.to(x.dtype)
