@@ -25,6 +25,8 @@ struct ttq_ctx {
     int *dev_status;  // device word the kernels OR failure bits into (bit 0: a bounded wait gave up)
     int *host_status; // pinned host copy of it, filled by the host entry points
     unsigned long long *trace;  // device timeline buffer, allocated only when TTQ_TRACE=1 is set at init
+    __half *wimg;               // fp16 expansion of one whole weight (plain GEMM mode of the formats without a
+    int64_t wimg_capacity;      //   fused dequant GEMM); in halves, grown when such a weight is created
     __half *xh;                 // fp16 activation scratch of the tcgen05 GEMM path
     int64_t xh_capacity;        // in halves
     // device staging for the *_host entry points
@@ -104,6 +106,24 @@ ttq_status alloc_weight(ttq_ctx *ctx, int fmt, int64_t N, int64_t K, ttq_weight 
     if (e != cudaSuccess) {
         delete w;
         return cuda_fail(ctx, e, "cudaMalloc(tiled weight)");
+    }
+    if (!gemm_supported(fmt)) {
+        // larger batches of this format run as expansion to fp16 + plain tensor-core GEMM: make sure the
+        // context's expansion scratch holds this matrix (load time; forward never allocates)
+        const int64_t need = gemm_wimg_rows(N) * w->SBp * TILE_K;
+        if (need > ctx->wimg_capacity) {
+            cudaDeviceSynchronize();
+            cudaFree(ctx->wimg);
+            ctx->wimg = nullptr;
+            ctx->wimg_capacity = 0;
+            e = cudaMalloc(&ctx->wimg, (size_t)need * sizeof(__half));
+            if (e != cudaSuccess) {
+                cudaFree(w->tiles);
+                delete w;
+                return cuda_fail(ctx, e, "cudaMalloc(fp16 expansion scratch)");
+            }
+            ctx->wimg_capacity = need;
+        }
     }
     *out = w;
     return TTQ_OK;
@@ -220,6 +240,7 @@ ttq_status ttq_destroy(ttq_ctx *ctx) {
     cudaFreeHost(ctx->host_status);
     cudaFree(ctx->trace);
     cudaFree(ctx->xh);
+    cudaFree(ctx->wimg);
     cudaFree(ctx->stage_x);
     cudaFree(ctx->stage_y);
     cudaFree(ctx->stage_b);
@@ -381,6 +402,21 @@ ttq_status ttq_linear_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_d
         cudaError_t e = launch_gemm(w->fmt, a, ctx->xh, ctx->xh_capacity, ctx->sms, ctx->dev_status, ctx->trace, st, &launches);
         ctx->launches += launches;
         if (e != cudaSuccess) return cuda_fail(ctx, e, "linear forward (GEMM) launch");
+        return TTQ_OK;
+    }
+    // formats without a fused dequant GEMM: beyond two decode passes, expand the weight to fp16 once and run
+    // the plain tensor-core GEMM on it
+    constexpr int64_t PLAIN_MIN_M = 2 * MAX_GEMV_M + 1;
+    if (M >= PLAIN_MIN_M && use_gemm && !gemm_supported(w->fmt) && ctx->wimg != nullptr &&
+        gemm_wimg_rows(w->N) * w->SBp * TILE_K <= ctx->wimg_capacity) {
+        cudaError_t e = launch_wimg(w->fmt, w->tiles, w->N, w->K, w->SBp, ctx->wimg, st);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "weight expansion launch");
+        ctx->launches++;
+        a.x = x_dev; a.M = M; a.y = y_dev;
+        int launches = 0;
+        e = launch_gemm(w->fmt, a, ctx->xh, ctx->xh_capacity, ctx->sms, ctx->dev_status, ctx->trace, st, &launches, ctx->wimg);
+        ctx->launches += launches;
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "linear forward (plain GEMM) launch");
         return TTQ_OK;
     }
     // decode path; more rows than one pass holds are processed in groups of MAX_GEMV_M

@@ -228,6 +228,10 @@ struct GemmParams {
     float *ws;    // splits > 1: fp32 partial outputs [split][Mp][N], summed by splitk_reduce_kernel
     // grouped (mixture-of-experts) mode, group_tiles != nullptr: every BM-row tile of x belongs to one
     // weight matrix (all of one shape); the number of row tiles in use is a device scalar
+    // plain mode (kernel template PLAIN): the weights arrive already expanded to fp16 tile images in the layout
+    // of xh_prep_kernel ([stage][row atom][1024 B], rows = output features padded to 256); `tiles` is unused
+    const __half *wimg;
+    int64_t Np;
     const uint8_t *const *group_tiles;  // per group: Q4_K tiled layout
     const int *mt_group;                // group of row tile mt
     const int *n_mt;                    // row tiles in use (<= Mp / BM)
@@ -252,7 +256,7 @@ struct GemmCfg {
     static constexpr int TOTAL = 1024 + STAGES * STAGE_BYTES + HDR_BYTES + BAR_BYTES;
 };
 
-template <int BM, int NSUB>
+template <int BM, int NSUB, bool PLAIN>
 __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel(GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     using C = GemmCfg<BM, NSUB>;
@@ -284,7 +288,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
 #ifdef TTQ_DIAG_NO_B
             mbar_init(full_bar + 8 * s, C::DEQ_WARPS);
 #else
-            mbar_init(full_bar + 8 * s, C::DEQ_WARPS + 1);
+            mbar_init(full_bar + 8 * s, PLAIN ? 1 : C::DEQ_WARPS + 1);
 #endif
             mbar_init(empty_bar + 8 * s, 1);
         }
@@ -384,6 +388,29 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
             __syncwarp();
             if (lane == 0) mbar_arrive(acce_bar + 8 * buf);
         }
+    } else if (PLAIN && warp < GEMM_EPI_WARPS + C::DEQ_WARPS) {
+        // ------------------------------------------------------------------ producer: both operands are bulk copies
+        if (warp == GEMM_EPI_WARPS && lane == 0) {
+            bool alive = true;
+            int git = 0;
+            const int64_t b_it_stride = (p.Mp >> 3) << 10, w_it_stride = (p.Np >> 3) << 10;
+            for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+                const int64_t otile = tile / splits, split = tile % splits;
+                const int64_t n_tile = otile / m_tiles, m_tile = otile % m_tiles;
+                const uint8_t *bsrc0 = reinterpret_cast<const uint8_t *>(p.xh) + (((m_tile * BM) >> 3) << 10) + split * iters * b_it_stride;
+                const uint8_t *wsrc0 = reinterpret_cast<const uint8_t *>(p.wimg) + (((n_tile * TILE_N) >> 3) << 10) + split * iters * w_it_stride;
+                for (int it = 0; it < iters; it++, git++) {
+                    const int stage = git % STAGES;
+                    if (git >= STAGES && alive)
+                        alive = mbar_wait_bounded(empty_bar + 8 * stage, (uint32_t)(((git / STAGES) - 1) & 1), p.status);
+                    const uint32_t a_stage = stages_u32 + stage * C::STAGE_BYTES;
+                    mbar_expect_tx(full_bar + 8 * stage, C::A_BYTES + C::B_BYTES);
+                    bulk_g2s(a_stage, wsrc0 + it * w_it_stride, C::A_BYTES, full_bar + 8 * stage);
+                    bulk_g2s(a_stage + C::A_BYTES, bsrc0 + it * b_it_stride, C::B_BYTES, full_bar + 8 * stage);
+                }
+            }
+        }
+        __syncwarp();
     } else if (warp < GEMM_EPI_WARPS + C::DEQ_WARPS) {
         // ------------------------------------------------------------------ dequantize A
         const int dwa = warp - GEMM_EPI_WARPS;  // dequant warp index
@@ -437,7 +464,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
         }
         const __half2 k1032 = __float2half2_rn(1032.f), k1152 = __float2half2_rn(1152.f);
         const bool trd = p.trace != nullptr && blockIdx.x == 0 && dwa == 0;
-        unsigned long long t_empty = 0, t_begin = trd ? global_ns() : 0;
+        unsigned long long t_empty = 0, t_conv = 0, t_begin = trd ? global_ns() : 0;
         for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             bool have_n[1];
             const uint8_t *tile0_n[1];
@@ -494,7 +521,11 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
                 unsigned long long tw0 = trd ? global_ns() : 0;
                 if (git >= STAGES && alive)
                     alive = mbar_wait_warp(empty_bar + 8 * stage, (uint32_t)(((git / STAGES) - 1) & 1), p.status, lane);
-                if (trd) t_empty += global_ns() - tw0;
+                if (trd) {
+                    tw0 = global_ns() - tw0;
+                    t_empty += tw0;
+                    tw0 = global_ns();
+                }
                 const uint32_t a_stage = stages_u32 + stage * C::STAGE_BYTES;
 #ifndef TTQ_DIAG_NO_B
                 if (dwa == 0 && lane == 0) {
@@ -548,6 +579,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
 #endif
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full_bar + 8 * stage);
+                if (trd) t_conv += global_ns() - tw0;
             }
 #pragma unroll
             for (int sub = 0; sub < 1; sub++) {
@@ -560,7 +592,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
             const unsigned long long slot = atomicAdd(p.trace, 1ull);
             if (slot < 8192) {
                 unsigned long long *e = p.trace + 8 + slot * 8;
-                e[0] = 4; e[1] = t_begin; e[2] = t_empty; e[3] = 0; e[4] = (unsigned long long)git; e[5] = global_ns();
+                e[0] = 4; e[1] = t_begin; e[2] = t_empty; e[3] = t_conv; e[4] = (unsigned long long)git; e[5] = global_ns();
                 e[6] = gridDim.x; e[7] = (unsigned long long)p.N;
             }
         }
@@ -571,7 +603,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
             const uint32_t idesc = idesc_f16(128 * NSUB);
             int git = 0, tcount = 0;
             const bool tr = p.trace != nullptr && blockIdx.x == 0;
-            unsigned long long t_start = tr ? global_ns() : 0, t_full = 0, t_acc = 0;
+            unsigned long long t_start = tr ? global_ns() : 0, t_full = 0, t_acc = 0, t_issue = 0;
             for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, tcount++) {
                 const int buf = tcount % C::NACC, use = tcount / C::NACC;
                 // the epilogue must have drained this accumulator set (its previous use)
@@ -586,7 +618,10 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
 #ifndef TTQ_DIAG_MMA_ONLY
                     if (alive) alive = mbar_wait_bounded(full_bar + 8 * stage, (uint32_t)((git / STAGES) & 1), p.status);
 #endif
-                    if (tr) t_full += global_ns() - t0;
+                    if (tr) {
+                        t_full += global_ns() - t0;
+                        t0 = global_ns();
+                    }
                     tc_fence_after();
                     const uint32_t a_stage = stages_u32 + stage * C::STAGE_BYTES;
                     // N side: the 128 * NSUB expanded weight rows of the stage (sub-tiles are contiguous 8-row atoms)
@@ -601,6 +636,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
                                      (it > 0 || kk > 0) ? 1u : 0u);
                     }
                     umma_commit(empty_bar + 8 * stage);
+                    if (tr) t_issue += global_ns() - t0;
                 }
                 umma_commit(accf_bar + 8 * buf);
             }
@@ -610,7 +646,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
                 if (slot < 8192) {
                     unsigned long long *e = p.trace + 8 + slot * 8;
                     e[0] = 3; e[1] = t_start; e[2] = t_full; e[3] = t_acc; e[4] = (unsigned long long)git; e[5] = global_ns();
-                    e[6] = gridDim.x; e[7] = (unsigned long long)p.N;
+                    e[6] = t_issue; e[7] = (unsigned long long)p.N;
                 }
             }
         }
@@ -637,18 +673,18 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restr
     }
 }
 
-template <int BM, int NSUB>
+template <int BM, int NSUB, bool PLAIN = false>
 cudaError_t launch_cfg(const GemmParams &p, int sms, cudaStream_t st) {
     using C = GemmCfg<BM, NSUB>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_q4k_kernel<BM, NSUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL);
+        cudaError_t e = cudaFuncSetAttribute(gemm_q4k_kernel<BM, NSUB, PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL);
         if (e != cudaSuccess) return e;
         configured = true;
     }
     const int64_t tiles = ((p.N + GEMM_BN * NSUB - 1) / (GEMM_BN * NSUB)) * (p.Mp / BM) * p.splits;
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-    gemm_q4k_kernel<BM, NSUB><<<grid, C::THREADS, C::TOTAL, st>>>(p);
+    gemm_q4k_kernel<BM, NSUB, PLAIN><<<grid, C::THREADS, C::TOTAL, st>>>(p);
     return cudaGetLastError();
 }
 
@@ -656,11 +692,15 @@ cudaError_t launch_cfg(const GemmParams &p, int sms, cudaStream_t st) {
 
 bool gemm_supported(int fmt) { return fmt == TTQ_FMT_Q4_K; }
 
+// Rows of the fp16 weight images the plain mode reads: output features padded to whole 256-row tiles.
+int64_t gemm_wimg_rows(int64_t N) { return (N + 255) / 256 * 256; }
+
 // x rows are processed in slabs that fit the fp16 activation scratch (capacity in halves).
 cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_capacity, int sms, int *status,
-                        unsigned long long *trace, cudaStream_t st, int *launches) {
+                        unsigned long long *trace, cudaStream_t st, int *launches, const __half *wimg) {
     *launches = 0;
-    if (fmt != TTQ_FMT_Q4_K) return cudaErrorNotSupported;
+    const bool plain = wimg != nullptr;
+    if (!plain && fmt != TTQ_FMT_Q4_K) return cudaErrorNotSupported;
     const int64_t Kp = a.SBp * TILE_K;
     const int BM = a.M <= 64 ? 64 : (a.M <= 128 ? 128 : 256);
     // two 128-row sub-tiles per CTA once there are enough tiles to keep every SM busy with them
@@ -668,12 +708,13 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
         const char *v = getenv("TTQ_GEMM_NSUB");
         return v ? atoi(v) : 0;
     }();
-    // a CTA with two sub-tiles does twice the work per activation stage in about 1.6x the time of one (measured)
+    // a CTA with two sub-tiles does twice the work per activation stage in about 1.25x the time of one (measured)
     const int64_t mt = (a.M + BM - 1) / BM;
     const int64_t tiles1 = ((a.N + 127) / 128) * mt, tiles2 = ((a.N + 255) / 256) * mt;
-    const double cost1 = (double)((tiles1 + sms - 1) / sms), cost2 = 1.6 * (double)((tiles2 + sms - 1) / sms);
+    const double cost1 = (double)((tiles1 + sms - 1) / sms), cost2 = 1.25 * (double)((tiles2 + sms - 1) / sms);
     int nsub = (a.N > 128 && cost2 < cost1) ? 2 : 1;
     if (force_nsub == 1 || force_nsub == 2) nsub = force_nsub;
+    if (plain) nsub = 2;  // no conversion work to balance: always the 256-row weight tile
     int64_t slab = (xh_capacity / Kp) / BM * BM;  // rows per pass
     if (slab < BM) return cudaErrorInvalidValue;
     const int esz_x = a.x_dt == TTQ_DT_F32 ? 4 : 2, esz_y = a.y_dt == TTQ_DT_F32 ? 4 : 2;
@@ -689,6 +730,7 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
         ++*launches;
         GemmParams p;
         p.tiles = a.tiles;
+        p.wimg = wimg; p.Np = gemm_wimg_rows(a.N);
         p.group_tiles = nullptr; p.mt_group = nullptr; p.n_mt = nullptr;
         p.N = a.N; p.NT = a.NT; p.SBp = a.SBp;
         p.xh = xh;
@@ -714,7 +756,11 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
             p.splits = splits;
             p.ws = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(xh) + ((xh_bytes + 255) & ~(size_t)255));
         }
-        if (nsub == 2) {
+        if (plain) {
+            if (BM == 64) e = launch_cfg<64, 2, true>(p, sms, st);
+            else if (BM == 128) e = launch_cfg<128, 2, true>(p, sms, st);
+            else e = launch_cfg<256, 2, true>(p, sms, st);
+        } else if (nsub == 2) {
             if (BM == 64) e = launch_cfg<64, 2>(p, sms, st);
             else if (BM == 128) e = launch_cfg<128, 2>(p, sms, st);
             else e = launch_cfg<256, 2>(p, sms, st);
@@ -755,6 +801,7 @@ cudaError_t launch_gemm_grouped(const GroupedArgs &g, __half *xh, int sms, int *
     ++*launches;
     GemmParams p;
     p.tiles = nullptr;
+    p.wimg = nullptr; p.Np = 0;
     p.group_tiles = g.group_tiles; p.mt_group = g.mt_group; p.n_mt = g.n_mt;
     p.N = g.N; p.NT = g.NT; p.SBp = g.SBp;
     p.xh = xh;

@@ -65,3 +65,23 @@ def test_same_rows_give_same_result_as_decode_path(ctx):
     small = lin.forward(x[:4], out_dtype=torch.float32)
     assert rel_l2(big[:4].cpu().numpy(), small.cpu().numpy()) < TOL
     lin.close()
+
+
+@pytest.mark.parametrize("fmt", [ttq.FMT_Q8_0, ttq.FMT_Q6_K], ids=["q8_0", "q6_k"])
+@pytest.mark.parametrize("n,k,m", [(256, 512, 33), (130, 768, 200), (512, 1024, 300), (100, 256, 64)])
+def test_formats_without_fused_gemm_expand_then_multiply(ctx, fmt, n, k, m):
+    """Q8_0 and Q6_K batches beyond two decode passes: whole-weight expansion to fp16 images + the plain
+    tensor-core GEMM (both operands bulk-copied)."""
+    from gpu_util import OFMT
+
+    blocks = make_weight(fmt, n, k, seed=n + k + m + fmt)
+    x = make_x(m, k, seed=m + 5)
+    bias = torch.from_numpy(np.random.default_rng(m).normal(0, 0.1, n).astype(np.float32))
+    lin = ttq.QuantLinear(ctx, fmt, torch.from_numpy(blocks), k, bias=bias.cuda())
+    c0 = ctx.launch_count
+    y = lin.forward(x.cuda(), out_dtype=torch.float32)
+    ctx.check_device_status()
+    assert ctx.launch_count - c0 <= 4  # expansion, activation images, GEMM (+ split-K sum)
+    want = oracle.linear(OFMT[fmt], blocks, x_bits(x), oracle.BF16, bias.numpy())
+    assert rel_l2(y.cpu().numpy(), want) < TOL
+    lin.close()
