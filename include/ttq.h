@@ -59,7 +59,18 @@ typedef enum ttq_status {
 typedef enum ttq_format {
     TTQ_FMT_Q8_0 = 0, /* 32 weights / 34 B: fp16 d, 32 x int8 */
     TTQ_FMT_Q4_K = 1, /* 256 weights / 144 B: fp16 d, fp16 dmin, 12 B of 6-bit scales+mins, 128 B nibbles */
-    TTQ_FMT_Q6_K = 2  /* 256 weights / 210 B: 128 B low nibbles, 64 B high 2 bits, 16 x int8 scales, fp16 d */
+    TTQ_FMT_Q6_K = 2, /* 256 weights / 210 B: 128 B low nibbles, 64 B high 2 bits, 16 x int8 scales, fp16 d */
+    /* Trellis-coded 3 bits per weight, Hadamard-rotated input and output (this library's own format in the
+     * family a reference configuration fixture names, tests/fixtures/configs/config-GLM-4.7-EXL3-3.84bpw.json:43-54;
+     * not interchangeable with other tools' checkpoints).  N and K multiples of 128.  One buffer of
+     * N*K*3/8 + 2N + K/8 bytes: tiles [N/16][K/16][96 B] | out_scale [N] fp16 | in_sign [K/8] bytes.
+     * Weight t = 16 r + c of a 16x16 tile is coded by the 16-bit window at bit 3t of the tile's 768-bit
+     * little-endian stream (zero beyond its end): h = window * 2654435761 mod 2^32,
+     * q = (byte0(h) + byte1(h) + byte2(h) + byte3(h) - 510) / 147.8.  The operator is
+     * y = out_scale * H_N(q . H_K(in_sign * x)) + bias, H = orthonormal Hadamard transform on blocks of 128.
+     * ttq_dequantize returns q (the decoded codes).  ttq_shard is not applied to this format: shard the
+     * buffer on the host (rows in multiples of 128, columns in multiples of 128). */
+    TTQ_FMT_TQ3 = 3
 } ttq_format;
 
 typedef enum ttq_dtype { TTQ_DT_BF16 = 0, TTQ_DT_F16 = 1, TTQ_DT_F32 = 2 } ttq_dtype;

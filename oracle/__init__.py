@@ -49,6 +49,12 @@ def lib() -> ctypes.CDLL:
         L.ttq_ref_f32_to_f16.argtypes = [ctypes.c_float]
         L.ttq_ref_f32_to_f16.restype = ctypes.c_uint16
         L.ttq_ref_num_threads.restype = ci
+        L.ttq_tq3_packed_bytes.argtypes = [i64, i64]
+        L.ttq_tq3_packed_bytes.restype = i64
+        L.ttq_tq3_decode.argtypes = [vp, i64, i64, vp]
+        L.ttq_tq3_effective_weight.argtypes = [vp, i64, i64, vp]
+        L.ttq_tq3_linear.argtypes = [vp, i64, i64, vp, ci, i64, i64, vp, vp, i64]
+        L.ttq_tq3_encode.argtypes = [vp, i64, i64, ctypes.c_uint32, vp, vp]
         _lib = L
     return _lib
 
@@ -165,3 +171,50 @@ def to_f16_bits(x: np.ndarray) -> np.ndarray:
 
 def num_threads() -> int:
     return int(lib().ttq_ref_num_threads())
+
+
+# ---- trellis-coded 3-bit format (oracle/ttq_trellis.c) ---------------------------------------------------
+TQ3 = 3
+
+
+def tq3_packed_bytes(n: int, k: int) -> int:
+    return int(lib().ttq_tq3_packed_bytes(n, k))
+
+
+def tq3_encode(w: np.ndarray, seed: int = 1):
+    """fp32 [N, K] -> (packed uint8 buffer, mean squared code error against the rotated unit-variance target)."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    n, k = w.shape
+    out = np.zeros(tq3_packed_bytes(n, k), dtype=np.uint8)
+    mse = ctypes.c_double()
+    rc = lib().ttq_tq3_encode(_ptr(w), n, k, seed, _ptr(out), ctypes.addressof(mse))
+    assert rc == 0, rc
+    return out, float(mse.value)
+
+
+def tq3_decode(packed: np.ndarray, n: int, k: int) -> np.ndarray:
+    """The decoded codes q [N, K] (before rotations and scales): bit-exact target of the device decode."""
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    assert packed.size == tq3_packed_bytes(n, k)
+    out = np.empty((n, k), dtype=np.float32)
+    assert lib().ttq_tq3_decode(_ptr(packed), n, k, _ptr(out)) == 0
+    return out
+
+
+def tq3_effective_weight(packed: np.ndarray, n: int, k: int) -> np.ndarray:
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    out = np.empty((n, k), dtype=np.float32)
+    assert lib().ttq_tq3_effective_weight(_ptr(packed), n, k, _ptr(out)) == 0
+    return out
+
+
+def tq3_linear(packed: np.ndarray, n: int, k: int, x: np.ndarray, x_dtype: int, bias: np.ndarray | None = None) -> np.ndarray:
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    x = _act(x, x_dtype)
+    m = x.shape[0]
+    assert x.shape[1] == k
+    y = np.empty((m, n), dtype=np.float32)
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    rc = lib().ttq_tq3_linear(_ptr(packed), n, k, _ptr(x), x_dtype, m, k, None if b is None else _ptr(b), _ptr(y), n)
+    assert rc == 0, rc
+    return y

@@ -10,7 +10,7 @@ with the dense weight replaced by GGUF-style block-quantized bytes.  All compute
 ``libttq.so`` through the C ABI of ``include/ttq.h``; torch is used only for device buffers and
 streams.  Importing this package does not need a GPU; creating a :class:`Context` does.
 """
-from ._lib import (DT_BF16, DT_F16, DT_F32, FMT_Q4_K, FMT_Q6_K, FMT_Q8_0, SHARD_COLUMN,
+from ._lib import (DT_BF16, DT_F16, DT_F32, FMT_Q4_K, FMT_Q6_K, FMT_Q8_0, FMT_TQ3, SHARD_COLUMN,
                    SHARD_COLUMN_GATED, SHARD_NONE, SHARD_ROW, TtqError)
 from .layers import ActivationKind, Context, GatedMLP, MoELayer, QuantLinear, silu_and_mul
 from .formats import BLOCK_BYTES, BLOCK_ELEMS, FORMAT_NAMES, packed_bytes
@@ -18,7 +18,7 @@ from . import tp
 
 __all__ = [
     "Context", "QuantLinear", "GatedMLP", "MoELayer", "ActivationKind", "silu_and_mul", "TtqError",
-    "FMT_Q8_0", "FMT_Q4_K", "FMT_Q6_K", "DT_BF16", "DT_F16", "DT_F32",
+    "FMT_Q8_0", "FMT_Q4_K", "FMT_Q6_K", "FMT_TQ3", "DT_BF16", "DT_F16", "DT_F32",
     "SHARD_NONE", "SHARD_COLUMN", "SHARD_COLUMN_GATED", "SHARD_ROW",
     "BLOCK_BYTES", "BLOCK_ELEMS", "FORMAT_NAMES", "packed_bytes",
 ]

@@ -12,7 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("TTQ_LIB") or os.path.join(_HERE, "libttq.so")
 
 # enums of include/ttq.h
-FMT_Q8_0, FMT_Q4_K, FMT_Q6_K = 0, 1, 2
+FMT_Q8_0, FMT_Q4_K, FMT_Q6_K, FMT_TQ3 = 0, 1, 2, 3
 DT_BF16, DT_F16, DT_F32 = 0, 1, 2
 SHARD_NONE, SHARD_COLUMN, SHARD_COLUMN_GATED, SHARD_ROW = 0, 1, 2, 3
 OK = 0

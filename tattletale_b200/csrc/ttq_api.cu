@@ -25,6 +25,8 @@ struct ttq_ctx {
     int *dev_status;  // device word the kernels OR failure bits into (bit 0: a bounded wait gave up)
     int *host_status; // pinned host copy of it, filled by the host entry points
     unsigned long long *trace;  // device timeline buffer, allocated only when TTQ_TRACE=1 is set at init
+    float *tq_x1, *tq_y1;       // TQ3: rotated activations [TQ3_SLAB][K] and raw results [TQ3_SLAB][N] (fp32; x1 also
+    int64_t tq_x1_cap, tq_y1_cap;  //   holds the fp16 form for the GEMM); capacities in floats, grown at weight creation
     __half *wimg;               // fp16 expansion of one whole weight (plain GEMM mode of the formats without a
     int64_t wimg_capacity;      //   fused dequant GEMM); in halves, grown when such a weight is created
     __half *xh;                 // fp16 activation scratch of the tcgen05 GEMM path
@@ -86,7 +88,8 @@ ttq_status cuda_fail(ttq_ctx *ctx, cudaError_t e, const char *what) {
         if (e__ != cudaSuccess) return cuda_fail(ctx, e__, #call); \
     } while (0)
 
-bool valid_fmt(int f) { return f == TTQ_FMT_Q8_0 || f == TTQ_FMT_Q4_K || f == TTQ_FMT_Q6_K; }
+bool valid_fmt(int f) { return f == TTQ_FMT_Q8_0 || f == TTQ_FMT_Q4_K || f == TTQ_FMT_Q6_K || f == TTQ_FMT_TQ3; }
+constexpr int64_t TQ3_SLAB = 512;  // rows of rotated activations / raw results the TQ3 scratch holds
 bool valid_dt(int d) { return d == TTQ_DT_BF16 || d == TTQ_DT_F16 || d == TTQ_DT_F32; }
 int dt_size(int d) { return d == TTQ_DT_F32 ? 4 : 2; }
 
@@ -100,7 +103,7 @@ ttq_status alloc_weight(ttq_ctx *ctx, int fmt, int64_t N, int64_t K, ttq_weight 
     w->K = K;
     w->NT = (N + TILE_ROWS - 1) / TILE_ROWS;
     w->SBp = (K + TILE_K - 1) / TILE_K;
-    w->tiled_bytes = (size_t)w->NT * w->SBp * tile_bytes(fmt);
+    w->tiled_bytes = fmt == TTQ_FMT_TQ3 ? (size_t)tq3_packed_bytes(N, K) : (size_t)w->NT * w->SBp * tile_bytes(fmt);
     w->tiles = nullptr;
     cudaError_t e = cudaMalloc(&w->tiles, w->tiled_bytes);
     if (e != cudaSuccess) {
@@ -125,6 +128,25 @@ ttq_status alloc_weight(ttq_ctx *ctx, int fmt, int64_t N, int64_t K, ttq_weight 
             ctx->wimg_capacity = need;
         }
     }
+    if (fmt == TTQ_FMT_TQ3) {
+        auto grow = [&](float **buf, int64_t *cap, int64_t need) -> cudaError_t {
+            if (need <= *cap) return cudaSuccess;
+            cudaDeviceSynchronize();
+            cudaFree(*buf);
+            *buf = nullptr;
+            *cap = 0;
+            cudaError_t ge = cudaMalloc(buf, (size_t)need * sizeof(float));
+            if (ge == cudaSuccess) *cap = need;
+            return ge;
+        };
+        e = grow(&ctx->tq_x1, &ctx->tq_x1_cap, TQ3_SLAB * K);
+        if (e == cudaSuccess) e = grow(&ctx->tq_y1, &ctx->tq_y1_cap, TQ3_SLAB * N);
+        if (e != cudaSuccess) {
+            cudaFree(w->tiles);
+            delete w;
+            return cuda_fail(ctx, e, "cudaMalloc(rotation scratch)");
+        }
+    }
     *out = w;
     return TTQ_OK;
 }
@@ -138,9 +160,65 @@ ttq_status check_create_args(ttq_ctx *ctx, int fmt, int64_t N, int64_t K, const 
     if (!valid_fmt(fmt)) return fail(ctx, TTQ_ERR_INVALID_ARG, "unknown format %d", fmt);
     if (N <= 0 || K <= 0) return fail(ctx, TTQ_ERR_SHAPE, "N and K must be positive (N=%lld K=%lld)", (long long)N, (long long)K);
     if (K % block_elems(fmt)) return fail(ctx, TTQ_ERR_SHAPE, "K=%lld is not a multiple of the block length %d", (long long)K, block_elems(fmt));
+    if (fmt == TTQ_FMT_TQ3 && N % 128) return fail(ctx, TTQ_ERR_SHAPE, "N=%lld is not a multiple of 128 (output rotation block)", (long long)N);
     if ((int64_t)nbytes != ttq_packed_bytes((ttq_format)fmt, N, K))
         return fail(ctx, TTQ_ERR_SHAPE, "nbytes=%zu but an [%lld][%lld] matrix of this format has %lld bytes", nbytes,
                     (long long)N, (long long)K, (long long)ttq_packed_bytes((ttq_format)fmt, N, K));
+    return TTQ_OK;
+}
+
+// y = out_scale * H_N(q . H_K(in_sign * x)) + bias in slabs of TQ3_SLAB rows: rotate in, multiply (decode kernel
+// for up to 32 rows, whole-weight expansion + plain tensor-core GEMM beyond), rotate out.
+ttq_status tq3_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_dev, int x_dt, int64_t M, int64_t ldx, const void *bias_dev,
+                       int bias_dt, void *y_dev, int y_dt, int64_t ldy, cudaStream_t st) {
+    const int64_t N = w->N, K = w->K;
+    const uint8_t *packed = w->tiles;
+    const __half *oscale = reinterpret_cast<const __half *>(packed + N * K * 3 / 8);
+    const uint8_t *isign = packed + N * K * 3 / 8 + 2 * N;
+    if (TQ3_SLAB * K > ctx->tq_x1_cap || TQ3_SLAB * N > ctx->tq_y1_cap)
+        return fail(ctx, TTQ_ERR_LIMIT, "rotation scratch smaller than this weight needs");
+    static const bool use_gemm = []() {
+        const char *v = getenv("TTQ_GEMM");
+        return !(v && v[0] == '0');
+    }();
+    const bool gemm = M > 2 * MAX_GEMV_M && use_gemm && ctx->wimg != nullptr &&
+                      gemm_wimg_rows(N) * w->SBp * TILE_K <= ctx->wimg_capacity;
+    cudaError_t e;
+    if (gemm) {
+        e = launch_tq3_wimg(packed, N, K, ctx->wimg, st);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "weight expansion launch");
+        ctx->launches++;
+    }
+    for (int64_t m0 = 0; m0 < M; m0 += TQ3_SLAB) {
+        const int64_t Ms = (M - m0) < TQ3_SLAB ? (M - m0) : TQ3_SLAB;
+        const uint8_t *xs = reinterpret_cast<const uint8_t *>(x_dev) + (size_t)m0 * ldx * dt_size(x_dt);
+        uint8_t *ys = reinterpret_cast<uint8_t *>(y_dev) + (size_t)m0 * ldy * dt_size(y_dt);
+        e = launch_tq3_rotate(xs, x_dt, Ms, K, ldx, isign, nullptr, nullptr, TTQ_DT_F32, ctx->tq_x1, gemm ? TTQ_DT_F16 : TTQ_DT_F32, K, st);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "input rotation launch");
+        ctx->launches++;
+        if (gemm) {
+            LinearArgs a;
+            a.tiles = nullptr;
+            a.N = N; a.K = K; a.NT = w->NT; a.SBp = w->SBp;
+            a.x = ctx->tq_x1; a.x_dt = TTQ_DT_F16; a.M = Ms; a.ldx = K;
+            a.bias = nullptr; a.bias_dt = TTQ_DT_F32;
+            a.y = ctx->tq_y1; a.y_dt = TTQ_DT_F32; a.ldy = N;
+            int launches = 0;
+            e = launch_gemm(w->fmt, a, ctx->xh, ctx->xh_capacity, ctx->sms, ctx->dev_status, ctx->trace, st, &launches, ctx->wimg);
+            ctx->launches += launches;
+            if (e != cudaSuccess) return cuda_fail(ctx, e, "linear forward (plain GEMM) launch");
+        } else {
+            for (int64_t r0 = 0; r0 < Ms; r0 += 8) {
+                const int rows = (int)((Ms - r0) < 8 ? (Ms - r0) : 8);
+                e = launch_tq3_gemv(packed, N, K, ctx->tq_x1 + r0 * K, rows, ctx->tq_y1 + r0 * N, st);
+                if (e != cudaSuccess) return cuda_fail(ctx, e, "decode-and-multiply launch");
+                ctx->launches++;
+            }
+        }
+        e = launch_tq3_rotate(ctx->tq_y1, TTQ_DT_F32, Ms, N, N, nullptr, oscale, bias_dev, bias_dt, ys, y_dt, ldy, st);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "output rotation launch");
+        ctx->launches++;
+    }
     return TTQ_OK;
 }
 
@@ -169,6 +247,7 @@ int64_t ttq_block_elems(ttq_format fmt) { return valid_fmt(fmt) ? block_elems(fm
 int64_t ttq_block_bytes(ttq_format fmt) { return valid_fmt(fmt) ? block_bytes(fmt) : 0; }
 int64_t ttq_packed_bytes(ttq_format fmt, int64_t N, int64_t K) {
     if (!valid_fmt(fmt) || N < 0 || K < 0 || K % block_elems(fmt)) return 0;
+    if (fmt == TTQ_FMT_TQ3) return N % 128 ? 0 : tq3_packed_bytes(N, K);
     return N * (K / block_elems(fmt)) * block_bytes(fmt);
 }
 
@@ -241,6 +320,8 @@ ttq_status ttq_destroy(ttq_ctx *ctx) {
     cudaFree(ctx->trace);
     cudaFree(ctx->xh);
     cudaFree(ctx->wimg);
+    cudaFree(ctx->tq_x1);
+    cudaFree(ctx->tq_y1);
     cudaFree(ctx->stage_x);
     cudaFree(ctx->stage_y);
     cudaFree(ctx->stage_b);
@@ -255,6 +336,16 @@ ttq_status ttq_weight_create_device(ttq_ctx *ctx, ttq_format fmt, int64_t N, int
     TTQ_CUDA(ctx, cudaSetDevice(ctx->device));
     ttq_weight *w = nullptr;
     if ((s = alloc_weight(ctx, fmt, N, K, &w)) != TTQ_OK) return s;
+    if (fmt == TTQ_FMT_TQ3) {
+        // kept as it is: tiles of a 16-row band are already contiguous along K
+        cudaError_t ce = cudaMemcpyAsync(w->tiles, dev_blocks, w->tiled_bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
+        if (ce != cudaSuccess) {
+            ttq_weight_destroy(w);
+            return cuda_fail(ctx, ce, "copy of the packed buffer");
+        }
+        *out = w;
+        return TTQ_OK;
+    }
     cudaError_t e = launch_repack(fmt, reinterpret_cast<const uint8_t *>(dev_blocks), w->tiles, N, K, w->NT, w->SBp,
                                   (cudaStream_t)stream);
     if (e != cudaSuccess) {
@@ -271,6 +362,20 @@ ttq_status ttq_weight_create(ttq_ctx *ctx, ttq_format fmt, int64_t N, int64_t K,
     ttq_status s = check_create_args(ctx, fmt, N, K, host_blocks, nbytes, out);
     if (s != TTQ_OK) return s;
     TTQ_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (fmt == TTQ_FMT_TQ3) {
+        if (shard && shard->kind != TTQ_SHARD_NONE)
+            return fail(ctx, TTQ_ERR_UNSUPPORTED, "ttq_shard is not applied to the trellis format: shard the buffer on the host");
+        ttq_weight *tw = nullptr;
+        if ((s = alloc_weight(ctx, fmt, N, K, &tw)) != TTQ_OK) return s;
+        cudaError_t ce = cudaMemcpyAsync(tw->tiles, host_blocks, nbytes, cudaMemcpyHostToDevice, ctx->host_stream);
+        if (ce == cudaSuccess) ce = cudaStreamSynchronize(ctx->host_stream);
+        if (ce != cudaSuccess) {
+            ttq_weight_destroy(tw);
+            return cuda_fail(ctx, ce, "upload of the packed buffer");
+        }
+        *out = tw;
+        return TTQ_OK;
+    }
     const int64_t be = block_elems(fmt), bb = block_bytes(fmt);
     const int64_t row_bytes = (K / be) * bb;
     const uint8_t *src = reinterpret_cast<const uint8_t *>(host_blocks);
@@ -359,7 +464,8 @@ ttq_status ttq_dequantize(ttq_ctx *ctx, const ttq_weight *w, float *dev_out, int
     if (!w || !dev_out) return fail(ctx, TTQ_ERR_INVALID_ARG, "weight or output pointer is NULL");
     if (w->ctx != ctx) return fail(ctx, TTQ_ERR_INVALID_ARG, "weight belongs to another context");
     if (ld < w->K) return fail(ctx, TTQ_ERR_SHAPE, "ld=%lld < K=%lld", (long long)ld, (long long)w->K);
-    cudaError_t e = launch_dequant(w->fmt, w->tiles, dev_out, ld, w->N, w->K, w->SBp, (cudaStream_t)stream);
+    cudaError_t e = w->fmt == TTQ_FMT_TQ3 ? launch_tq3_decode(w->tiles, w->N, w->K, dev_out, ld, (cudaStream_t)stream)
+                                          : launch_dequant(w->fmt, w->tiles, dev_out, ld, w->N, w->K, w->SBp, (cudaStream_t)stream);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "dequantize launch");
     ctx->launches++;
     return TTQ_OK;
@@ -383,6 +489,7 @@ ttq_status ttq_linear_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_d
         return fail(ctx, TTQ_ERR_LIMIT, "K=%lld exceeds the activation scratch capacity %lld", (long long)w->K,
                     (long long)ctx->xq_capacity_k);
     cudaStream_t st = (cudaStream_t)stream;
+    if (w->fmt == TTQ_FMT_TQ3) return tq3_forward(ctx, w, x_dev, x_dt, M, ldx, bias_dev, bias_dt, y_dev, y_dt, ldy, st);
     LinearArgs a;
     a.tiles = w->tiles;
     a.N = w->N; a.K = w->K; a.NT = w->NT; a.SBp = w->SBp;
@@ -558,6 +665,8 @@ ttq_status ttq_linear_forward_allreduce(ttq_ctx *ctx, const ttq_weight *w, const
     if (x_dt != TTQ_DT_BF16 && x_dt != TTQ_DT_F16) return fail(ctx, TTQ_ERR_INVALID_ARG, "x dtype must be bf16 or f16");
     if (!valid_dt(y_dt) || (bias_dev && !valid_dt(bias_dt))) return fail(ctx, TTQ_ERR_INVALID_ARG, "unknown dtype");
     if (ldx < w->K || ldy < w->N) return fail(ctx, TTQ_ERR_SHAPE, "leading dimension smaller than the row length");
+    if (w->fmt == TTQ_FMT_TQ3)
+        return fail(ctx, TTQ_ERR_UNSUPPORTED, "the fused exchange serves the block formats: use ttq_linear_forward and a library all-reduce");
     if (M > comm->view.m_cap || w->N > comm->view.n_cap)
         return fail(ctx, TTQ_ERR_UNSUPPORTED, "M=%lld / N=%lld exceed the exchange buffer (m_cap=%d, n_cap=%lld): use ttq_linear_forward and a library all-reduce",
                     (long long)M, (long long)w->N, comm->view.m_cap, (long long)comm->view.n_cap);

@@ -1031,6 +1031,10 @@ extern "C" TTQ_API ttq_status ttq_linear_forward_static(const ttq_weight *w, con
         set_msg(errbuf, errbuf_len, "unsupported dtype (x: bf16|f16; y, bias: bf16|f16|f32)");
         return TTQ_ERR_INVALID_ARG;
     }
+    if (w->fmt == TTQ_FMT_TQ3) {
+        set_msg(errbuf, errbuf_len, "the trellis format needs the context's rotation scratch: use ttq_linear_forward");
+        return TTQ_ERR_UNSUPPORTED;
+    }
     if (M > TTQ_STATIC_MAX_M || w->SBp * TILE_K > TTQ_STATIC_MAX_K) {
         set_msg(errbuf, errbuf_len, "ttq_linear_forward_static is limited to M <= 4 and K <= 16384 (fixed scratch array)");
         return TTQ_ERR_LIMIT;

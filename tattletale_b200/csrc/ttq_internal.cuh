@@ -52,7 +52,7 @@ constexpr int TILE_K = 256;
 __host__ __device__ constexpr int tile_bytes(int fmt) {
     return fmt == TTQ_FMT_Q8_0 ? 4352 : (fmt == TTQ_FMT_Q4_K ? 2304 : 3360);
 }
-__host__ __device__ constexpr int block_elems(int fmt) { return fmt == TTQ_FMT_Q8_0 ? 32 : 256; }
+__host__ __device__ constexpr int block_elems(int fmt) { return fmt == TTQ_FMT_Q8_0 ? 32 : (fmt == TTQ_FMT_TQ3 ? 128 : 256); }
 __host__ __device__ constexpr int block_bytes(int fmt) {
     return fmt == TTQ_FMT_Q8_0 ? 34 : (fmt == TTQ_FMT_Q4_K ? 144 : 210);
 }
@@ -133,6 +133,14 @@ struct GroupedArgs {
     int64_t ldy;
 };
 cudaError_t launch_gemm_grouped(const GroupedArgs &g, __half *xh, int sms, int *status, cudaStream_t st, int *launches);
+
+// Trellis-coded 3-bit format (ttq_tq3.cu); `packed` is the canonical buffer on the device.
+inline int64_t tq3_packed_bytes(int64_t N, int64_t K) { return N * K * 3 / 8 + 2 * N + K / 8; }
+cudaError_t launch_tq3_decode(const uint8_t *packed, int64_t N, int64_t K, float *out, int64_t ld, cudaStream_t st);
+cudaError_t launch_tq3_wimg(const uint8_t *packed, int64_t N, int64_t K, __half *wimg, cudaStream_t st);
+cudaError_t launch_tq3_rotate(const void *in, int in_dt, int64_t M, int64_t C, int64_t ld_in, const uint8_t *sign, const __half *scale,
+                              const void *bias, int bias_dt, void *out, int out_dt, int64_t ld_out, cudaStream_t st);
+cudaError_t launch_tq3_gemv(const uint8_t *packed, int64_t N, int64_t K, const float *x1, int rows, float *y1, cudaStream_t st);
 
 // Routing and combination of a mixture-of-experts layer (ttq_moe.cu).
 struct MoeRouting {

@@ -1,0 +1,212 @@
+// Trellis-coded 3-bit weights (TQ3): decode, Hadamard rotations and the decode-and-multiply kernel.
+//
+// Format (see include/ttq.h): W [N][K], N and K multiples of 128; one buffer of
+//   tiles [N/16][K/16][96 B] | out_scale [N] fp16 | in_sign [K/8] bytes.
+// Weight t = 16 r + c of a tile is coded by the 16-bit window at bit 3t of the tile's 768-bit stream
+// (zero beyond the end): state -> h = state * 2654435761 -> q = (sum of the 4 bytes of h - 510) / 147.8.
+// The operator is  y = out_scale * H_N( q . H_K(in_sign * x) ) + bias  with H the orthonormal Hadamard
+// transform on blocks of 128.  The device keeps the buffer as it is: tiles of one 16-row band are
+// contiguous along K, which is the order the kernels stream them in.
+//
+// Kernels
+//   tq3_decode_kernel     q as fp32 [N][ld] (test hook, bit-exact) or as fp16 tile images for the plain GEMM
+//   tq3_rotate_kernel     Hadamard-128 of activation rows (signs in, fp32 | fp16 out) and of result rows
+//                         (scale and bias out); one warp per 128 block, four values per lane
+//   tq3_gemv_kernel<MR>   M <= 8 rows per pass: one CTA per 16-row band, its 8 warps split K; a lane owns
+//                         8 consecutive weights of one row per tile (5 bytes of the stream), decodes them
+//                         with one multiply and one byte-sum each and accumulates in fp32
+//
+// The reference has no counterpart (a model configuration fixture names the format family only:
+// tests/fixtures/configs/config-GLM-4.7-EXL3-3.84bpw.json:43-54).
+#include "ttq_internal.cuh"
+
+namespace ttq {
+namespace {
+
+constexpr float TQ3_UNIT = 1.0f / 147.8f;
+constexpr int TQ3_TILE_BYTES = 96;
+
+__device__ __forceinline__ int tq3_isum(uint32_t state) {
+    const uint32_t h = state * 2654435761u;
+    return (int)__dp4a(h, 0x01010101u, 0u) - 510;
+}
+
+__device__ __forceinline__ uint32_t tq3_window(const uint8_t *tile, int t) {
+    const int bit = 3 * t, byte = bit >> 3;
+    uint32_t v = 0;
+#pragma unroll
+    for (int i = 0; i < 3; i++)
+        if (byte + i < TQ3_TILE_BYTES) v |= (uint32_t)tile[byte + i] << (8 * i);
+    return (v >> (bit & 7)) & 0xffffu;
+}
+
+// IMAGES = false: out is float [N][ld];  true: out is the fp16 tile-image layout of the plain GEMM
+// ([Kp/64][Np/8][1024 B], 128-byte swizzle, in-chunk K order 0 2 1 3 | 4 6 5 7), zero outside N x K.
+template <bool IMAGES>
+__global__ void __launch_bounds__(256) tq3_decode_kernel(const uint8_t *__restrict__ tiles, int64_t N, int64_t K, void *__restrict__ out,
+                                                         int64_t ld, int64_t Np, int64_t Kp) {
+    const int64_t tk = K / 16;
+    if (!IMAGES) {
+        const int64_t total = N * K;
+        for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+            const int64_t n = e / K, k = e % K;
+            const uint8_t *tb = tiles + ((n >> 4) * tk + (k >> 4)) * TQ3_TILE_BYTES;
+            reinterpret_cast<float *>(out)[n * ld + k] = (float)tq3_isum(tq3_window(tb, (int)((n & 15) * 16 + (k & 15)))) * TQ3_UNIT;
+        }
+    } else {
+        const int64_t total = Np * (Kp / 8);
+        for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < total; c += (int64_t)gridDim.x * blockDim.x) {
+            const int j = (int)(c & 7);
+            const int64_t n = (c >> 3) % Np, it = (c >> 3) / Np;
+            const int64_t k0 = (it >> 2) * 256 + 32 * j + 8 * (it & 3);  // 8 consecutive K: half a tile row
+            __half o[8];
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                const int i = (q & 4) + ((q & 1) << 1) + ((q & 2) >> 1);
+                float v = 0.f;
+                if (n < N && k0 + i < K) {
+                    const uint8_t *tb = tiles + ((n >> 4) * tk + ((k0 + i) >> 4)) * TQ3_TILE_BYTES;
+                    v = (float)tq3_isum(tq3_window(tb, (int)((n & 15) * 16 + ((k0 + i) & 15)))) * TQ3_UNIT;
+                }
+                o[q] = __float2half_rn(v);
+            }
+            const int64_t dst = ((it * (Np >> 3) + (n >> 3)) << 10) + ((n & 7) << 7) + ((int64_t)(j ^ (int)(n & 7)) << 4);
+            *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(out) + dst) = *reinterpret_cast<const uint4 *>(o);
+        }
+    }
+}
+
+// One warp per (row, block of 128): out = H128(in * sign) * scale + bias.
+//   in:  [M][ld_in] of in_dt;  sign: bit per column or nullptr;  scale: fp16 per column or nullptr;
+//   bias: per column of bias_dt or nullptr;  out: [M][ld_out] of out_dt.
+__global__ void __launch_bounds__(256) tq3_rotate_kernel(const void *__restrict__ in, int in_dt, int64_t M, int64_t C, int64_t ld_in,
+                                                         const uint8_t *__restrict__ sign, const __half *__restrict__ scale,
+                                                         const void *__restrict__ bias, int bias_dt, void *__restrict__ out, int out_dt,
+                                                         int64_t ld_out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t blocks_per_row = C / 128, total = M * blocks_per_row;
+    for (int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < total; w += ((int64_t)gridDim.x * blockDim.x) >> 5) {
+        const int64_t m = w / blocks_per_row, c0 = (w % blocks_per_row) * 128 + 4 * lane;
+        float v[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) v[i] = load_as_float(in, in_dt, m * ld_in + c0 + i);
+        if (sign != nullptr) {
+            const uint32_t bits = (uint32_t)sign[c0 >> 3] >> (c0 & 7);
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                if ((bits >> i) & 1) v[i] = -v[i];
+        }
+        // strides 1 and 2 inside the lane, 4 .. 64 across lanes
+        float a = v[0] + v[1], b = v[0] - v[1], c = v[2] + v[3], d = v[2] - v[3];
+        v[0] = a + c; v[2] = a - c; v[1] = b + d; v[3] = b - d;
+#pragma unroll
+        for (int s = 1; s < 32; s <<= 1) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float o = __shfl_xor_sync(0xffffffffu, v[i], s);
+                v[i] = (lane & s) ? o - v[i] : v[i] + o;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float r = v[i] * 0.08838834764831845f;
+            if (scale != nullptr) r *= __half2float(scale[c0 + i]);
+            if (bias != nullptr) r += load_as_float(bias, bias_dt, c0 + i);
+            store_from_float(out, out_dt, m * ld_out + c0 + i, r);
+        }
+    }
+}
+
+// y1 [MR][N] (fp32) = q . x1^T for rows m0 .. m0+MR-1 of x1 [M][K] (fp32, already rotated).
+template <int MR>
+__global__ void __launch_bounds__(256) tq3_gemv_kernel(const uint8_t *__restrict__ tiles, int64_t N, int64_t K, const float *__restrict__ x1,
+                                                       float *__restrict__ y1) {
+    __shared__ float red[8][16][MR];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t tk = K / 16, band = blockIdx.x;
+    const uint8_t *band_base = tiles + band * tk * TQ3_TILE_BYTES;
+    // the lane's 8 weights: row lane / 2 of the tile, columns 8 * (lane & 1) .. + 7 -> stream bits 24 * lane .. + 36
+    const int bo = 3 * lane, wo = bo & ~3, sh = (bo & 3) * 8;
+    const int64_t t_begin = tk * warp / 8, t_end = tk * (warp + 1) / 8;
+    float acc[MR];
+#pragma unroll
+    for (int m = 0; m < MR; m++) acc[m] = 0.f;
+#pragma unroll 4
+    for (int64_t tile = t_begin; tile < t_end; tile++) {
+        const uint8_t *tb = band_base + tile * TQ3_TILE_BYTES;
+        const uint32_t w0 = *reinterpret_cast<const uint32_t *>(tb + wo);
+        const uint32_t w1 = wo + 4 < TQ3_TILE_BYTES ? *reinterpret_cast<const uint32_t *>(tb + wo + 4) : 0u;
+        const uint64_t v = (((uint64_t)w1 << 32) | w0) >> sh;
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) f[i] = (float)tq3_isum((uint32_t)(v >> (3 * i)) & 0xffffu);
+        const int64_t k = tile * 16 + 8 * (lane & 1);
+#pragma unroll
+        for (int m = 0; m < MR; m++) {
+            const float4 xa = __ldg(reinterpret_cast<const float4 *>(x1 + m * K + k));
+            const float4 xb = __ldg(reinterpret_cast<const float4 *>(x1 + m * K + k + 4));
+            float s = acc[m];
+            s = fmaf(f[0], xa.x, s); s = fmaf(f[1], xa.y, s); s = fmaf(f[2], xa.z, s); s = fmaf(f[3], xa.w, s);
+            s = fmaf(f[4], xb.x, s); s = fmaf(f[5], xb.y, s); s = fmaf(f[6], xb.z, s); s = fmaf(f[7], xb.w, s);
+            acc[m] = s;
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MR; m++) {
+        acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], 1);
+        if ((lane & 1) == 0) red[warp][lane >> 1][m] = acc[m];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 16 * MR; i += blockDim.x) {
+        const int r = i / MR, m = i % MR;
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; w++) s += red[w][r][m];
+        y1[(int64_t)m * N + band * 16 + r] = s * TQ3_UNIT;
+    }
+}
+
+unsigned grid_of(int64_t items, int per_block, int cap) {
+    int64_t b = (items + per_block - 1) / per_block;
+    if (b < 1) b = 1;
+    return (unsigned)(b < cap ? b : cap);
+}
+
+}  // namespace
+
+cudaError_t launch_tq3_decode(const uint8_t *packed, int64_t N, int64_t K, float *out, int64_t ld, cudaStream_t st) {
+    tq3_decode_kernel<false><<<grid_of(N * K, 256 * 4, 148 * 32), 256, 0, st>>>(packed, N, K, out, ld, 0, 0);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_tq3_wimg(const uint8_t *packed, int64_t N, int64_t K, __half *wimg, cudaStream_t st) {
+    const int64_t Np = gemm_wimg_rows(N), Kp = (K + TILE_K - 1) / TILE_K * TILE_K;
+    tq3_decode_kernel<true><<<grid_of(Np * (Kp / 8), 256, 148 * 32), 256, 0, st>>>(packed, N, K, wimg, 0, Np, Kp);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_tq3_rotate(const void *in, int in_dt, int64_t M, int64_t C, int64_t ld_in, const uint8_t *sign, const __half *scale,
+                              const void *bias, int bias_dt, void *out, int out_dt, int64_t ld_out, cudaStream_t st) {
+    tq3_rotate_kernel<<<grid_of(M * (C / 128), 8, 148 * 16), 256, 0, st>>>(in, in_dt, M, C, ld_in, sign, scale, bias, bias_dt, out, out_dt,
+                                                                           ld_out);
+    return cudaGetLastError();
+}
+
+// rows m0 .. m0 + rows - 1 (rows <= 8) of x1 [.][K] -> y1 [.][N]
+cudaError_t launch_tq3_gemv(const uint8_t *packed, int64_t N, int64_t K, const float *x1, int rows, float *y1, cudaStream_t st) {
+    const unsigned grid = (unsigned)(N / 16);
+    switch (rows) {
+        case 1: tq3_gemv_kernel<1><<<grid, 256, 0, st>>>(packed, N, K, x1, y1); break;
+        case 2: tq3_gemv_kernel<2><<<grid, 256, 0, st>>>(packed, N, K, x1, y1); break;
+        case 3: tq3_gemv_kernel<3><<<grid, 256, 0, st>>>(packed, N, K, x1, y1); break;
+        case 4: tq3_gemv_kernel<4><<<grid, 256, 0, st>>>(packed, N, K, x1, y1); break;
+        case 5: tq3_gemv_kernel<5><<<grid, 256, 0, st>>>(packed, N, K, x1, y1); break;
+        case 6: tq3_gemv_kernel<6><<<grid, 256, 0, st>>>(packed, N, K, x1, y1); break;
+        case 7: tq3_gemv_kernel<7><<<grid, 256, 0, st>>>(packed, N, K, x1, y1); break;
+        case 8: tq3_gemv_kernel<8><<<grid, 256, 0, st>>>(packed, N, K, x1, y1); break;
+        default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace ttq

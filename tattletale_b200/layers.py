@@ -76,12 +76,17 @@ class QuantLinear:
     """
 
     def __init__(self, ctx: Context, fmt: int, blocks: torch.Tensor, in_features: int,
-                 bias: Optional[torch.Tensor] = None, shard: Optional[tuple[int, int, int]] = None):
-        if blocks.dtype != torch.uint8 or blocks.dim() != 2:
+                 bias: Optional[torch.Tensor] = None, shard: Optional[tuple[int, int, int]] = None,
+                 out_features: Optional[int] = None):
+        if fmt == _lib.FMT_TQ3:
+            # one flat buffer (tiles | out_scale | in_sign): the row count cannot be read off its shape
+            if blocks.dtype != torch.uint8 or blocks.dim() != 1 or out_features is None:
+                raise TtqError(1, "the trellis format takes a 1-D uint8 buffer and out_features")
+        elif blocks.dtype != torch.uint8 or blocks.dim() != 2:
             raise TtqError(1, "blocks must be a 2-D uint8 tensor [out_features, bytes_per_row]")
         self.ctx, self.fmt = ctx, fmt
         lib = ctx._lib
-        n, k = int(blocks.shape[0]), int(in_features)
+        n, k = int(out_features if fmt == _lib.FMT_TQ3 else blocks.shape[0]), int(in_features)
         blocks = blocks.contiguous()
         h = ctypes.c_void_p()
         if blocks.is_cuda:
