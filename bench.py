@@ -618,6 +618,95 @@ def moe_arm(args):
     _finish_distributed(dist, world)
 
 
+def trellis_arm(args):
+    """Trellis-coded 3-bit linears on the Llama-3-70B projection shapes (BASELINE.json configs[3]): 8192->10240,
+    8192->8192, 8192->57344, 28672->8192 at M = --m rows, weights N(0, 0.015) coded by the package's beam-search
+    encoder (or uniformly random code bits with --trellis-codes random: the kernels' speed does not depend on
+    the bit values).  One step = one pass over --layers layers of four linears."""
+    import tattletale_b200 as ttq
+    from tattletale_b200 import formats
+    from tattletale_b200 import quantize as Q
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    ctx = ttq.Context(0)
+    shapes = [(8192, 10240), (8192, 8192), (8192, 57344), (28672, 8192)]
+    n_layers = args.layers if args.layers != 32 else 2
+    m = args.m
+    lins = []
+    t_enc = time.perf_counter()
+    for layer in range(n_layers):
+        for idx, (k, n) in enumerate(shapes):
+            g = torch.Generator(device=dev).manual_seed(4000 + 16 * layer + idx)
+            if args.trellis_codes == "random":
+                packed = torch.randint(0, 256, (formats.packed_bytes(ttq.FMT_TQ3, n, k),), generator=g, device=dev, dtype=torch.uint8)
+                sc = (torch.randn(n, generator=g, device=dev) * 0.015).to(torch.float16)
+                packed[n * k * 3 // 8: n * k * 3 // 8 + 2 * n] = sc.view(torch.uint8)
+            else:
+                w = torch.randn(n, k, generator=g, device=dev) * 0.015
+                packed = Q.quantize_tq3(w, seed=4000 + idx, beam=4, tile_chunk=1 << 16)
+                del w
+            lins.append((k, n, ttq.QuantLinear(ctx, ttq.FMT_TQ3, packed, k, out_features=n)))
+            del packed
+    torch.cuda.synchronize()
+    t_enc = time.perf_counter() - t_enc
+    xs = {k: torch.randn(m, k, device=dev).to(torch.bfloat16) for k in (8192, 28672)}
+    ys = {n: torch.empty(m, n, dtype=torch.bfloat16, device=dev) for n in (10240, 8192, 57344)}
+
+    def step():
+        for k, n, lin in lins:
+            lin.forward(xs[k], out=ys[n])
+
+    step()
+    torch.cuda.synchronize()
+    c0 = ctx.launch_count
+    step()
+    torch.cuda.synchronize()
+    launches_per_step = ctx.launch_count - c0
+    for _ in range(max(args.warmup, 3)):
+        step()
+    steps = min(args.steps, 100)
+    sampler = ClockSampler(visible_physical_index(0))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.start()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms_step = e0.elapsed_time(e1) / steps
+    ctx.check_device_status()
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    w_bytes = sum(formats.packed_bytes(ttq.FMT_TQ3, n, k) for k, n, _ in lins)
+    io_bytes = sum(m * k * 2 + m * n * 2 for k, n, _ in lins)
+    flops = sum(2.0 * m * n * k for k, n, _ in lins)
+    gbs = (w_bytes + io_bytes) / (ms_step * 1e-3) / 1e9
+    tf = flops / (ms_step * 1e-3) / 1e12
+    hbm_bound = m <= 32
+    roof = ({"bound": "hbm", "achieved": round(gbs, 1), "peak": float(peaks.get("hbm_gbs", 6650.0)), "unit": "GB/s"} if hbm_bound else
+            {"bound": "tensor", "achieved": round(tf, 1), "peak": float(peaks.get("bf16_tflops", 1590.0)), "unit": "TFLOP/s"})
+    roof["frac"] = round(roof["achieved"] / roof["peak"], 4)
+    roof["traffic"] = None
+    roof["kernel"] = "tq3_gemv_kernel (decode-and-multiply)" if hbm_bound else "tq3_decode_kernel (expansion) + gemm kernel (plain mode)"
+    line = {
+        "metric": "trellis 3-bit linear GB/s" if hbm_bound else "trellis 3-bit linear TFLOP/s",
+        "value": round(gbs, 1) if hbm_bound else round(tf, 1), "unit": "GB/s" if hbm_bound else "TFLOP/s", "n_gpus": 1,
+        "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32" if hbm_bound else "f16", "data": "synthetic",
+        "config": {"workload": f"Llama-3-70B projection shapes, trellis-coded 3.0 bits/weight, M={m}, {n_layers} layers x 4 linears",
+                   "shapes_k_to_n": [[k, n] for k, n in shapes], "M": m, "layers": n_layers, "codes": args.trellis_codes,
+                   "l2": f"{w_bytes / 1e6:.0f} MB of packed weights per step, larger than L2", "encode_seconds": round(t_enc, 1)},
+        "roofline": roof, "gpu_launches": int(launches_per_step * steps), "launches_per_step": int(launches_per_step), "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def _finish_distributed(dist, world):
     """Leave a multi-rank run without tearing NCCL down: a captured graph still references the communicator,
     and destroying the process group under it has been seen to block; the process simply exits."""
@@ -636,9 +725,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=1, help="decode batch (rows of x)")
-    ap.add_argument("--workload", default="linears", choices=["linears", "decode", "moe"],
+    ap.add_argument("--workload", default="linears", choices=["linears", "decode", "moe", "trellis"],
                     help="linears: the headline Q4_K GEMV pass (default); decode: full decoder stack, tokens/s; "
-                         "moe: one mixture-of-experts layer, TFLOP/s")
+                         "moe: one mixture-of-experts layer, TFLOP/s; trellis: trellis-coded 3-bit linears on 70B shapes")
+    ap.add_argument("--trellis-codes", default="encoded", choices=["encoded", "random"],
+                    help="trellis workload: code bits from the beam-search encoder or uniformly random")
     ap.add_argument("--tokens", type=int, default=4096, help="moe workload: tokens per step (all ranks together)")
     ap.add_argument("--batch", type=int, default=1, help="decode workload: sequences decoded together")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
@@ -656,6 +747,8 @@ def main():
         decode_arm(args)
     elif args.workload == "moe":
         moe_arm(args)
+    elif args.workload == "trellis":
+        trellis_arm(args)
     else:
         ours_arm(args)
 

@@ -89,6 +89,7 @@ ttq_status cuda_fail(ttq_ctx *ctx, cudaError_t e, const char *what) {
     } while (0)
 
 bool valid_fmt(int f) { return f == TTQ_FMT_Q8_0 || f == TTQ_FMT_Q4_K || f == TTQ_FMT_Q6_K || f == TTQ_FMT_TQ3; }
+constexpr int64_t TQ3_GEMV_MAX_M = 4;
 constexpr int64_t TQ3_SLAB = 512;  // rows of rotated activations / raw results the TQ3 scratch holds
 bool valid_dt(int d) { return d == TTQ_DT_BF16 || d == TTQ_DT_F16 || d == TTQ_DT_F32; }
 int dt_size(int d) { return d == TTQ_DT_F32 ? 4 : 2; }
@@ -181,7 +182,9 @@ ttq_status tq3_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_dev, int
         const char *v = getenv("TTQ_GEMM");
         return !(v && v[0] == '0');
     }();
-    const bool gemm = M > 2 * MAX_GEMV_M && use_gemm && ctx->wimg != nullptr &&
+    // the decode-and-multiply kernel re-decodes every weight per 8 rows; beyond TQ3_GEMV_MAX_M rows one expansion
+    // to fp16 and the tensor-core GEMM is cheaper
+    const bool gemm = M > TQ3_GEMV_MAX_M && use_gemm && ctx->wimg != nullptr &&
                       gemm_wimg_rows(N) * w->SBp * TILE_K <= ctx->wimg_capacity;
     cudaError_t e;
     if (gemm) {
@@ -208,8 +211,8 @@ ttq_status tq3_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_dev, int
             ctx->launches += launches;
             if (e != cudaSuccess) return cuda_fail(ctx, e, "linear forward (plain GEMM) launch");
         } else {
-            for (int64_t r0 = 0; r0 < Ms; r0 += 8) {
-                const int rows = (int)((Ms - r0) < 8 ? (Ms - r0) : 8);
+            for (int64_t r0 = 0; r0 < Ms; r0 += TQ3_GEMV_MAX_M) {
+                const int rows = (int)((Ms - r0) < TQ3_GEMV_MAX_M ? (Ms - r0) : TQ3_GEMV_MAX_M);
                 e = launch_tq3_gemv(packed, N, K, ctx->tq_x1 + r0 * K, rows, ctx->tq_y1 + r0 * N, st);
                 if (e != cudaSuccess) return cuda_fail(ctx, e, "decode-and-multiply launch");
                 ctx->launches++;

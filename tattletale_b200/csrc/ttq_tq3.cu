@@ -12,9 +12,9 @@
 //   tq3_decode_kernel     q as fp32 [N][ld] (test hook, bit-exact) or as fp16 tile images for the plain GEMM
 //   tq3_rotate_kernel     Hadamard-128 of activation rows (signs in, fp32 | fp16 out) and of result rows
 //                         (scale and bias out); one warp per 128 block, four values per lane
-//   tq3_gemv_kernel<MR>   M <= 8 rows per pass: one CTA per 16-row band, its 8 warps split K; a lane owns
-//                         8 consecutive weights of one row per tile (5 bytes of the stream), decodes them
-//                         with one multiply and one byte-sum each and accumulates in fp32
+//   tq3_gemv_kernel<MR>   M <= 4 rows per pass: one CTA per 16-row band, its 8 warps split K; a lane owns two
+//                         rows of a tile (32 weights = 3 words of the stream), decodes each weight with one
+//                         multiply and one byte-sum and accumulates in fp32
 //
 // The reference has no counterpart (a model configuration fixture names the format family only:
 // tests/fixtures/configs/config-GLM-4.7-EXL3-3.84bpw.json:43-54).
@@ -29,6 +29,22 @@ constexpr int TQ3_TILE_BYTES = 96;
 __device__ __forceinline__ int tq3_isum(uint32_t state) {
     const uint32_t h = state * 2654435761u;
     return (int)__dp4a(h, 0x01010101u, 0u) - 510;
+}
+
+// The 8 consecutive weights whose stream bits start at byte `bo` = 3 * (2 r + c / 8) of a tile (row r, columns
+// c .. c + 7, c = 0 | 8): returns sum - 510 of each as an exact float.  Two aligned 32-bit loads cover the 37
+// bits; the byte sum lands on the mantissa of 2^23 (the dp4a accumulator), so one subtraction replaces the
+// integer-to-float conversion.
+__device__ __forceinline__ void tq3_decode8(const uint8_t *tile, int bo, float (&f)[8]) {
+    const int wo = bo & ~3, sh = (bo & 3) * 8;
+    const uint32_t w0 = *reinterpret_cast<const uint32_t *>(tile + wo);
+    const uint32_t w1 = wo + 4 < TQ3_TILE_BYTES ? *reinterpret_cast<const uint32_t *>(tile + wo + 4) : 0u;
+    const uint32_t lo = __funnelshift_r(w0, w1, sh), hi = w1 >> sh;  // stream bits 8 bo .. 8 bo + 63 (zero-extended)
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const uint32_t st = (3 * i + 16 <= 32 ? (lo >> (3 * i)) : __funnelshift_r(lo, hi, 3 * i)) & 0xffffu;
+        f[i] = __int_as_float((int)__dp4a(st * 2654435761u, 0x01010101u, 0x4B000000u)) - 8389118.0f;  // 2^23 + 510
+    }
 }
 
 __device__ __forceinline__ uint32_t tq3_window(const uint8_t *tile, int t) {
@@ -59,17 +75,12 @@ __global__ void __launch_bounds__(256) tq3_decode_kernel(const uint8_t *__restri
             const int j = (int)(c & 7);
             const int64_t n = (c >> 3) % Np, it = (c >> 3) / Np;
             const int64_t k0 = (it >> 2) * 256 + 32 * j + 8 * (it & 3);  // 8 consecutive K: half a tile row
+            float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (n < N && k0 < K)  // K is a multiple of 16: the 8 values are inside or outside together
+                tq3_decode8(tiles + ((n >> 4) * tk + (k0 >> 4)) * TQ3_TILE_BYTES, 3 * (2 * (int)(n & 15) + (int)((k0 >> 3) & 1)), f);
             __half o[8];
 #pragma unroll
-            for (int q = 0; q < 8; q++) {
-                const int i = (q & 4) + ((q & 1) << 1) + ((q & 2) >> 1);
-                float v = 0.f;
-                if (n < N && k0 + i < K) {
-                    const uint8_t *tb = tiles + ((n >> 4) * tk + ((k0 + i) >> 4)) * TQ3_TILE_BYTES;
-                    v = (float)tq3_isum(tq3_window(tb, (int)((n & 15) * 16 + ((k0 + i) & 15)))) * TQ3_UNIT;
-                }
-                o[q] = __float2half_rn(v);
-            }
+            for (int q = 0; q < 8; q++) o[q] = __float2half_rn(f[(q & 4) + ((q & 1) << 1) + ((q & 2) >> 1)] * TQ3_UNIT);
             const int64_t dst = ((it * (Np >> 3) + (n >> 3)) << 10) + ((n & 7) << 7) + ((int64_t)(j ^ (int)(n & 7)) << 4);
             *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(out) + dst) = *reinterpret_cast<const uint4 *>(o);
         }
@@ -117,45 +128,63 @@ __global__ void __launch_bounds__(256) tq3_rotate_kernel(const void *__restrict_
     }
 }
 
-// y1 [MR][N] (fp32) = q . x1^T for rows m0 .. m0+MR-1 of x1 [M][K] (fp32, already rotated).
+// y1 [MR][N] (fp32) = q . x1^T for MR rows of x1 [.][K] (fp32, already rotated).
+// One CTA per 16-row band, its 8 warps split K.  Per iteration a warp covers 4 tiles: lane (g, j) = (lane / 8,
+// lane % 8) owns rows 2j and 2j+1 of tile g -- 32 weights = exactly three 32-bit words of the stream plus the
+// 13 bits of the next word its last windows reach into.
 template <int MR>
 __global__ void __launch_bounds__(256) tq3_gemv_kernel(const uint8_t *__restrict__ tiles, int64_t N, int64_t K, const float *__restrict__ x1,
                                                        float *__restrict__ y1) {
     __shared__ float red[8][16][MR];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 3, j = lane & 7;
     const int64_t tk = K / 16, band = blockIdx.x;
     const uint8_t *band_base = tiles + band * tk * TQ3_TILE_BYTES;
-    // the lane's 8 weights: row lane / 2 of the tile, columns 8 * (lane & 1) .. + 7 -> stream bits 24 * lane .. + 36
-    const int bo = 3 * lane, wo = bo & ~3, sh = (bo & 3) * 8;
     const int64_t t_begin = tk * warp / 8, t_end = tk * (warp + 1) / 8;
-    float acc[MR];
+    float acc[MR][2];
 #pragma unroll
-    for (int m = 0; m < MR; m++) acc[m] = 0.f;
-#pragma unroll 4
-    for (int64_t tile = t_begin; tile < t_end; tile++) {
-        const uint8_t *tb = band_base + tile * TQ3_TILE_BYTES;
-        const uint32_t w0 = *reinterpret_cast<const uint32_t *>(tb + wo);
-        const uint32_t w1 = wo + 4 < TQ3_TILE_BYTES ? *reinterpret_cast<const uint32_t *>(tb + wo + 4) : 0u;
-        const uint64_t v = (((uint64_t)w1 << 32) | w0) >> sh;
-        float f[8];
+    for (int m = 0; m < MR; m++) acc[m][0] = acc[m][1] = 0.f;
+#pragma unroll 2
+    for (int64_t t0 = t_begin; t0 < t_end; t0 += 4) {
+        const int64_t tile = t0 + g;
+        if (tile < t_end) {
+            const uint32_t *tw = reinterpret_cast<const uint32_t *>(band_base + tile * TQ3_TILE_BYTES) + 3 * j;
+            uint32_t w[5];
+            w[0] = tw[0]; w[1] = tw[1]; w[2] = tw[2];
+            w[3] = j < 7 ? tw[3] : 0u;  // the stream ends with the tile
+            w[4] = 0u;
+            float f[32];
 #pragma unroll
-        for (int i = 0; i < 8; i++) f[i] = (float)tq3_isum((uint32_t)(v >> (3 * i)) & 0xffffu);
-        const int64_t k = tile * 16 + 8 * (lane & 1);
+            for (int i = 0; i < 32; i++) {
+                const int word = (3 * i) >> 5, off = (3 * i) & 31;
+                const uint32_t st = (off + 16 <= 32 ? (w[word] >> off) : __funnelshift_r(w[word], w[word + 1], off)) & 0xffffu;
+                f[i] = __int_as_float((int)__dp4a(st * 2654435761u, 0x01010101u, 0x4B000000u)) - 8389118.0f;
+            }
 #pragma unroll
-        for (int m = 0; m < MR; m++) {
-            const float4 xa = __ldg(reinterpret_cast<const float4 *>(x1 + m * K + k));
-            const float4 xb = __ldg(reinterpret_cast<const float4 *>(x1 + m * K + k + 4));
-            float s = acc[m];
-            s = fmaf(f[0], xa.x, s); s = fmaf(f[1], xa.y, s); s = fmaf(f[2], xa.z, s); s = fmaf(f[3], xa.w, s);
-            s = fmaf(f[4], xb.x, s); s = fmaf(f[5], xb.y, s); s = fmaf(f[6], xb.z, s); s = fmaf(f[7], xb.w, s);
-            acc[m] = s;
+            for (int m = 0; m < MR; m++) {
+                const float4 *xp = reinterpret_cast<const float4 *>(x1 + m * K + tile * 16);
+                float s0 = acc[m][0], s1 = acc[m][1];
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const float4 xv = __ldg(xp + q);
+                    s0 = fmaf(f[4 * q], xv.x, s0); s0 = fmaf(f[4 * q + 1], xv.y, s0);
+                    s0 = fmaf(f[4 * q + 2], xv.z, s0); s0 = fmaf(f[4 * q + 3], xv.w, s0);
+                    s1 = fmaf(f[16 + 4 * q], xv.x, s1); s1 = fmaf(f[16 + 4 * q + 1], xv.y, s1);
+                    s1 = fmaf(f[16 + 4 * q + 2], xv.z, s1); s1 = fmaf(f[16 + 4 * q + 3], xv.w, s1);
+                }
+                acc[m][0] = s0; acc[m][1] = s1;
+            }
         }
     }
 #pragma unroll
-    for (int m = 0; m < MR; m++) {
-        acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], 1);
-        if ((lane & 1) == 0) red[warp][lane >> 1][m] = acc[m];
-    }
+    for (int m = 0; m < MR; m++)
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            float s = acc[m][r];
+            s += __shfl_xor_sync(0xffffffffu, s, 8);
+            s += __shfl_xor_sync(0xffffffffu, s, 16);
+            if (g == 0) red[warp][2 * j + r][m] = s;
+        }
     __syncthreads();
     for (int i = threadIdx.x; i < 16 * MR; i += blockDim.x) {
         const int r = i / MR, m = i % MR;
@@ -192,7 +221,7 @@ cudaError_t launch_tq3_rotate(const void *in, int in_dt, int64_t M, int64_t C, i
     return cudaGetLastError();
 }
 
-// rows m0 .. m0 + rows - 1 (rows <= 8) of x1 [.][K] -> y1 [.][N]
+// `rows` (1..4) rows of x1 [.][K] -> y1 [.][N]
 cudaError_t launch_tq3_gemv(const uint8_t *packed, int64_t N, int64_t K, const float *x1, int rows, float *y1, cudaStream_t st) {
     const unsigned grid = (unsigned)(N / 16);
     switch (rows) {
@@ -200,10 +229,6 @@ cudaError_t launch_tq3_gemv(const uint8_t *packed, int64_t N, int64_t K, const f
         case 2: tq3_gemv_kernel<2><<<grid, 256, 0, st>>>(packed, N, K, x1, y1); break;
         case 3: tq3_gemv_kernel<3><<<grid, 256, 0, st>>>(packed, N, K, x1, y1); break;
         case 4: tq3_gemv_kernel<4><<<grid, 256, 0, st>>>(packed, N, K, x1, y1); break;
-        case 5: tq3_gemv_kernel<5><<<grid, 256, 0, st>>>(packed, N, K, x1, y1); break;
-        case 6: tq3_gemv_kernel<6><<<grid, 256, 0, st>>>(packed, N, K, x1, y1); break;
-        case 7: tq3_gemv_kernel<7><<<grid, 256, 0, st>>>(packed, N, K, x1, y1); break;
-        case 8: tq3_gemv_kernel<8><<<grid, 256, 0, st>>>(packed, N, K, x1, y1); break;
         default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();

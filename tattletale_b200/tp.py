@@ -151,3 +151,35 @@ class ExpertParallelMoE:
         slots[order] = back.float()
         y = (slots.view(t, k, -1) * topk_weights.reshape(t, k, 1).float()).sum(dim=1)
         return y.to(x.dtype)
+
+
+def shard_trellis(packed: torch.Tensor, out_features: int, in_features: int, kind: int, rank: int, world: int):
+    """Tensor-parallel slice of a trellis-coded (TTQ_FMT_TQ3) buffer: returns (local buffer, local N, local K).
+
+    COLUMN keeps rows ``[rank * N/P, (rank + 1) * N/P)`` (tiles and out_scale of those rows, all of in_sign);
+    ROW keeps the K columns of the rank (tile columns and in_sign of the slice, all of out_scale) -- the output
+    rotation and scale are linear, so the ranks' results simply add.  Slices must be multiples of 128, the
+    Hadamard block, so that a shard rotates locally.
+    """
+    n, k = out_features, in_features
+    tiles_end = n * k * 3 // 8
+    tiles = packed[:tiles_end].reshape(n // 16, k // 16, 96)
+    scale = packed[tiles_end:tiles_end + 2 * n]
+    sign = packed[tiles_end + 2 * n:]
+    if kind == SHARD_NONE or world == 1:
+        return packed, n, k
+    if not 0 <= rank < world:
+        raise ValueError(f"bad rank {rank} of {world}")
+    if kind == SHARD_COLUMN:
+        if n % (128 * world):
+            raise ValueError("out_features / world must be a multiple of 128")
+        nl = n // world
+        t = tiles[rank * nl // 16:(rank + 1) * nl // 16]
+        return torch.cat((t.reshape(-1), scale[2 * rank * nl:2 * (rank + 1) * nl], sign)), nl, k
+    if kind == SHARD_ROW:
+        if k % (128 * world):
+            raise ValueError("in_features / world must be a multiple of 128")
+        kl = k // world
+        t = tiles[:, rank * kl // 16:(rank + 1) * kl // 16]
+        return torch.cat((t.reshape(-1), scale, sign[rank * kl // 8:(rank + 1) * kl // 8])), n, kl
+    raise ValueError(f"shard kind {kind} does not apply to the trellis format")

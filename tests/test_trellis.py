@@ -72,3 +72,27 @@ def test_beam_encoder_is_a_valid_code_close_to_the_exact_search():
     rel_exact = np.linalg.norm(oracle.tq3_effective_weight(exact, n, k) - w) / np.linalg.norm(w)
     assert rel_exact < 0.2
     assert rel_beam < 1.35 * rel_exact
+
+
+def test_tensor_parallel_slices_add_up():
+    """Column slices concatenate and row slices sum to the full operator (host-side shard helper + checker)."""
+    from tattletale_b200 import SHARD_COLUMN, SHARD_ROW, tp
+
+    rng = np.random.default_rng(8)
+    n, k, world = 256, 512, 2
+    packed = rng.integers(0, 256, oracle.tq3_packed_bytes(n, k), dtype=np.uint8)
+    packed[n * k * 3 // 8: n * k * 3 // 8 + 2 * n] = rng.normal(0, 0.02, n).astype(np.float16).view(np.uint8)
+    x = rng.normal(0, 1, (3, k)).astype(np.float32)
+    full = oracle.tq3_linear(packed, n, k, x, oracle.F32)
+    cols, rows = [], np.zeros_like(full, dtype=np.float64)
+    for r in range(world):
+        p, nl, kl = tp.shard_trellis(torch.from_numpy(packed), n, k, SHARD_COLUMN, r, world)
+        assert (nl, kl) == (n // world, k) and p.numel() == oracle.tq3_packed_bytes(nl, kl)
+        cols.append(oracle.tq3_linear(p.numpy(), nl, kl, x, oracle.F32))
+        p, nl, kl = tp.shard_trellis(torch.from_numpy(packed), n, k, SHARD_ROW, r, world)
+        assert (nl, kl) == (n, k // world) and p.numel() == oracle.tq3_packed_bytes(nl, kl)
+        rows += oracle.tq3_linear(p.numpy(), nl, kl, np.ascontiguousarray(x[:, r * kl:(r + 1) * kl]), oracle.F32)
+    assert np.array_equal(np.concatenate(cols, axis=1), full)
+    assert np.linalg.norm(rows - full) / np.linalg.norm(full) < 1e-6
+    with pytest.raises(ValueError):
+        tp.shard_trellis(torch.from_numpy(packed), n, k, SHARD_ROW, 0, 8)

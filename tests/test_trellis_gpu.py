@@ -1,5 +1,5 @@
 """Trellis-coded 3-bit linear on the GPU against the CPU checker, through the C ABI: bit-exact decode, the
-decode-and-multiply kernel (up to 32 rows), and the expansion + tensor-core GEMM path beyond."""
+decode-and-multiply kernel (up to 4 rows), and the expansion + tensor-core GEMM path beyond."""
 import os
 
 import numpy as np
@@ -46,7 +46,7 @@ def test_decode_random_codes_bit_exact(ctx, n, k):
     lin.close()
 
 
-@pytest.mark.parametrize("m", [1, 2, 3, 5, 8, 9, 16, 20, 32])
+@pytest.mark.parametrize("m", [1, 2, 3, 4])
 def test_decode_and_multiply_rows(ctx, m):
     n, k = 256, 1024
     packed = random_packed(n, k, seed=40 + m)
@@ -58,7 +58,7 @@ def test_decode_and_multiply_rows(ctx, m):
     lin.close()
 
 
-@pytest.mark.parametrize("m", [33, 100, 300, 700])
+@pytest.mark.parametrize("m", [5, 8, 16, 33, 100, 300, 700])
 def test_expansion_and_tensor_core_gemm(ctx, m):
     n, k = 384, 640
     packed = random_packed(n, k, seed=60 + m)
