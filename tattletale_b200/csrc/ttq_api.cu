@@ -757,7 +757,7 @@ ttq_status ttq_moe_create(ttq_ctx *ctx, int32_t n_experts, const ttq_weight *con
     const size_t b_a = b_xh1 > b_o2 ? b_xh1 : b_o2;  // the routed input images and the routed outputs are never live together
     const size_t b_h1 = up256(sizeof(__half) * (size_t)m->rows_cap * (size_t)(2 * I));
     const size_t b_xh2 = up256(sizeof(__half) * (size_t)m->rows_cap * (size_t)(m->SBp2 * TILE_K));
-    const size_t total = 2 * b_tab + 3 * b_e + 256 + b_mt + b_rows + b_pairs + b_a + b_h1 + b_xh2;
+    const size_t total = 2 * b_tab + 3 * b_e + 256 + 3 * b_mt + b_rows + b_pairs + b_a + b_h1 + b_xh2;
     cudaError_t e = cudaMalloc(&m->ws, total);
     if (e != cudaSuccess) {
         delete m;
@@ -771,6 +771,8 @@ ttq_status ttq_moe_create(ttq_ctx *ctx, int32_t n_experts, const ttq_weight *con
     m->route.cursor = reinterpret_cast<int *>(q); q += b_e;
     m->route.n_mt = reinterpret_cast<int *>(q); q += 256;
     m->route.mt_group = reinterpret_cast<int *>(q); q += b_mt;
+    m->route.mt_row0 = reinterpret_cast<int *>(q); q += b_mt;
+    m->route.mt_mh = reinterpret_cast<int *>(q); q += b_mt;
     m->route.row_src = reinterpret_cast<int *>(q); q += b_rows;
     m->route.slot_of = reinterpret_cast<int *>(q); q += b_pairs;
     m->xh1 = reinterpret_cast<__half *>(q); m->o2 = m->xh1; q += b_a;
@@ -815,16 +817,21 @@ ttq_status ttq_moe_forward(ttq_ctx *ctx, ttq_moe *m, const void *x_dev, ttq_dtyp
     cudaStream_t st = (cudaStream_t)stream;
     // row-tile height from the mean number of rows per expert; capacity of this call in rows
     const int64_t pairs = T * m->top_k, mean = pairs / m->E;
+    // TTQ_MOE_BM=384 selects tiles of one to three 128-row blocks (rows padded to 128 only, one expansion of an
+    // expert's weight rows for up to 384 of its rows); measured 5 % slower than 256-row tiles at 256 rows per
+    // expert because it runs with one 128-row weight sub-tile per CTA
     int BM = mean <= 64 ? 64 : (mean <= 128 ? 128 : 256);
     static const int force_bm = []() {
         const char *v = getenv("TTQ_MOE_BM");
         return v ? atoi(v) : 0;
     }();
-    if (force_bm == 64 || force_bm == 128 || force_bm == 256) BM = force_bm;
-    int64_t Mp = ((pairs + (int64_t)m->E * BM + BM - 1) / BM) * BM;
-    if (Mp > m->rows_cap) Mp = m->rows_cap / BM * BM;
+    if (force_bm == 64 || force_bm == 128 || force_bm == 256 || force_bm == 384) BM = force_bm;
+    const int64_t unit = BM == 384 ? 128 : BM;
+    int64_t Mp = ((pairs + (int64_t)m->E * unit + unit - 1) / unit) * unit;
+    if (Mp > m->rows_cap) Mp = m->rows_cap / unit * unit;
+    const int64_t mt_cap = BM == 384 ? pairs / 384 + m->E + 1 : Mp / BM;
     int n = 0;
-    cudaError_t e = launch_moe_route(m->route, topk_ids_dev, T, m->top_k, m->E, BM, Mp, st, &n);
+    cudaError_t e = launch_moe_route(m->route, topk_ids_dev, T, m->top_k, m->E, BM, Mp, mt_cap, st, &n);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "routing launch");
     ctx->launches += n;
     GroupedArgs g;
@@ -834,6 +841,7 @@ ttq_status ttq_moe_forward(ttq_ctx *ctx, ttq_moe *m, const void *x_dev, ttq_dtyp
     g.row_src = m->route.row_src; g.gated = false;
     g.Mp = Mp; g.BM = BM;
     g.mt_group = m->route.mt_group; g.n_mt = m->route.n_mt;
+    g.mt_row0 = m->route.mt_row0; g.mt_mh = m->route.mt_mh; g.rows_total = m->route.n_mt + 1; g.mt_cap = mt_cap;
     g.y = m->h1; g.y_dt = TTQ_DT_F16; g.ldy = 2 * m->I;
     e = launch_gemm_grouped(g, m->xh1, ctx->sms, ctx->dev_status, st, &n);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "grouped gate|up launch");

@@ -234,7 +234,10 @@ struct GemmParams {
     int64_t Np;
     const uint8_t *const *group_tiles;  // per group: Q4_K tiled layout
     const int *mt_group;                // group of row tile mt
-    const int *n_mt;                    // row tiles in use (<= Mp / BM)
+    const int *mt_row0;                 // first row of row tile mt in the routed row space (a multiple of 64)
+    const int *mt_mh;                   // BM = 384 only: 128-row blocks of row tile mt in use (1..3)
+    const int *n_mt;                    // row tiles in use (<= mt_cap)
+    int64_t mt_cap;                     // row tiles the tables and the grid are sized for
 };
 
 template <int BM, int NSUB>
@@ -248,7 +251,7 @@ struct GemmCfg {
     static constexpr int MH = BM > 128 ? BM / 128 : 1;
     static constexpr int ACC_COLS = MH * 128 * NSUB;
     static constexpr int NACC = (2 * ACC_COLS <= 512) ? 2 : 1;   // accumulator sets in tensor memory
-    static constexpr int TMEM_COLS = NACC * ACC_COLS;             // 128 .. 512, a power of two
+    static constexpr int TMEM_COLS = NACC * ACC_COLS <= 128 ? 128 : (NACC * ACC_COLS <= 256 ? 256 : 512);  // a power of two
     static constexpr int DEQ_WARPS = gemm_deq_warps(NSUB), WARPS = gemm_warps(NSUB), THREADS = WARPS * 32;
     static constexpr int HDR_BYTES = DEQ_WARPS * 1280;  // per dequant warp: 16 rows x 80 bytes
     static constexpr int BAR_BYTES = 128;
@@ -279,8 +282,11 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
     int64_t m_tiles = p.Mp / BM;
     if (grouped) {
         const int64_t used = *p.n_mt;
-        m_tiles = used < m_tiles ? used : m_tiles;
+        m_tiles = used < p.mt_cap ? used : p.mt_cap;
     }
+    // first activation row of a row tile; 128-row blocks of it in use (variable only for the 384-row grouped tile)
+    auto tile_row0 = [&](int64_t m_tile) -> int64_t { return grouped ? (int64_t)p.mt_row0[m_tile] : m_tile * BM; };
+    auto tile_mh = [&](int64_t m_tile) -> int { return (grouped && BM == 384) ? p.mt_mh[m_tile] : C::MH; };
     const int64_t n_tiles = (p.N + TILE_N - 1) / TILE_N, total_tiles = n_tiles * m_tiles * splits;
 
     if (threadIdx.x == 0) {
@@ -320,11 +326,12 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
             const int buf = tcount % C::NACC, use = tcount / C::NACC;
             if (alive) alive = mbar_wait_warp(accf_bar + 8 * buf, (uint32_t)(use & 1), p.status, lane);
             tc_fence_after();
-            const int64_t m0 = m_tile * BM;
+            const int64_t m0 = tile_row0(m_tile);
+            const int mh = tile_mh(m_tile);
             float *wsp = p.ws + (size_t)split * p.Mp * p.N;
             const int esz = p.y_dt == TTQ_DT_F32 ? 4 : 2;
 #pragma unroll 1
-            for (int hb = 0; hb < C::MH; hb++) {
+            for (int hb = 0; hb < mh; hb++) {
                 // lane = activation row, columns = consecutive output features: 16 of them per load, stored as one run
                 const int64_t m = m0 + hb * 128 + warp * 32 + lane;
                 const bool row_ok = m < p.M && hb * 128 + warp * 32 + lane < BM;  // a 64-row tile fills lanes 0..63 only
@@ -397,7 +404,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
             for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
                 const int64_t otile = tile / splits, split = tile % splits;
                 const int64_t n_tile = otile / m_tiles, m_tile = otile % m_tiles;
-                const uint8_t *bsrc0 = reinterpret_cast<const uint8_t *>(p.xh) + (((m_tile * BM) >> 3) << 10) + split * iters * b_it_stride;
+                const uint8_t *bsrc0 = reinterpret_cast<const uint8_t *>(p.xh) + ((tile_row0(m_tile) >> 3) << 10) + split * iters * b_it_stride;
                 const uint8_t *wsrc0 = reinterpret_cast<const uint8_t *>(p.wimg) + (((n_tile * TILE_N) >> 3) << 10) + split * iters * w_it_stride;
                 for (int it = 0; it < iters; it++, git++) {
                     const int stage = git % STAGES;
@@ -470,8 +477,10 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
             const uint8_t *tile0_n[1];
 #pragma unroll
             for (int sub = 0; sub < 1; sub++) tile0_n[sub] = tile_ptr(tile + gridDim.x, sub, have_n[sub]);
-            const uint8_t *bsrc0 = reinterpret_cast<const uint8_t *>(p.xh) + (((((tile / splits) % m_tiles) * BM) >> 3) << 10) +
+            const int64_t m_tile_b = (tile / splits) % m_tiles;
+            const uint8_t *bsrc0 = reinterpret_cast<const uint8_t *>(p.xh) + ((tile_row0(m_tile_b) >> 3) << 10) +
                                    (tile % splits) * iters * b_it_stride;
+            const uint32_t b_bytes = BM == 384 ? (uint32_t)tile_mh(m_tile_b) * (128u * 128u) : (uint32_t)C::B_BYTES;
             for (int it = 0; it < iters; it++, git++) {
 #ifdef TTQ_DIAG_MMA_ONLY
                 continue;
@@ -530,8 +539,8 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
 #ifndef TTQ_DIAG_NO_B
                 if (dwa == 0 && lane == 0) {
                     // the activation tile of this stage: one bulk copy, counted on the same full barrier
-                    mbar_expect_tx(full_bar + 8 * stage, C::B_BYTES);
-                    bulk_g2s(a_stage + C::A_BYTES, bsrc0 + it * b_it_stride, C::B_BYTES, full_bar + 8 * stage);
+                    mbar_expect_tx(full_bar + 8 * stage, b_bytes);
+                    bulk_g2s(a_stage + C::A_BYTES, bsrc0 + it * b_it_stride, b_bytes, full_bar + 8 * stage);
                 }
 #endif
 #ifdef TTQ_DIAG_NO_CONVERT
@@ -612,6 +621,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
                 if (tr) t_acc += global_ns() - t0;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * C::ACC_COLS);
+                const int mh = tile_mh((tile / splits) % m_tiles);
                 for (int it = 0; it < iters; it++, git++) {
                     const int stage = git % STAGES;
                     if (tr) t0 = global_ns();
@@ -628,6 +638,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
                     const uint64_t wdesc = smem_desc_sw128(a_stage);
 #pragma unroll
                     for (int hb = 0; hb < C::MH; hb++) {
+                        if (hb >= mh) break;
                         // M side: 128 activation rows (a 64-row tile leaves lanes 64..127 unused)
                         const uint64_t xdesc = smem_desc_sw128(a_stage + C::A_BYTES + hb * (128 * 128));
 #pragma unroll
@@ -682,7 +693,7 @@ cudaError_t launch_cfg(const GemmParams &p, int sms, cudaStream_t st) {
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    const int64_t tiles = ((p.N + GEMM_BN * NSUB - 1) / (GEMM_BN * NSUB)) * (p.Mp / BM) * p.splits;
+    const int64_t tiles = ((p.N + GEMM_BN * NSUB - 1) / (GEMM_BN * NSUB)) * (p.group_tiles != nullptr ? p.mt_cap : p.Mp / BM) * p.splits;
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
     gemm_q4k_kernel<BM, NSUB, PLAIN><<<grid, C::THREADS, C::TOTAL, st>>>(p);
     return cudaGetLastError();
@@ -731,7 +742,7 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
         GemmParams p;
         p.tiles = a.tiles;
         p.wimg = wimg; p.Np = gemm_wimg_rows(a.N);
-        p.group_tiles = nullptr; p.mt_group = nullptr; p.n_mt = nullptr;
+        p.group_tiles = nullptr; p.mt_group = nullptr; p.mt_row0 = nullptr; p.mt_mh = nullptr; p.n_mt = nullptr; p.mt_cap = 0;
         p.N = a.N; p.NT = a.NT; p.SBp = a.SBp;
         p.xh = xh;
         p.M = Ms; p.Mp = Mp; p.Kp = Kp;
@@ -788,21 +799,22 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
 cudaError_t launch_gemm_grouped(const GroupedArgs &g, __half *xh, int sms, int *status, cudaStream_t st, int *launches) {
     *launches = 0;
     const int64_t Kp = g.SBp * TILE_K;
-    if (g.BM != 64 && g.BM != 128 && g.BM != 256) return cudaErrorInvalidValue;
-    if (g.Mp % g.BM) return cudaErrorInvalidValue;
+    if (g.BM != 64 && g.BM != 128 && g.BM != 256 && g.BM != 384) return cudaErrorInvalidValue;
+    if (g.Mp % 128 && g.Mp % g.BM) return cudaErrorInvalidValue;
     const int64_t chunks = g.Mp * (Kp / 8);
     const unsigned grid = (unsigned)((chunks + 255) / 256 < 148 * 16 ? (chunks + 255) / 256 : 148 * 16);
     if (g.gated)
-        xh_prep_kernel<true><<<grid, 256, 0, st>>>(g.x, g.x_dt, g.x_rows, g.Mp, g.K, Kp, g.ldx, xh, g.row_src, g.n_mt, g.BM);
+        xh_prep_kernel<true><<<grid, 256, 0, st>>>(g.x, g.x_dt, g.x_rows, g.Mp, g.K, Kp, g.ldx, xh, g.row_src, g.rows_total, 1);
     else
-        xh_prep_kernel<false><<<grid, 256, 0, st>>>(g.x, g.x_dt, g.x_rows, g.Mp, g.K, Kp, g.ldx, xh, g.row_src, g.n_mt, g.BM);
+        xh_prep_kernel<false><<<grid, 256, 0, st>>>(g.x, g.x_dt, g.x_rows, g.Mp, g.K, Kp, g.ldx, xh, g.row_src, g.rows_total, 1);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     ++*launches;
     GemmParams p;
     p.tiles = nullptr;
     p.wimg = nullptr; p.Np = 0;
-    p.group_tiles = g.group_tiles; p.mt_group = g.mt_group; p.n_mt = g.n_mt;
+    p.group_tiles = g.group_tiles; p.mt_group = g.mt_group; p.mt_row0 = g.mt_row0; p.mt_mh = g.mt_mh; p.n_mt = g.n_mt;
+    p.mt_cap = g.mt_cap;
     p.N = g.N; p.NT = g.NT; p.SBp = g.SBp;
     p.xh = xh;
     p.M = g.Mp; p.Mp = g.Mp; p.Kp = Kp;
@@ -813,14 +825,16 @@ cudaError_t launch_gemm_grouped(const GroupedArgs &g, __half *xh, int sms, int *
     p.splits = 1;
     p.ws = nullptr;
     // two sub-tiles per CTA when the expected tile count still covers the SMs
-    const int64_t mt_cap = g.Mp / g.BM;
+    const int64_t mt_cap = g.mt_cap;
     int nsub = (g.N >= 256 && ((g.N + 255) / 256) * mt_cap >= 2 * (int64_t)sms) ? 2 : 1;
     static const int force_nsub = []() {
         const char *v = getenv("TTQ_MOE_NSUB");
         return v ? atoi(v) : 0;
     }();
     if (force_nsub == 1 || force_nsub == 2) nsub = force_nsub;
-    if (nsub == 2) {
+    if (g.BM == 384) {
+        e = launch_cfg<384, 1>(p, sms, st);  // up to three 128-row blocks share one expansion of the weight rows
+    } else if (nsub == 2) {
         if (g.BM == 64) e = launch_cfg<64, 2>(p, sms, st);
         else if (g.BM == 128) e = launch_cfg<128, 2>(p, sms, st);
         else e = launch_cfg<256, 2>(p, sms, st);

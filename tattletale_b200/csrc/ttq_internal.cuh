@@ -125,9 +125,12 @@ struct GroupedArgs {
     int64_t x_rows, ldx;
     const int *row_src;                 // device [Mp]: source row of each routed row (-1 = padding) or nullptr (identity)
     bool gated;                         // source rows hold 2K values, the operand is silu(x[k]) * x[K + k]
-    int64_t Mp;                         // capacity in routed rows, a multiple of BM
-    int BM;                             // row-tile height: 64, 128 or 256
+    int64_t Mp;                         // capacity in routed rows (a multiple of 128, or of BM)
+    int BM;                             // row-tile height: 64, 128, 256, or 384 = one to three 128-row blocks per tile
     const int *mt_group, *n_mt;         // device: group of each row tile, number of row tiles in use
+    const int *mt_row0, *mt_mh;         // device: first routed row of each row tile; its 128-row blocks (BM = 384)
+    const int *rows_total;              // device: routed rows in use (rows beyond are not converted)
+    int64_t mt_cap;                     // row tiles the tables hold
     void *y;                            // [Mp][ldy] routed output rows
     int y_dt;
     int64_t ldy;
@@ -145,13 +148,13 @@ cudaError_t launch_tq3_gemv(const uint8_t *packed, int64_t N, int64_t K, const f
 // Routing and combination of a mixture-of-experts layer (ttq_moe.cu).
 struct MoeRouting {
     int *counts, *row_start, *cursor;  // [E]
-    int *n_mt;                         // [1]
-    int *mt_group;                     // [Mp / 64]
+    int *n_mt;                         // [1] row tiles in use; [1] routed rows in use
+    int *mt_group, *mt_row0, *mt_mh;   // [Mp / 64] each
     int *row_src;                      // [Mp]
     int *slot_of;                      // [T * top_k]
 };
 cudaError_t launch_moe_route(const MoeRouting &r, const int *topk_ids, int64_t T, int top_k, int E, int BM, int64_t Mp,
-                             cudaStream_t st, int *launches);
+                             int64_t mt_cap, cudaStream_t st, int *launches);
 cudaError_t launch_moe_combine(const MoeRouting &r, const void *o, int o_dt, int64_t ldo, const float *topk_w, int64_t T,
                                int top_k, int64_t H, void *y, int y_dt, int64_t ldy, cudaStream_t st);
 

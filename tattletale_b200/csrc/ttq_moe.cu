@@ -25,26 +25,44 @@ __global__ void __launch_bounds__(256) route_count_kernel(const int *__restrict_
     }
 }
 
-// One block.  Expert counts -> tile-aligned row ranges.  `mt_cap` bounds the table (it cannot overflow when the
-// capacity was sized as pairs + E * BM rows; the check keeps a bad call from writing out of bounds).
+// One block.  Expert counts -> padded row ranges and the row-tile tables.  Fixed tile heights (64, 128, 256): an
+// expert's rows are padded to whole tiles.  BM = 384: rows are padded to 128 and a tile holds up to three
+// 128-row blocks of ONE expert, so that the expert's weight rows are expanded once for (almost always) all of
+// its rows.  `mt_cap` bounds the tables (they cannot overflow when the capacity was sized as the launcher does;
+// the check keeps a bad call from writing out of bounds).
 __global__ void __launch_bounds__(1024) route_plan_kernel(const int *__restrict__ counts, int E, int BM, int mt_cap,
                                                           int *__restrict__ row_start, int *__restrict__ cursor,
-                                                          int *__restrict__ mt_group, int *__restrict__ n_mt) {
-    extern __shared__ int tile_start[];  // [E + 1]
+                                                          int *__restrict__ mt_group, int *__restrict__ mt_row0,
+                                                          int *__restrict__ mt_mh, int *__restrict__ n_mt) {
+    extern __shared__ int plan_s[];  // tile_start [E + 1], row_begin [E + 1]
+    int *tile_start = plan_s, *row_begin = plan_s + E + 1;
+    const int unit = BM == 384 ? 128 : BM;
     if (threadIdx.x == 0) {
-        int acc = 0;
+        int tiles = 0, rows = 0;
         for (int e = 0; e < E; e++) {
-            tile_start[e] = acc;
-            acc += (counts[e] + BM - 1) / BM;
+            tile_start[e] = tiles;
+            row_begin[e] = rows;
+            const int padded = (counts[e] + unit - 1) / unit * unit;
+            tiles += (padded + BM - 1) / BM;
+            rows += padded;
         }
-        tile_start[E] = acc;
-        *n_mt = acc < mt_cap ? acc : mt_cap;
+        tile_start[E] = tiles;
+        row_begin[E] = rows;
+        n_mt[0] = tiles < mt_cap ? tiles : mt_cap;
+        n_mt[1] = rows;
     }
     __syncthreads();
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        row_start[e] = tile_start[e] * BM;
+        row_start[e] = row_begin[e];
         cursor[e] = 0;
-        for (int t = tile_start[e]; t < tile_start[e + 1] && t < mt_cap; t++) mt_group[t] = e;
+        const int padded = row_begin[e + 1] - row_begin[e];
+        for (int t = tile_start[e]; t < tile_start[e + 1] && t < mt_cap; t++) {
+            const int off = (t - tile_start[e]) * BM;
+            mt_group[t] = e;
+            mt_row0[t] = row_begin[e] + off;
+            const int left = padded - off;
+            mt_mh[t] = BM == 384 ? (left >= 384 ? 3 : left / 128) : (BM > 128 ? BM / 128 : 1);
+        }
     }
 }
 
@@ -107,7 +125,7 @@ unsigned grid_of(int64_t items, int cap) {
 }  // namespace
 
 cudaError_t launch_moe_route(const MoeRouting &r, const int *topk_ids, int64_t T, int top_k, int E, int BM, int64_t Mp,
-                             cudaStream_t st, int *launches) {
+                             int64_t mt_cap, cudaStream_t st, int *launches) {
     *launches = 0;
     const int64_t pairs = T * top_k;
     cudaError_t e = cudaMemsetAsync(r.counts, 0, sizeof(int) * (size_t)E, st);
@@ -115,8 +133,8 @@ cudaError_t launch_moe_route(const MoeRouting &r, const int *topk_ids, int64_t T
     e = cudaMemsetAsync(r.row_src, 0xff, sizeof(int) * (size_t)Mp, st);  // every row is padding until a pair claims it
     if (e != cudaSuccess) return e;
     route_count_kernel<<<grid_of(pairs, 148 * 4), 256, 0, st>>>(topk_ids, pairs, E, r.counts);
-    route_plan_kernel<<<1, 1024, sizeof(int) * (size_t)(E + 1), st>>>(r.counts, E, BM, (int)(Mp / BM), r.row_start, r.cursor, r.mt_group,
-                                                                      r.n_mt);
+    route_plan_kernel<<<1, 1024, 2 * sizeof(int) * (size_t)(E + 1), st>>>(r.counts, E, BM, (int)mt_cap, r.row_start, r.cursor, r.mt_group,
+                                                                          r.mt_row0, r.mt_mh, r.n_mt);
     route_scatter_kernel<<<grid_of(pairs, 148 * 4), 256, 0, st>>>(topk_ids, pairs, top_k, E, Mp, r.row_start, r.cursor, r.slot_of,
                                                                   r.row_src);
     *launches = 3;
