@@ -444,7 +444,7 @@ def decode_arm(args):
         from tattletale_b200 import tp
 
         comm = tp.Communicator(ctx, n_cap=cfg.hidden, m_cap=4)
-    stack = DecoderStack(ctx, cfg, args.batch, rank, world, comm=comm)
+    stack = DecoderStack(ctx, cfg, args.batch, rank, world, comm=comm, fused_glue=not args.torch_glue)
     g = torch.Generator(device=dev).manual_seed(3100)
     ids = torch.randint(0, cfg.vocab, (args.batch,), generator=g, device=dev)
     out = stack.step(ids)
@@ -509,7 +509,9 @@ def decode_arm(args):
             "config": {"workload": f"Llama-3-8B decoder stack, {cfg.n_layers} layers, Q4_K linears + Q6_K lm_head, decode batch "
                                    f"{args.batch} at context {cfg.context}", "batch": args.batch, "context": cfg.context,
                        "parallelism": "single GPU" if world == 1 else f"tp{world}",
-                       "glue": "RMSNorm, RoPE, KV cache and attention are torch ops (not part of the quantized-linear path)"},
+                       "glue": ("RMSNorm, RoPE, KV cache and attention are torch ops" if args.torch_glue else
+                                "residual + RMSNorm, RoPE + KV append and single-query attention are libttq kernels; "
+                                "embedding lookup and argmax are torch ops")},
             "roofline": {"bound": "hbm", "achieved": round(gbs / world, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / world / peak, 4),
                          "traffic": None, "bytes_per_step": {"weights": int(w_bytes), "kv_cache": int(kv_bytes)}},
             "gpu_launches": int(launches_per_step * args.steps), "launches_per_step": int(launches_per_step),
@@ -732,6 +734,8 @@ def main():
                     help="trellis workload: code bits from the beam-search encoder or uniformly random")
     ap.add_argument("--tokens", type=int, default=4096, help="moe workload: tokens per step (all ranks together)")
     ap.add_argument("--batch", type=int, default=1, help="decode workload: sequences decoded together")
+    ap.add_argument("--torch-glue", action="store_true",
+                    help="decode workload: run norm / RoPE / attention as torch ops instead of the library's decode-step kernels")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--nccl-allreduce", action="store_true", help="N > 1: use NCCL for the row-parallel sums instead of the fused exchange")

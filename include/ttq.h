@@ -212,6 +212,32 @@ TTQ_API ttq_status ttq_linear_forward_static(const ttq_weight *w, const void *x_
 TTQ_API ttq_status ttq_silu_and_mul(ttq_ctx *ctx, const void *in_dev, ttq_dtype dt, int64_t M, int64_t H,
                             int64_t ld_in, void *out_dev, int64_t ld_out, void *stream);
 
+/* ---- adjacent steps of a decode layer: residual + RMSNorm, RoPE + KV-cache append, attention ----------
+ * 16-bit tensors only (bf16 or f16, one dtype per call), fp32 arithmetic, asynchronous on `stream`. */
+
+/* h[m][:] += delta[m][:] when delta != NULL (the sum is stored back, rounded), then
+ * out[m][:] = h[m][:] * rsqrt(mean(h[m][:]^2) + eps) * weight[:].  RmsNorm.forward and forward_with_residual,
+ * workspace/transformers/src/layers/norm.nim:23-38 (the reference runs add and norm as separate ops, TODO at :35).
+ * H a multiple of 8, rows and weight 16-byte aligned. */
+TTQ_API ttq_status ttq_add_rmsnorm(ttq_ctx *ctx, void *h_dev, const void *delta_dev, const void *weight_dev, ttq_dtype dt,
+                                   int64_t M, int64_t H, int64_t ld_h, int64_t ld_delta, float eps, void *out_dev,
+                                   int64_t ld_out, void *stream);
+
+/* Rotary embedding in the rotate-half form (workspace/transformers/src/layers/rope.nim:29-92) of the q and k heads
+ * of fused qkv rows [B][ld_qkv] = [hq q heads | hkv k heads | hkv v heads] x d, for ONE position `pos` whose
+ * cos / sin vectors [d] the caller supplies; q goes to q_out [B][hq][d], k and v into the caches
+ * [B][hkv][ctx_len][d] at `pos` (the preallocated-cache form of attn.nim:97-104). */
+TTQ_API ttq_status ttq_rope_kv_append(ttq_ctx *ctx, const void *qkv_dev, ttq_dtype dt, int64_t B, int64_t ld_qkv, int32_t hq,
+                                      int32_t hkv, int32_t d, const void *cos_dev, const void *sin_dev, void *q_out_dev,
+                                      void *k_cache_dev, void *v_cache_dev, int64_t ctx_len, int64_t pos, void *stream);
+
+/* One query per sequence, grouped-query attention over cache positions 0 .. n_ctx-1 (attn.nim:149-189 at a
+ * single new token): out[b][h][:] = softmax_p(q[b][h] . k[b][h / (hq/hkv)][p] / sqrt(d)) . v.  d = 128,
+ * hq / hkv in {1, 2, 4, 8}.  TTQ_ERR_LIMIT when B * hq * ceil(n_ctx / 128) exceeds the context's scratch. */
+TTQ_API ttq_status ttq_decode_attention(ttq_ctx *ctx, const void *q_dev, const void *k_cache_dev, const void *v_cache_dev,
+                                        ttq_dtype dt, int64_t B, int32_t hq, int32_t hkv, int32_t d, int64_t ctx_len,
+                                        int64_t n_ctx, void *out_dev, void *stream);
+
 /* ---- mixture-of-experts layer (grouped quantized GEMM) -----------------------------------------
  * No reference counterpart: the reference has dense gated MLPs only
  * (workspace/transformers/src/layers/mlp.nim:31-60).  The layer applies that gated MLP per expert:

@@ -27,6 +27,8 @@ struct ttq_ctx {
     unsigned long long *trace;  // device timeline buffer, allocated only when TTQ_TRACE=1 is set at init
     float *tq_x1, *tq_y1;       // TQ3: rotated activations [TQ3_SLAB][K] and raw results [TQ3_SLAB][N] (fp32; x1 also
     int64_t tq_x1_cap, tq_y1_cap;  //   holds the fp16 form for the GEMM); capacities in floats, grown at weight creation
+    float *att_part;            // partial results of the decode attention slices (fixed at init)
+    int64_t att_part_cap;       // in floats
     __half *wimg;               // fp16 expansion of one whole weight (plain GEMM mode of the formats without a
     int64_t wimg_capacity;      //   fused dequant GEMM); in halves, grown when such a weight is created
     __half *xh;                 // fp16 activation scratch of the tcgen05 GEMM path
@@ -306,6 +308,12 @@ ttq_status ttq_init(int device, ttq_ctx **out) {
     ctx->xq.sx = reinterpret_cast<float *>(b + planes_b + s16_b + s32_b);
     ctx->xq_capacity_k = Kc;
     ctx->xh_capacity = XH_CAPACITY;
+    ctx->att_part_cap = 8ll << 20;  // 32 MB: e.g. 32 sequences x 32 heads x 64 slices of 128 positions
+    if (cudaMalloc(&ctx->att_part, (size_t)ctx->att_part_cap * sizeof(float)) != cudaSuccess) {
+        ctx->att_part = nullptr;
+        ctx->att_part_cap = 0;
+        cudaGetLastError();
+    }
     ctx->stage_x_bytes = STAGE_X_BYTES;
     ctx->stage_y_bytes = STAGE_Y_BYTES;
     ctx->stage_b_bytes = STAGE_B_BYTES;
@@ -325,6 +333,7 @@ ttq_status ttq_destroy(ttq_ctx *ctx) {
     cudaFree(ctx->wimg);
     cudaFree(ctx->tq_x1);
     cudaFree(ctx->tq_y1);
+    cudaFree(ctx->att_part);
     cudaFree(ctx->stage_x);
     cudaFree(ctx->stage_y);
     cudaFree(ctx->stage_b);
@@ -857,6 +866,63 @@ ttq_status ttq_moe_forward(ttq_ctx *ctx, ttq_moe *m, const void *x_dev, ttq_dtyp
     e = launch_moe_combine(m->route, m->o2, TTQ_DT_F16, m->H, topk_weights_dev, T, m->top_k, m->H, y_dev, y_dt, ldy, st);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "combine launch");
     ctx->launches++;
+    return TTQ_OK;
+}
+
+ttq_status ttq_add_rmsnorm(ttq_ctx *ctx, void *h_dev, const void *delta_dev, const void *weight_dev, ttq_dtype dt, int64_t M,
+                           int64_t H, int64_t ld_h, int64_t ld_delta, float eps, void *out_dev, int64_t ld_out, void *stream) {
+    if (!ctx) return TTQ_ERR_INVALID_ARG;
+    if (M < 0 || H <= 0) return fail(ctx, TTQ_ERR_SHAPE, "bad size (M=%lld H=%lld)", (long long)M, (long long)H);
+    if (M == 0) return TTQ_OK;
+    if (!h_dev || !weight_dev || !out_dev) return fail(ctx, TTQ_ERR_INVALID_ARG, "a device pointer is NULL");
+    if (dt != TTQ_DT_BF16 && dt != TTQ_DT_F16) return fail(ctx, TTQ_ERR_INVALID_ARG, "dtype must be bf16 or f16");
+    if (H % 8 || ld_h % 8 || ld_out % 8 || (delta_dev && ld_delta % 8) || ld_h < H || ld_out < H || (delta_dev && ld_delta < H))
+        return fail(ctx, TTQ_ERR_SHAPE, "H and the leading dimensions must be multiples of 8 and at least H");
+    if (((uintptr_t)h_dev | (uintptr_t)weight_dev | (uintptr_t)out_dev | (uintptr_t)delta_dev) & 15)
+        return fail(ctx, TTQ_ERR_INVALID_ARG, "pointers must be 16-byte aligned");
+    cudaError_t e = launch_add_rmsnorm(h_dev, delta_dev, weight_dev, dt, M, H, ld_h, ld_delta, eps, out_dev, ld_out, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "add_rmsnorm launch");
+    ctx->launches++;
+    return TTQ_OK;
+}
+
+ttq_status ttq_rope_kv_append(ttq_ctx *ctx, const void *qkv_dev, ttq_dtype dt, int64_t B, int64_t ld_qkv, int32_t hq, int32_t hkv,
+                              int32_t d, const void *cos_dev, const void *sin_dev, void *q_out_dev, void *k_cache_dev,
+                              void *v_cache_dev, int64_t ctx_len, int64_t pos, void *stream) {
+    if (!ctx) return TTQ_ERR_INVALID_ARG;
+    if (B < 0 || hq <= 0 || hkv <= 0 || d <= 0 || d % 2 || d > 2048) return fail(ctx, TTQ_ERR_SHAPE, "bad head geometry");
+    if (B == 0) return TTQ_OK;
+    if (B > 65535) return fail(ctx, TTQ_ERR_LIMIT, "B=%lld exceeds 65535", (long long)B);
+    if (!qkv_dev || !cos_dev || !sin_dev || !q_out_dev || !k_cache_dev || !v_cache_dev) return fail(ctx, TTQ_ERR_INVALID_ARG, "a device pointer is NULL");
+    if (dt != TTQ_DT_BF16 && dt != TTQ_DT_F16) return fail(ctx, TTQ_ERR_INVALID_ARG, "dtype must be bf16 or f16");
+    if (ld_qkv < (int64_t)(hq + 2 * hkv) * d) return fail(ctx, TTQ_ERR_SHAPE, "ld_qkv smaller than (hq + 2 hkv) * d");
+    if (pos < 0 || pos >= ctx_len) return fail(ctx, TTQ_ERR_SHAPE, "pos=%lld outside the cache of %lld positions", (long long)pos, (long long)ctx_len);
+    cudaError_t e = launch_rope_kv(qkv_dev, dt, B, ld_qkv, hq, hkv, d, cos_dev, sin_dev, q_out_dev, k_cache_dev, v_cache_dev, ctx_len, pos,
+                                   (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "rope_kv launch");
+    ctx->launches++;
+    return TTQ_OK;
+}
+
+ttq_status ttq_decode_attention(ttq_ctx *ctx, const void *q_dev, const void *k_cache_dev, const void *v_cache_dev, ttq_dtype dt, int64_t B,
+                                int32_t hq, int32_t hkv, int32_t d, int64_t ctx_len, int64_t n_ctx, void *out_dev, void *stream) {
+    if (!ctx) return TTQ_ERR_INVALID_ARG;
+    if (B < 0 || hq <= 0 || hkv <= 0 || hq % hkv) return fail(ctx, TTQ_ERR_SHAPE, "bad head counts (hq=%d hkv=%d)", hq, hkv);
+    if (B == 0) return TTQ_OK;
+    const int G = hq / hkv;
+    if (d != 128 || (G != 1 && G != 2 && G != 4 && G != 8))
+        return fail(ctx, TTQ_ERR_UNSUPPORTED, "decode attention serves d = 128 and hq / hkv in {1, 2, 4, 8}");
+    if (!q_dev || !k_cache_dev || !v_cache_dev || !out_dev) return fail(ctx, TTQ_ERR_INVALID_ARG, "a device pointer is NULL");
+    if (dt != TTQ_DT_BF16 && dt != TTQ_DT_F16) return fail(ctx, TTQ_ERR_INVALID_ARG, "dtype must be bf16 or f16");
+    if (n_ctx <= 0 || n_ctx > ctx_len) return fail(ctx, TTQ_ERR_SHAPE, "n_ctx=%lld outside 1..ctx_len=%lld", (long long)n_ctx, (long long)ctx_len);
+    if (B > 65535 || hkv > 65535) return fail(ctx, TTQ_ERR_LIMIT, "B or hkv exceeds 65535");
+    if (((uintptr_t)k_cache_dev) & 15) return fail(ctx, TTQ_ERR_INVALID_ARG, "the K cache must be 16-byte aligned");
+    if (decode_attention_scratch_floats(B, hq, n_ctx) > ctx->att_part_cap)
+        return fail(ctx, TTQ_ERR_LIMIT, "B * hq * ceil(n_ctx / 128) exceeds the attention scratch of the context");
+    cudaError_t e = launch_decode_attention(q_dev, k_cache_dev, v_cache_dev, dt, B, hq, hkv, d, ctx_len, n_ctx, ctx->att_part, out_dev,
+                                            (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "decode attention launch");
+    ctx->launches += 2;
     return TTQ_OK;
 }
 

@@ -1,0 +1,313 @@
+// Decode-step kernels around the quantized linears: residual add + RMSNorm, RoPE + KV-cache append, and
+// single-query grouped-query attention over a contiguous KV cache.  These are the steps that sit between two
+// linears of a decoder layer in the reference:
+//   RmsNorm.forward / forward_with_residual   workspace/transformers/src/layers/norm.nim:23-38 (the unfused add +
+//                                             norm is flagged TODO at :35)
+//   rotary embedding (rotate-half form)        workspace/transformers/src/layers/rope.nim:29-92
+//   attention with a growing KV cache          workspace/transformers/src/layers/attn.nim:97-104,149-189
+// All 16-bit tensors are bf16 or f16 (one dtype per call), arithmetic is fp32.
+//
+//   add_rmsnorm_kernel        one CTA per row: h += delta (optional), out = h * rsqrt(mean(h^2) + eps) * weight
+//   rope_kv_kernel            one CTA per (sequence, head of the fused qkv row): rotates q and k heads, writes q to
+//                             its own buffer, k and v into the cache at `pos`
+//   decode_attn_kernel        one CTA per (sequence, kv head, slice of 128 cache positions): thread t scores
+//                             position t against the G query heads of the group (K row read as 16 vector loads),
+//                             block softmax statistics, then thread t accumulates output dimension t over the
+//                             slice (V read coalesced); partial (max, sum, output) per slice
+//   decode_attn_merge_kernel  one CTA per (sequence, query head): merges the slices
+#include "ttq_internal.cuh"
+
+namespace ttq {
+namespace {
+
+constexpr int ATT_D = 128;      // head dimension served by the attention kernels
+constexpr int ATT_SLICE = 128;  // cache positions per CTA
+
+__device__ __forceinline__ void unpack8(const uint4 &raw, int dt, float (&f)[8]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        if (dt == TTQ_DT_BF16) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        } else {
+            const float2 v = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+            f[2 * i] = v.x;
+            f[2 * i + 1] = v.y;
+        }
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8], int dt) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        if (dt == TTQ_DT_BF16) {
+            const __nv_bfloat162 t = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<const uint32_t *>(&t);
+        } else {
+            const __half2 t = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<const uint32_t *>(&t);
+        }
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+__device__ __forceinline__ float block_sum(float v, float *red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float s = 0.f;
+    for (int i = 0; i < nw; i++) s += red[i];
+    return s;
+}
+// H % 8 == 0, rows 16-byte aligned (checked by the launcher).
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(void *__restrict__ h, const void *__restrict__ delta, const void *__restrict__ weight,
+                                                          int dt, int64_t H, int64_t ld_h, int64_t ld_delta, float eps,
+                                                          void *__restrict__ out, int64_t ld_out) {
+    __shared__ float red[8];
+    const int64_t m = blockIdx.x;
+    uint8_t *hrow = reinterpret_cast<uint8_t *>(h) + m * ld_h * 2;
+    const uint8_t *drow = delta ? reinterpret_cast<const uint8_t *>(delta) + m * ld_delta * 2 : nullptr;
+    float ss = 0.f;
+    for (int64_t c = threadIdx.x; c < H / 8; c += blockDim.x) {
+        float v[8];
+        unpack8(*reinterpret_cast<const uint4 *>(hrow + c * 16), dt, v);
+        if (drow) {
+            float d[8];
+            unpack8(*reinterpret_cast<const uint4 *>(drow + c * 16), dt, d);
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] += d[i];
+            const uint4 packed = pack8(v, dt);
+            *reinterpret_cast<uint4 *>(hrow + c * 16) = packed;
+            unpack8(packed, dt, v);  // the norm sees the stored (rounded) residual stream, as the unfused sequence does
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) ss = fmaf(v[i], v[i], ss);
+    }
+    const float inv = rsqrtf(block_sum(ss, red) / (float)H + eps);
+    uint8_t *orow = reinterpret_cast<uint8_t *>(out) + m * ld_out * 2;
+    for (int64_t c = threadIdx.x; c < H / 8; c += blockDim.x) {
+        float v[8], w[8];
+        unpack8(*reinterpret_cast<const uint4 *>(hrow + c * 16), dt, v);
+        unpack8(*reinterpret_cast<const uint4 *>(reinterpret_cast<const uint8_t *>(weight) + c * 16), dt, w);
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = v[i] * inv * w[i];
+        *reinterpret_cast<uint4 *>(orow + c * 16) = pack8(v, dt);
+    }
+}
+
+// grid (hq + 2 hkv, B), d / 2 threads.  qkv row: [hq heads | hkv k heads | hkv v heads] of d values.
+__global__ void rope_kv_kernel(const void *__restrict__ qkv, int dt, int64_t ld_qkv, int hq, int hkv, int d, const void *__restrict__ cosv,
+                               const void *__restrict__ sinv, void *__restrict__ q_out, void *__restrict__ k_cache, void *__restrict__ v_cache,
+                               int64_t ctx_len, int64_t pos) {
+    const int head = blockIdx.x, b = blockIdx.y, i = threadIdx.x, half = d / 2;
+    const int64_t src = (int64_t)b * ld_qkv + (int64_t)head * d;
+    const float x1 = load_as_float(qkv, dt, src + i), x2 = load_as_float(qkv, dt, src + half + i);
+    if (head < hq + hkv) {
+        // rotate-half: out = x * cos + rotate_half(x) * sin, rotate_half(x) = [-x2, x1]; fp32, rounded once
+        const float c1 = load_as_float(cosv, dt, i), c2 = load_as_float(cosv, dt, half + i);
+        const float s1 = load_as_float(sinv, dt, i), s2 = load_as_float(sinv, dt, half + i);
+        const float o1 = x1 * c1 - x2 * s1, o2 = x2 * c2 + x1 * s2;
+        if (head < hq) {
+            const int64_t dst = ((int64_t)b * hq + head) * d;
+            store_from_float(q_out, dt, dst + i, o1);
+            store_from_float(q_out, dt, dst + half + i, o2);
+        } else {
+            const int64_t dst = (((int64_t)b * hkv + (head - hq)) * ctx_len + pos) * d;
+            store_from_float(k_cache, dt, dst + i, o1);
+            store_from_float(k_cache, dt, dst + half + i, o2);
+        }
+    } else {
+        const int64_t dst = (((int64_t)b * hkv + (head - hq - hkv)) * ctx_len + pos) * d;
+        store_from_float(v_cache, dt, dst + i, x1);
+        store_from_float(v_cache, dt, dst + half + i, x2);
+    }
+}
+
+// grid (slices, hkv, B), 128 threads.  part: [B][hkv][slices][G][2 + 128] floats = (max, sum, unnormalised output).
+// Scores: a half-warp reads one K row per load (16 lanes x 16 bytes, two rows per warp instruction, all 16 loads of
+// a warp's 32 positions in flight together), partial dots are folded over the 16 lanes.  Output: thread (pg, dg)
+// accumulates dimensions 8 dg .. 8 dg + 7 over positions pg, pg + 8, ... with 16-byte V loads, the 8 position
+// groups are summed through shared memory.
+template <int G>
+__global__ void __launch_bounds__(ATT_SLICE) decode_attn_kernel(const void *__restrict__ q, const void *__restrict__ k_cache,
+                                                                const void *__restrict__ v_cache, int dt, int hq, int hkv, int64_t ctx_len,
+                                                                int64_t n_ctx, float scale, float *__restrict__ part) {
+    __shared__ float q_s[G][ATT_D];
+    __shared__ float p_s[G][ATT_SLICE];
+    __shared__ float o_s[8][G][ATT_D];
+    const int slice = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, t = threadIdx.x;
+    const int warp = t >> 5, lane = t & 31;
+    const int slices = gridDim.x;
+    for (int i = t; i < G * ATT_D; i += ATT_SLICE)
+        q_s[i / ATT_D][i % ATT_D] = load_as_float(q, dt, ((int64_t)b * hq + (int64_t)kvh * G + i / ATT_D) * ATT_D + i % ATT_D) * scale;
+    __syncthreads();
+    const int64_t p0 = (int64_t)slice * ATT_SLICE;
+    const int64_t n_here = n_ctx - p0 < ATT_SLICE ? n_ctx - p0 : ATT_SLICE;
+    const uint8_t *kbase = reinterpret_cast<const uint8_t *>(k_cache) + ((((int64_t)b * hkv + kvh) * ctx_len + p0) * ATT_D) * 2;
+    const uint8_t *vbase = reinterpret_cast<const uint8_t *>(v_cache) + ((((int64_t)b * hkv + kvh) * ctx_len + p0) * ATT_D) * 2;
+    {
+        const int hw = lane >> 4, c = lane & 15;
+#pragma unroll 1
+        for (int half = 0; half < 2; half++) {
+        uint4 raw[8];
+#pragma unroll
+        for (int i8 = 0; i8 < 8; i8++) {
+            const int j = 32 * warp + 2 * (8 * half + i8) + hw;
+            raw[i8] = j < n_here ? *reinterpret_cast<const uint4 *>(kbase + (int64_t)j * (ATT_D * 2) + 16 * c) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int i8 = 0; i8 < 8; i8++) {
+            const int it = 8 * half + i8;
+            float kv[8];
+            unpack8(raw[i8], dt, kv);
+            float s[G];
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                float a = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; i++) a = fmaf(kv[i], q_s[g][8 * c + i], a);
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+                s[g] = a;
+            }
+            if (c == 0) {
+                const int j = 32 * warp + 2 * it + hw;
+#pragma unroll
+                for (int g = 0; g < G; g++) p_s[g][j] = s[g];
+            }
+        }
+        }
+    }
+    __syncthreads();
+    float *my = part + ((((int64_t)b * hkv + kvh) * slices + slice) * G) * (2 + ATT_D);
+    // softmax statistics of the slice: one warp per query head, four positions per lane
+    for (int g = warp; g < G; g += ATT_SLICE / 32) {
+        float sc[4], mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            sc[i] = lane + 32 * i < n_here ? p_s[g][lane + 32 * i] : -INFINITY;
+            mx = fmaxf(mx, sc[i]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float e = lane + 32 * i < n_here ? __expf(sc[i] - mx) : 0.f;
+            p_s[g][lane + 32 * i] = e;
+            sum += e;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) {
+            my[g * (2 + ATT_D)] = mx;
+            my[g * (2 + ATT_D) + 1] = sum;
+        }
+    }
+    __syncthreads();
+    {
+        const int pg = t >> 4, dg = t & 15;
+        float o[G][8];
+#pragma unroll
+        for (int g = 0; g < G; g++)
+#pragma unroll
+            for (int i = 0; i < 8; i++) o[g][i] = 0.f;
+#pragma unroll 1
+        for (int half = 0; half < 2; half++) {
+        uint4 raw[8];
+#pragma unroll
+        for (int i8 = 0; i8 < 8; i8++) {
+            const int j = pg + 8 * (8 * half + i8);
+            raw[i8] = j < n_here ? *reinterpret_cast<const uint4 *>(vbase + (int64_t)j * (ATT_D * 2) + 16 * dg) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int i8 = 0; i8 < 8; i8++) {
+            const int j = pg + 8 * (8 * half + i8);
+            float v[8];
+            unpack8(raw[i8], dt, v);
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                const float pw = p_s[g][j];  // zero beyond n_here
+#pragma unroll
+                for (int i = 0; i < 8; i++) o[g][i] = fmaf(pw, v[i], o[g][i]);
+            }
+        }
+        }
+#pragma unroll
+        for (int g = 0; g < G; g++)
+#pragma unroll
+            for (int i = 0; i < 8; i++) o_s[pg][g][8 * dg + i] = o[g][i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        float a = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; r++) a += o_s[r][g][t];
+        my[g * (2 + ATT_D) + 2 + t] = a;
+    }
+}
+
+// grid (hq, B), 128 threads
+__global__ void __launch_bounds__(ATT_D) decode_attn_merge_kernel(const float *__restrict__ part, int hq, int hkv, int G, int slices,
+                                                                  void *__restrict__ out, int dt) {
+    const int h = blockIdx.x, b = blockIdx.y, t = threadIdx.x;
+    const int kvh = h / G, g = h % G;
+    const float *base = part + (((int64_t)b * hkv + kvh) * slices * G + g) * (2 + ATT_D);
+    const int64_t stride = (int64_t)G * (2 + ATT_D);
+    float mx = -INFINITY;
+    for (int s = 0; s < slices; s++) mx = fmaxf(mx, base[s * stride]);
+    float den = 0.f, num = 0.f;
+    for (int s = 0; s < slices; s++) {
+        const float w = __expf(base[s * stride] - mx);
+        den = fmaf(w, base[s * stride + 1], den);
+        num = fmaf(w, base[s * stride + 2 + t], num);
+    }
+    store_from_float(out, dt, ((int64_t)b * hq + h) * ATT_D + t, num / den);
+}
+
+}  // namespace
+
+cudaError_t launch_add_rmsnorm(void *h, const void *delta, const void *weight, int dt, int64_t M, int64_t H, int64_t ld_h, int64_t ld_delta,
+                               float eps, void *out, int64_t ld_out, cudaStream_t st) {
+    add_rmsnorm_kernel<<<(unsigned)M, 256, 0, st>>>(h, delta, weight, dt, H, ld_h, ld_delta, eps, out, ld_out);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rope_kv(const void *qkv, int dt, int64_t B, int64_t ld_qkv, int hq, int hkv, int d, const void *cosv, const void *sinv,
+                           void *q_out, void *k_cache, void *v_cache, int64_t ctx_len, int64_t pos, cudaStream_t st) {
+    rope_kv_kernel<<<dim3((unsigned)(hq + 2 * hkv), (unsigned)B), d / 2, 0, st>>>(qkv, dt, ld_qkv, hq, hkv, d, cosv, sinv, q_out, k_cache,
+                                                                                    v_cache, ctx_len, pos);
+    return cudaGetLastError();
+}
+
+int64_t decode_attention_scratch_floats(int64_t B, int hq, int64_t n_ctx) {
+    const int64_t slices = (n_ctx + ATT_SLICE - 1) / ATT_SLICE;
+    return B * hq * slices * (2 + ATT_D);
+}
+
+cudaError_t launch_decode_attention(const void *q, const void *k_cache, const void *v_cache, int dt, int64_t B, int hq, int hkv, int d,
+                                    int64_t ctx_len, int64_t n_ctx, float *part, void *out, cudaStream_t st) {
+    if (d != ATT_D || hq % hkv) return cudaErrorInvalidValue;
+    const int G = hq / hkv;
+    const int slices = (int)((n_ctx + ATT_SLICE - 1) / ATT_SLICE);
+    const float scale = rsqrtf((float)d);
+    const dim3 grid((unsigned)slices, (unsigned)hkv, (unsigned)B);
+    switch (G) {
+        case 1: decode_attn_kernel<1><<<grid, ATT_SLICE, 0, st>>>(q, k_cache, v_cache, dt, hq, hkv, ctx_len, n_ctx, scale, part); break;
+        case 2: decode_attn_kernel<2><<<grid, ATT_SLICE, 0, st>>>(q, k_cache, v_cache, dt, hq, hkv, ctx_len, n_ctx, scale, part); break;
+        case 4: decode_attn_kernel<4><<<grid, ATT_SLICE, 0, st>>>(q, k_cache, v_cache, dt, hq, hkv, ctx_len, n_ctx, scale, part); break;
+        case 8: decode_attn_kernel<8><<<grid, ATT_SLICE, 0, st>>>(q, k_cache, v_cache, dt, hq, hkv, ctx_len, n_ctx, scale, part); break;
+        default: return cudaErrorInvalidValue;
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    decode_attn_merge_kernel<<<dim3((unsigned)hq, (unsigned)B), ATT_D, 0, st>>>(part, hq, hkv, G, slices, out, dt);
+    return cudaGetLastError();
+}
+
+}  // namespace ttq

@@ -145,6 +145,15 @@ cudaError_t launch_tq3_rotate(const void *in, int in_dt, int64_t M, int64_t C, i
                               const void *bias, int bias_dt, void *out, int out_dt, int64_t ld_out, cudaStream_t st);
 cudaError_t launch_tq3_gemv(const uint8_t *packed, int64_t N, int64_t K, const float *x1, int rows, float *y1, cudaStream_t st);
 
+// Decode-step kernels around the linears (ttq_decode.cu).
+cudaError_t launch_add_rmsnorm(void *h, const void *delta, const void *weight, int dt, int64_t M, int64_t H, int64_t ld_h, int64_t ld_delta,
+                               float eps, void *out, int64_t ld_out, cudaStream_t st);
+cudaError_t launch_rope_kv(const void *qkv, int dt, int64_t B, int64_t ld_qkv, int hq, int hkv, int d, const void *cosv, const void *sinv,
+                           void *q_out, void *k_cache, void *v_cache, int64_t ctx_len, int64_t pos, cudaStream_t st);
+int64_t decode_attention_scratch_floats(int64_t B, int hq, int64_t n_ctx);
+cudaError_t launch_decode_attention(const void *q, const void *k_cache, const void *v_cache, int dt, int64_t B, int hq, int hkv, int d,
+                                    int64_t ctx_len, int64_t n_ctx, float *part, void *out, cudaStream_t st);
+
 // Routing and combination of a mixture-of-experts layer (ttq_moe.cu).
 struct MoeRouting {
     int *counts, *row_start, *cursor;  // [E]

@@ -1,10 +1,10 @@
 """Llama-style decoder stack wired from QuantLinear layers, for the decode-throughput benchmark.
 
-Only the linears (and silu_and_mul) run in libttq; RMSNorm, RoPE, the KV cache and attention are plain
-torch ops -- glue that stands in for the reference's own layers (workspace/transformers/src/layers:
-norm.nim:23-38, rope.nim:29-92, attn.nim:56-88,149-189) and is not part of the quantized-linear path.
-Dataflow of one layer follows the reference's long-residual block (transformer.nim:122-156):
-attn_norm -> attention -> residual -> mlp_norm -> gated MLP -> residual.
+The linears, silu_and_mul and (by default) the steps between them -- residual add + RMSNorm, RoPE + KV-cache
+append, single-query attention -- run in libttq; ``fused_glue=False`` runs those steps as plain torch ops
+instead.  They stand for the reference's own layers (workspace/transformers/src/layers: norm.nim:23-38,
+rope.nim:29-92, attn.nim:56-88,149-189).  Dataflow of one layer follows the reference's long-residual block
+(transformer.nim:122-156): attn_norm -> attention -> residual -> mlp_norm -> gated MLP -> residual.
 
 Weights are synthetic: every rank draws its own tensor-parallel shard (N(0, 0.02), quantized on the
 device) -- q/kv heads and FFN rows split over ranks, O and down split along K with a sum over ranks.
@@ -18,7 +18,7 @@ import torch
 
 from . import quantize as Q
 from ._lib import FMT_Q4_K, FMT_Q6_K
-from .layers import Context, QuantLinear, silu_and_mul
+from .layers import Context, QuantLinear, add_rmsnorm, decode_attention, rope_kv_append, silu_and_mul
 
 
 @dataclass
@@ -43,10 +43,12 @@ def _qlinear(ctx, fmt, n, k, seed, dev):
 
 
 class DecoderStack:
-    def __init__(self, ctx: Context, cfg: DecoderConfig, batch: int, rank: int = 0, world: int = 1, seed: int = 3000, comm=None):
+    def __init__(self, ctx: Context, cfg: DecoderConfig, batch: int, rank: int = 0, world: int = 1, seed: int = 3000, comm=None,
+                 fused_glue: bool = True):
         assert cfg.n_q_heads % world == 0 and cfg.n_kv_heads % world == 0 and cfg.ffn % (256 * world) == 0
         self.ctx, self.cfg, self.batch, self.rank, self.world = ctx, cfg, batch, rank, world
         self.comm = comm  # tp.Communicator: row-parallel sums fused into the linears when the batch fits
+        self.fused_glue = fused_glue
         dev = ctx.device
         self.dev = dev
         hq, hkv, d = cfg.n_q_heads // world, cfg.n_kv_heads // world, cfg.head_dim
@@ -100,8 +102,26 @@ class DecoderStack:
         dist.all_reduce(y)
         return y
 
+    def _step_fused(self, token_ids: torch.Tensor) -> torch.Tensor:
+        """The layer loop with the library's decode-step kernels: 9 launches per layer besides the linears' own."""
+        cfg, B, d, ctx = self.cfg, self.batch, self.cfg.head_dim, self.ctx
+        h = self.emb_rows[token_ids % self.emb_rows.shape[0]].contiguous()
+        delta = None
+        for L in self.layers:
+            x = add_rmsnorm(ctx, h, delta, L["attn_norm"], cfg.rms_eps)
+            qkv = L["qkv"].forward(x)
+            q = rope_kv_append(ctx, qkv, self.hq, self.hkv, d, self.cos, self.sin, L["k"], L["v"], self.pos)
+            att = decode_attention(ctx, q, L["k"], L["v"], cfg.context)
+            o = self._row_parallel(L["o"], att.view(B, self.hq * d))
+            x = add_rmsnorm(ctx, h, o, L["mlp_norm"], cfg.rms_eps)
+            act = silu_and_mul(ctx, L["gate_up"].forward(x))
+            delta = self._row_parallel(L["down"], act)
+        return add_rmsnorm(ctx, h, delta, self.final_norm, cfg.rms_eps)
+
     def step(self, token_ids: torch.Tensor) -> torch.Tensor:
         """One decode step for `batch` sequences at position context-1; returns next token ids."""
+        if self.fused_glue:
+            return self._pick(self.lm_head.forward(self._step_fused(token_ids), out_dtype=torch.float32))
         cfg, B, d = self.cfg, self.batch, self.cfg.head_dim
         h = self.emb_rows[token_ids % self.emb_rows.shape[0]]
         for L in self.layers:
@@ -120,7 +140,10 @@ class DecoderStack:
             gu = L["gate_up"].forward(x)
             act = silu_and_mul(self.ctx, gu)
             h = h + self._row_parallel(L["down"], act)
-        logits = self.lm_head.forward(self._rms(h, self.final_norm), out_dtype=torch.float32)
+        return self._pick(self.lm_head.forward(self._rms(h, self.final_norm), out_dtype=torch.float32))
+
+    def _pick(self, logits: torch.Tensor) -> torch.Tensor:
+        """Greedy token over the (vocabulary-parallel) logits."""
         if self.world > 1:
             import torch.distributed as dist
 

@@ -307,3 +307,45 @@ class MoELayer:
             self.close()
         except Exception:
             pass
+
+
+def add_rmsnorm(ctx: Context, h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``h += delta`` in place (skipped when ``delta`` is None), returns ``rmsnorm(h) * weight``
+    (norm.nim:23-38, ``forward_with_residual`` fused).  2-D contiguous 16-bit tensors."""
+    m, hid = h.shape
+    if out is None:
+        out = torch.empty_like(h)
+    st = ctx._lib.ttq_add_rmsnorm(ctx.handle, h.data_ptr(), None if delta is None else delta.data_ptr(), weight.data_ptr(),
+                                  _dt(h.dtype), m, hid, h.stride(0), hid if delta is None else delta.stride(0), eps,
+                                  out.data_ptr(), out.stride(0), _stream_ptr(h.device))
+    check(ctx.handle, st)
+    return out
+
+
+def rope_kv_append(ctx: Context, qkv: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int, cos: torch.Tensor,
+                   sin: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: int,
+                   q_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rotate the q and k heads of fused qkv rows for position ``pos`` (rope.nim:29-92, rotate-half), append k and v
+    to the caches ``[B, kv heads, context, head_dim]``; returns q ``[B, q heads, head_dim]``."""
+    b = qkv.shape[0]
+    if q_out is None:
+        q_out = torch.empty((b, n_q_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+    st = ctx._lib.ttq_rope_kv_append(ctx.handle, qkv.data_ptr(), _dt(qkv.dtype), b, qkv.stride(0), n_q_heads, n_kv_heads, head_dim,
+                                     cos.data_ptr(), sin.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                     k_cache.shape[2], pos, _stream_ptr(qkv.device))
+    check(ctx.handle, st)
+    return q_out
+
+
+def decode_attention(ctx: Context, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, n_ctx: int,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Single-query grouped-query attention over cache positions ``0 .. n_ctx-1`` (attn.nim:149-189 for one new
+    token): q ``[B, q heads, 128]``, caches ``[B, kv heads, context, 128]`` -> ``[B, q heads, 128]``."""
+    b, hq, d = q.shape
+    if out is None:
+        out = torch.empty_like(q)
+    st = ctx._lib.ttq_decode_attention(ctx.handle, q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dt(q.dtype), b, hq,
+                                       k_cache.shape[1], d, k_cache.shape[2], n_ctx, out.data_ptr(), _stream_ptr(q.device))
+    check(ctx.handle, st)
+    return out

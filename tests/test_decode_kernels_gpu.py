@@ -1,0 +1,100 @@
+"""Decode-step kernels around the linears (residual + RMSNorm, RoPE + KV append, single-query attention) against
+plain fp32 torch references of the same operations.  Floating-point kernels: tolerances are the 16-bit
+storage rounding (bf16 8 bits, f16 11 bits of mantissa)."""
+import math
+
+import pytest
+import torch
+
+import tattletale_b200 as ttq
+
+pytestmark = pytest.mark.gpu
+
+
+def rel(a, b):
+    return float((a.float() - b.float()).norm() / b.float().norm())
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 6e-3), (torch.float16, 8e-4)])
+@pytest.mark.parametrize("m,hid", [(1, 4096), (5, 1024), (32, 4096), (3, 264)])
+def test_add_rmsnorm(ctx, dtype, tol, m, hid):
+    g = torch.Generator(device="cuda").manual_seed(m + hid)
+    h = torch.randn(m, hid, generator=g, device="cuda").to(dtype)
+    d = torch.randn(m, hid, generator=g, device="cuda").to(dtype)
+    w = (1 + 0.1 * torch.randn(hid, generator=g, device="cuda")).to(dtype)
+    h_ref = (h.float() + d.float()).to(dtype)                      # the residual stream is stored in 16 bits
+    want = torch.nn.functional.rms_norm(h_ref.float(), (hid,), w.float(), 1e-5)
+    h2 = h.clone()
+    out = ttq.add_rmsnorm(ctx, h2, d, w, 1e-5)
+    assert torch.equal(h2, h_ref)
+    assert rel(out, want) < tol
+    # without a residual the stream is untouched
+    h3 = h.clone()
+    out = ttq.add_rmsnorm(ctx, h3, None, w, 1e-5)
+    assert torch.equal(h3, h)
+    assert rel(out, torch.nn.functional.rms_norm(h.float(), (hid,), w.float(), 1e-5)) < tol
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 6e-3), (torch.float16, 8e-4)])
+def test_rope_kv_append(ctx, dtype, tol):
+    b, hq, hkv, d, ctx_len, pos = 3, 8, 2, 128, 64, 17
+    g = torch.Generator(device="cuda").manual_seed(5)
+    qkv = torch.randn(b, (hq + 2 * hkv) * d, generator=g, device="cuda").to(dtype)
+    inv = 1.0 / (500000.0 ** (torch.arange(0, d, 2, device="cuda", dtype=torch.float64) / d))
+    ang = pos * inv
+    cos = torch.cat([ang.cos(), ang.cos()]).to(dtype)
+    sin = torch.cat([ang.sin(), ang.sin()]).to(dtype)
+    kc = torch.zeros(b, hkv, ctx_len, d, device="cuda", dtype=dtype)
+    vc = torch.zeros_like(kc)
+    q = ttq.rope_kv_append(ctx, qkv, hq, hkv, d, cos, sin, kc, vc, pos)
+
+    def rope(t):
+        t = t.float()
+        rot = torch.cat([-t[..., d // 2:], t[..., :d // 2]], dim=-1)
+        return t * cos.float() + rot * sin.float()
+
+    q_ref = rope(qkv[:, :hq * d].view(b, hq, d))
+    k_ref = rope(qkv[:, hq * d:(hq + hkv) * d].view(b, hkv, d))
+    v_ref = qkv[:, (hq + hkv) * d:].view(b, hkv, d)
+    assert rel(q, q_ref) < tol
+    assert rel(kc[:, :, pos], k_ref) < tol
+    assert torch.equal(vc[:, :, pos], v_ref)
+    kc[:, :, pos] = 0
+    vc[:, :, pos] = 0
+    assert not kc.any() and not vc.any()  # nothing else was written
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 6e-3), (torch.float16, 1e-3)])
+@pytest.mark.parametrize("b,hq,hkv,n_ctx", [(1, 32, 8, 2048), (2, 8, 8, 130), (3, 16, 2, 1), (2, 4, 2, 128), (1, 8, 4, 777)])
+def test_decode_attention(ctx, dtype, tol, b, hq, hkv, n_ctx):
+    d, ctx_len = 128, max(n_ctx, 256)
+    g = torch.Generator(device="cuda").manual_seed(b * 100 + n_ctx)
+    q = torch.randn(b, hq, d, generator=g, device="cuda").to(dtype)
+    kc = torch.randn(b, hkv, ctx_len, d, generator=g, device="cuda").to(dtype)
+    vc = torch.randn(b, hkv, ctx_len, d, generator=g, device="cuda").to(dtype)
+    out = ttq.decode_attention(ctx, q, kc, vc, n_ctx)
+    grp = hq // hkv
+    k = kc[:, :, :n_ctx].float().repeat_interleave(grp, dim=1)
+    v = vc[:, :, :n_ctx].float().repeat_interleave(grp, dim=1)
+    s = torch.einsum("bhd,bhpd->bhp", q.float(), k) / math.sqrt(d)
+    want = torch.einsum("bhp,bhpd->bhd", torch.softmax(s, dim=-1), v)
+    assert rel(out, want) < tol
+    # positions beyond n_ctx are never read: poison them
+    if n_ctx < ctx_len:
+        kc[:, :, n_ctx:] = float("nan")
+        vc[:, :, n_ctx:] = float("nan")
+        assert torch.equal(ttq.decode_attention(ctx, q, kc, vc, n_ctx), out)
+
+
+def test_argument_errors(ctx):
+    q = torch.zeros(1, 6, 128, device="cuda", dtype=torch.bfloat16)
+    kc = torch.zeros(1, 4, 16, 128, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(ttq.TtqError):
+        ttq.decode_attention(ctx, q, kc, kc, 8)       # 6 query heads over 4 kv heads
+    q = torch.zeros(1, 4, 64, device="cuda", dtype=torch.bfloat16)
+    kc = torch.zeros(1, 4, 16, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(ttq.TtqError):
+        ttq.decode_attention(ctx, q, kc, kc, 8)       # head dimension other than 128
+    h = torch.zeros(2, 100, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(ttq.TtqError):
+        ttq.add_rmsnorm(ctx, h, None, torch.ones(100, device="cuda", dtype=torch.bfloat16), 1e-5)  # H % 8
