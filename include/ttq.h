@@ -205,6 +205,14 @@ TTQ_API ttq_status ttq_linear_forward_static(const ttq_weight *w, const void *x_
                                              ttq_dtype y_dt, int64_t ldy, void *stream, char *errbuf,
                                              size_t errbuf_len);
 
+/* The down projection of a gated MLP with the activation folded into its input conversion
+ * (GatedMLP.forward, workspace/transformers/src/layers/mlp.nim:56-60: silu_and_mul then down_proj):
+ * gate_up_dev is [M][ld_gate_up] with 2K used columns [gate | up], y = (silu(gate) * up) . W^T + b.
+ * Same conventions as ttq_linear_forward; block formats only (TTQ_ERR_UNSUPPORTED for TTQ_FMT_TQ3). */
+TTQ_API ttq_status ttq_linear_forward_gated(ttq_ctx *ctx, const ttq_weight *w, const void *gate_up_dev, ttq_dtype x_dt,
+                                            int64_t M, int64_t ld_gate_up, const void *bias_dev, ttq_dtype bias_dt,
+                                            void *y_dev, ttq_dtype y_dt, int64_t ldy, void *stream);
+
 /* ---- adjacent step: silu_and_mul (kernels/activations.nim:14-38) ---------------------------- */
 
 /* out[m][h] = silu(in[m][h]) * in[m][H + h]; in is [M][ld_in] with 2H used columns, out [M][ld_out].

@@ -483,9 +483,9 @@ ttq_status ttq_dequantize(ttq_ctx *ctx, const ttq_weight *w, float *dev_out, int
     return TTQ_OK;
 }
 
-ttq_status ttq_linear_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_dev, ttq_dtype x_dt, int64_t M,
+static ttq_status linear_forward_impl(ttq_ctx *ctx, const ttq_weight *w, const void *x_dev, ttq_dtype x_dt, int64_t M,
                               int64_t ldx, const void *bias_dev, ttq_dtype bias_dt, void *y_dev, ttq_dtype y_dt,
-                              int64_t ldy, void *stream) {
+                              int64_t ldy, void *stream, bool gated) {
     if (!ctx) return TTQ_ERR_INVALID_ARG;
     if (!w) return fail(ctx, TTQ_ERR_INVALID_ARG, "weight is NULL");
     if (w->ctx != ctx) return fail(ctx, TTQ_ERR_INVALID_ARG, "weight belongs to another context");
@@ -495,7 +495,9 @@ ttq_status ttq_linear_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_d
     if (x_dt != TTQ_DT_BF16 && x_dt != TTQ_DT_F16) return fail(ctx, TTQ_ERR_INVALID_ARG, "x dtype must be bf16 or f16");
     if (!valid_dt(y_dt)) return fail(ctx, TTQ_ERR_INVALID_ARG, "unknown y dtype %d", (int)y_dt);
     if (bias_dev && !valid_dt(bias_dt)) return fail(ctx, TTQ_ERR_INVALID_ARG, "unknown bias dtype %d", (int)bias_dt);
-    if (ldx < w->K) return fail(ctx, TTQ_ERR_SHAPE, "ldx=%lld < K=%lld", (long long)ldx, (long long)w->K);
+    if (ldx < (gated ? 2 : 1) * w->K)
+        return fail(ctx, TTQ_ERR_SHAPE, "ldx=%lld < %s=%lld", (long long)ldx, gated ? "2K" : "K", (long long)((gated ? 2 : 1) * w->K));
+    if (gated && w->fmt == TTQ_FMT_TQ3) return fail(ctx, TTQ_ERR_UNSUPPORTED, "the gated form serves the block formats");
     if (ldy < w->N) return fail(ctx, TTQ_ERR_SHAPE, "ldy=%lld < N=%lld", (long long)ldy, (long long)w->N);
     if (w->SBp * TILE_K > ctx->xq_capacity_k)
         return fail(ctx, TTQ_ERR_LIMIT, "K=%lld exceeds the activation scratch capacity %lld", (long long)w->K,
@@ -508,6 +510,7 @@ ttq_status ttq_linear_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_d
     a.x_dt = x_dt; a.ldx = ldx;
     a.bias = bias_dev; a.bias_dt = bias_dt;
     a.y_dt = y_dt; a.ldy = ldy;
+    a.gated = gated;
     static const bool use_gemm = []() {
         const char *v = getenv("TTQ_GEMM");
         return !(v && v[0] == '0');
@@ -550,6 +553,17 @@ ttq_status ttq_linear_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_d
         if (e != cudaSuccess) return cuda_fail(ctx, e, "linear forward launch");
     }
     return TTQ_OK;
+}
+
+ttq_status ttq_linear_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_dev, ttq_dtype x_dt, int64_t M, int64_t ldx,
+                              const void *bias_dev, ttq_dtype bias_dt, void *y_dev, ttq_dtype y_dt, int64_t ldy, void *stream) {
+    return linear_forward_impl(ctx, w, x_dev, x_dt, M, ldx, bias_dev, bias_dt, y_dev, y_dt, ldy, stream, false);
+}
+
+ttq_status ttq_linear_forward_gated(ttq_ctx *ctx, const ttq_weight *w, const void *gate_up_dev, ttq_dtype x_dt, int64_t M,
+                                    int64_t ld_gate_up, const void *bias_dev, ttq_dtype bias_dt, void *y_dev, ttq_dtype y_dt,
+                                    int64_t ldy, void *stream) {
+    return linear_forward_impl(ctx, w, gate_up_dev, x_dt, M, ld_gate_up, bias_dev, bias_dt, y_dev, y_dt, ldy, stream, true);
 }
 
 ttq_status ttq_linear_forward_host(ttq_ctx *ctx, const ttq_weight *w, const void *x_host, ttq_dtype x_dt, int64_t M,

@@ -68,6 +68,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(void *__restrict__ h, 
                                                           int dt, int64_t H, int64_t ld_h, int64_t ld_delta, float eps,
                                                           void *__restrict__ out, int64_t ld_out) {
     __shared__ float red[8];
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int64_t m = blockIdx.x;
     uint8_t *hrow = reinterpret_cast<uint8_t *>(h) + m * ld_h * 2;
     const uint8_t *drow = delta ? reinterpret_cast<const uint8_t *>(delta) + m * ld_delta * 2 : nullptr;
@@ -103,6 +105,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(void *__restrict__ h, 
 __global__ void rope_kv_kernel(const void *__restrict__ qkv, int dt, int64_t ld_qkv, int hq, int hkv, int d, const void *__restrict__ cosv,
                                const void *__restrict__ sinv, void *__restrict__ q_out, void *__restrict__ k_cache, void *__restrict__ v_cache,
                                int64_t ctx_len, int64_t pos) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int head = blockIdx.x, b = blockIdx.y, i = threadIdx.x, half = d / 2;
     const int64_t src = (int64_t)b * ld_qkv + (int64_t)head * d;
     const float x1 = load_as_float(qkv, dt, src + i), x2 = load_as_float(qkv, dt, src + half + i);
@@ -139,6 +143,8 @@ __global__ void __launch_bounds__(ATT_SLICE) decode_attn_kernel(const void *__re
     __shared__ float q_s[G][ATT_D];
     __shared__ float p_s[G][ATT_SLICE];
     __shared__ float o_s[8][G][ATT_D];
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int slice = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, t = threadIdx.x;
     const int warp = t >> 5, lane = t & 31;
     const int slices = gridDim.x;
@@ -255,6 +261,8 @@ __global__ void __launch_bounds__(ATT_SLICE) decode_attn_kernel(const void *__re
 // grid (hq, B), 128 threads
 __global__ void __launch_bounds__(ATT_D) decode_attn_merge_kernel(const float *__restrict__ part, int hq, int hkv, int G, int slices,
                                                                   void *__restrict__ out, int dt) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int h = blockIdx.x, b = blockIdx.y, t = threadIdx.x;
     const int kvh = h / G, g = h % G;
     const float *base = part + (((int64_t)b * hkv + kvh) * slices * G + g) * (2 + ATT_D);
@@ -274,15 +282,13 @@ __global__ void __launch_bounds__(ATT_D) decode_attn_merge_kernel(const float *_
 
 cudaError_t launch_add_rmsnorm(void *h, const void *delta, const void *weight, int dt, int64_t M, int64_t H, int64_t ld_h, int64_t ld_delta,
                                float eps, void *out, int64_t ld_out, cudaStream_t st) {
-    add_rmsnorm_kernel<<<(unsigned)M, 256, 0, st>>>(h, delta, weight, dt, H, ld_h, ld_delta, eps, out, ld_out);
-    return cudaGetLastError();
+    return launch_pdl(add_rmsnorm_kernel, dim3((unsigned)M), dim3(256), 0, st, h, delta, weight, dt, H, ld_h, ld_delta, eps, out, ld_out);
 }
 
 cudaError_t launch_rope_kv(const void *qkv, int dt, int64_t B, int64_t ld_qkv, int hq, int hkv, int d, const void *cosv, const void *sinv,
                            void *q_out, void *k_cache, void *v_cache, int64_t ctx_len, int64_t pos, cudaStream_t st) {
-    rope_kv_kernel<<<dim3((unsigned)(hq + 2 * hkv), (unsigned)B), d / 2, 0, st>>>(qkv, dt, ld_qkv, hq, hkv, d, cosv, sinv, q_out, k_cache,
-                                                                                    v_cache, ctx_len, pos);
-    return cudaGetLastError();
+    return launch_pdl(rope_kv_kernel, dim3((unsigned)(hq + 2 * hkv), (unsigned)B), dim3((unsigned)(d / 2)), 0, st, qkv, dt, ld_qkv, hq, hkv, d,
+                      cosv, sinv, q_out, k_cache, v_cache, ctx_len, pos);
 }
 
 int64_t decode_attention_scratch_floats(int64_t B, int hq, int64_t n_ctx) {
@@ -297,17 +303,17 @@ cudaError_t launch_decode_attention(const void *q, const void *k_cache, const vo
     const int slices = (int)((n_ctx + ATT_SLICE - 1) / ATT_SLICE);
     const float scale = rsqrtf((float)d);
     const dim3 grid((unsigned)slices, (unsigned)hkv, (unsigned)B);
+    cudaError_t e;
+    const dim3 blk(ATT_SLICE);
     switch (G) {
-        case 1: decode_attn_kernel<1><<<grid, ATT_SLICE, 0, st>>>(q, k_cache, v_cache, dt, hq, hkv, ctx_len, n_ctx, scale, part); break;
-        case 2: decode_attn_kernel<2><<<grid, ATT_SLICE, 0, st>>>(q, k_cache, v_cache, dt, hq, hkv, ctx_len, n_ctx, scale, part); break;
-        case 4: decode_attn_kernel<4><<<grid, ATT_SLICE, 0, st>>>(q, k_cache, v_cache, dt, hq, hkv, ctx_len, n_ctx, scale, part); break;
-        case 8: decode_attn_kernel<8><<<grid, ATT_SLICE, 0, st>>>(q, k_cache, v_cache, dt, hq, hkv, ctx_len, n_ctx, scale, part); break;
+        case 1: e = launch_pdl(decode_attn_kernel<1>, grid, blk, 0, st, q, k_cache, v_cache, dt, hq, hkv, ctx_len, n_ctx, scale, part); break;
+        case 2: e = launch_pdl(decode_attn_kernel<2>, grid, blk, 0, st, q, k_cache, v_cache, dt, hq, hkv, ctx_len, n_ctx, scale, part); break;
+        case 4: e = launch_pdl(decode_attn_kernel<4>, grid, blk, 0, st, q, k_cache, v_cache, dt, hq, hkv, ctx_len, n_ctx, scale, part); break;
+        case 8: e = launch_pdl(decode_attn_kernel<8>, grid, blk, 0, st, q, k_cache, v_cache, dt, hq, hkv, ctx_len, n_ctx, scale, part); break;
         default: return cudaErrorInvalidValue;
     }
-    cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    decode_attn_merge_kernel<<<dim3((unsigned)hq, (unsigned)B), ATT_D, 0, st>>>(part, hq, hkv, G, slices, out, dt);
-    return cudaGetLastError();
+    return launch_pdl(decode_attn_merge_kernel, dim3((unsigned)hq, (unsigned)B), dim3(ATT_D), 0, st, (const float *)part, hq, hkv, G, slices, out, dt);
 }
 
 }  // namespace ttq

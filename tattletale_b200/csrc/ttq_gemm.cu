@@ -735,7 +735,8 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
         const uint8_t *xs = reinterpret_cast<const uint8_t *>(a.x) + (size_t)m0 * a.ldx * esz_x;
         const int64_t chunks = Mp * (Kp / 8);
         const unsigned grid = (unsigned)((chunks + 255) / 256 < 148 * 16 ? (chunks + 255) / 256 : 148 * 16);
-        xh_prep_kernel<false><<<grid, 256, 0, st>>>(xs, a.x_dt, Ms, Mp, a.K, Kp, a.ldx, xh, nullptr, nullptr, 0);
+        if (a.gated) xh_prep_kernel<true><<<grid, 256, 0, st>>>(xs, a.x_dt, Ms, Mp, a.K, Kp, a.ldx, xh, nullptr, nullptr, 0);
+        else xh_prep_kernel<false><<<grid, 256, 0, st>>>(xs, a.x_dt, Ms, Mp, a.K, Kp, a.ldx, xh, nullptr, nullptr, 0);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
         ++*launches;

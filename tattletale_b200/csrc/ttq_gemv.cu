@@ -84,8 +84,6 @@ __device__ __forceinline__ void named_barrier(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
-__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
@@ -147,6 +145,7 @@ __device__ __forceinline__ RawChunk xprep_load(const void *xrow, int x_dt, int64
 
 // One warp converts the 256-wide chunk `sb` of activation row `xrow` (nullptr = emit zeros):
 // xq = round(x * 32639 / amax) in [-32639, 32639], stored as two int8 planes with xq = 256*hi + lo.
+__device__ __forceinline__ void xprep_convert_vals(const float (&v)[8], int sb, int lane, const XqRow &dst);
 __device__ __forceinline__ void xprep_convert(const RawChunk &rc, const void *xrow, int x_dt, int64_t K, int sb, int lane,
                                               const XqRow &dst) {
     const int64_t k0 = (int64_t)sb * TILE_K + 8 * lane;
@@ -171,6 +170,11 @@ __device__ __forceinline__ void xprep_convert(const RawChunk &rc, const void *xr
         for (int i = 0; i < 8; i++)
             if (k0 + i < K) v[i] = load_as_float(xrow, x_dt, k0 + i);
     }
+    xprep_convert_vals(v, sb, lane, dst);
+}
+// the 8 values of this lane (k0 = 256 sb + 8 lane, zero beyond K) -> planes, group sums, chunk scale
+__device__ __forceinline__ void xprep_convert_vals(const float (&v)[8], int sb, int lane, const XqRow &dst) {
+    const int64_t k0 = (int64_t)sb * TILE_K + 8 * lane;
     float amax = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
@@ -209,7 +213,7 @@ __device__ __forceinline__ void xprep_chunk(const void *xrow, int x_dt, int64_t 
 // Separate conversion pass: (Mpad x SBp) chunks, one warp each; rows >= M are written as zeros.
 __global__ void __launch_bounds__(GEMV_THREADS) xprep_kernel(const void *__restrict__ x, int x_dt, int64_t M,
                                                              int64_t Mpad, int64_t K, int64_t ldx, int64_t SBp,
-                                                             XqView xq, unsigned long long *trace) {
+                                                             XqView xq, unsigned long long *trace, int gated) {
     unsigned long long *te = trace_open(trace, 1);
     grid_launch_dependents();
     grid_dependency_wait();  // the scratch planes may still be read by the preceding kernel
@@ -227,7 +231,23 @@ __global__ void __launch_bounds__(GEMV_THREADS) xprep_kernel(const void *__restr
         const int esz = x_dt == TTQ_DT_F32 ? 4 : 2;
         xrow = reinterpret_cast<const uint8_t *>(x) + m * ldx * esz;
     }
-    xprep_chunk(xrow, x_dt, K, sb, lane, dst);
+    if (gated && xrow != nullptr) {
+        // the row holds 2K values [gate | up]: the operand is silu(gate[k]) * up[k] (the gated-MLP activation,
+        // kernels/activations.nim:14-38, folded into the conversion)
+        const int64_t k0 = (int64_t)sb * TILE_K + 8 * lane;
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            v[i] = 0.f;
+            if (k0 + i < K) {
+                const float gv = load_as_float(xrow, x_dt, k0 + i), uv = load_as_float(xrow, x_dt, K + k0 + i);
+                v[i] = gv / (1.f + expf(-gv)) * uv;
+            }
+        }
+        xprep_convert_vals(v, sb, lane, dst);
+    } else {
+        xprep_chunk(xrow, x_dt, K, sb, lane, dst);
+    }
     if (te) {
         te[5] = global_ns();
         te[6] = gridDim.x;
@@ -837,29 +857,6 @@ int pick_wk(int64_t NT, int64_t SBp, int64_t cap, int nw) {
     return best;
 }
 
-bool env_flag(const char *name, bool dflt) {
-    const char *v = getenv(name);
-    if (!v || !*v) return dflt;
-    return v[0] != '0';
-}
-
-// Launch with programmatic stream serialization (the kernel calls griddepcontrol.wait itself).
-template <typename... KArgs, typename... Args>
-cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
-    static const bool pdl = env_flag("TTQ_PDL", true);
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kernel, args...);
-}
-
 constexpr size_t GEMV_SMEM_BIG = 200 * 1024;  // one CTA per SM
 
 template <int FMT, int XSRC, int MR, int NPASS, int NW>
@@ -941,6 +938,7 @@ cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t 
         return XSRC_COPY;                           // "separate" (default)
     }();
     int mode = pref;
+    if (a.gated && mode == XSRC_CONVERT) mode = XSRC_COPY;  // the gated activation lives in the separate pass
     const int nw = (a.M <= 4 && mode != XSRC_GLOBAL) ? pick_nw(fmt, mode, a.M, a.SBp) : 0;
     if (nw == 0) mode = XSRC_GLOBAL;
     const bool shared = mode != XSRC_GLOBAL;
@@ -949,7 +947,7 @@ cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t 
         const int64_t Mpad = shared ? a.M : (a.M <= 4 ? 4 : (a.M <= 8 ? 8 : 16));
         const int64_t units = Mpad * a.SBp;
         e = launch_pdl(xprep_kernel, dim3((unsigned)((units + GEMV_WARPS - 1) / GEMV_WARPS)), dim3(GEMV_THREADS), 0, st, a.x,
-                       a.x_dt, a.M, Mpad, a.K, a.ldx, a.SBp, xq, trace);
+                       a.x_dt, a.M, Mpad, a.K, a.ldx, a.SBp, xq, trace, a.gated ? 1 : 0);
         if (e != cudaSuccess) return e;
         ++*launches;
     }

@@ -4,6 +4,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <cstdlib>
 #include <stdint.h>
 
 #include "ttq.h"
@@ -113,7 +114,38 @@ struct LinearArgs {
     void *y;
     int y_dt;
     int64_t ldy;
+    bool gated = false;  // x rows hold 2K values [gate | up]; the operand is silu(gate[k]) * up[k]
 };
+
+// ---- programmatic dependent launch ---------------------------------------------------------------------
+// Kernels of a decode chain are launched with programmatic stream serialization: a kernel tells the scheduler
+// early that its successor may be set up (grid_launch_dependents) and every such kernel waits for its
+// predecessor's completion and memory flush (grid_dependency_wait) before it touches anything that depends on
+// it -- only loads of constant data (weights) may precede the wait.  TTQ_PDL=0 launches plainly.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool env_flag(const char *name, bool dflt) {
+    const char *v = getenv(name);
+    if (!v || !*v) return dflt;
+    return v[0] != '0';
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    static const bool pdl = env_flag("TTQ_PDL", true);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
 
 // Grouped (mixture-of-experts) GEMM on the tensor-core path: activation rows are routed into BM-row
 // tiles, each owned by one weight matrix; all matrices share N x K.

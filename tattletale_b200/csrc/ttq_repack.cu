@@ -203,6 +203,8 @@ __global__ void __launch_bounds__(256) wimg_kernel(const uint8_t *__restrict__ t
 template <typename T>
 __global__ void __launch_bounds__(256) silu_and_mul_kernel(const T *__restrict__ in, T *__restrict__ out,
                                                            int64_t M, int64_t H, int64_t ld_in, int64_t ld_out) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int64_t total = M * H;
     for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
          e += (int64_t)gridDim.x * blockDim.x) {
@@ -251,12 +253,11 @@ cudaError_t launch_silu_and_mul(const void *in, int dt, int64_t M, int64_t H, in
                                 int64_t ld_out, cudaStream_t st) {
     int grid = grid_for(M * H, 256 * 4, 148 * 16);
     if (dt == TTQ_DT_BF16)
-        silu_and_mul_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16 *)in, (__nv_bfloat16 *)out, M, H, ld_in, ld_out);
-    else if (dt == TTQ_DT_F16)
-        silu_and_mul_kernel<__half><<<grid, 256, 0, st>>>((const __half *)in, (__half *)out, M, H, ld_in, ld_out);
-    else
-        silu_and_mul_kernel<float><<<grid, 256, 0, st>>>((const float *)in, (float *)out, M, H, ld_in, ld_out);
-    return cudaGetLastError();
+        return launch_pdl(silu_and_mul_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16 *)in, (__nv_bfloat16 *)out, M, H,
+                          ld_in, ld_out);
+    if (dt == TTQ_DT_F16)
+        return launch_pdl(silu_and_mul_kernel<__half>, dim3(grid), dim3(256), 0, st, (const __half *)in, (__half *)out, M, H, ld_in, ld_out);
+    return launch_pdl(silu_and_mul_kernel<float>, dim3(grid), dim3(256), 0, st, (const float *)in, (float *)out, M, H, ld_in, ld_out);
 }
 
 }  // namespace ttq

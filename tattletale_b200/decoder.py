@@ -114,8 +114,11 @@ class DecoderStack:
             att = decode_attention(ctx, q, L["k"], L["v"], cfg.context)
             o = self._row_parallel(L["o"], att.view(B, self.hq * d))
             x = add_rmsnorm(ctx, h, o, L["mlp_norm"], cfg.rms_eps)
-            act = silu_and_mul(ctx, L["gate_up"].forward(x))
-            delta = self._row_parallel(L["down"], act)
+            gu = L["gate_up"].forward(x)
+            if self.world == 1:
+                delta = L["down"].forward_gated(gu)  # silu(gate) * up folded into the projection's input conversion
+            else:
+                delta = self._row_parallel(L["down"], silu_and_mul(ctx, gu))
         return add_rmsnorm(ctx, h, delta, self.final_norm, cfg.rms_eps)
 
     def step(self, token_ids: torch.Tensor) -> torch.Tensor:

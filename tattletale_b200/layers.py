@@ -152,6 +152,27 @@ class QuantLinear:
 
     __call__ = forward
 
+    def forward_gated(self, gate_up: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``forward(silu(gate) * up)`` for ``gate_up = [gate | up]`` of ``2 * in_features`` columns: the activation
+        of the gated MLP (mlp.nim:56-60) folded into the input conversion of this (down) projection."""
+        if gate_up.shape[-1] != 2 * self.in_features:
+            raise TtqError(2, f"gate_up has {gate_up.shape[-1]} columns, expected {2 * self.in_features}")
+        x2 = gate_up.reshape(-1, 2 * self.in_features)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        m = x2.shape[0]
+        if out is None:
+            out = torch.empty((m, self.out_features), dtype=out_dtype or gate_up.dtype, device=gate_up.device)
+        y2 = out.reshape(-1, self.out_features)
+        b = self.bias
+        st = self.ctx._lib.ttq_linear_forward_gated(
+            self.ctx.handle, self.handle, x2.data_ptr(), _dt(x2.dtype), m, x2.stride(0) if m > 1 else 2 * self.in_features,
+            None if b is None else b.data_ptr(), _lib.DT_F32 if b is None else _dt(b.dtype),
+            y2.data_ptr(), _dt(y2.dtype), y2.stride(0) if m > 1 else self.out_features, _stream_ptr(gate_up.device))
+        check(self.ctx.handle, st)
+        return out.reshape(*gate_up.shape[:-1], self.out_features)
+
     def forward_allreduce(self, x: torch.Tensor, comm, out_dtype: Optional[torch.dtype] = None,
                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Row-parallel forward: this rank's K shard, summed over all ranks.  Decode-size batches go through the

@@ -212,3 +212,22 @@ def test_launch_counter_moves(ctx):
     lin.forward(torch.zeros(64, 256, dtype=torch.bfloat16, device="cuda"))
     assert ctx.launch_count == before + 6  # activation pass + tensor-core GEMM
     lin.close()
+
+
+@pytest.mark.parametrize("fmt", ALL_FMTS, ids=FMT_IDS)
+@pytest.mark.parametrize("m", [1, 3, 8, 40])
+def test_gated_input_conversion(ctx, fmt, m):
+    """y = W (silu(gate) * up) with the activation folded into the input conversion (decode kernel, fused GEMM
+    for Q4_K, expansion + GEMM for the other formats), against the checker's silu_and_mul + linear."""
+    n, k = 96, 512
+    blocks = make_weight(fmt, n, k, seed=300 + m)
+    gu = make_x(m, 2 * k, seed=301 + m)
+    lin = ttq.QuantLinear(ctx, fmt, torch.from_numpy(blocks), k)
+    y = lin.forward_gated(gu.cuda(), out_dtype=torch.float32)
+    ctx.check_device_status()
+    act = oracle.silu_and_mul(gu.float().numpy())
+    want = oracle.linear(OFMT[fmt], blocks, act, oracle.F32)
+    assert rel_l2(y.cpu().numpy(), want) < TOL
+    with pytest.raises(ttq.TtqError):
+        lin.forward_gated(gu.cuda()[:, : k])
+    lin.close()
