@@ -328,7 +328,7 @@ def ours_arm(args):
         e2e_s = (time.perf_counter() - t0) / e2e_steps
         e2e = {"value": round(step_bytes / e2e_s / 1e9, 3), "unit": "GB/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_s * 1e3, 4), "steps": e2e_steps,
-               "api": "ttq_linear_forward_host (one call per linear: H2D, kernel, D2H, sync)"}
+               "api": "ttq_linear_forward_host, one call per linear on pinned host buffers: the kernels read x and write y through the buffers' device mappings (no staging copy), status word copied back, one sync per call"}
 
     # ---- per-shape breakdown (device-resident, cold L2: the 32 layers' copies are rotated)
     per_shape = {}

@@ -582,12 +582,38 @@ ttq_status ttq_linear_forward_host(ttq_ctx *ctx, const ttq_weight *w, const void
         return fail(ctx, TTQ_ERR_LIMIT, "host-entry staging capacity exceeded (x %zu B, y %zu B)", xb, yb);
     TTQ_CUDA(ctx, cudaSetDevice(ctx->device));
     cudaStream_t st = ctx->host_stream;
-    TTQ_CUDA(ctx, cudaMemcpyAsync(ctx->stage_x, x_host, xb, cudaMemcpyHostToDevice, st));
-    if (bias_host) TTQ_CUDA(ctx, cudaMemcpyAsync(ctx->stage_b, bias_host, bbytes, cudaMemcpyHostToDevice, st));
-    ttq_status s = ttq_linear_forward(ctx, w, ctx->stage_x, x_dt, M, ldx, bias_host ? ctx->stage_b : nullptr, bias_dt,
-                                      ctx->stage_y, y_dt, ldy, st);
-    if (s != TTQ_OK) return s;
-    TTQ_CUDA(ctx, cudaMemcpyAsync(y_host, ctx->stage_y, yb, cudaMemcpyDeviceToHost, st));
+    // Decode-size calls on page-locked buffers skip the staging copies: the kernels read x and write y through
+    // the buffers' device mappings (8-60 KB over the host link), which leaves one small copy (the status word)
+    // and one synchronisation per call.  Pageable buffers and larger transfers go through the staging copies.
+    const void *x_map = nullptr, *b_map = nullptr;
+    void *y_map = nullptr;
+    bool direct = xb + yb + bbytes <= (1u << 20);
+    if (direct) {
+        auto mapped = [](const void *p) -> void * {
+            cudaPointerAttributes at;
+            if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+                cudaGetLastError();
+                return nullptr;
+            }
+            return at.type == cudaMemoryTypeHost ? at.devicePointer : nullptr;
+        };
+        x_map = mapped(x_host);
+        y_map = mapped(y_host);
+        if (bias_host) b_map = mapped(bias_host);
+        direct = x_map && y_map && (!bias_host || b_map);
+    }
+    ttq_status s;
+    if (direct) {
+        s = ttq_linear_forward(ctx, w, x_map, x_dt, M, ldx, b_map, bias_dt, y_map, y_dt, ldy, st);
+        if (s != TTQ_OK) return s;
+    } else {
+        TTQ_CUDA(ctx, cudaMemcpyAsync(ctx->stage_x, x_host, xb, cudaMemcpyHostToDevice, st));
+        if (bias_host) TTQ_CUDA(ctx, cudaMemcpyAsync(ctx->stage_b, bias_host, bbytes, cudaMemcpyHostToDevice, st));
+        s = ttq_linear_forward(ctx, w, ctx->stage_x, x_dt, M, ldx, bias_host ? ctx->stage_b : nullptr, bias_dt, ctx->stage_y, y_dt,
+                               ldy, st);
+        if (s != TTQ_OK) return s;
+        TTQ_CUDA(ctx, cudaMemcpyAsync(y_host, ctx->stage_y, yb, cudaMemcpyDeviceToHost, st));
+    }
     // the status word rides along with the result: one synchronisation per call
     TTQ_CUDA(ctx, cudaMemcpyAsync(ctx->host_status, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, st));
     TTQ_CUDA(ctx, cudaStreamSynchronize(st));

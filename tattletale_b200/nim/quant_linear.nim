@@ -34,6 +34,16 @@ proc ttq_linear_forward(ctx: ptr TtqCtx, w: ptr TtqWeight, x: pointer, xDt: TtqD
                         stream: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
 proc ttq_silu_and_mul(ctx: ptr TtqCtx, inp: pointer, dt: TtqDtype, M, H, ldIn: int64, outp: pointer,
                       ldOut: int64, stream: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_linear_forward_gated(ctx: ptr TtqCtx, w: ptr TtqWeight, gateUp: pointer, xDt: TtqDtype, M, ldGateUp: int64,
+                              bias: pointer, biasDt: TtqDtype, y: pointer, yDt: TtqDtype, ldy: int64,
+                              stream: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_add_rmsnorm(ctx: ptr TtqCtx, h, delta, weight: pointer, dt: TtqDtype, M, H, ldH, ldDelta: int64,
+                     eps: cfloat, outp: pointer, ldOut: int64, stream: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_rope_kv_append(ctx: ptr TtqCtx, qkv: pointer, dt: TtqDtype, B, ldQkv: int64, hq, hkv, d: int32,
+                        cosv, sinv, qOut, kCache, vCache: pointer, ctxLen, pos: int64,
+                        stream: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_decode_attention(ctx: ptr TtqCtx, q, kCache, vCache: pointer, dt: TtqDtype, B: int64, hq, hkv, d: int32,
+                          ctxLen, nCtx: int64, outp: pointer, stream: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
 
 template check(ctx: ptr TtqCtx, rc: TtqStatus) =
   ## Non-zero status -> ValueError, the exception style of the reference's own loaders
@@ -118,3 +128,28 @@ proc silu_and_mul*(ctx: TtqContext, x: TorchTensor, stream: pointer = nil): Torc
   result = F.empty(outShape, x.options())
   check(ctx.handle, ttq_silu_and_mul(ctx.handle, x2.data_ptr(byte), ttqDtype(x2.scalarType()), x2.size(0).int64,
                                      H.int64, (2 * H).int64, result.data_ptr(byte), H.int64, stream))
+
+
+proc forward_gated*(self: QuantLinear, gate_up: TorchTensor, stream: pointer = nil): TorchTensor =
+  ## ``down_proj.forward(silu_and_mul(gate_up))`` of GatedMLP.forward (workspace/transformers/src/layers/mlp.nim:56-60)
+  ## in one call: the activation is computed inside the projection's input conversion.
+  let g2 = gate_up.reshape([-1, 2 * self.in_features]).contiguous()
+  var outShape = gate_up.sizes().asNimView().toSeq()
+  outShape[^1] = self.out_features
+  result = F.empty(outShape, gate_up.options())
+  let biasPtr = if self.bias.isSome: self.bias.get().data_ptr(byte) else: nil
+  let biasDt = if self.bias.isSome: ttqDtype(self.bias.get().scalarType()) else: kTtqF32
+  check(self.ctx, ttq_linear_forward_gated(self.ctx, self.weight, g2.data_ptr(byte), ttqDtype(g2.scalarType()),
+                                           g2.size(0).int64, (2 * self.in_features).int64, biasPtr, biasDt,
+                                           result.data_ptr(byte), ttqDtype(result.scalarType()),
+                                           self.out_features.int64, stream))
+
+proc add_rmsnorm*(ctx: TtqContext, h: var TorchTensor, delta: Option[TorchTensor], weight: TorchTensor, eps: float32,
+                  stream: pointer = nil): TorchTensor =
+  ## ``RmsNorm.forward_with_residual`` (workspace/transformers/src/layers/norm.nim:27-38) as one kernel:
+  ## h += delta in place, returns rmsnorm(h) * weight.  h is 2-D and contiguous.
+  result = F.empty_like(h)
+  let dPtr = if delta.isSome: delta.get().data_ptr(byte) else: nil
+  check(ctx.handle, ttq_add_rmsnorm(ctx.handle, h.data_ptr(byte), dPtr, weight.data_ptr(byte), ttqDtype(h.scalarType()),
+                                    h.size(0).int64, h.size(1).int64, h.size(1).int64, h.size(1).int64, eps.cfloat,
+                                    result.data_ptr(byte), h.size(1).int64, stream))
