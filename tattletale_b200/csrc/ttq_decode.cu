@@ -136,7 +136,9 @@ __global__ void rope_kv_kernel(const void *__restrict__ qkv, int dt, int64_t ld_
 // a warp's 32 positions in flight together), partial dots are folded over the 16 lanes.  Output: thread (pg, dg)
 // accumulates dimensions 8 dg .. 8 dg + 7 over positions pg, pg + 8, ... with 16-byte V loads, the 8 position
 // groups are summed through shared memory.
-template <int G>
+// PREFETCH: the first half of a thread's V rows is requested before the softmax statistics (helps while the grid
+// leaves SMs under-occupied, costs registers and therefore occupancy on large grids).
+template <int G, bool PREFETCH>
 __global__ void __launch_bounds__(ATT_SLICE) decode_attn_kernel(const void *__restrict__ q, const void *__restrict__ k_cache,
                                                                 const void *__restrict__ v_cache, int dt, int hq, int hkv, int64_t ctx_len,
                                                                 int64_t n_ctx, float scale, float *__restrict__ part) {
@@ -188,6 +190,16 @@ __global__ void __launch_bounds__(ATT_SLICE) decode_attn_kernel(const void *__re
         }
         }
     }
+    // first half of this thread's V rows: in flight while the softmax statistics are computed
+    const int pg = t >> 4, dg = t & 15;
+    uint4 vraw[PREFETCH ? 8 : 1];
+    if (PREFETCH) {
+#pragma unroll
+        for (int i8 = 0; i8 < (PREFETCH ? 8 : 1); i8++) {
+            const int j = pg + 8 * i8;
+            vraw[i8] = j < n_here ? *reinterpret_cast<const uint4 *>(vbase + (int64_t)j * (ATT_D * 2) + 16 * dg) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    }
     __syncthreads();
     float *my = part + ((((int64_t)b * hkv + kvh) * slices + slice) * G) * (2 + ATT_D);
     // softmax statistics of the slice: one warp per query head, four positions per lane
@@ -216,7 +228,6 @@ __global__ void __launch_bounds__(ATT_SLICE) decode_attn_kernel(const void *__re
     }
     __syncthreads();
     {
-        const int pg = t >> 4, dg = t & 15;
         float o[G][8];
 #pragma unroll
         for (int g = 0; g < G; g++)
@@ -228,7 +239,8 @@ __global__ void __launch_bounds__(ATT_SLICE) decode_attn_kernel(const void *__re
 #pragma unroll
         for (int i8 = 0; i8 < 8; i8++) {
             const int j = pg + 8 * (8 * half + i8);
-            raw[i8] = j < n_here ? *reinterpret_cast<const uint4 *>(vbase + (int64_t)j * (ATT_D * 2) + 16 * dg) : make_uint4(0u, 0u, 0u, 0u);
+            if (PREFETCH && half == 0) raw[i8] = vraw[PREFETCH ? i8 : 0];
+            else raw[i8] = j < n_here ? *reinterpret_cast<const uint4 *>(vbase + (int64_t)j * (ATT_D * 2) + 16 * dg) : make_uint4(0u, 0u, 0u, 0u);
         }
 #pragma unroll
         for (int i8 = 0; i8 < 8; i8++) {
@@ -305,13 +317,18 @@ cudaError_t launch_decode_attention(const void *q, const void *k_cache, const vo
     const dim3 grid((unsigned)slices, (unsigned)hkv, (unsigned)B);
     cudaError_t e;
     const dim3 blk(ATT_SLICE);
+    const bool pre = (int64_t)slices * hkv * B <= 2048;  // up to about two waves of CTAs
+#define TTQ_ATT_LAUNCH(GG)                                                                                                          \
+    e = pre ? launch_pdl(decode_attn_kernel<GG, true>, grid, blk, 0, st, q, k_cache, v_cache, dt, hq, hkv, ctx_len, n_ctx, scale, part) \
+            : launch_pdl(decode_attn_kernel<GG, false>, grid, blk, 0, st, q, k_cache, v_cache, dt, hq, hkv, ctx_len, n_ctx, scale, part)
     switch (G) {
-        case 1: e = launch_pdl(decode_attn_kernel<1>, grid, blk, 0, st, q, k_cache, v_cache, dt, hq, hkv, ctx_len, n_ctx, scale, part); break;
-        case 2: e = launch_pdl(decode_attn_kernel<2>, grid, blk, 0, st, q, k_cache, v_cache, dt, hq, hkv, ctx_len, n_ctx, scale, part); break;
-        case 4: e = launch_pdl(decode_attn_kernel<4>, grid, blk, 0, st, q, k_cache, v_cache, dt, hq, hkv, ctx_len, n_ctx, scale, part); break;
-        case 8: e = launch_pdl(decode_attn_kernel<8>, grid, blk, 0, st, q, k_cache, v_cache, dt, hq, hkv, ctx_len, n_ctx, scale, part); break;
+        case 1: TTQ_ATT_LAUNCH(1); break;
+        case 2: TTQ_ATT_LAUNCH(2); break;
+        case 4: TTQ_ATT_LAUNCH(4); break;
+        case 8: TTQ_ATT_LAUNCH(8); break;
         default: return cudaErrorInvalidValue;
     }
+#undef TTQ_ATT_LAUNCH
     if (e != cudaSuccess) return e;
     return launch_pdl(decode_attn_merge_kernel, dim3((unsigned)hq, (unsigned)B), dim3(ATT_D), 0, st, (const float *)part, hq, hkv, G, slices, out, dt);
 }
