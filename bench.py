@@ -388,7 +388,12 @@ def ours_arm(args):
     gemv_launches = N_LAYERS * len(SHAPES)
     roofline = {
         "bound": "hbm", "achieved": round(value / world, 2), "peak": peak, "unit": "GB/s",
-        "frac": round(value / world / peak, 4), "traffic": None, "peak_source": peak_kind,
+        "frac": round(value / world / peak, 4),
+        # dram read + write per launch from the committed ncu capture (profiles/gemv_q4k_m1_llama8b.md: 123.14 MB over the
+        # four linears of a layer at M = 1, against 122.83 MB algorithmic); other batch sizes and shards have no capture
+        "traffic": 30785000 if (m == 1 and world == 1) else None,
+        "traffic_source": "ncu capture of a 2-layer case, mean over one layer's four launches" if (m == 1 and world == 1) else None,
+        "peak_source": peak_kind,
         "kernel": "xprep_kernel + gemv_kernel<Q4_K> (activation planes bulk-copied from scratch)",
         "avg_launch_us": round(ms_step * 1e3 / gemv_launches, 3),
         "algorithmic_bytes_per_launch": step_bytes // gemv_launches,
