@@ -32,8 +32,10 @@ namespace ttq {
 namespace {
 
 constexpr int GEMM_EPI_WARPS = 4;
-// dequant warps: one per packed row tile of the CTA's weight rows (8 per 128-row sub-tile); + 1 MMA warp
-__host__ __device__ constexpr int gemm_deq_warps(int nsub) { return 8 * nsub; }
+// 16 dequant warps + 1 MMA warp.  Two sub-tiles: one warp per packed row tile of the CTA's 256 weight rows, every
+// warp works on every stage.  One sub-tile: the 8 row tiles are served by two groups of 8 warps that take the
+// even and the odd stages, so that two stages are expanded at the same time.
+__host__ __device__ constexpr int gemm_deq_warps(int) { return 16; }
 __host__ __device__ constexpr int gemm_warps(int nsub) { return GEMM_EPI_WARPS + gemm_deq_warps(nsub) + 1; }
 constexpr int GEMM_BN = 128;                     // weight rows per CTA = MMA M
 constexpr int A_STAGE_BYTES = GEMM_BN * 128;     // 128 rows x 64 fp16
@@ -294,7 +296,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
 #ifdef TTQ_DIAG_NO_B
             mbar_init(full_bar + 8 * s, C::DEQ_WARPS);
 #else
-            mbar_init(full_bar + 8 * s, PLAIN ? 1 : C::DEQ_WARPS + 1);
+            mbar_init(full_bar + 8 * s, PLAIN ? 1 : (NSUB == 1 ? 8 : C::DEQ_WARPS) + 1);
 #endif
             mbar_init(empty_bar + 8 * s, 1);
         }
@@ -421,7 +423,11 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
     } else if (warp < GEMM_EPI_WARPS + C::DEQ_WARPS) {
         // ------------------------------------------------------------------ dequantize A
         const int dwa = warp - GEMM_EPI_WARPS;  // dequant warp index
-        const int dw = dwa & 7, my_sub = dwa >> 3;  // row tile inside the 128-row sub-tile, sub-tile
+        constexpr bool PARITY = NSUB == 1;  // two groups of 8 warps alternate over the stages of the single sub-tile
+        constexpr int STRIDE = PARITY ? 2 : 1;
+        const int dw = dwa & 7;                      // row tile inside the 128-row sub-tile
+        const int my_sub = PARITY ? 0 : dwa >> 3;    // sub-tile
+        const int grp = PARITY ? dwa >> 3 : 0;       // first stage of a tile this warp expands
         const int g = lane >> 2, t = lane & 3;
         const int r = lane & 15, h = lane >> 4;
         const uint32_t my_hdr = hdr_u32 + dwa * 1280;
@@ -438,7 +444,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
             hdr_off[sl] = (uint32_t)((g + 8 * (sl & 1)) * 80 + 2 * u * 8);
         }
         bool alive = true;
-        int git = 0;  // stage counter across tiles
+        int git_base = 0;  // stage counter across tiles, at the start of the current tile
         const int64_t b_it_stride = (p.Mp >> 3) << 10;
         // packed row tiles of this warp in a tile: sub s -> row tile (n_tile*NSUB + s)*8 + dw
         auto tile_ptr = [&](int64_t tile, int sub, bool &have) {
@@ -465,8 +471,8 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
 #pragma unroll
         for (int sub = 0; sub < 1; sub++) {
             tile0[sub] = tile_ptr(blockIdx.x, sub, have[sub]);
-            next[sub] = chunk_at(tile0[sub], have[sub], 0);
-            next2[sub] = chunk_at(tile0[sub], have[sub] && iters > 1, 1);
+            next[sub] = chunk_at(tile0[sub], have[sub], grp);
+            next2[sub] = chunk_at(tile0[sub], have[sub] && grp + STRIDE < iters, grp + STRIDE);
             hv_next[sub] = header_at(tile0[sub], have[sub], 0);
         }
         const __half2 k1032 = __float2half2_rn(1032.f), k1152 = __float2half2_rn(1152.f);
@@ -481,10 +487,11 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
             const uint8_t *bsrc0 = reinterpret_cast<const uint8_t *>(p.xh) + ((tile_row0(m_tile_b) >> 3) << 10) +
                                    (tile % splits) * iters * b_it_stride;
             const uint32_t b_bytes = BM == 384 ? (uint32_t)tile_mh(m_tile_b) * (128u * 128u) : (uint32_t)C::B_BYTES;
-            for (int it = 0; it < iters; it++, git++) {
+            for (int it = grp; it < iters; it += STRIDE) {
 #ifdef TTQ_DIAG_MMA_ONLY
                 continue;
 #endif
+                const int git = git_base + it;  // iters is a multiple of 4: a warp group keeps its stage parity across tiles
                 const int sb = it >> 2;
                 const int stage = git % STAGES;
                 uint4 w[1];
@@ -492,11 +499,11 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
                 for (int sub = 0; sub < 1; sub++) {
                     w[sub] = next[sub];
                     next[sub] = next2[sub];
-                    if (it + 2 < iters) next2[sub] = chunk_at(tile0[sub], have[sub], it + 2);
-                    else next2[sub] = chunk_at(tile0_n[sub], have_n[sub] && (it + 2 - iters) < iters, it + 2 - iters);
+                    if (it + 2 * STRIDE < iters) next2[sub] = chunk_at(tile0[sub], have[sub], it + 2 * STRIDE);
+                    else next2[sub] = chunk_at(tile0_n[sub], have_n[sub] && (it + 2 * STRIDE - iters) < iters, it + 2 * STRIDE - iters);
                 }
-                if ((it & 3) == 0) {
-                    // headers of (row tile, super-block): lane (r, h) unpacks sub-blocks 4h..4h+3 of row r into
+                if ((it & 3) == grp) {
+                    // first own stage of a super-block: headers of (row tile, super-block): lane (r, h) unpacks sub-blocks 4h..4h+3 of row r into
                     // {scale, scale, offset, offset} halves: w = scale*(q-8) + offset (high nibbles arrive as 16*(q-8))
                     __syncwarp();
 #pragma unroll
@@ -537,7 +544,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
                 }
                 const uint32_t a_stage = stages_u32 + stage * C::STAGE_BYTES;
 #ifndef TTQ_DIAG_NO_B
-                if (dwa == 0 && lane == 0) {
+                if (dw == 0 && my_sub == 0 && lane == 0) {
                     // the activation tile of this stage: one bulk copy, counted on the same full barrier
                     mbar_expect_tx(full_bar + 8 * stage, b_bytes);
                     bulk_g2s(a_stage + C::A_BYTES, bsrc0 + it * b_it_stride, b_bytes, full_bar + 8 * stage);
@@ -595,13 +602,14 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
                 tile0[sub] = tile0_n[sub];
                 have[sub] = have_n[sub];
             }
+            git_base += iters;
         }
         if (trd && lane == 0) {
             // timeline entry of kind 4: dequant warp 0 -- start, time spent waiting for free stages, stages, end
             const unsigned long long slot = atomicAdd(p.trace, 1ull);
             if (slot < 8192) {
                 unsigned long long *e = p.trace + 8 + slot * 8;
-                e[0] = 4; e[1] = t_begin; e[2] = t_empty; e[3] = t_conv; e[4] = (unsigned long long)git; e[5] = global_ns();
+                e[0] = 4; e[1] = t_begin; e[2] = t_empty; e[3] = t_conv; e[4] = (unsigned long long)git_base; e[5] = global_ns();
                 e[6] = gridDim.x; e[7] = (unsigned long long)p.N;
             }
         }
@@ -719,10 +727,11 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
         const char *v = getenv("TTQ_GEMM_NSUB");
         return v ? atoi(v) : 0;
     }();
-    // a CTA with two sub-tiles does twice the work per activation stage in about 1.25x the time of one (measured)
+    // a CTA with two sub-tiles does twice the work per activation stage in about 1.7x the time of one (measured; the
+    // single sub-tile is expanded by two warp groups on alternating stages)
     const int64_t mt = (a.M + BM - 1) / BM;
     const int64_t tiles1 = ((a.N + 127) / 128) * mt, tiles2 = ((a.N + 255) / 256) * mt;
-    const double cost1 = (double)((tiles1 + sms - 1) / sms), cost2 = 1.25 * (double)((tiles2 + sms - 1) / sms);
+    const double cost1 = (double)((tiles1 + sms - 1) / sms), cost2 = 1.7 * (double)((tiles2 + sms - 1) / sms);
     int nsub = (a.N > 128 && cost2 < cost1) ? 2 : 1;
     if (force_nsub == 1 || force_nsub == 2) nsub = force_nsub;
     if (plain) nsub = 2;  // no conversion work to balance: always the 256-row weight tile
