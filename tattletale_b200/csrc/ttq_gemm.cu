@@ -695,11 +695,15 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restr
 template <int BM, int NSUB, bool PLAIN = false>
 cudaError_t launch_cfg(const GemmParams &p, int sms, cudaStream_t st) {
     using C = GemmCfg<BM, NSUB>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_q4k_kernel<BM, NSUB, PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL);
+    static bool configured[64] = {};  // per device: the shared-memory opt-in belongs to the device's copy of the function
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!configured[dev]) {
+        e = cudaFuncSetAttribute(gemm_q4k_kernel<BM, NSUB, PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL);
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured[dev] = true;
     }
     const int64_t tiles = ((p.N + GEMM_BN * NSUB - 1) / (GEMM_BN * NSUB)) * (p.group_tiles != nullptr ? p.mt_cap : p.Mp / BM) * p.splits;
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);

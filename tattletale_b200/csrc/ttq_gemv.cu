@@ -863,13 +863,17 @@ template <int FMT, int XSRC, int MR, int NPASS, int NW>
 cudaError_t launch_one(GemvParams &p, int sms, cudaStream_t st) {
     auto kernel = gemv_kernel<FMT, XSRC, MR, NPASS, NW>;
     const size_t smem = smem_layout(FMT, MR * NPASS, XSRC == XSRC_GLOBAL ? 0 : MR, p.a.SBp, NW).total;
-    static bool configured = false;  // per instantiation; contexts on several devices share the setting
+    // per instantiation and per device: the shared-memory opt-in belongs to the device's copy of the function
+    static bool configured[64] = {};
     static int occ_cache_smem = -1, occ_cache = 0;
     cudaError_t e;
-    if (!configured) {
+    int dev = 0;
+    if ((e = cudaGetDevice(&dev))) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!configured[dev]) {
         const int lim = (int)(NW > 8 ? GEMV_SMEM_BIG : GEMV_SMEM_LIMIT);
         if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, lim))) return e;
-        configured = true;
+        configured[dev] = true;
     }
     if (occ_cache_smem != (int)smem) {
         if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ_cache, kernel, NW * 32, smem))) return e;

@@ -73,3 +73,26 @@ def test_fused_allreduce_matches_full_matrix():
         assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
         assert all(e < 1e-3 for e in out["errs"]), out["errs"]
         assert all(out["agree"]), "ranks disagree on the reduced result"
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_contexts_in_one_process():
+    """One process, one context per device: every device gets its own kernel configuration (shared-memory opt-in)."""
+    import oracle
+    import tattletale_b200 as ttq
+
+    rng = np.random.default_rng(77)
+    blocks = oracle.quantize(oracle.Q4_K, rng.normal(0, 0.02, (N, K)).astype(np.float32))
+    for m in (1, 64):  # decode kernel and tensor-core GEMM
+        x = torch.from_numpy(rng.normal(0, 1, (m, K)).astype(np.float32)).to(torch.bfloat16)
+        want = oracle.linear(oracle.Q4_K, blocks, x.view(torch.int16).numpy().view(np.uint16), oracle.BF16)
+        for dev in (0, 1):
+            with torch.cuda.device(dev):
+                ctx = ttq.Context(dev)
+                lin = ttq.QuantLinear(ctx, ttq.FMT_Q4_K, torch.from_numpy(blocks), K)
+                y = lin.forward(x.to(f"cuda:{dev}"), out_dtype=torch.float32)
+                ctx.check_device_status()
+                err = float(np.linalg.norm(y.cpu().numpy() - want) / np.linalg.norm(want))
+                assert err < 1e-3, (dev, m, err)
+                lin.close()
+                ctx.close()
