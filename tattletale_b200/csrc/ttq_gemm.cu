@@ -143,6 +143,8 @@ __global__ void __launch_bounds__(256) xh_prep_kernel(const void *__restrict__ x
                                                       int64_t Kp, int64_t ldx, __half *__restrict__ xh,
                                                       const int *__restrict__ row_src, const int *__restrict__ rows_used,
                                                       int rows_unit) {
+    grid_launch_dependents();
+    grid_dependency_wait();  // x, the routing tables and the image buffer belong to preceding kernels until here
     const int64_t chunks_per_row = Kp / 8;
     const int64_t total = Mp * chunks_per_row;
     const int64_t m_used = rows_used != nullptr ? (int64_t)(*rows_used) * rows_unit : Mp;
@@ -281,6 +283,11 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
     const int iters = sb_per_unit * 4;  // stages per work unit (tile x K split)
     constexpr int TILE_N = GEMM_BN * NSUB;
     const bool grouped = p.group_tiles != nullptr;
+    // Programmatic dependent launch: the set-up below (barriers, tensor memory) and the first loads of packed
+    // weights -- constant data -- run while the preceding kernel drains; everything that touches activations,
+    // routing tables or outputs comes after grid_dependency_wait.
+    grid_launch_dependents();
+    if (grouped) grid_dependency_wait();  // the row-tile tables are read right away
     int64_t m_tiles = p.Mp / BM;
     if (grouped) {
         const int64_t used = *p.n_mt;
@@ -320,6 +327,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
 
     if (warp < GEMM_EPI_WARPS) {
         // ------------------------------------------------------------------ epilogue
+        grid_dependency_wait();  // the output may still be read by a preceding kernel
         bool alive = true;
         int tcount = 0;
         for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, tcount++) {
@@ -400,6 +408,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
     } else if (PLAIN && warp < GEMM_EPI_WARPS + C::DEQ_WARPS) {
         // ------------------------------------------------------------------ producer: both operands are bulk copies
         if (warp == GEMM_EPI_WARPS && lane == 0) {
+            grid_dependency_wait();  // both operands are written by preceding kernels
             bool alive = true;
             int git = 0;
             const int64_t b_it_stride = (p.Mp >> 3) << 10, w_it_stride = (p.Np >> 3) << 10;
@@ -475,6 +484,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
             next2[sub] = chunk_at(tile0[sub], have[sub] && grp + STRIDE < iters, grp + STRIDE);
             hv_next[sub] = header_at(tile0[sub], have[sub], 0);
         }
+        grid_dependency_wait();  // the first packed chunks and headers are in flight; activations come next
         const __half2 k1032 = __float2half2_rn(1032.f), k1152 = __float2half2_rn(1152.f);
         const bool trd = p.trace != nullptr && blockIdx.x == 0 && dwa == 0;
         unsigned long long t_empty = 0, t_conv = 0, t_begin = trd ? global_ns() : 0;
@@ -682,6 +692,8 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
 // Sum of the split-K partials (+ bias) into y.
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ ws, int splits, int64_t M, int64_t Mp, int64_t N,
                                                             const void *bias, int bias_dt, void *y, int y_dt, int64_t ldy) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int64_t total = M * N;
     for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
         const int64_t m = e / N, n = e % N;
@@ -707,8 +719,7 @@ cudaError_t launch_cfg(const GemmParams &p, int sms, cudaStream_t st) {
     }
     const int64_t tiles = ((p.N + GEMM_BN * NSUB - 1) / (GEMM_BN * NSUB)) * (p.group_tiles != nullptr ? p.mt_cap : p.Mp / BM) * p.splits;
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-    gemm_q4k_kernel<BM, NSUB, PLAIN><<<grid, C::THREADS, C::TOTAL, st>>>(p);
-    return cudaGetLastError();
+    return launch_pdl(gemm_q4k_kernel<BM, NSUB, PLAIN>, dim3(grid), dim3(C::THREADS), (size_t)C::TOTAL, st, p);
 }
 
 }  // namespace
@@ -748,9 +759,11 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
         const uint8_t *xs = reinterpret_cast<const uint8_t *>(a.x) + (size_t)m0 * a.ldx * esz_x;
         const int64_t chunks = Mp * (Kp / 8);
         const unsigned grid = (unsigned)((chunks + 255) / 256 < 148 * 16 ? (chunks + 255) / 256 : 148 * 16);
-        if (a.gated) xh_prep_kernel<true><<<grid, 256, 0, st>>>(xs, a.x_dt, Ms, Mp, a.K, Kp, a.ldx, xh, nullptr, nullptr, 0);
-        else xh_prep_kernel<false><<<grid, 256, 0, st>>>(xs, a.x_dt, Ms, Mp, a.K, Kp, a.ldx, xh, nullptr, nullptr, 0);
-        cudaError_t e = cudaGetLastError();
+        const int *no_tab = nullptr;
+        cudaError_t e = a.gated ? launch_pdl(xh_prep_kernel<true>, dim3(grid), dim3(256), 0, st, (const void *)xs, a.x_dt, Ms, Mp, a.K, Kp, a.ldx,
+                                             xh, no_tab, no_tab, 0)
+                                : launch_pdl(xh_prep_kernel<false>, dim3(grid), dim3(256), 0, st, (const void *)xs, a.x_dt, Ms, Mp, a.K, Kp, a.ldx,
+                                             xh, no_tab, no_tab, 0);
         if (e != cudaSuccess) return e;
         ++*launches;
         GemmParams p;
@@ -799,8 +812,8 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
         if (splits > 1) {
             const int64_t total = Ms * a.N;
             const unsigned rg = (unsigned)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-            splitk_reduce_kernel<<<rg, 256, 0, st>>>(p.ws, splits, Ms, Mp, a.N, a.bias, a.bias_dt, p.y, a.y_dt, a.ldy);
-            e = cudaGetLastError();
+            e = launch_pdl(splitk_reduce_kernel, dim3(rg), dim3(256), 0, st, (const float *)p.ws, splits, Ms, Mp, a.N, a.bias, a.bias_dt, p.y,
+                           a.y_dt, a.ldy);
             if (e != cudaSuccess) return e;
             ++*launches;
         }
@@ -817,11 +830,10 @@ cudaError_t launch_gemm_grouped(const GroupedArgs &g, __half *xh, int sms, int *
     if (g.Mp % 128 && g.Mp % g.BM) return cudaErrorInvalidValue;
     const int64_t chunks = g.Mp * (Kp / 8);
     const unsigned grid = (unsigned)((chunks + 255) / 256 < 148 * 16 ? (chunks + 255) / 256 : 148 * 16);
-    if (g.gated)
-        xh_prep_kernel<true><<<grid, 256, 0, st>>>(g.x, g.x_dt, g.x_rows, g.Mp, g.K, Kp, g.ldx, xh, g.row_src, g.rows_total, 1);
-    else
-        xh_prep_kernel<false><<<grid, 256, 0, st>>>(g.x, g.x_dt, g.x_rows, g.Mp, g.K, Kp, g.ldx, xh, g.row_src, g.rows_total, 1);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = g.gated ? launch_pdl(xh_prep_kernel<true>, dim3(grid), dim3(256), 0, st, g.x, g.x_dt, g.x_rows, g.Mp, g.K, Kp, g.ldx, xh,
+                                         g.row_src, g.rows_total, 1)
+                            : launch_pdl(xh_prep_kernel<false>, dim3(grid), dim3(256), 0, st, g.x, g.x_dt, g.x_rows, g.Mp, g.K, Kp, g.ldx, xh,
+                                         g.row_src, g.rows_total, 1);
     if (e != cudaSuccess) return e;
     ++*launches;
     GemmParams p;
