@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--m M]
 
-Workload (BASELINE.json configs[1], the configuration the metric is quoted on): the four
+Workload (the configuration the headline metric is quoted on): the four
 Llama-3-8B projection shapes in Q4_K -- 4096->6144 (QKV), 4096->4096 (O), 4096->28672 (gate|up),
 14336->4096 (down) -- at decode batch M (default 1), for 32 layers with distinct weights.  One step
 is one pass over all 128 linears (3.93 GB of packed weights, far larger than the 126 MB L2, so every
@@ -427,7 +427,7 @@ def ours_arm(args):
 
 
 def decode_arm(args):
-    """BASELINE configs[2]: full Llama-3-8B decoder stack (random init), one decode step at context 2048."""
+    """Full Llama-3-8B decoder stack (random init), one decode step at context 2048."""
     import tattletale_b200 as ttq
     from tattletale_b200.decoder import DecoderConfig, DecoderStack
 
@@ -527,7 +527,7 @@ def decode_arm(args):
 
 
 def moe_arm(args):
-    """Mixture-of-experts layer of BASELINE.json configs[4]: hidden 2048, 128 experts of FFN 768 (gated), top-8
+    """Mixture-of-experts layer, Qwen3-30B-A3B-like: hidden 2048, 128 experts of FFN 768 (gated), top-8
     routing from N(0,1) router logits, 4096 tokens, Q4_K experts ~N(0, 0.02).  N > 1: expert parallel (each rank
     holds E/N experts and T/N tokens; NCCL all-to-all dispatch and combine around the local grouped GEMM)."""
     import torch.distributed as dist
@@ -626,7 +626,7 @@ def moe_arm(args):
 
 
 def trellis_arm(args):
-    """Trellis-coded 3-bit linears on the Llama-3-70B projection shapes (BASELINE.json configs[3]): 8192->10240,
+    """Trellis-coded 3-bit linears on the Llama-3-70B projection shapes: 8192->10240,
     8192->8192, 8192->57344, 28672->8192 at M = --m rows, weights N(0, 0.015) coded by the package's beam-search
     encoder (or uniformly random code bits with --trellis-codes random: the kernels' speed does not depend on
     the bit values).  One step = one pass over --layers layers of four linears."""

@@ -23,7 +23,7 @@ from .layers import Context, QuantLinear, add_rmsnorm, decode_attention, rope_kv
 
 @dataclass
 class DecoderConfig:
-    """Llama-3-8B geometry (BASELINE configs[2])."""
+    """Llama-3-8B geometry."""
     n_layers: int = 32
     hidden: int = 4096
     n_q_heads: int = 32

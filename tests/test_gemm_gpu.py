@@ -51,7 +51,7 @@ def test_bias_and_output_types(ctx):
 
 
 def test_llama_projection_prefill(ctx):
-    """4096 -> 4096 at M = 256 (one of the BASELINE configs[1] points)."""
+    """4096 -> 4096 at M = 256 (one of the prefill points of the headline configuration)."""
     got, want = run(ctx, 4096, 4096, 256, seed=2001)
     assert rel_l2(got, want) < TOL
 
