@@ -515,8 +515,13 @@ static ttq_status linear_forward_impl(ttq_ctx *ctx, const ttq_weight *w, const v
         const char *v = getenv("TTQ_GEMM");
         return !(v && v[0] == '0');
     }();
-    // measured cross-over of the two paths on the Llama-3-8B shapes: 8 rows
-    constexpr int64_t GEMM_MIN_M = 9;
+    // measured cross-over of the two paths on the Llama-3-8B shapes: the decode kernel re-runs its MMA sets per row and
+    // is as fast as the tensor-core path at 4 rows, slower from 5 (TTQ_GEMM_MIN_M overrides)
+    static const int64_t GEMM_MIN_M = []() -> int64_t {
+        const char *v = getenv("TTQ_GEMM_MIN_M");
+        const int64_t n = v ? atoll(v) : 0;
+        return n >= 1 ? n : 5;
+    }();
     if (M >= GEMM_MIN_M && use_gemm && gemm_supported(w->fmt)) {
         // prefill / larger batches: tensor-core path
         a.x = x_dev; a.M = M; a.y = y_dev;
