@@ -349,7 +349,7 @@ def ours_arm(args):
             us = a.elapsed_time(b) * 1e3 / (reps * N_LAYERS)
             per_shape[f"{k}x{n}"] = {"us": round(us, 3), "gbs": round(algorithmic_bytes(m, k, n) / us / 1e3, 1)}
 
-    # ---- batched rows on the same weights: M = 4, 16 (decode kernel) and 64, 256, 2048 (tcgen05 GEMM), layer 0
+    # ---- batched rows on the same weights: M = 4 (decode kernel) and 16, 64, 256, 2048 (tcgen05 GEMM), layer 0
     sweep = {}
     if world == 1 and not args.no_e2e and not args.no_sweep:
         for ms in (4, 16, 64, 256, 2048):
