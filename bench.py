@@ -670,8 +670,25 @@ def trellis_arm(args):
     step()
     torch.cuda.synchronize()
     launches_per_step = ctx.launch_count - c0
+    graph = None
+    if not args.no_graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+        except Exception as exc:
+            print(f"[bench] CUDA graph capture failed, running eagerly: {exc}", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
+    run = graph.replay if graph is not None else step
     for _ in range(max(args.warmup, 3)):
-        step()
+        run()
     steps = min(args.steps, 100)
     sampler = ClockSampler(visible_physical_index(0))
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -679,7 +696,7 @@ def trellis_arm(args):
     torch.cuda.synchronize()
     e0.record()
     for _ in range(steps):
-        step()
+        run()
     e1.record()
     torch.cuda.synchronize()
     clocks = sampler.stop()
@@ -709,7 +726,8 @@ def trellis_arm(args):
         "config": {"workload": f"Llama-3-70B projection shapes, trellis-coded 3.0 bits/weight, M={m}, {n_layers} layers x 4 linears",
                    "shapes_k_to_n": [[k, n] for k, n in shapes], "M": m, "layers": n_layers, "codes": args.trellis_codes,
                    "l2": f"{w_bytes / 1e6:.0f} MB of packed weights per step, larger than L2", "encode_seconds": round(t_enc, 1)},
-        "roofline": roof, "gpu_launches": int(launches_per_step * steps), "launches_per_step": int(launches_per_step), "clocks": clocks,
+        "roofline": roof, "gpu_launches": int(launches_per_step * steps), "launches_per_step": int(launches_per_step),
+        "cuda_graph": graph is not None, "clocks": clocks,
     }
     print(json.dumps(line), flush=True)
 

@@ -94,6 +94,8 @@ __global__ void __launch_bounds__(256) tq3_rotate_kernel(const void *__restrict_
                                                          const uint8_t *__restrict__ sign, const __half *__restrict__ scale,
                                                          const void *__restrict__ bias, int bias_dt, void *__restrict__ out, int out_dt,
                                                          int64_t ld_out) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int lane = threadIdx.x & 31;
     const int64_t blocks_per_row = C / 128, total = M * blocks_per_row;
     for (int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < total; w += ((int64_t)gridDim.x * blockDim.x) >> 5) {
@@ -136,6 +138,8 @@ template <int MR>
 __global__ void __launch_bounds__(256) tq3_gemv_kernel(const uint8_t *__restrict__ tiles, int64_t N, int64_t K, const float *__restrict__ x1,
                                                        float *__restrict__ y1) {
     __shared__ float red[8][16][MR];
+    grid_launch_dependents();
+    grid_dependency_wait();  // the rotated activations come from the preceding kernel
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 3, j = lane & 7;
     const int64_t tk = K / 16, band = blockIdx.x;
@@ -216,22 +220,21 @@ cudaError_t launch_tq3_wimg(const uint8_t *packed, int64_t N, int64_t K, __half 
 
 cudaError_t launch_tq3_rotate(const void *in, int in_dt, int64_t M, int64_t C, int64_t ld_in, const uint8_t *sign, const __half *scale,
                               const void *bias, int bias_dt, void *out, int out_dt, int64_t ld_out, cudaStream_t st) {
-    tq3_rotate_kernel<<<grid_of(M * (C / 128), 8, 148 * 16), 256, 0, st>>>(in, in_dt, M, C, ld_in, sign, scale, bias, bias_dt, out, out_dt,
-                                                                           ld_out);
-    return cudaGetLastError();
+    return launch_pdl(tq3_rotate_kernel, dim3(grid_of(M * (C / 128), 8, 148 * 16)), dim3(256), 0, st, in, in_dt, M, C, ld_in, sign, scale, bias,
+                      bias_dt, out, out_dt, ld_out);
 }
 
 // `rows` (1..4) rows of x1 [.][K] -> y1 [.][N]
 cudaError_t launch_tq3_gemv(const uint8_t *packed, int64_t N, int64_t K, const float *x1, int rows, float *y1, cudaStream_t st) {
     const unsigned grid = (unsigned)(N / 16);
+    const dim3 blk(256);
     switch (rows) {
-        case 1: tq3_gemv_kernel<1><<<grid, 256, 0, st>>>(packed, N, K, x1, y1); break;
-        case 2: tq3_gemv_kernel<2><<<grid, 256, 0, st>>>(packed, N, K, x1, y1); break;
-        case 3: tq3_gemv_kernel<3><<<grid, 256, 0, st>>>(packed, N, K, x1, y1); break;
-        case 4: tq3_gemv_kernel<4><<<grid, 256, 0, st>>>(packed, N, K, x1, y1); break;
+        case 1: return launch_pdl(tq3_gemv_kernel<1>, dim3(grid), blk, 0, st, packed, N, K, x1, y1);
+        case 2: return launch_pdl(tq3_gemv_kernel<2>, dim3(grid), blk, 0, st, packed, N, K, x1, y1);
+        case 3: return launch_pdl(tq3_gemv_kernel<3>, dim3(grid), blk, 0, st, packed, N, K, x1, y1);
+        case 4: return launch_pdl(tq3_gemv_kernel<4>, dim3(grid), blk, 0, st, packed, N, K, x1, y1);
         default: return cudaErrorInvalidValue;
     }
-    return cudaGetLastError();
 }
 
 }  // namespace ttq
