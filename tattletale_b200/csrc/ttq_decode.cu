@@ -73,8 +73,59 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(void *__restrict__ h, 
     const int64_t m = blockIdx.x;
     uint8_t *hrow = reinterpret_cast<uint8_t *>(h) + m * ld_h * 2;
     const uint8_t *drow = delta ? reinterpret_cast<const uint8_t *>(delta) + m * ld_delta * 2 : nullptr;
+    const uint8_t *wrow = reinterpret_cast<const uint8_t *>(weight);
+    uint8_t *orow = reinterpret_cast<uint8_t *>(out) + m * ld_out * 2;
+    const int64_t chunks = H / 8;
+    constexpr int KEEP = 4;  // chunks of 8 values a thread keeps in registers between the two passes (H <= 8192)
+    if (chunks <= (int64_t)KEEP * blockDim.x) {
+        // all loads first (row, residual, weight), one reduction, then the output straight from registers
+        uint4 hv[KEEP], dv[KEEP], wv[KEEP];
+#pragma unroll
+        for (int i = 0; i < KEEP; i++) {
+            const int64_t c = threadIdx.x + (int64_t)i * blockDim.x;
+            if (c < chunks) {
+                hv[i] = *reinterpret_cast<const uint4 *>(hrow + c * 16);
+                if (drow) dv[i] = *reinterpret_cast<const uint4 *>(drow + c * 16);
+                wv[i] = *reinterpret_cast<const uint4 *>(wrow + c * 16);
+            }
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < KEEP; i++) {
+            const int64_t c = threadIdx.x + (int64_t)i * blockDim.x;
+            if (c < chunks) {
+                float v[8];
+                unpack8(hv[i], dt, v);
+                if (drow) {
+                    float d[8];
+                    unpack8(dv[i], dt, d);
+#pragma unroll
+                    for (int q = 0; q < 8; q++) v[q] += d[q];
+                    hv[i] = pack8(v, dt);  // the residual stream is stored (and normalised) in its 16-bit rounding
+                    *reinterpret_cast<uint4 *>(hrow + c * 16) = hv[i];
+                    unpack8(hv[i], dt, v);
+                }
+#pragma unroll
+                for (int q = 0; q < 8; q++) ss = fmaf(v[q], v[q], ss);
+            }
+        }
+        const float inv = rsqrtf(block_sum(ss, red) / (float)H + eps);
+#pragma unroll
+        for (int i = 0; i < KEEP; i++) {
+            const int64_t c = threadIdx.x + (int64_t)i * blockDim.x;
+            if (c < chunks) {
+                float v[8], w[8];
+                unpack8(hv[i], dt, v);
+                unpack8(wv[i], dt, w);
+#pragma unroll
+                for (int q = 0; q < 8; q++) v[q] = v[q] * inv * w[q];
+                *reinterpret_cast<uint4 *>(orow + c * 16) = pack8(v, dt);
+            }
+        }
+        return;
+    }
     float ss = 0.f;
-    for (int64_t c = threadIdx.x; c < H / 8; c += blockDim.x) {
+    for (int64_t c = threadIdx.x; c < chunks; c += blockDim.x) {
         float v[8];
         unpack8(*reinterpret_cast<const uint4 *>(hrow + c * 16), dt, v);
         if (drow) {
@@ -90,11 +141,10 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(void *__restrict__ h, 
         for (int i = 0; i < 8; i++) ss = fmaf(v[i], v[i], ss);
     }
     const float inv = rsqrtf(block_sum(ss, red) / (float)H + eps);
-    uint8_t *orow = reinterpret_cast<uint8_t *>(out) + m * ld_out * 2;
-    for (int64_t c = threadIdx.x; c < H / 8; c += blockDim.x) {
+    for (int64_t c = threadIdx.x; c < chunks; c += blockDim.x) {
         float v[8], w[8];
         unpack8(*reinterpret_cast<const uint4 *>(hrow + c * 16), dt, v);
-        unpack8(*reinterpret_cast<const uint4 *>(reinterpret_cast<const uint8_t *>(weight) + c * 16), dt, w);
+        unpack8(*reinterpret_cast<const uint4 *>(wrow + c * 16), dt, w);
 #pragma unroll
         for (int i = 0; i < 8; i++) v[i] = v[i] * inv * w[i];
         *reinterpret_cast<uint4 *>(orow + c * 16) = pack8(v, dt);
