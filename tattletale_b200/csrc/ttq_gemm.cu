@@ -293,10 +293,16 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
         const int64_t used = *p.n_mt;
         m_tiles = used < p.mt_cap ? used : p.mt_cap;
     }
+    const int64_t n_tiles = (p.N + TILE_N - 1) / TILE_N, total_tiles = n_tiles * m_tiles * splits;
+    // Order of the output tiles.  Dense: all row tiles of one weight tile are neighbours (few row tiles, the weights are
+    // the big operand and are read once).  Grouped: all weight tiles of one row tile are neighbours, so that the CTAs
+    // running together share the row tile's activation images and an expert's weights through L2 -- the routed
+    // activations (hundreds of MB) would otherwise be re-read from DRAM once per weight tile.
+    auto tile_n = [&](int64_t otile) -> int64_t { return grouped ? otile % n_tiles : otile / m_tiles; };
+    auto tile_m = [&](int64_t otile) -> int64_t { return grouped ? otile / n_tiles : otile % m_tiles; };
     // first activation row of a row tile; 128-row blocks of it in use (variable only for the 384-row grouped tile)
     auto tile_row0 = [&](int64_t m_tile) -> int64_t { return grouped ? (int64_t)p.mt_row0[m_tile] : m_tile * BM; };
     auto tile_mh = [&](int64_t m_tile) -> int { return (grouped && BM == 384) ? p.mt_mh[m_tile] : C::MH; };
-    const int64_t n_tiles = (p.N + TILE_N - 1) / TILE_N, total_tiles = n_tiles * m_tiles * splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -332,7 +338,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
         int tcount = 0;
         for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, tcount++) {
             const int64_t otile = tile / splits, split = tile % splits;
-            const int64_t n_tile = otile / m_tiles, m_tile = otile % m_tiles;
+            const int64_t n_tile = tile_n(otile), m_tile = tile_m(otile);
             const int buf = tcount % C::NACC, use = tcount / C::NACC;
             if (alive) alive = mbar_wait_warp(accf_bar + 8 * buf, (uint32_t)(use & 1), p.status, lane);
             tc_fence_after();
@@ -414,7 +420,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
             const int64_t b_it_stride = (p.Mp >> 3) << 10, w_it_stride = (p.Np >> 3) << 10;
             for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
                 const int64_t otile = tile / splits, split = tile % splits;
-                const int64_t n_tile = otile / m_tiles, m_tile = otile % m_tiles;
+                const int64_t n_tile = tile_n(otile), m_tile = tile_m(otile);
                 const uint8_t *bsrc0 = reinterpret_cast<const uint8_t *>(p.xh) + ((tile_row0(m_tile) >> 3) << 10) + split * iters * b_it_stride;
                 const uint8_t *wsrc0 = reinterpret_cast<const uint8_t *>(p.wimg) + (((n_tile * TILE_N) >> 3) << 10) + split * iters * w_it_stride;
                 for (int it = 0; it < iters; it++, git++) {
@@ -457,10 +463,10 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
         const int64_t b_it_stride = (p.Mp >> 3) << 10;
         // packed row tiles of this warp in a tile: sub s -> row tile (n_tile*NSUB + s)*8 + dw
         auto tile_ptr = [&](int64_t tile, int sub, bool &have) {
-            const int64_t nt = (((tile / splits) / m_tiles) * NSUB + my_sub + sub) * (GEMM_BN / TILE_ROWS) + dw;
+            const int64_t nt = (tile_n(tile / splits) * NSUB + my_sub + sub) * (GEMM_BN / TILE_ROWS) + dw;
             have = tile < total_tiles && nt < p.NT;
             const uint8_t *wbase = p.tiles;
-            if (grouped && have) wbase = p.group_tiles[p.mt_group[(tile / splits) % m_tiles]];
+            if (grouped && have) wbase = p.group_tiles[p.mt_group[tile_m(tile / splits)]];
             return wbase + ((have ? nt : 0) * p.SBp + (tile % splits) * sb_per_unit) * 2304;
         };
         auto chunk_at = [&](const uint8_t *t0, bool ok, int it) {
@@ -493,7 +499,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
             const uint8_t *tile0_n[1];
 #pragma unroll
             for (int sub = 0; sub < 1; sub++) tile0_n[sub] = tile_ptr(tile + gridDim.x, sub, have_n[sub]);
-            const int64_t m_tile_b = (tile / splits) % m_tiles;
+            const int64_t m_tile_b = tile_m(tile / splits);
             const uint8_t *bsrc0 = reinterpret_cast<const uint8_t *>(p.xh) + ((tile_row0(m_tile_b) >> 3) << 10) +
                                    (tile % splits) * iters * b_it_stride;
             const uint32_t b_bytes = BM == 384 ? (uint32_t)tile_mh(m_tile_b) * (128u * 128u) : (uint32_t)C::B_BYTES;
@@ -639,7 +645,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
                 if (tr) t_acc += global_ns() - t0;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * C::ACC_COLS);
-                const int mh = tile_mh((tile / splits) % m_tiles);
+                const int mh = tile_mh(tile_m(tile / splits));
                 for (int it = 0; it < iters; it++, git++) {
                     const int stage = git % STAGES;
                     if (tr) t0 = global_ns();
