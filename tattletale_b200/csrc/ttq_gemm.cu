@@ -143,7 +143,6 @@ __global__ void __launch_bounds__(256) xh_prep_kernel(const void *__restrict__ x
                                                       int64_t Kp, int64_t ldx, __half *__restrict__ xh,
                                                       const int *__restrict__ row_src, const int *__restrict__ rows_used,
                                                       int rows_unit) {
-    grid_launch_dependents();
     grid_dependency_wait();  // x, the routing tables and the image buffer belong to preceding kernels until here
     const int64_t chunks_per_row = Kp / 8;
     const int64_t total = Mp * chunks_per_row;
@@ -214,6 +213,9 @@ __global__ void __launch_bounds__(256) xh_prep_kernel(const void *__restrict__ x
         const int64_t dst = ((it * (Mp >> 3) + (mi >> 3)) << 10) + ((mi & 7) << 7) + ((int64_t)(j ^ (int)(mi & 7)) << 4);
         *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(xh) + dst) = *reinterpret_cast<const uint4 *>(out);
     }
+    // only now may the GEMM be set up: its one-per-SM CTAs would otherwise take the SMs from the waves of this
+    // bandwidth-bound pass that are still queued
+    grid_launch_dependents();
 }
 
 struct GemmParams {
