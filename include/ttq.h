@@ -180,6 +180,16 @@ TTQ_API ttq_status ttq_device_status(ttq_ctx *ctx, void *stream);
 TTQ_API ttq_status ttq_comm_create(ttq_ctx *ctx, int rank, int world, int64_t n_cap, int m_cap, ttq_comm **out,
                                    void *ipc_handle_out);
 TTQ_API ttq_status ttq_comm_connect(ttq_comm *comm, const void *all_handles);
+/* Single-process form of the connection (the reference is one application without a launcher): ttq_comm_local_buffer returns this rank's exchange
+ * buffer and its size; ttq_comm_connect_pointers takes, in rank order, device pointers through which THIS
+ * rank's device can reach every rank's buffer (peer access enabled by the host; the own entry is ignored).
+ * No reference counterpart. */
+TTQ_API ttq_status ttq_comm_local_buffer(ttq_comm *comm, void **base_out, size_t *bytes_out);
+TTQ_API ttq_status ttq_comm_connect_pointers(ttq_comm *comm, void *const *bases);
+/* Number of polls of a peer's counter after which the fused exchange gives up (default 2^22, a few
+ * seconds); the give-up is reported as TTQ_ERR_TIMEOUT by ttq_device_status and the context stays usable.
+ * No reference counterpart. */
+TTQ_API ttq_status ttq_comm_set_wait_limit(ttq_comm *comm, int64_t polls);
 TTQ_API ttq_status ttq_comm_destroy(ttq_comm *comm);
 TTQ_API ttq_status ttq_linear_forward_allreduce(ttq_ctx *ctx, const ttq_weight *w, const void *x_dev, ttq_dtype x_dt,
                                                 int64_t M, int64_t ldx, const void *bias_dev, ttq_dtype bias_dt,
@@ -189,7 +199,7 @@ TTQ_API ttq_status ttq_linear_forward_allreduce(ttq_ctx *ctx, const ttq_weight *
  * Some hosts are not allowed to call cudaMalloc at all: a server that has given every byte of device
  * memory to its own pool, or a plug-in under a framework that forbids allocation after start-up.  Such
  * a host cannot create a ttq_ctx (ttq_init allocates scratch and staging buffers).  This call needs no
- * context and allocates nothing: its activation scratch is a fixed 173,120-byte array inside the
+ * context and allocates nothing: its activation scratch is a fixed 157,760-byte array inside the
  * library image, present on every GPU that loads the library until the process exits.
  *   Limits: M <= 4 and K <= 16384; larger requests return TTQ_ERR_LIMIT (message in errbuf).
  *   The weight's device must be the current device.  x, bias, y and the weight (created elsewhere,
@@ -197,13 +207,22 @@ TTQ_API ttq_status ttq_linear_forward_allreduce(ttq_ctx *ctx, const ttq_weight *
  *   The first call on a device looks up the array's device address (cudaGetSymbolAddress, checked)
  *   and the SM count; make that first call before starting any stream capture.
  *   All calls share the one array, which keeps the previous call's contents; every call rewrites what
- *   it reads and clears its status word.  Calls that overlap on the GPU (two streams, two threads)
- *   race on it: keep them on one stream.  Not thread-safe on the host either.
+ *   it reads.  Calls that overlap on the GPU (two streams, two threads) race on it: keep them on one
+ *   stream.  Not thread-safe on the host either.
+ *   A kernel that gives up a bounded device-side wait records it in a status word inside the array and
+ *   carries on with invalid data; the call itself has long returned TTQ_OK by then.  Read the word with
+ *   ttq_static_status (below) before trusting y -- after every call, or once per batch of calls.
  *   errbuf (optional) receives a message when the status is not TTQ_OK. */
 TTQ_API ttq_status ttq_linear_forward_static(const ttq_weight *w, const void *x_dev, ttq_dtype x_dt, int64_t M,
                                              int64_t ldx, const void *bias_dev, ttq_dtype bias_dt, void *y_dev,
                                              ttq_dtype y_dt, int64_t ldy, void *stream, char *errbuf,
                                              size_t errbuf_len);
+
+/* Companion of ttq_linear_forward_static, equally allocation-free and context-free (no counterpart in the
+ * reference): synchronises `stream`, reads the status word of the static array on the current device with one
+ * 4-byte copy and returns TTQ_ERR_TIMEOUT (clearing the word) if any ttq_linear_forward_static kernel since
+ * the last check gave up a wait, TTQ_OK otherwise. */
+TTQ_API ttq_status ttq_static_status(void *stream, char *errbuf, size_t errbuf_len);
 
 /* The down projection of a gated MLP with the activation folded into its input conversion
  * (GatedMLP.forward, workspace/transformers/src/layers/mlp.nim:56-60: silu_and_mul then down_proj):

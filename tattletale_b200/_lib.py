@@ -47,9 +47,13 @@ SIGNATURES = {
     "ttq_linear_forward": (_ci, [_vp, _vp, _vp, _ci, _i64, _i64, _vp, _ci, _vp, _ci, _i64, _vp]),
     "ttq_linear_forward_host": (_ci, [_vp, _vp, _vp, _ci, _i64, _i64, _vp, _ci, _vp, _ci, _i64]),
     "ttq_linear_forward_static": (_ci, [_vp, _vp, _ci, _i64, _i64, _vp, _ci, _vp, _ci, _i64, _vp, ctypes.c_char_p, _sz]),
+    "ttq_static_status": (_ci, [_vp, ctypes.c_char_p, _sz]),
     "ttq_linear_forward_gated": (_ci, [_vp, _vp, _vp, _ci, _i64, _i64, _vp, _ci, _vp, _ci, _i64, _vp]),
     "ttq_comm_create": (_ci, [_vp, _ci, _ci, _i64, _ci, _pp, _vp]),
     "ttq_comm_connect": (_ci, [_vp, _vp]),
+    "ttq_comm_local_buffer": (_ci, [_vp, _pp, ctypes.POINTER(_sz)]),
+    "ttq_comm_connect_pointers": (_ci, [_vp, _pp]),
+    "ttq_comm_set_wait_limit": (_ci, [_vp, _i64]),
     "ttq_comm_destroy": (_ci, [_vp]),
     "ttq_linear_forward_allreduce": (_ci, [_vp, _vp, _vp, _ci, _i64, _i64, _vp, _ci, _vp, _ci, _i64, _vp, _vp]),
     "ttq_silu_and_mul": (_ci, [_vp, _vp, _ci, _i64, _i64, _i64, _vp, _i64, _vp]),

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libttq.so")
-SOURCES = ["ttq_api.cu", "ttq_repack.cu", "ttq_gemv.cu", "ttq_gemm.cu", "ttq_moe.cu", "ttq_tq3.cu", "ttq_decode.cu"]
+SOURCES = ["ttq_api.cu", "ttq_repack.cu", "ttq_gemv.cu", "ttq_q4k_mma.cu", "ttq_gemm.cu", "ttq_moe.cu", "ttq_tq3.cu", "ttq_decode.cu"]
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-I", os.path.join(ROOT, "include"),
@@ -37,23 +37,8 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False, defines: tuple[str, ...] = (), out: str | None = None) -> str:
-    """Compile and link.  ``defines``/``out`` build an experimental variant next to the default library
-    (select it at load time with the TTQ_LIB environment variable)."""
-    if defines or out:
-        return _build_variant(verbose, defines, out or LIB)
-    return _build_default(force, verbose)
-
-
-def _build_variant(verbose: bool, defines: tuple[str, ...], out: str) -> str:
-    nvcc = _nvcc()
-    extra = ["-Xptxas", "-v"] if verbose else []
-    srcs = [os.path.join(CSRC, s) for s in SOURCES]
-    subprocess.check_call([nvcc, *NVCC_FLAGS, *extra, *[f"-D{d}" for d in defines], "-shared", "-o", out, *srcs])
-    return out
-
-
-def _build_default(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile every translation unit that is out of date, then link."""
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(ROOT, "include", "ttq.h"))
     objs = []
@@ -72,6 +57,4 @@ def _build_default(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    defs = tuple(a[2:] for a in sys.argv[1:] if a.startswith("-D"))
-    outs = [a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--out=")]
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, defines=defs, out=outs[0] if outs else None))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

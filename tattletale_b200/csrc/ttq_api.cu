@@ -33,6 +33,10 @@ struct ttq_ctx {
     int64_t wimg_capacity;      //   fused dequant GEMM); in halves, grown when such a weight is created
     __half *xh;                 // fp16 activation scratch of the tcgen05 GEMM path
     int64_t xh_capacity;        // in halves
+    float *split_ws;            // fp32 partial sums of decode linears whose K is split across CTAs (fixed at init)
+    size_t split_ws_bytes;
+    unsigned *split_counters;   // their per-row-tile arrival counters, zero between launches
+    int64_t split_counters_cap;
     // device staging for the *_host entry points
     uint8_t *stage_x, *stage_y, *stage_b;
     size_t stage_x_bytes, stage_y_bytes, stage_b_bytes;
@@ -68,6 +72,9 @@ constexpr size_t STAGE_X_BYTES = 64u << 20;       // host-entry staging: activat
 constexpr size_t STAGE_Y_BYTES = 128u << 20;      // host-entry staging: outputs
 constexpr size_t STAGE_B_BYTES = 4u << 20;        // host-entry staging: bias
 constexpr int64_t XH_CAPACITY = 32ll << 20;       // halves (64 MB): fp16 activations of one GEMM slab
+constexpr size_t SPLIT_WS_BYTES = 16u << 20;      // K-split partial sums: 8 slices x 16 rows x 32768 outputs of fp32
+constexpr int64_t SPLIT_COUNTERS = 1 << 16;       // row tiles (N <= 1M) a K-split decode linear may have
+constexpr int DEFAULT_PEER_WAIT_LIMIT = 1 << 22;  // polls of a peer's counter in the fused row-parallel exchange
 
 ttq_status fail(ttq_ctx *ctx, ttq_status s, const char *fmt, ...) {
     if (ctx) {
@@ -291,11 +298,13 @@ ttq_status ttq_init(int device, ttq_ctx **out) {
         if (e == cudaSuccess) e = cudaMemset(ctx->trace, 0, tb);
     }
     if (e == cudaSuccess) e = cudaMalloc(&ctx->xh, (size_t)XH_CAPACITY * sizeof(__half));
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->split_ws, SPLIT_WS_BYTES);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->split_counters, (size_t)SPLIT_COUNTERS * sizeof(unsigned));
+    if (e == cudaSuccess) e = cudaMemset(ctx->split_counters, 0, (size_t)SPLIT_COUNTERS * sizeof(unsigned));
     if (e == cudaSuccess) e = cudaMalloc(&ctx->stage_x, STAGE_X_BYTES);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->stage_y, STAGE_Y_BYTES);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->stage_b, STAGE_B_BYTES);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->host_stream, cudaStreamNonBlocking);
-    if (e == cudaSuccess) e = gemv_configure();
     if (e != cudaSuccess) {
         cudaGetLastError();
         ttq_destroy(ctx);
@@ -308,6 +317,8 @@ ttq_status ttq_init(int device, ttq_ctx **out) {
     ctx->xq.sx = reinterpret_cast<float *>(b + planes_b + s16_b + s32_b);
     ctx->xq_capacity_k = Kc;
     ctx->xh_capacity = XH_CAPACITY;
+    ctx->split_ws_bytes = SPLIT_WS_BYTES;
+    ctx->split_counters_cap = SPLIT_COUNTERS;
     ctx->att_part_cap = 8ll << 20;  // 32 MB: e.g. 32 sequences x 32 heads x 64 slices of 128 positions
     if (cudaMalloc(&ctx->att_part, (size_t)ctx->att_part_cap * sizeof(float)) != cudaSuccess) {
         ctx->att_part = nullptr;
@@ -330,6 +341,8 @@ ttq_status ttq_destroy(ttq_ctx *ctx) {
     cudaFreeHost(ctx->host_status);
     cudaFree(ctx->trace);
     cudaFree(ctx->xh);
+    cudaFree(ctx->split_ws);
+    cudaFree(ctx->split_counters);
     cudaFree(ctx->wimg);
     cudaFree(ctx->tq_x1);
     cudaFree(ctx->tq_y1);
@@ -515,8 +528,23 @@ static ttq_status linear_forward_impl(ttq_ctx *ctx, const ttq_weight *w, const v
         const char *v = getenv("TTQ_GEMM");
         return !(v && v[0] == '0');
     }();
-    // measured cross-over of the two paths on the Llama-3-8B shapes: the decode kernel re-runs its MMA sets per row and
-    // is as fast as the tensor-core path at 4 rows, slower from 5 (TTQ_GEMM_MIN_M overrides)
+    // Q4_K batches of 3 to 16 rows: one kernel (fp16 tensor-core instructions on exact integer operands, activations
+    // converted inside the kernel).  Up to 2 rows the integer decode kernel below is faster, beyond 16 the tcgen05 path.
+    // TTQ_Q4K_MMA=0 switches the kernel off.
+    static const bool use_mma = env_flag("TTQ_Q4K_MMA", true);
+    constexpr int64_t MMA_MIN_M = 3, MMA_MAX_M = 16;
+    if (w->fmt == TTQ_FMT_Q4_K && use_mma && M >= MMA_MIN_M && M <= MMA_MAX_M) {
+        a.x = x_dev; a.M = M; a.y = y_dev;
+        int launches = 0;
+        cudaError_t e = launch_q4k_mma(a, ctx->sms, ctx->dev_status, ctx->trace, ctx->split_ws, ctx->split_ws_bytes, ctx->split_counters,
+                                       ctx->split_counters_cap, st, &launches);
+        ctx->launches += launches;
+        if (e == cudaSuccess) return TTQ_OK;
+        if (e != cudaErrorNotSupported) return cuda_fail(ctx, e, "linear forward (Q4_K decode) launch");
+        // shape outside the kernel's plans: the other paths below
+    }
+    // crossover between the decode kernel of the other formats (per-row MMA sets) and the tensor-core path
+    // (TTQ_GEMM_MIN_M overrides)
     static const int64_t GEMM_MIN_M = []() -> int64_t {
         const char *v = getenv("TTQ_GEMM_MIN_M");
         const int64_t n = v ? atoll(v) : 0;
@@ -625,6 +653,7 @@ ttq_status ttq_linear_forward_host(ttq_ctx *ctx, const ttq_weight *w, const void
     if (*ctx->host_status != 0) {
         const int seen = *ctx->host_status;
         cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), st);
+        cudaMemsetAsync(ctx->split_counters, 0, (size_t)ctx->split_counters_cap * sizeof(unsigned), st);
         return fail(ctx, TTQ_ERR_TIMEOUT, "a kernel gave up a bounded wait (status word 0x%x); results of that call are invalid", seen);
     }
     return TTQ_OK;
@@ -637,6 +666,8 @@ ttq_status ttq_device_status(ttq_ctx *ctx, void *stream) {
     TTQ_CUDA(ctx, cudaStreamSynchronize((cudaStream_t)stream));
     if (host != 0) {
         cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), (cudaStream_t)stream);
+        // a kernel that gave up may have left K-split arrival counters behind
+        cudaMemsetAsync(ctx->split_counters, 0, (size_t)ctx->split_counters_cap * sizeof(unsigned), (cudaStream_t)stream);
         return fail(ctx, TTQ_ERR_TIMEOUT, "a kernel gave up a bounded wait (status word 0x%x); results of that call are invalid", host);
     }
     return TTQ_OK;
@@ -673,6 +704,7 @@ ttq_status ttq_comm_create(ttq_ctx *ctx, int rank, int world, int64_t n_cap, int
     }
     c->view.rank = rank;
     c->view.world = world;
+    c->view.wait_limit = DEFAULT_PEER_WAIT_LIMIT;
     c->view.nt_cap = (int)nt_cap;
     c->view.m_cap = m_cap;
     c->view.n_cap = n_cap;
@@ -694,6 +726,33 @@ ttq_status ttq_comm_connect(ttq_comm *c, const void *all_handles) {
         c->view.flags[r] = reinterpret_cast<uint32_t *>(base);
         c->view.data[r] = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(base) + c->flag_bytes);
     }
+    return TTQ_OK;
+}
+
+ttq_status ttq_comm_local_buffer(ttq_comm *c, void **base_out, size_t *bytes_out) {
+    if (!c || !base_out) return TTQ_ERR_INVALID_ARG;
+    *base_out = c->local;
+    if (bytes_out) *bytes_out = c->bytes;
+    return TTQ_OK;
+}
+
+ttq_status ttq_comm_connect_pointers(ttq_comm *c, void *const *bases) {
+    if (!c || !bases) return TTQ_ERR_INVALID_ARG;
+    ttq_ctx *ctx = c->ctx;
+    for (int r = 0; r < c->view.world; r++) {
+        void *base = r == c->view.rank ? c->local : bases[r];
+        if (!base) return fail(ctx, TTQ_ERR_INVALID_ARG, "exchange buffer of rank %d is NULL", r);
+        if (reinterpret_cast<uintptr_t>(base) & 255) return fail(ctx, TTQ_ERR_INVALID_ARG, "exchange buffer of rank %d is not 256-byte aligned", r);
+        c->view.flags[r] = reinterpret_cast<uint32_t *>(base);
+        c->view.data[r] = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(base) + c->flag_bytes);
+    }
+    return TTQ_OK;
+}
+
+ttq_status ttq_comm_set_wait_limit(ttq_comm *c, int64_t polls) {
+    if (!c) return TTQ_ERR_INVALID_ARG;
+    if (polls < 1 || polls > (1ll << 30)) return fail(c->ctx, TTQ_ERR_INVALID_ARG, "polls=%lld outside 1..2^30", (long long)polls);
+    c->view.wait_limit = (int)polls;
     return TTQ_OK;
 }
 
@@ -734,9 +793,19 @@ ttq_status ttq_linear_forward_allreduce(ttq_ctx *ctx, const ttq_weight *w, const
     a.bias = bias_dev; a.bias_dt = bias_dt;
     a.y = y_dev; a.y_dt = y_dt; a.ldy = ldy;
     int launches = 0;
-    cudaError_t e = launch_gemv(w->fmt, a, ctx->xq, ctx->xq_capacity_k, reinterpret_cast<const uint8_t *>(ctx->dev_status) + 256, ctx->sms,
-                                ctx->dev_status, ctx->trace, (cudaStream_t)stream, &launches, &comm->view);
-    ctx->launches += launches;
+    cudaError_t e = cudaErrorNotSupported;
+    static const bool use_mma = env_flag("TTQ_Q4K_MMA", true);
+    if (w->fmt == TTQ_FMT_Q4_K && use_mma && M >= 3) {
+        e = launch_q4k_mma(a, ctx->sms, ctx->dev_status, ctx->trace, ctx->split_ws, ctx->split_ws_bytes, ctx->split_counters,
+                           ctx->split_counters_cap, (cudaStream_t)stream, &launches, &comm->view);
+        ctx->launches += launches;
+    }
+    if (e == cudaErrorNotSupported) {
+        if (M > MAX_GEMV_M) return fail(ctx, TTQ_ERR_UNSUPPORTED, "M=%lld exceeds the decode kernel's %d rows", (long long)M, MAX_GEMV_M);
+        e = launch_gemv(w->fmt, a, ctx->xq, ctx->xq_capacity_k, reinterpret_cast<const uint8_t *>(ctx->dev_status) + 256, ctx->sms,
+                        ctx->dev_status, ctx->trace, (cudaStream_t)stream, &launches, &comm->view);
+        ctx->launches += launches;
+    }
     if (e != cudaSuccess) return cuda_fail(ctx, e, "row-parallel linear launch");
     return TTQ_OK;
 }

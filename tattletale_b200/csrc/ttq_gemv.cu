@@ -23,7 +23,7 @@
 // while its predecessor drains and executes griddepcontrol.wait before touching activations.
 #include <cstdlib>
 
-#include "ttq_internal.cuh"
+#include "ttq_devutil.cuh"
 
 namespace ttq {
 
@@ -47,74 +47,6 @@ __device__ __forceinline__ void mma_k32_s8s8(int (&c)[4], uint32_t a0, uint32_t 
         "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
         : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// ---- bulk-copy ring primitives (all waits are bounded) ---------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Waits for a stage; gives up after WAIT_LIMIT polls, records the failure and lets the caller go on
-// (with garbage data) so that every warp still reaches its barriers and the kernel returns.
-constexpr int WAIT_LIMIT = 1 << 20;
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int *status) {
-    for (int i = 0; i < WAIT_LIMIT; i++)
-        if (mbar_try_wait(bar, parity)) return true;
-    atomicOr(status, 1);
-    return false;
-}
-__device__ __forceinline__ void named_barrier(int id, int nthreads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
-
-
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-constexpr int TRACE_CAP = 8192;  // entries
-// Timeline entry of one kernel (written by thread 0 of block 0 when tracing is on):
-// [0] kind (1 = activation pass, 2 = GEMV), [1] start, [2] after the dependency wait, [3] activations ready,
-// [4] first weight tile ready, [5] end of block 0, [6] grid size, [7] N
-__device__ __forceinline__ unsigned long long *trace_open(unsigned long long *trace, unsigned long long kind) {
-    if (trace == nullptr || blockIdx.x != 0 || threadIdx.x != 0) return nullptr;
-    const unsigned long long slot = atomicAdd(trace, 1ull);
-    if (slot >= TRACE_CAP) return nullptr;
-    unsigned long long *e = trace + 8 + slot * 8;
-    e[0] = kind;
-    e[1] = global_ns();
-    return e;
-}
-
-// compile-time loop: f(std::integral_constant<int, I>) for I in [0, N)
-template <int V>
-struct IC {
-    static constexpr int value = V;
-};
-template <int I, int N, class F>
-__device__ __forceinline__ void static_for(F &&f) {
-    if constexpr (I < N) {
-        f(IC<I>{});
-        static_for<I + 1, N>(f);
-    }
 }
 
 // ---- activation conversion -------------------------------------------------------------------
@@ -254,57 +186,6 @@ __global__ void __launch_bounds__(GEMV_THREADS) xprep_kernel(const void *__restr
     }
 }
 
-// ---- shared-memory access with 32-bit addresses and immediate offsets ----------------------------
-template <int OFF>
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
-    return v;
-}
-template <int OFF>
-__device__ __forceinline__ float ldsf(uint32_t addr) {
-    float v;
-    asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(addr), "n"(OFF));
-    return v;
-}
-template <int OFF>
-__device__ __forceinline__ float2 lds64f(uint32_t addr) {
-    float2 v;
-    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2+%3];" : "=f"(v.x), "=f"(v.y) : "r"(addr), "n"(OFF));
-    return v;
-}
-template <int OFF>
-__device__ __forceinline__ uint2 lds64(uint32_t addr) {
-    uint2 v;
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF));
-    return v;
-}
-template <int OFF>
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "r"(addr), "n"(OFF));
-    return v;
-}
-template <int OFF>
-__device__ __forceinline__ float4 lds128f(uint32_t addr) {
-    float4 v;
-    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4+%5];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                 : "r"(addr), "n"(OFF));
-    return v;
-}
-template <int OFF>
-__device__ __forceinline__ void stsf(uint32_t addr, float v) {
-    asm volatile("st.shared.f32 [%0+%1], %2;" ::"r"(addr), "n"(OFF), "f"(v) : "memory");
-}
-
-template <int OFF>
-__device__ __forceinline__ void sts128f(uint32_t addr, float a, float b, float c, float d) {
-    asm volatile("st.shared.v4.f32 [%0+%1], {%2,%3,%4,%5};" ::"r"(addr), "n"(OFF), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-
 // ---- the GEMV --------------------------------------------------------------------------------
 struct GemvParams {
     LinearArgs a;
@@ -316,10 +197,7 @@ struct GemvParams {
     CommView comm;         // row-parallel exchange over peer memory (world <= 1: none)
 };
 
-#ifndef TTQ_RING_STAGES
-#define TTQ_RING_STAGES 2
-#endif
-constexpr int RING_STAGES = TTQ_RING_STAGES;  // stages of each warp's bulk-copy ring
+constexpr int RING_STAGES = 2;  // stages of each warp's bulk-copy ring (the barrier area below is sized from it)
 constexpr int XSRC_CONVERT = 0, XSRC_COPY = 1, XSRC_GLOBAL = 2;
 constexpr int ZERO_BYTES = 512;
 
@@ -803,7 +681,7 @@ __global__ void __launch_bounds__(NW * 32, NW > 8 ? 1 : (XSRC == XSRC_GLOBAL ? 2
                     uint32_t seen;
                     do {
                         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(my_flag) : "memory");
-                        if (++spins > (1 << 22)) {  // bounded: give up, flag the failure, keep going
+                        if (++spins > cm.wait_limit) {  // bounded: give up, flag the failure, keep going
                             ok = false;
                             break;
                         }
@@ -923,8 +801,6 @@ cudaError_t dispatch(GemvParams &p, int mode, int nw, int sms, cudaStream_t st) 
 
 }  // namespace
 
-cudaError_t gemv_configure() { return cudaSuccess; }
-
 cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t xq_capacity_k, const uint8_t *zeros,
                         int sms, int *status, unsigned long long *trace, cudaStream_t st, int *launches, const CommView *comm) {
     GemvParams p{a, xq, zeros, 1, status, trace, {}};
@@ -976,8 +852,8 @@ cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t 
 //
 // Limits: M <= TTQ_STATIC_MAX_M rows, K <= TTQ_STATIC_MAX_K (after rounding K up to 256).
 // The array is shared by all calls and keeps whatever the last call left in it; each call rewrites
-// every byte it will read (padding rows are written as zeros by the conversion pass) and clears the
-// status word, and the zero page at its start is never written.  Two calls that overlap on the GPU
+// every byte it will read (padding rows are written as zeros by the conversion pass); the zero page at
+// its start is never written, and the status word in it is cleared by ttq_static_status only.  Two calls that overlap on the GPU
 // (different streams, or different host threads) race on the array: issue them on one stream.
 // ================================================================================================
 namespace ttq {
@@ -990,7 +866,8 @@ constexpr size_t ST_PLANES = (size_t)2 * TTQ_STATIC_MAX_M * TTQ_STATIC_MAX_K;  /
 constexpr size_t ST_SUM16 = (size_t)TTQ_STATIC_MAX_M * (TTQ_STATIC_MAX_K / 16) * 4;
 constexpr size_t ST_SUM32 = (size_t)TTQ_STATIC_MAX_M * (TTQ_STATIC_MAX_K / 32) * 4;
 constexpr size_t ST_SX = (size_t)TTQ_STATIC_MAX_M * (TTQ_STATIC_MAX_K / 256 + 4) * 4;
-constexpr size_t ST_TOTAL = ST_ZERO + ST_PLANES + ST_SUM16 + ST_SUM32 + ST_SX;  // 173,120 bytes
+constexpr size_t ST_TOTAL = ST_ZERO + ST_PLANES + ST_SUM16 + ST_SUM32 + ST_SX;
+static_assert(ST_TOTAL == 157760, "the documented size of the static scratch array (ttq.h) must follow this sum");
 
 // In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
 static __device__ __align__(256) unsigned char g_static_scratch[ST_TOTAL];
@@ -1064,10 +941,12 @@ extern "C" TTQ_API ttq_status ttq_linear_forward_static(const ttq_weight *w, con
     xq.sum16 = reinterpret_cast<float *>(sd.base + ST_ZERO + ST_PLANES);
     xq.sum32 = reinterpret_cast<float *>(sd.base + ST_ZERO + ST_PLANES + ST_SUM16);
     xq.sx = reinterpret_cast<float *>(sd.base + ST_ZERO + ST_PLANES + ST_SUM16 + ST_SUM32);
+    // the status word starts at zero with the module image and is cleared only by ttq_static_status, so that a
+    // failure stays visible until the host has read it; everything else the kernels read is rewritten below
     int *status = reinterpret_cast<int *>(sd.base + 768);
     cudaStream_t st = (cudaStream_t)stream;
-    cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int), st);  // must start at zero; the rest is rewritten below
-    if (e == cudaSuccess) {
+    cudaError_t e = cudaSuccess;
+    {
         LinearArgs a;
         a.tiles = w->tiles;
         a.N = w->N; a.K = w->K; a.NT = w->NT; a.SBp = w->SBp;
@@ -1084,3 +963,32 @@ extern "C" TTQ_API ttq_status ttq_linear_forward_static(const ttq_weight *w, con
     return TTQ_OK;
 }
 
+
+// Reads (and clears) the status word of the static scratch array: the allocation-free counterpart of
+// ttq_device_status.  One 4-byte copy from the array's device address into the caller's stack and one stream
+// synchronisation; nothing is allocated.
+extern "C" TTQ_API ttq_status ttq_static_status(void *stream, char *errbuf, size_t errbuf_len) {
+    using namespace ttq;
+    set_msg(errbuf, errbuf_len, "");
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        set_msg(errbuf, errbuf_len, "no current CUDA device");
+        return TTQ_ERR_DEVICE;
+    }
+    StaticDevice &sd = g_static_dev[dev];
+    if (!sd.ready) return TTQ_OK;  // ttq_linear_forward_static has not run on this device: nothing to report
+    cudaStream_t st = (cudaStream_t)stream;
+    int host = 0;
+    cudaError_t e = cudaMemcpyAsync(&host, sd.base + 768, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e == cudaSuccess && host != 0) e = cudaMemsetAsync(sd.base + 768, 0, sizeof(int), st);
+    if (e != cudaSuccess) {
+        set_msg(errbuf, errbuf_len, cudaGetErrorString(e));
+        return TTQ_ERR_CUDA;
+    }
+    if (host != 0) {
+        set_msg(errbuf, errbuf_len, "a kernel launched by ttq_linear_forward_static gave up a bounded wait; results since the last check are invalid");
+        return TTQ_ERR_TIMEOUT;
+    }
+    return TTQ_OK;
+}

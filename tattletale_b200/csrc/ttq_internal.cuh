@@ -97,6 +97,7 @@ constexpr int TTQ_MAX_RANKS = 8;
 struct CommView {
     int rank, world;
     int nt_cap, m_cap;
+    int wait_limit;                  // polls of a peer's counter before the wait is given up (status bit 2)
     int64_t n_cap;
     uint32_t *sent;                  // local [nt_cap]: exchanges this rank has completed per row tile
     uint32_t *flags[TTQ_MAX_RANKS];  // flag array of every rank
@@ -208,6 +209,12 @@ cudaError_t launch_dequant(int fmt, const uint8_t *tiled, float *out, int64_t ld
 cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t xq_capacity_k, const uint8_t *zeros,
                         int sms, int *status, unsigned long long *trace, cudaStream_t st, int *launches,
                         const CommView *comm = nullptr);
+// Q4_K decode linear on fp16 tensor-core instructions, M <= 16, activations converted inside the kernel
+// (ttq_q4k_mma.cu).  `ws` / `counters`: fp32 workspace and per-row-tile arrival counters (zero between launches)
+// for matrices whose K is split across CTAs.  cudaErrorNotSupported: the caller takes another path.
+bool q4k_mma_supported(const LinearArgs &a);
+cudaError_t launch_q4k_mma(const LinearArgs &a, int sms, int *status, unsigned long long *trace, float *ws, size_t ws_bytes,
+                           unsigned *counters, int64_t counters_cap, cudaStream_t st, int *launches, const CommView *comm = nullptr);
 constexpr int TTQ_TRACE_ENTRIES = 8192;
 // tcgen05 dequant-GEMM for M > MAX_GEMV_M (formats for which gemm_supported() is true)
 bool gemm_supported(int fmt);
@@ -220,7 +227,6 @@ int64_t gemm_wimg_rows(int64_t N);
 cudaError_t launch_wimg(int fmt, const uint8_t *tiled, int64_t N, int64_t K, int64_t SBp, __half *wimg, cudaStream_t st);
 cudaError_t launch_silu_and_mul(const void *in, int dt, int64_t M, int64_t H, int64_t ld_in, void *out,
                                 int64_t ld_out, cudaStream_t st);
-cudaError_t gemv_configure();  // one-time cudaFuncSetAttribute calls
 
 // ---------------------------------------------------------------------------------------------
 // small device helpers

@@ -36,10 +36,15 @@ class DecoderConfig:
     context: int = 2048
 
 
-def _qlinear(ctx, fmt, n, k, seed, dev):
+def synthetic_blocks(fmt, n, k, seed, dev):
+    """Canonical blocks of a seeded N(0, 0.02) matrix, quantized on the device (what the stack's linears hold)."""
     g = torch.Generator(device=dev).manual_seed(seed)
     w = torch.randn(n, k, generator=g, device=dev) * 0.02
-    return QuantLinear(ctx, fmt, Q.quantize(fmt, w), k)
+    return Q.quantize(fmt, w)
+
+
+def _qlinear(ctx, fmt, n, k, seed, dev):
+    return QuantLinear(ctx, fmt, synthetic_blocks(fmt, n, k, seed, dev), k)
 
 
 class DecoderStack:
@@ -70,10 +75,15 @@ class DecoderStack:
             })
         vocab_l = cfg.vocab // world
         self.lm_head = _qlinear(ctx, FMT_Q6_K, vocab_l, cfg.hidden, seed + 900 + rank, dev)     # column parallel
-        # embedding: Q6_K rows, expanded once at load time (the lookup reads only `batch` rows per step)
-        emb_q = _qlinear(ctx, FMT_Q6_K, 4096, cfg.hidden, seed + 901, dev)
-        self.emb_rows = emb_q.dequantize().to(torch.bfloat16)  # a 4096-row slice of the table is enough for timing
-        emb_q.close()
+        # embedding: the full vocabulary as Q6_K rows, expanded once at load time to bf16 (the lookup reads only
+        # `batch` rows per step); built in slabs so that the fp32 expansion stays small
+        self.emb_rows = torch.empty((cfg.vocab, cfg.hidden), dtype=torch.bfloat16, device=dev)
+        slab = 16032
+        for r0 in range(0, cfg.vocab, slab):
+            rows = min(slab, cfg.vocab - r0)
+            emb_q = _qlinear(ctx, FMT_Q6_K, rows, cfg.hidden, seed + 901 + r0, dev)
+            self.emb_rows[r0:r0 + rows] = emb_q.dequantize().to(torch.bfloat16)
+            emb_q.close()
         self.final_norm = torch.ones(cfg.hidden, device=dev, dtype=torch.bfloat16)
         pos = cfg.context - 1
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, d, 2, device=dev, dtype=torch.float64) / d))
@@ -105,7 +115,7 @@ class DecoderStack:
     def _step_fused(self, token_ids: torch.Tensor) -> torch.Tensor:
         """The layer loop with the library's decode-step kernels: 9 launches per layer besides the linears' own."""
         cfg, B, d, ctx = self.cfg, self.batch, self.cfg.head_dim, self.ctx
-        h = self.emb_rows[token_ids % self.emb_rows.shape[0]].contiguous()
+        h = self.emb_rows[token_ids].contiguous()
         delta = None
         for L in self.layers:
             x = add_rmsnorm(ctx, h, delta, L["attn_norm"], cfg.rms_eps)
@@ -126,7 +136,7 @@ class DecoderStack:
         if self.fused_glue:
             return self._pick(self.lm_head.forward(self._step_fused(token_ids), out_dtype=torch.float32))
         cfg, B, d = self.cfg, self.batch, self.cfg.head_dim
-        h = self.emb_rows[token_ids % self.emb_rows.shape[0]]
+        h = self.emb_rows[token_ids]
         for L in self.layers:
             x = self._rms(h, L["attn_norm"])
             qkv = L["qkv"].forward(x)

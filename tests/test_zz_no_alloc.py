@@ -14,9 +14,10 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
 import tattletale_b200 as ttq
 from conftest import rel_l2
-from gpu_util import make_weight, make_x
+from gpu_util import OFMT, make_weight, make_x, x_bits
 from tattletale_b200 import _lib
 
 pytestmark = pytest.mark.gpu
@@ -34,10 +35,17 @@ def static_forward(lin, x, bias=None):
     return st, err.value.decode(), y
 
 
+def static_status():
+    """The allocation-free status check: 0, or 8 (TTQ_ERR_TIMEOUT) if a kernel of an earlier call gave up a wait."""
+    err = ctypes.create_string_buffer(256)
+    return _lib.load().ttq_static_status(torch.cuda.current_stream().cuda_stream, err, 256)
+
+
 @pytest.mark.parametrize("fmt", [ttq.FMT_Q4_K, ttq.FMT_Q8_0, ttq.FMT_Q6_K], ids=["q4_k", "q8_0", "q6_k"])
 def test_two_calls_in_a_row_match_the_regular_entry_point(ctx, fmt):
     n, k = 192, 2048
-    lin = ttq.QuantLinear(ctx, fmt, torch.from_numpy(make_weight(fmt, n, k, seed=600)), k)
+    blocks = make_weight(fmt, n, k, seed=600)
+    lin = ttq.QuantLinear(ctx, fmt, torch.from_numpy(blocks), k)
     bias = torch.from_numpy(np.random.default_rng(601).normal(0, 0.1, n).astype(np.float32)).cuda()
     # second call: fewer rows and other values, so stale planes of the first call are still in the array
     for m, seed, b in ((4, 610, None), (1, 611, bias)):
@@ -48,7 +56,12 @@ def test_two_calls_in_a_row_match_the_regular_entry_point(ctx, fmt):
         assert st == 0, msg
         torch.cuda.synchronize()
         assert rel_l2(got.cpu().numpy(), want.cpu().numpy()) < TOL
-        assert torch.equal(got, want)  # same kernels, same arithmetic: expected to agree exactly
+        if fmt != ttq.FMT_Q4_K or m <= 2:
+            assert torch.equal(got, want)  # same kernels, same arithmetic: expected to agree exactly
+        # and against the CPU checker, not only against the library's other entry point
+        ref = oracle.linear(OFMT[fmt], blocks, x_bits(x.cpu()), oracle.BF16, None if b is None else b.cpu().numpy())
+        assert rel_l2(got.cpu().numpy(), ref) < TOL
+        assert static_status() == 0  # no kernel of the call gave up a bounded wait
     lin.bias = None
     lin.close()
 
@@ -64,6 +77,7 @@ def test_large_k_reads_planes_from_the_array(ctx):
         assert st == 0, msg
         torch.cuda.synchronize()
         assert rel_l2(got.cpu().numpy(), want.cpu().numpy()) < TOL
+        assert static_status() == 0
     lin.close()
 
 
