@@ -160,13 +160,14 @@ def reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = min(args.steps, 50)
-    gbs, ms, cores, port_gbs, done = time_cpu_reference(args.m, steps, min(args.warmup, 3))
+    # exactly the requested warm-up and step counts (a step is one layer, ~3 ms: hundreds of steps stay within seconds;
+    # the time budget only guards against a pathological host)
+    gbs, ms, cores, port_gbs, done = time_cpu_reference(args.m, args.steps, args.warmup, budget_s=240.0)
     sample = (f"one Llama-3-8B layer (4 linears, M={args.m}) per step, {done} steps; ATen linear on "
               f"dequantized bf16 weights, {cores} threads")
     line = {
         "impl": "reference", "metric": "Q4_K dequant-GEMV GB/s", "value": round(gbs, 3), "unit": "GB/s",
-        "n_gpus": args.gpus, "steps": done, "warmup": min(args.warmup, 3), "ms_per_step": round(ms, 4),
+        "n_gpus": args.gpus, "steps": done, "warmup": args.warmup, "ms_per_step": round(ms, 4),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(args.m, args.gpus),
         "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": "reference",
@@ -239,7 +240,7 @@ def ours_arm(args):
     if world > 1 and not args.nccl_allreduce:
         from tattletale_b200 import tp
 
-        comm = tp.Communicator(ctx, n_cap=4096, m_cap=4)  # row-parallel outputs are [M, 4096]
+        comm = tp.Communicator(ctx, n_cap=4096, m_cap=16)  # row-parallel outputs are [M, 4096]
 
     def step():
         for entry in layers:
@@ -328,7 +329,7 @@ def ours_arm(args):
         e2e_s = (time.perf_counter() - t0) / e2e_steps
         e2e = {"value": round(step_bytes / e2e_s / 1e9, 3), "unit": "GB/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_s * 1e3, 4), "steps": e2e_steps,
-               "api": "ttq_linear_forward_host, one call per linear on pinned host buffers: the kernels read x and write y through the buffers' device mappings (no staging copy), status word copied back, one sync per call"}
+               "api": "ttq_linear_forward_host, one call per linear on pinned host buffers: the kernels read x and write y through the buffers' device mappings (no staging copy), failure flag in mapped host memory, one sync per call"}
 
     # ---- per-shape breakdown (device-resident, cold L2: the 32 layers' copies are rotated)
     per_shape = {}
@@ -349,30 +350,37 @@ def ours_arm(args):
             us = a.elapsed_time(b) * 1e3 / (reps * N_LAYERS)
             per_shape[f"{k}x{n}"] = {"us": round(us, 3), "gbs": round(algorithmic_bytes(m, k, n) / us / 1e3, 1)}
 
-    # ---- batched rows on the same weights: M = 4 (decode kernel) and 16, 64, 256, 2048 (tcgen05 GEMM), layer 0
+    # ---- batched rows: M = 2 .. 2048 on every shape.  One launch per layer's weight (32 distinct matrices per shape,
+    # 0.3 - 2.1 GB: cold L2 for the memory-bound sizes), replayed as a CUDA graph so that host launch time stays out
     sweep = {}
     if world == 1 and not args.no_e2e and not args.no_sweep:
-        for ms in (4, 16, 64, 256, 2048):
+        for ms in (2, 4, 8, 16, 64, 256, 2048):
             for idx, (name, k, n) in enumerate(SHAPES):
-                lin = layers[0][idx][1]
+                lins = [layers[l][idx][1] for l in range(N_LAYERS if ms <= 64 else min(N_LAYERS, 4))]
                 g = torch.Generator(device=dev).manual_seed(2100 + ms)
                 xs = torch.randn(ms, k, generator=g, device=dev).to(torch.bfloat16)
                 ys = torch.empty(ms, n, dtype=torch.bfloat16, device=dev)
-                for _ in range(2):
-                    lin.forward(xs, out=ys)
-                torch.cuda.synchronize()
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                reps = 10
-                a.record()
-                for _ in range(reps):
-                    lin.forward(xs, out=ys)
-                b.record()
-                torch.cuda.synchronize()
-                us = a.elapsed_time(b) * 1e3 / reps
+
+                def sweep_step():
+                    for lin in lins:
+                        lin.forward(xs, out=ys)
+
+                us = _time_graph(sweep_step, reps=4) / len(lins)
                 sweep[f"M{ms}_{k}x{n}"] = {"us": round(us, 2), "tflops": round(2.0 * ms * n * k / us / 1e6, 1),
                                             "gbs": round(algorithmic_bytes(ms, k, n) / us / 1e3, 1)}
                 del xs, ys
         ctx.check_device_status()
+
+    # ---- the other half of the metric: decode tokens/s of the full decoder stack (one GPU)
+    decode_stack = None
+    if world == 1 and not args.no_e2e and not args.no_decode_stack:
+        decode_stack = _decode_stack_numbers(ttq, ctx, dev, layers)
+
+    # ---- N > 1: the configurations where sharding has more to give than at M = 1 -- the decoder stack at batch 1 and
+    # 32 (tokens/s) and trellis-coded linears on the Llama-3-70B shapes at M = 16, all tensor-parallel over the ranks
+    tp_extras = None
+    if world > 1 and not args.no_e2e:
+        tp_extras = _tp_extras(ttq, ctx, dev, rank, world, comm, dist)
 
     if rank != 0:
         _finish_distributed(dist, world)
@@ -389,9 +397,9 @@ def ours_arm(args):
     roofline = {
         "bound": "hbm", "achieved": round(value / world, 2), "peak": peak, "unit": "GB/s",
         "frac": round(value / world / peak, 4),
-        # dram read + write per launch from the committed ncu capture (profiles/gemv_q4k_m1_llama8b.md: 123.14 MB over the
-        # four linears of a layer at M = 1, against 122.83 MB algorithmic); other batch sizes and shards have no capture
-        "traffic": 30785000 if (m == 1 and world == 1) else None,
+        # dram read + write per launch, measured by ncu on a 2-layer case of the same kernels and shapes (the traffic of a
+        # launch does not depend on the layer count); other batch sizes and shards have no capture
+        "traffic": _measured_traffic("gemv_q4k_m1_llama8b_per_launch") if (m == 1 and world == 1) else None,
         "traffic_source": "ncu capture of a 2-layer case, mean over one layer's four launches" if (m == 1 and world == 1) else None,
         "peak_source": peak_kind,
         "kernel": "xprep_kernel + gemv_kernel<Q4_K> (activation planes bulk-copied from scratch)",
@@ -414,16 +422,173 @@ def ours_arm(args):
         "cuda_graph": graph is not None, "clocks": clocks, "per_shape": per_shape,
         "decode_linears_tokens_per_s": round(m / (ms_step * 1e-3), 1),
     }
+    if decode_stack:
+        line["decode_stack"] = decode_stack
+    if tp_extras:
+        line["tensor_parallel"] = tp_extras
     if sweep:
         best = max(v["tflops"] for key, v in sweep.items() if key.startswith("M2048_"))
         tpeak = float(peaks.get("bf16_tflops", 1590.0))
         line["sweep"] = sweep
         line["roofline_gemm"] = {"bound": "tensor", "achieved": best, "peak": tpeak, "unit": "TFLOP/s",
                                  "frac": round(best / tpeak, 4), "kernel": "gemm_q4k_kernel (tcgen05, fp16 operands, fp32 accumulate)",
-                                 "workload": "best of the four Q4_K shapes at M=2048 (hot L2, includes the activation pass)",
+                                 "workload": "best of the four Q4_K shapes at M=2048 (graph replay over 4 layers' weights, includes the activation pass)",
                                  "peak_source": "MEASURED_PEAKS.json bf16_tflops (burst)" if "bf16_tflops" in peaks else "fallback 1590"}
     print(json.dumps(line), flush=True)
     _finish_distributed(dist, world)
+
+
+def _time_graph(step, reps: int = 4, warm: int = 2) -> float:
+    """Microseconds of one `step()` replayed as a CUDA graph (capture on a side stream, `warm` untimed replays)."""
+    step()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for _ in range(warm):
+        graph.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    del graph
+    return a.elapsed_time(b) * 1e3 / reps
+
+
+def _decode_stack_numbers(ttq, ctx, dev, layers=None):
+    """Decode tokens/s of the Llama-3-8B decoder stack (configs[2]: 32 layers, Q4_K linears, Q6_K vocabulary
+    projection over the full 128256-row table, context 2048) at batch 1, 8 and 32 on this GPU."""
+    from tattletale_b200.decoder import DecoderConfig, DecoderStack
+
+    cfg = DecoderConfig()
+    peaks = _peaks()
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    torch.manual_seed(3000)
+    stack = DecoderStack(ctx, cfg, 32)
+    out = {}
+    for batch in (1, 8, 32):
+        g = torch.Generator(device=dev).manual_seed(3100 + batch)
+        ids = torch.randint(0, cfg.vocab, (batch,), generator=g, device=dev)
+        us = _time_graph(lambda: stack.step(ids), reps=10, warm=3)
+        kv_bytes = 2 * cfg.n_layers * batch * cfg.n_kv_heads * cfg.context * cfg.head_dim * 2
+        gbs = (stack.weight_bytes + kv_bytes) / us / 1e3
+        out[str(batch)] = {"tokens_per_s": round(batch / (us * 1e-6), 1), "ms_per_step": round(us / 1e3, 4),
+                           "hbm_gbs": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4),
+                           "bytes_per_step": {"weights": int(stack.weight_bytes), "kv_cache": int(kv_bytes)}}
+    ctx.check_device_status()
+    del stack
+    torch.cuda.empty_cache()
+    return out
+
+
+def _max_over_ranks(us: float, dev, dist) -> float:
+    t = torch.tensor([us], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _tp_extras(ttq, ctx, dev, rank, world, comm, dist):
+    """Tensor-parallel numbers beside the headline (device-timed, max over ranks): decoder stack tokens/s at batch 1 and
+    32 (QKV and gate|up split by rows, O and down by columns with the sum over ranks fused into the linear up to 16
+    rows and through NCCL beyond), and one layer of trellis-coded 3-bit linears on the Llama-3-70B shapes at M = 16
+    (column split for QKV and gate|up, row split + NCCL all-reduce for O and down)."""
+    from tattletale_b200 import formats, tp
+    from tattletale_b200._lib import SHARD_COLUMN, SHARD_ROW
+    from tattletale_b200.decoder import DecoderConfig, DecoderStack
+
+    out = {}
+    cfg = DecoderConfig()
+    torch.manual_seed(3000 + rank)
+    stack = DecoderStack(ctx, cfg, 32, rank, world, comm=comm)
+    for batch in (1, 32):
+        g = torch.Generator(device=dev).manual_seed(3100 + batch)
+        ids = torch.randint(0, cfg.vocab, (batch,), generator=g, device=dev)
+        dist.barrier()
+        try:
+            us = _time_graph(lambda: stack.step(ids), reps=10, warm=3)
+            graph = True
+        except Exception:  # a collective that cannot be captured: time eager steps
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            for _ in range(3):
+                stack.step(ids)
+            a.record()
+            for _ in range(10):
+                stack.step(ids)
+            b.record()
+            torch.cuda.synchronize()
+            us, graph = a.elapsed_time(b) * 1e3 / 10, False
+        us = _max_over_ranks(us, dev, dist)
+        out[f"decode_batch{batch}"] = {"tokens_per_s": round(batch / (us * 1e-6), 1), "ms_per_step": round(us / 1e3, 4), "cuda_graph": graph}
+    del stack
+    torch.cuda.empty_cache()
+    # trellis-coded linears, random code bits (the kernels' speed does not depend on the bit values)
+    shapes = [("qkv", 8192, 10240, SHARD_COLUMN), ("o", 8192, 8192, SHARD_ROW), ("gate_up", 8192, 57344, SHARD_COLUMN),
+              ("down", 28672, 8192, SHARD_ROW)]
+    m = 16
+    lins = []
+    for idx, (name, k, n, kind) in enumerate(shapes):
+        g = torch.Generator(device="cpu").manual_seed(4000 + idx)
+        packed = torch.randint(0, 256, (formats.packed_bytes(ttq.FMT_TQ3, n, k),), generator=g, dtype=torch.uint8)
+        sc = (torch.randn(n, generator=g) * 0.015).to(torch.float16)
+        packed[n * k * 3 // 8: n * k * 3 // 8 + 2 * n] = sc.view(torch.uint8)
+        local, nl, kl = tp.shard_trellis(packed, n, k, kind, rank, world)
+        lin = ttq.QuantLinear(ctx, ttq.FMT_TQ3, local.contiguous().to(dev), kl, out_features=nl)
+        x = torch.randn(m, kl, device=dev).to(torch.bfloat16)
+        lins.append((kind, lin, x))
+
+    def trellis_step():
+        for kind, lin, x in lins:
+            if kind == SHARD_ROW:
+                lin.forward_reduce(x)
+            else:
+                lin.forward(x)
+
+    dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(3):
+        trellis_step()
+    a.record()
+    for _ in range(10):
+        trellis_step()
+    b.record()
+    torch.cuda.synchronize()
+    us = _max_over_ranks(a.elapsed_time(b) * 1e3 / 10, dev, dist)
+    out["trellis_m16_llama70b_layer"] = {"us_per_layer": round(us, 1), "shapes_k_to_n": [[k, n] for _, k, n, _ in shapes]}
+    ctx.check_device_status()
+    return out
+
+
+def _peaks():
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        return {}
+
+
+def _measured_traffic(key: str):
+    """DRAM read + write bytes per launch from the committed ncu capture of this kernel (a `key = bytes` line of
+    profiles/ncu_traffic.txt, written when the capture is summarised); None when no capture covers the case."""
+    try:
+        for ln in open(os.path.join(ROOT, "profiles", "ncu_traffic.txt")):
+            ln = ln.split("#", 1)[0].strip()
+            if "=" in ln:
+                name, val = (t.strip() for t in ln.split("=", 1))
+                if name == key:
+                    return int(float(val))
+    except Exception:
+        pass
+    return None
 
 
 def decode_arm(args):
@@ -448,7 +613,7 @@ def decode_arm(args):
     if world > 1 and not args.nccl_allreduce:
         from tattletale_b200 import tp
 
-        comm = tp.Communicator(ctx, n_cap=cfg.hidden, m_cap=4)
+        comm = tp.Communicator(ctx, n_cap=cfg.hidden, m_cap=16)
     stack = DecoderStack(ctx, cfg, args.batch, rank, world, comm=comm, fused_glue=not args.torch_glue)
     g = torch.Generator(device=dev).manual_seed(3100)
     ids = torch.randint(0, cfg.vocab, (args.batch,), generator=g, device=dev)
@@ -763,7 +928,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--nccl-allreduce", action="store_true", help="N > 1: use NCCL for the row-parallel sums instead of the fused exchange")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
-    ap.add_argument("--no-sweep", action="store_true", help="skip the M = 4..2048 sweep on layer 0")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the M = 2..2048 sweep")
+    ap.add_argument("--no-decode-stack", action="store_true", help="skip the decoder-stack tokens/s numbers of the default line")
     ap.add_argument("--layers", type=int, default=32,
                     help="layers in the pass (default 32; smaller values are for profiler captures only)")
     args = ap.parse_args()

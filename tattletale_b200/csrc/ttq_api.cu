@@ -23,7 +23,10 @@ struct ttq_ctx {
     void *xq_base;
     int sms;          // multiprocessor count of the device
     int *dev_status;  // device word the kernels OR failure bits into (bit 0: a bounded wait gave up)
-    int *host_status; // pinned host copy of it, filled by the host entry points
+    int *host_status; // pinned, device-mapped host words: [0] raised by a failing kernel (see report_failure), [1] copy of the status word
+    // device mappings of the page-locked host buffers most recently passed to the host entry points
+    struct { const void *host; void *dev; } map_cache[8];
+    int map_next;
     unsigned long long *trace;  // device timeline buffer, allocated only when TTQ_TRACE=1 is set at init
     float *tq_x1, *tq_y1;       // TQ3: rotated activations [TQ3_SLAB][K] and raw results [TQ3_SLAB][N] (fp32; x1 also
     int64_t tq_x1_cap, tq_y1_cap;  //   holds the fp16 form for the GEMM); capacities in floats, grown at weight creation
@@ -47,8 +50,8 @@ struct ttq_ctx {
 struct ttq_comm {
     ttq_ctx *ctx;
     CommView view;
-    void *local;    // this rank's buffer (flags + data), exported through CUDA IPC
-    size_t bytes, flag_bytes;
+    void *local;    // this rank's buffer of {value, epoch} cells, exported through CUDA IPC
+    size_t bytes;
     void *peer_map[TTQ_MAX_RANKS];  // IPC mappings of the peers' buffers (nullptr for the own rank)
 };
 
@@ -290,7 +293,14 @@ ttq_status ttq_init(int device, ttq_ctx **out) {
     cudaError_t e = cudaMalloc(&ctx->xq_base, planes_b + s16_b + s32_b + sx_b);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->dev_status, 1024);  // status word, then 768 zero bytes
     if (e == cudaSuccess) e = cudaMemset(ctx->dev_status, 0, 1024);
-    if (e == cudaSuccess) e = cudaMallocHost(&ctx->host_status, sizeof(int));
+    if (e == cudaSuccess) e = cudaHostAlloc(&ctx->host_status, 2 * sizeof(int), cudaHostAllocMapped);
+    if (e == cudaSuccess) {
+        // words 2..3 of the status area: device-visible address of the host flag
+        ctx->host_status[0] = ctx->host_status[1] = 0;
+        void *flag_dev = nullptr;
+        e = cudaHostGetDevicePointer(&flag_dev, ctx->host_status, 0);
+        if (e == cudaSuccess) e = cudaMemcpy(ctx->dev_status + 2, &flag_dev, sizeof(void *), cudaMemcpyHostToDevice);
+    }
     const char *tr = getenv("TTQ_TRACE");
     if (e == cudaSuccess && tr && tr[0] == '1') {
         const size_t tb = (size_t)(8 + 8 * TTQ_TRACE_ENTRIES) * sizeof(unsigned long long);
@@ -622,13 +632,19 @@ ttq_status ttq_linear_forward_host(ttq_ctx *ctx, const ttq_weight *w, const void
     void *y_map = nullptr;
     bool direct = xb + yb + bbytes <= (1u << 20);
     if (direct) {
-        auto mapped = [](const void *p) -> void * {
+        // the driver query costs about a microsecond per pointer: buffers that come back call after call are remembered
+        auto mapped = [ctx](const void *p) -> void * {
+            for (auto &c : ctx->map_cache)
+                if (c.host == p) return c.dev;
             cudaPointerAttributes at;
             if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
                 cudaGetLastError();
                 return nullptr;
             }
-            return at.type == cudaMemoryTypeHost ? at.devicePointer : nullptr;
+            if (at.type != cudaMemoryTypeHost) return nullptr;
+            ctx->map_cache[ctx->map_next] = {p, at.devicePointer};
+            ctx->map_next = (ctx->map_next + 1) % 8;
+            return at.devicePointer;
         };
         x_map = mapped(x_host);
         y_map = mapped(y_host);
@@ -647,11 +663,13 @@ ttq_status ttq_linear_forward_host(ttq_ctx *ctx, const ttq_weight *w, const void
         if (s != TTQ_OK) return s;
         TTQ_CUDA(ctx, cudaMemcpyAsync(y_host, ctx->stage_y, yb, cudaMemcpyDeviceToHost, st));
     }
-    // the status word rides along with the result: one synchronisation per call
-    TTQ_CUDA(ctx, cudaMemcpyAsync(ctx->host_status, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, st));
+    // one synchronisation per call; a kernel that gave up a wait has raised the mapped host flag by then
     TTQ_CUDA(ctx, cudaStreamSynchronize(st));
-    if (*ctx->host_status != 0) {
-        const int seen = *ctx->host_status;
+    if (*reinterpret_cast<volatile int *>(ctx->host_status) != 0) {
+        ctx->host_status[0] = 0;
+        TTQ_CUDA(ctx, cudaMemcpyAsync(ctx->host_status + 1, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, st));
+        TTQ_CUDA(ctx, cudaStreamSynchronize(st));
+        const int seen = ctx->host_status[1];
         cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), st);
         cudaMemsetAsync(ctx->split_counters, 0, (size_t)ctx->split_counters_cap * sizeof(unsigned), st);
         return fail(ctx, TTQ_ERR_TIMEOUT, "a kernel gave up a bounded wait (status word 0x%x); results of that call are invalid", seen);
@@ -665,6 +683,7 @@ ttq_status ttq_device_status(ttq_ctx *ctx, void *stream) {
     TTQ_CUDA(ctx, cudaMemcpyAsync(&host, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     TTQ_CUDA(ctx, cudaStreamSynchronize((cudaStream_t)stream));
     if (host != 0) {
+        ctx->host_status[0] = 0;
         cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), (cudaStream_t)stream);
         // a kernel that gave up may have left K-split arrival counters behind
         cudaMemsetAsync(ctx->split_counters, 0, (size_t)ctx->split_counters_cap * sizeof(unsigned), (cudaStream_t)stream);
@@ -688,8 +707,7 @@ ttq_status ttq_comm_create(ttq_ctx *ctx, int rank, int world, int64_t n_cap, int
     c->ctx = ctx;
     const int64_t nt_cap = (n_cap + TILE_ROWS - 1) / TILE_ROWS;
     n_cap = nt_cap * TILE_ROWS;
-    c->flag_bytes = ((size_t)world * nt_cap * sizeof(uint32_t) + 255) & ~(size_t)255;
-    c->bytes = c->flag_bytes + (size_t)2 * world * m_cap * n_cap * sizeof(float);
+    c->bytes = (size_t)2 * world * m_cap * n_cap * sizeof(uint2);
     cudaError_t e = cudaMalloc(&c->local, c->bytes);
     if (e == cudaSuccess) e = cudaMemset(c->local, 0, c->bytes);
     if (e == cudaSuccess) e = cudaMalloc(&c->view.sent, (size_t)nt_cap * sizeof(uint32_t));
@@ -723,8 +741,7 @@ ttq_status ttq_comm_connect(ttq_comm *c, const void *all_handles) {
             TTQ_CUDA(ctx, cudaIpcOpenMemHandle(&c->peer_map[r], h[r], cudaIpcMemLazyEnablePeerAccess));
             base = c->peer_map[r];
         }
-        c->view.flags[r] = reinterpret_cast<uint32_t *>(base);
-        c->view.data[r] = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(base) + c->flag_bytes);
+        c->view.cells[r] = reinterpret_cast<uint2 *>(base);
     }
     return TTQ_OK;
 }
@@ -743,8 +760,7 @@ ttq_status ttq_comm_connect_pointers(ttq_comm *c, void *const *bases) {
         void *base = r == c->view.rank ? c->local : bases[r];
         if (!base) return fail(ctx, TTQ_ERR_INVALID_ARG, "exchange buffer of rank %d is NULL", r);
         if (reinterpret_cast<uintptr_t>(base) & 255) return fail(ctx, TTQ_ERR_INVALID_ARG, "exchange buffer of rank %d is not 256-byte aligned", r);
-        c->view.flags[r] = reinterpret_cast<uint32_t *>(base);
-        c->view.data[r] = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(base) + c->flag_bytes);
+        c->view.cells[r] = reinterpret_cast<uint2 *>(base);
     }
     return TTQ_OK;
 }
@@ -774,7 +790,7 @@ ttq_status ttq_linear_forward_allreduce(ttq_ctx *ctx, const ttq_weight *w, const
     if (!ctx) return TTQ_ERR_INVALID_ARG;
     if (!w || !comm) return fail(ctx, TTQ_ERR_INVALID_ARG, "weight or communicator is NULL");
     if (w->ctx != ctx || comm->ctx != ctx) return fail(ctx, TTQ_ERR_INVALID_ARG, "weight or communicator belongs to another context");
-    if (comm->view.flags[comm->view.world - 1] == nullptr) return fail(ctx, TTQ_ERR_INVALID_ARG, "communicator is not connected");
+    if (comm->view.cells[comm->view.world - 1] == nullptr) return fail(ctx, TTQ_ERR_INVALID_ARG, "communicator is not connected");
     if (M < 0) return fail(ctx, TTQ_ERR_SHAPE, "M=%lld is negative", (long long)M);
     if (M == 0) return TTQ_OK;
     if (!x_dev || !y_dev) return fail(ctx, TTQ_ERR_INVALID_ARG, "x or y pointer is NULL");

@@ -36,7 +36,7 @@ constexpr int WAIT_LIMIT = 1 << 20;
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int *status) {
     for (int i = 0; i < WAIT_LIMIT; i++)
         if (mbar_try_wait(bar, parity)) return true;
-    atomicOr(status, 1);
+    report_failure(status, 1);
     return false;
 }
 __device__ __forceinline__ void named_barrier(int id, int nthreads) {

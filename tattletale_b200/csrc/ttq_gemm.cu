@@ -65,7 +65,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int *status) {
     for (int i = 0; i < GEMM_WAIT_LIMIT; i++)
         if (mbar_try_wait(bar, parity)) return true;
-    atomicOr(status, 2);
+    report_failure(status, 2);
     return false;
 }
 // Warp-wide form: lane 0 polls, the others park at the warp barrier (fewer shared-memory polls next to the

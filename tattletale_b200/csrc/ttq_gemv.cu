@@ -148,11 +148,20 @@ __global__ void __launch_bounds__(GEMV_THREADS) xprep_kernel(const void *__restr
                                                              XqView xq, unsigned long long *trace, int gated) {
     unsigned long long *te = trace_open(trace, 1);
     grid_launch_dependents();
-    grid_dependency_wait();  // the scratch planes may still be read by the preceding kernel
-    if (te) te[2] = global_ns();
     const int lane = threadIdx.x & 31;
     const int64_t Kp = SBp * TILE_K;
     const int64_t unit = (int64_t)blockIdx.x * GEMV_WARPS + (threadIdx.x >> 5);
+    // Pull this warp's 512 bytes of x into L2 before the wait (a hint: L2 is the coherence point, so a line the
+    // preceding kernel has yet to write is still read correctly afterwards); with cold activations this takes
+    // their DRAM latency off the path behind the wait.
+    if (unit < M * SBp && x_dt != TTQ_DT_F32) {
+        const int64_t pm = unit / SBp, psb = unit % SBp;
+        const uint8_t *line = reinterpret_cast<const uint8_t *>(x) + (pm * ldx + psb * TILE_K) * 2 + (lane & 3) * 128;
+        if (lane < (gated ? 8 : 4) && psb * TILE_K + (lane & 3) * 64 < K)  // only lines that start inside the row
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(line + (lane >> 2) * K * 2));
+    }
+    grid_dependency_wait();  // the scratch planes may still be read by the preceding kernel
+    if (te) te[2] = global_ns();
     if (unit >= Mpad * SBp) return;
     const int64_t m = unit / SBp;
     const int sb = (int)(unit % SBp);
@@ -648,59 +657,22 @@ __global__ void __launch_bounds__(NW * 32, NW > 8 ? 1 : (XSRC == XSRC_GLOBAL ? 2
                     }
                 }
             } else {
-                // Row-parallel linear: the partial sums of this row tile are pushed into every rank's buffer over
-                // NVLink (plain peer stores), a per-row-tile counter tells the peers they have landed, and every
-                // rank adds the partials of all ranks in rank order -- the all-reduce happens here, tile by tile,
-                // while other warps are still streaming weights.
-                const uint32_t epoch = cm.sent[rt] + 1u;  // exchanges are counted per row tile; all ranks agree
-                const size_t slab = (size_t)cm.m_cap * cm.n_cap;
-                const size_t par_off = (size_t)(epoch & 1u) * cm.world * slab;
-                for (int o = lane; o < MP * TILE_ROWS; o += 32) {
-                    const int row = o & 15, mm = o >> 4;
-                    const int64_t n = rt * TILE_ROWS + row;
-                    if (mm < M && n < a.N) {
+                // Row-parallel linear: the all-reduce happens here, tile by tile, over peer memory, while other warps
+                // are still streaming weights.
+                exchange_row_tile(
+                    cm, rt, M, a.N, lane, p.status,
+                    [&](int o) {
                         float acc = 0.f;
                         for (int w = 0; w < WK; w++) {
                             const float *rw = red_s + (grp * WK + w) * (2 * MP * TILE_ROWS);
                             acc += rw[o] - rw[MP * TILE_ROWS + o];
                         }
-                        const size_t off = par_off + (size_t)cm.rank * slab + (size_t)mm * cm.n_cap + n;
-                        for (int q = 0; q < cm.world; q++) __stcg(cm.data[q] + off, acc);
-                    }
-                }
-                // the warp barrier orders every lane's pushes before the release stores of the counter lanes
-                __syncwarp();
-                if (lane < cm.world) {
-                    uint32_t *peer_flag = cm.flags[lane] + (size_t)cm.rank * cm.nt_cap + rt;
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_flag), "r"(epoch) : "memory");
-                }
-                bool ok = true;
-                if (lane < cm.world) {
-                    const uint32_t *my_flag = cm.flags[cm.rank] + (size_t)lane * cm.nt_cap + rt;
-                    int spins = 0;
-                    uint32_t seen;
-                    do {
-                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(my_flag) : "memory");
-                        if (++spins > cm.wait_limit) {  // bounded: give up, flag the failure, keep going
-                            ok = false;
-                            break;
-                        }
-                    } while ((int32_t)(seen - epoch) < 0);
-                }
-                if (!__all_sync(0xffffffffu, ok) && lane == 0) atomicOr(p.status, 4);
-                const float *mine = cm.data[cm.rank] + par_off;
-                for (int o = lane; o < MP * TILE_ROWS; o += 32) {
-                    const int row = o & 15, mm = o >> 4;
-                    const int64_t n = rt * TILE_ROWS + row;
-                    if (mm < M && n < a.N) {
-                        float acc = 0.f;
-                        for (int q = 0; q < cm.world; q++) acc += __ldcv(mine + (size_t)q * slab + (size_t)mm * cm.n_cap + n);
-                        if (a.bias != nullptr) acc += load_as_float(a.bias, a.bias_dt, n);
-                        store_from_float(a.y, a.y_dt, mm * a.ldy + n, acc);
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) cm.sent[rt] = epoch;
+                        return acc;
+                    },
+                    [&](int mm, int64_t n, float v) {
+                        if (a.bias != nullptr) v += load_as_float(a.bias, a.bias_dt, n);
+                        store_from_float(a.y, a.y_dt, mm * a.ldy + n, v);
+                    });
             }
         }
         if (WK > 1) named_barrier(1 + grp, WK * 32);  // the partial-sum area is free again

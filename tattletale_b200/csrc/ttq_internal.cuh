@@ -88,20 +88,19 @@ struct XqView {
     float *sx;        // [Mpad][SBp]
 };
 
-// Peer-memory exchange area of a row-parallel linear (tensor parallelism).  Passed by value to the
-// decode kernel; world <= 1 means "no exchange".  Every rank owns one buffer holding
-//   flags [world][nt_cap] u32   slot [src][rt]: how many exchanges rank src has completed for row tile rt
-//   data  [2][world][m_cap][n_cap] f32   partial outputs pushed by rank src, double-buffered by exchange parity
-// and knows the base addresses of all ranks' buffers (its own and the peers' IPC mappings).
+// Peer-memory exchange area of a row-parallel linear (tensor parallelism).  Passed by value to the decode
+// kernels; world <= 1 means "no exchange".  Every rank owns one buffer of 8-byte cells {value bits, epoch},
+//   cells [2][world][m_cap][n_cap]   partial outputs pushed by rank src, double-buffered by exchange parity,
+// and knows the base addresses of all ranks' buffers (its own and the peers' mappings).  A cell is written with
+// ONE 8-byte store, so the value and the epoch that validates it arrive together: no fence, no separate flag.
 constexpr int TTQ_MAX_RANKS = 8;
 struct CommView {
     int rank, world;
     int nt_cap, m_cap;
-    int wait_limit;                  // polls of a peer's counter before the wait is given up (status bit 2)
+    int wait_limit;                  // polls of a peer's cell before the wait is given up (status bit 2)
     int64_t n_cap;
     uint32_t *sent;                  // local [nt_cap]: exchanges this rank has completed per row tile
-    uint32_t *flags[TTQ_MAX_RANKS];  // flag array of every rank
-    float *data[TTQ_MAX_RANKS];      // partial-output buffer of every rank
+    uint2 *cells[TTQ_MAX_RANKS];     // exchange buffer of every rank
 };
 
 struct LinearArgs {
@@ -117,6 +116,66 @@ struct LinearArgs {
     int64_t ldy;
     bool gated = false;  // x rows hold 2K values [gate | up]; the operand is silu(gate[k]) * up[k]
 };
+
+// ---- failure reporting --------------------------------------------------------------------------------------
+// A kernel that gives up a bounded wait ORs a bit into the status word it was given (bit 0: copy ring, bit 1:
+// tensor-core pipeline, bit 2: peer exchange) and, when the two words behind it hold the address of a mapped host
+// flag, raises that flag too, so that a host entry point learns of the failure from its own memory without a
+// device-to-host copy on every call.  The static scratch array keeps those two words zero: no host flag.
+__device__ __forceinline__ void report_failure(int *status, int bit) {
+    atomicOr(status, bit);
+    volatile int *host_flag = *reinterpret_cast<volatile int *volatile *>(status + 2);
+    if (host_flag != nullptr) *host_flag = 1;
+}
+
+// ---- row-parallel exchange --------------------------------------------------------------------------------
+// One 16-row tile of a row-parallel linear, called by a full warp: `value(o)` is this rank's partial sum of output
+// o = m * 16 + row.  Every lane pushes its outputs into the cells of ALL ranks (its own included) with single
+// 8-byte stores {value, epoch}, then polls -- bounded -- its own buffer until the cells of every rank carry this
+// exchange's epoch and adds them in rank order, so all ranks end with bit-identical sums.  The epoch counts the
+// exchanges of the row tile (all ranks issue the same sequence of calls); two parities of cells alternate, so a
+// rank that runs one exchange ahead never overwrites cells a slower rank has yet to read.
+template <class ValueFn, class StoreFn>
+__device__ __forceinline__ void exchange_row_tile(const CommView &cm, int64_t rt, int M, int64_t N, int lane, int *status, ValueFn &&value,
+                                                  StoreFn &&store) {
+    const uint32_t epoch = cm.sent[rt] + 1u;
+    const size_t slab = (size_t)cm.m_cap * cm.n_cap;
+    const size_t par_off = (size_t)(epoch & 1u) * cm.world * slab;
+    const int outs = M * TILE_ROWS;
+    for (int o = lane; o < outs; o += 32) {
+        const int row = o & 15, mm = o >> 4;
+        const int64_t n = rt * TILE_ROWS + row;
+        if (n < N) {
+            const uint32_t bits = __float_as_uint(value(o));
+            const size_t off = par_off + (size_t)cm.rank * slab + (size_t)mm * cm.n_cap + n;
+            for (int q = 0; q < cm.world; q++)
+                asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(cm.cells[q] + off), "r"(bits), "r"(epoch) : "memory");
+        }
+    }
+    bool ok = true;
+    const uint2 *mine = cm.cells[cm.rank] + par_off;
+    for (int o = lane; o < outs; o += 32) {
+        const int row = o & 15, mm = o >> 4;
+        const int64_t n = rt * TILE_ROWS + row;
+        if (n < N) {
+            float acc = 0.f;
+            for (int q = 0; q < cm.world; q++) {
+                const uint2 *cell = mine + (size_t)q * slab + (size_t)mm * cm.n_cap + n;
+                uint32_t bits = 0, seen = epoch - 1u;
+                for (int spins = 0; ok; spins++) {
+                    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits), "=r"(seen) : "l"(cell) : "memory");
+                    if (seen == epoch) break;
+                    if (spins >= cm.wait_limit) ok = false;  // bounded: give up, flag the failure, keep going
+                }
+                acc += __uint_as_float(bits);
+            }
+            store(mm, n, acc);
+        }
+    }
+    if (!__all_sync(0xffffffffu, ok) && lane == 0) report_failure(status, 4);
+    __syncwarp();
+    if (lane == 0) cm.sent[rt] = epoch;
+}
 
 // ---- programmatic dependent launch ---------------------------------------------------------------------
 // Kernels of a decode chain are launched with programmatic stream serialization: a kernel tells the scheduler

@@ -631,55 +631,12 @@ __global__ void __launch_bounds__(B::THREADS, B::MIN_CTAS) q4k_decode_kernel(QmP
                             }
                         }
                     } else {
-                        // Row-parallel linear: the sums of this row tile are pushed into every rank's buffer over NVLink
-                        // (plain peer stores), a per-row-tile counter tells the peers they have landed, and every rank adds
-                        // the partials of all ranks in rank order -- the all-reduce happens here, tile by tile, while other
+                        // Row-parallel linear: the all-reduce happens here, tile by tile, over peer memory, while other
                         // warps are still streaming weights.
-                        const uint32_t epoch = cm.sent[rt] + 1u;  // exchanges are counted per row tile; all ranks agree
-                        const size_t slab = (size_t)cm.m_cap * cm.n_cap;
-                        const size_t par_off = (size_t)(epoch & 1u) * cm.world * slab;
-                        for (int o = lane; o < outs; o += 32) {
-                            const int row = o & 15, mm = o >> 4;
-                            const int64_t n = rt * TILE_ROWS + row;
-                            if (n < a.N) {
-                                const float v = full_sum(o);
-                                const size_t off = par_off + (size_t)cm.rank * slab + (size_t)mm * cm.n_cap + n;
-                                for (int q = 0; q < cm.world; q++) __stcg(cm.data[q] + off, v);
-                            }
-                        }
-                        // the warp barrier orders every lane's pushes before the release stores of the counter lanes
-                        __syncwarp();
-                        if (lane < cm.world) {
-                            uint32_t *peer_flag = cm.flags[lane] + (size_t)cm.rank * cm.nt_cap + rt;
-                            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_flag), "r"(epoch) : "memory");
-                        }
-                        bool ok = true;
-                        if (lane < cm.world) {
-                            const uint32_t *my_flag = cm.flags[cm.rank] + (size_t)lane * cm.nt_cap + rt;
-                            int spins = 0;
-                            uint32_t seen;
-                            do {
-                                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(my_flag) : "memory");
-                                if (++spins > cm.wait_limit) {  // bounded: give up, flag the failure, keep going
-                                    ok = false;
-                                    break;
-                                }
-                            } while ((int32_t)(seen - epoch) < 0);
-                        }
-                        if (!__all_sync(0xffffffffu, ok) && lane == 0) atomicOr(p.status, 4);
-                        const float *mine_rx = cm.data[cm.rank] + par_off;
-                        for (int o = lane; o < outs; o += 32) {
-                            const int row = o & 15, mm = o >> 4;
-                            const int64_t n = rt * TILE_ROWS + row;
-                            if (n < a.N) {
-                                float v = 0.f;
-                                for (int q = 0; q < cm.world; q++) v += __ldcv(mine_rx + (size_t)q * slab + (size_t)mm * cm.n_cap + n);
-                                if (a.bias != nullptr) v += load_as_float(a.bias, a.bias_dt, n);
-                                store_from_float(a.y, a.y_dt, mm * a.ldy + n, v);
-                            }
-                        }
-                        __syncwarp();
-                        if (lane == 0) cm.sent[rt] = epoch;
+                        exchange_row_tile(cm, rt, M, a.N, lane, p.status, full_sum, [&](int mm, int64_t n, float v) {
+                            if (a.bias != nullptr) v += load_as_float(a.bias, a.bias_dt, n);
+                            store_from_float(a.y, a.y_dt, mm * a.ldy + n, v);
+                        });
                     }
                 }
             }

@@ -106,15 +106,11 @@ class DecoderStack:
             return lin.forward(x)
         if self.comm is not None:
             return lin.forward_allreduce(x, self.comm)
-        import torch.distributed as dist
-
-        y = lin.forward(x)
-        dist.all_reduce(y)
-        return y
+        return lin.forward_reduce(x)
 
     def _step_fused(self, token_ids: torch.Tensor) -> torch.Tensor:
         """The layer loop with the library's decode-step kernels: 9 launches per layer besides the linears' own."""
-        cfg, B, d, ctx = self.cfg, self.batch, self.cfg.head_dim, self.ctx
+        cfg, B, d, ctx = self.cfg, token_ids.shape[0], self.cfg.head_dim, self.ctx  # any batch up to the one the caches hold
         h = self.emb_rows[token_ids].contiguous()
         delta = None
         for L in self.layers:
@@ -135,7 +131,7 @@ class DecoderStack:
         """One decode step for `batch` sequences at position context-1; returns next token ids."""
         if self.fused_glue:
             return self._pick(self.lm_head.forward(self._step_fused(token_ids), out_dtype=torch.float32))
-        cfg, B, d = self.cfg, self.batch, self.cfg.head_dim
+        cfg, B, d = self.cfg, token_ids.shape[0], self.cfg.head_dim
         h = self.emb_rows[token_ids]
         for L in self.layers:
             x = self._rms(h, L["attn_norm"])
@@ -144,9 +140,9 @@ class DecoderStack:
             k = qkv[:, self.hq * d:(self.hq + self.hkv) * d].view(B, self.hkv, 1, d)
             v = qkv[:, (self.hq + self.hkv) * d:].view(B, self.hkv, 1, d)
             q, k = self._rope(q), self._rope(k)
-            L["k"][:, :, self.pos:self.pos + 1] = k
-            L["v"][:, :, self.pos:self.pos + 1] = v
-            att = torch.nn.functional.scaled_dot_product_attention(q, L["k"], L["v"], enable_gqa=True)
+            L["k"][:B, :, self.pos:self.pos + 1] = k
+            L["v"][:B, :, self.pos:self.pos + 1] = v
+            att = torch.nn.functional.scaled_dot_product_attention(q, L["k"][:B], L["v"][:B], enable_gqa=True)
             o = self._row_parallel(L["o"], att.reshape(B, self.hq * d))
             h = h + o
             x = self._rms(h, L["mlp_norm"])

@@ -128,7 +128,7 @@ class QuantLinear:
         return out
 
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out: Optional[torch.Tensor] = None, use_bias: bool = True) -> torch.Tensor:
         if not x.is_cuda:
             raise TtqError(1, "x must live on the context's CUDA device (use forward_host for host buffers)")
         if x.shape[-1] != self.in_features:
@@ -142,7 +142,7 @@ class QuantLinear:
         if out is None:
             out = torch.empty((m, self.out_features), dtype=odt, device=x.device)
         y2 = out.reshape(-1, self.out_features)
-        b = self.bias
+        b = self.bias if use_bias else None
         st = self.ctx._lib.ttq_linear_forward(
             self.ctx.handle, self.handle, x2.data_ptr(), _dt(x2.dtype), m, x2.stride(0) if m > 1 else self.in_features,
             None if b is None else b.data_ptr(), _lib.DT_F32 if b is None else _dt(b.dtype),
@@ -183,11 +183,7 @@ class QuantLinear:
         if out is None:
             out = torch.empty((m, self.out_features), dtype=odt, device=x.device)
         if m > comm.m_cap or self.out_features > comm.n_cap:
-            import torch.distributed as dist
-
-            self.forward(x, out=out)
-            dist.all_reduce(out)
-            return out.reshape(*x.shape[:-1], self.out_features)
+            return self.forward_reduce(x, getattr(comm, "group", None), out=out)
         if x2.stride(-1) != 1:
             x2 = x2.contiguous()
         y2 = out.reshape(-1, self.out_features)
@@ -197,6 +193,21 @@ class QuantLinear:
             None if b is None else b.data_ptr(), _lib.DT_F32 if b is None else _dt(b.dtype),
             y2.data_ptr(), _dt(y2.dtype), y2.stride(0) if m > 1 else self.out_features, comm.handle, _stream_ptr(x.device))
         check(self.ctx.handle, st)
+        return out.reshape(*x.shape[:-1], self.out_features)
+
+    def forward_reduce(self, x: torch.Tensor, group=None, out_dtype: Optional[torch.dtype] = None,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Row-parallel forward through a library all-reduce: the rank's partial product without the bias, summed over
+        ``group`` in fp32, the bias added once after the sum (what the fused exchange does inside the kernel)."""
+        import torch.distributed as dist
+
+        part = self.forward(x, out_dtype=torch.float32, use_bias=False)
+        dist.all_reduce(part, group=group)
+        if self.bias is not None:
+            part += self.bias.to(torch.float32)
+        if out is None:
+            return part.to(out_dtype or x.dtype)
+        out.reshape(part.shape).copy_(part)
         return out.reshape(*x.shape[:-1], self.out_features)
 
     def forward_host(self, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:

@@ -61,6 +61,7 @@ class Communicator:
         from ._lib import check
 
         self.ctx = ctx
+        self.group = group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.m_cap, self.n_cap = m_cap, n_cap
         lib = ctx._lib

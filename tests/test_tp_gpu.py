@@ -32,10 +32,11 @@ def _worker(rank, world, port, out):
     blocks = oracle.quantize(oracle.Q4_K, rng.normal(0, 0.02, (N, K)).astype(np.float32))
     bias = torch.from_numpy(rng.normal(0, 0.1, N).astype(np.float32)).cuda()
     lin = ttq.QuantLinear(ctx, ttq.FMT_Q4_K, torch.from_numpy(blocks), K, bias=bias, shard=(ttq.SHARD_ROW, rank, world))
-    comm = tp.Communicator(ctx, n_cap=N, m_cap=4)
+    comm = tp.Communicator(ctx, n_cap=N, m_cap=16)
     kl = K // world
     errs, agree = [], []
-    for call, m in enumerate((1, 4, 2, 1, 3)):  # consecutive exchanges reuse both parities of the buffers
+    # consecutive exchanges reuse both parities of the buffers; 1..2 rows: integer decode kernel, 3..16: fp16 kernel
+    for call, m in enumerate((1, 4, 2, 1, 3, 16, 9, 1)):
         x = torch.from_numpy(rng.normal(0, 1, (m, K)).astype(np.float32)).to(torch.bfloat16)
         y = lin.forward_allreduce(x[:, rank * kl:(rank + 1) * kl].cuda(), comm, out_dtype=torch.float32)
         ctx.check_device_status()
@@ -45,10 +46,10 @@ def _worker(rank, world, port, out):
         dist.all_gather(ys, y)
         agree.append(all(torch.equal(ys[0], t) for t in ys))
     # a batch larger than the exchange buffer falls back to forward + library all-reduce
+    # (the bias stays on: the fallback must add it once, after the sum over ranks)
     x = torch.from_numpy(rng.normal(0, 1, (24, K)).astype(np.float32)).to(torch.bfloat16)
-    lin.bias = None
     y = lin.forward_allreduce(x[:, rank * kl:(rank + 1) * kl].cuda(), comm, out_dtype=torch.float32)
-    want = oracle.linear(oracle.Q4_K, blocks, x.view(torch.int16).numpy().view(np.uint16), oracle.BF16)
+    want = oracle.linear(oracle.Q4_K, blocks, x.view(torch.int16).numpy().view(np.uint16), oracle.BF16, bias.cpu().numpy())
     errs.append(float(np.linalg.norm(y.cpu().numpy() - want) / np.linalg.norm(want)))
     if rank == 0:
         out["errs"], out["agree"] = errs, agree
