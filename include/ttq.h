@@ -53,7 +53,7 @@ typedef enum ttq_status {
     TTQ_ERR_OOM = 5,         /* device or host allocation failed */
     TTQ_ERR_DEVICE = 6,      /* no sm_100 device / wrong device current */
     TTQ_ERR_LIMIT = 7,       /* request exceeds a fixed capacity (scratch, static buffers) */
-    TTQ_ERR_TIMEOUT = 8      /* a kernel gave up a bounded wait on its copy pipeline; results invalid */
+    TTQ_ERR_TIMEOUT = 8      /* a kernel gave up a bounded wait (copy pipeline, tensor-core pipeline, absent peer); results invalid */
 } ttq_status;
 
 typedef enum ttq_format {
@@ -143,7 +143,11 @@ TTQ_API ttq_status ttq_dequantize(ttq_ctx *ctx, const ttq_weight *w, float *dev_
 
 /* y[m][n] = sum_k x[m][k] * W[n][k] (+ bias[n]).  x: bf16 or f16 device matrix; bias: NULL or a
  * device vector of N elements of bias_dt; y: f32, bf16 or f16 device matrix.  Any M >= 0.
- * Integer dot products are exact and scales are applied in fp32. */
+ * Decode batches use exact integer products with scales applied in fp32; larger batches expand the weights
+ * to fp16 for the tensor cores (fp32 accumulation).  Asynchronous on `stream`, allocates nothing: every
+ * scratch buffer was sized when the context and the weights were created -- so create ALL weights before
+ * capturing forwards into a CUDA graph (creating a larger Q8_0 / Q6_K / trellis weight later may move the
+ * context's expansion scratch, which an already captured graph would still address). */
 TTQ_API ttq_status ttq_linear_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_dev, ttq_dtype x_dt,
                               int64_t M, int64_t ldx, const void *bias_dev, ttq_dtype bias_dt,
                               void *y_dev, ttq_dtype y_dt, int64_t ldy, void *stream);
@@ -161,12 +165,13 @@ TTQ_API ttq_status ttq_linear_forward_host(ttq_ctx *ctx, const ttq_weight *w, co
 TTQ_API ttq_status ttq_device_status(ttq_ctx *ctx, void *stream);
 
 /* ---- row-parallel linear with the all-reduce fused in (tensor parallelism) --------------------
- * No reference counterpart (the reference has no parallelism).  One process per GPU.  For a ROW shard
- * the outputs of all ranks must be summed; for decode-size batches the sum is done inside the linear's
- * own kernel: every warp that finishes a 16-row tile pushes its partial sums into all ranks' exchange
- * buffers over NVLink (plain peer stores on CUDA-IPC mappings, no multicast), raises a per-tile counter
- * in the peers' memory, waits -- bounded -- for the peers' counters and adds the partials in rank
- * order, so every rank ends with the same full result in y.
+ * No reference counterpart (the reference has no parallelism).  One process per GPU (or one process driving
+ * several, see ttq_comm_connect_pointers).  For a ROW shard the outputs of all ranks must be summed; for
+ * decode-size batches the sum is done inside the linear's own kernel: the warp that finishes a 16-row tile
+ * writes its partial sums into the exchange buffers of ALL ranks over NVLink as single 8-byte stores of
+ * {value, epoch} (plain peer stores on mapped memory, no multicast, no fence, no separate flag: the epoch that
+ * validates a value arrives with it), then polls -- bounded -- its own buffer until every rank's cells carry
+ * this exchange's epoch and adds them in rank order, so every rank ends with the same full result in y.
  *   ttq_comm_create   allocates this rank's exchange buffer (sized for N <= n_cap, M <= m_cap <= 16) and
  *                     returns its 64-byte CUDA IPC handle in ipc_handle_out;
  *   ttq_comm_connect  takes the handles of ALL ranks (world x 64 bytes, in rank order; exchanged by the
@@ -175,8 +180,9 @@ TTQ_API ttq_status ttq_device_status(ttq_ctx *ctx, void *stream);
  *   ttq_linear_forward_allreduce  as ttq_linear_forward on the rank's ROW shard, y = sum over ranks
  *                     (+ bias, added once).  Every rank must issue the same sequence of calls.  Returns
  *                     TTQ_ERR_UNSUPPORTED when M or N exceed the buffer: fall back to ttq_linear_forward
- *                     plus a library all-reduce.  A peer that never arrives ends the wait after a fixed
- *                     number of polls and is reported as TTQ_ERR_TIMEOUT by ttq_device_status. */
+ *                     plus a library all-reduce.  A peer that never arrives ends the wait after a set
+ *                     number of polls (ttq_comm_set_wait_limit) and is reported as TTQ_ERR_TIMEOUT by
+ *                     ttq_device_status; the kernel returns and the context stays usable. */
 TTQ_API ttq_status ttq_comm_create(ttq_ctx *ctx, int rank, int world, int64_t n_cap, int m_cap, ttq_comm **out,
                                    void *ipc_handle_out);
 TTQ_API ttq_status ttq_comm_connect(ttq_comm *comm, const void *all_handles);
@@ -186,7 +192,7 @@ TTQ_API ttq_status ttq_comm_connect(ttq_comm *comm, const void *all_handles);
  * No reference counterpart. */
 TTQ_API ttq_status ttq_comm_local_buffer(ttq_comm *comm, void **base_out, size_t *bytes_out);
 TTQ_API ttq_status ttq_comm_connect_pointers(ttq_comm *comm, void *const *bases);
-/* Number of polls of a peer's counter after which the fused exchange gives up (default 2^22, a few
+/* Number of polls of a peer's cell after which the fused exchange gives up (default 2^22, a few
  * seconds); the give-up is reported as TTQ_ERR_TIMEOUT by ttq_device_status and the context stays usable.
  * No reference counterpart. */
 TTQ_API ttq_status ttq_comm_set_wait_limit(ttq_comm *comm, int64_t polls);

@@ -8,8 +8,7 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# TTQ_LIB selects another build of the same library (tuning experiments); default: the in-tree build
-LIB_PATH = os.environ.get("TTQ_LIB") or os.path.join(_HERE, "libttq.so")
+LIB_PATH = os.path.join(_HERE, "libttq.so")
 
 # enums of include/ttq.h
 FMT_Q8_0, FMT_Q4_K, FMT_Q6_K, FMT_TQ3 = 0, 1, 2, 3

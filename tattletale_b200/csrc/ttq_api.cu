@@ -560,7 +560,9 @@ static ttq_status linear_forward_impl(ttq_ctx *ctx, const ttq_weight *w, const v
         const int64_t n = v ? atoll(v) : 0;
         return n >= 1 ? n : 5;
     }();
-    if (M >= GEMM_MIN_M && use_gemm && gemm_supported(w->fmt)) {
+    // Q8_0 / Q6_K: the integer decode kernel serves 16 rows per pass; from 9 rows the fused tensor-core GEMM is used
+    const int64_t gemm_min_m = w->fmt == TTQ_FMT_Q4_K ? GEMM_MIN_M : (GEMM_MIN_M > 9 ? GEMM_MIN_M : 9);
+    if (M >= gemm_min_m && use_gemm && gemm_supported(w->fmt)) {
         // prefill / larger batches: tensor-core path
         a.x = x_dev; a.M = M; a.y = y_dev;
         int launches = 0;
@@ -1027,6 +1029,8 @@ ttq_status ttq_rope_kv_append(ttq_ctx *ctx, const void *qkv_dev, ttq_dtype dt, i
     if (dt != TTQ_DT_BF16 && dt != TTQ_DT_F16) return fail(ctx, TTQ_ERR_INVALID_ARG, "dtype must be bf16 or f16");
     if (ld_qkv < (int64_t)(hq + 2 * hkv) * d) return fail(ctx, TTQ_ERR_SHAPE, "ld_qkv smaller than (hq + 2 hkv) * d");
     if (pos < 0 || pos >= ctx_len) return fail(ctx, TTQ_ERR_SHAPE, "pos=%lld outside the cache of %lld positions", (long long)pos, (long long)ctx_len);
+    if ((((uintptr_t)qkv_dev) | ((uintptr_t)q_out_dev) | ((uintptr_t)k_cache_dev) | ((uintptr_t)v_cache_dev)) & 3)
+        return fail(ctx, TTQ_ERR_INVALID_ARG, "qkv, q_out and the caches must be 4-byte aligned");
     cudaError_t e = launch_rope_kv(qkv_dev, dt, B, ld_qkv, hq, hkv, d, cos_dev, sin_dev, q_out_dev, k_cache_dev, v_cache_dev, ctx_len, pos,
                                    (cudaStream_t)stream);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "rope_kv launch");
@@ -1046,7 +1050,8 @@ ttq_status ttq_decode_attention(ttq_ctx *ctx, const void *q_dev, const void *k_c
     if (dt != TTQ_DT_BF16 && dt != TTQ_DT_F16) return fail(ctx, TTQ_ERR_INVALID_ARG, "dtype must be bf16 or f16");
     if (n_ctx <= 0 || n_ctx > ctx_len) return fail(ctx, TTQ_ERR_SHAPE, "n_ctx=%lld outside 1..ctx_len=%lld", (long long)n_ctx, (long long)ctx_len);
     if (B > 65535 || hkv > 65535) return fail(ctx, TTQ_ERR_LIMIT, "B or hkv exceeds 65535");
-    if (((uintptr_t)k_cache_dev) & 15) return fail(ctx, TTQ_ERR_INVALID_ARG, "the K cache must be 16-byte aligned");
+    if ((((uintptr_t)k_cache_dev) | ((uintptr_t)v_cache_dev) | ((uintptr_t)q_dev) | ((uintptr_t)out_dev)) & 15)
+        return fail(ctx, TTQ_ERR_INVALID_ARG, "q, out and the K and V caches must be 16-byte aligned");
     if (decode_attention_scratch_floats(B, hq, n_ctx) > ctx->att_part_cap)
         return fail(ctx, TTQ_ERR_LIMIT, "B * hq * ceil(n_ctx / 128) exceeds the attention scratch of the context");
     cudaError_t e = launch_decode_attention(q_dev, k_cache_dev, v_cache_dev, dt, B, hq, hkv, d, ctx_len, n_ctx, ctx->att_part, out_dev,

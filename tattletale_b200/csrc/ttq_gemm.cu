@@ -1,28 +1,32 @@
-// Prefill / batched side: y[M][N] = x . W^T for M > 16 on the 5th-generation tensor cores.
+// Prefill / batched side: y[M][N] = x . W^T on the 5th-generation tensor cores (tcgen05.mma, kind::f16,
+// cta_group::1, fp32 accumulators in tensor memory).
 //
-// The contraction is issued as tcgen05.mma (kind::f16, cta_group::1) with the accumulator in tensor
-// memory.  Operand roles are swapped with respect to the GEMM's names: the 128 rows of the MMA are
-// 128 weight rows (n), its N dimension is a tile of BM activation rows (m), so that any batch from 17
-// rows up maps onto a legal instruction shape (N = 64, 128 or 256).
+// Operand roles.  The 128 rows (tensor-memory lanes) of the MMA are 128 ACTIVATION rows; its N dimension is the
+// CTA's 128 * NSUB expanded weight rows, so an epilogue thread owns one output row and stores runs of 16
+// consecutive features.  A row tile of BM = 64, 128 or 256 (grouped mode also 384) activation rows is MH = BM / 128
+// row blocks that share one expanded weight stage.
 //
-// Persistent CTAs (one per SM) walk output tiles of (128*NSUB weight rows) x (BM activation rows);
-// with NSUB = 2 one activation stage feeds two MMAs, which halves the L2 -> shared-memory traffic of
-// the activation operand (the first bound this kernel met).  13 warps per CTA:
-//   warps 0-3   epilogue: tcgen05.ld of their 32 accumulator lanes -> bias -> y.  Two accumulators
-//               in tensor memory alternate, so the epilogue of a tile overlaps the next tile's MMAs.
-//   warps 4-11  dequantize: each owns 16 weight rows (one row tile of the packed layout), reads one
-//               512-byte chunk per stage straight from global memory (16 bytes per lane, prefetched
-//               one stage ahead), expands nibbles to fp16 with the 1024-offset bit trick, applies the
-//               sub-block scale and offset with one HFMA2 per pair, and writes the 128-byte-swizzled
-//               K-major A tile.
-//               Lane 0 of the first of them also brings the activation tile in with a single bulk
-//               async copy per stage (xh_prep_kernel stores fp16 activations as ready-made swizzled
-//               tile images).
-//   warp 12     allocates tensor memory, issues the MMAs (one elected lane) and commits them to the
-//               stage barriers.
-// A stage is one window of one 256-weight super-block: 64 K values (8 from each sub-block), in the
-// order the packed chunk delivers them; the activation pass applies the same K permutation, so the
-// dequant warps never shuffle.  Every mbarrier wait is bounded; tensor memory is always released.
+// Persistent CTAs (one per SM) walk output tiles of (128 * NSUB weight rows) x (BM activation rows); K may be cut
+// into `splits` work units whose fp32 partials a small kernel sums when the tiles alone cannot fill the SMs.
+// 21 warps per CTA:
+//   warps 0-3    epilogue: tcgen05.ld of their 32 accumulator lanes -> bias -> y (or split-K partials).  Two
+//                accumulator sets in tensor memory alternate when they fit, so the epilogue of a tile overlaps the
+//                next tile's MMAs.
+//   warps 4-19   dequantize: with two sub-tiles every warp owns one packed row tile (16 weight rows) of the CTA's 256
+//                and works on every stage; with one sub-tile two groups of 8 warps take the even and the odd
+//                stages.  A warp reads one 512-byte chunk per stage straight from global memory (16 bytes per lane,
+//                prefetched two stages ahead), expands nibbles to fp16 with the 1024-offset bit trick, applies the
+//                sub-block scale and offset with one HFMA2 per pair, and writes the 128-byte-swizzled K-major
+//                weight tile.  Lane 0 of the first of them also brings the activation tile in with a single bulk
+//                async copy per stage (xh_prep_kernel stores fp16 activations as ready-made swizzled tile images).
+//                In the plain mode (weights already expanded to fp16 images by another kernel) these warps idle
+//                except for one producer lane that bulk-copies both operands.
+//   warp 20      allocates tensor memory, issues the MMAs (one elected lane) and commits them to the stage
+//                barriers.
+// A stage is one window of one 256-weight super-block: 64 K values (8 from each sub-block), in the order the
+// packed chunk delivers them; the activation pass applies the same K permutation, so the dequant warps never
+// shuffle.  Grouped (mixture-of-experts) mode: every row tile belongs to one weight matrix, named by device-side
+// tables.  Every mbarrier wait is bounded; tensor memory is always released.
 #include <cstdlib>
 
 #include "ttq_internal.cuh"
@@ -48,13 +52,10 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-#ifndef TTQ_GEMM_WAIT_OP
-#define TTQ_GEMM_WAIT_OP "mbarrier.try_wait"
-#endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
-        "{\n .reg .pred p;\n " TTQ_GEMM_WAIT_OP ".parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
         : "=r"(ok)
         : "r"(bar), "r"(parity)
         : "memory");
@@ -138,11 +139,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 // (-1 = a padding row of zeros), `rows_used` (optional, device scalar in units of `rows_unit` rows)
 // bounds the rows worth converting, and GATED = true reads a row of 2K values and emits
 // silu(x[k]) * x[K + k] (the gated-MLP activation, fused into the conversion).
+// `kmap` = 1 selects the Q6_K stage order: slot j of stage s = 2s' + n holds window n of the 16-wide sub-block
+// 4s' + 8 (j & 1) + (j >> 1) (low nibbles: set s', high nibbles: set s' + 2 of the packed chunk).
 template <bool GATED>
 __global__ void __launch_bounds__(256) xh_prep_kernel(const void *__restrict__ x, int x_dt, int64_t M, int64_t Mp, int64_t K,
                                                       int64_t Kp, int64_t ldx, __half *__restrict__ xh,
                                                       const int *__restrict__ row_src, const int *__restrict__ rows_used,
-                                                      int rows_unit) {
+                                                      int rows_unit, int kmap) {
     grid_dependency_wait();  // x, the routing tables and the image buffer belong to preceding kernels until here
     const int64_t chunks_per_row = Kp / 8;
     const int64_t total = Mp * chunks_per_row;
@@ -154,7 +157,7 @@ __global__ void __launch_bounds__(256) xh_prep_kernel(const void *__restrict__ x
         if (mi >= m_used) continue;
         const int64_t sb = it >> 2;
         const int s = (int)(it & 3);
-        const int64_t k0 = sb * 256 + 32 * j + 8 * s;
+        const int64_t k0 = kmap == 0 ? sb * 256 + 32 * j + 8 * s : sb * 256 + 16 * (4 * (s >> 1) + 8 * (j & 1) + (j >> 1)) + 8 * (s & 1);
         // source row: the image row itself, or the row the routing table names (negative = padding)
         int64_t m = mi;
         if (row_src != nullptr) {
@@ -265,8 +268,14 @@ struct GemmCfg {
     static constexpr int TOTAL = 1024 + STAGES * STAGE_BYTES + HDR_BYTES + BAR_BYTES;
 };
 
-template <int BM, int NSUB, bool PLAIN>
+// MODE: which weights the CTA multiplies -- a packed format expanded by the dequant warps (GM_Q4K, GM_Q8_0, GM_Q6K)
+// or fp16 tile images expanded beforehand by another kernel (GM_PLAIN).
+constexpr int GM_Q4K = 0, GM_PLAIN = 1, GM_Q8_0 = 2, GM_Q6K = 3;
+__host__ __device__ constexpr int gm_format(int mode) { return mode == GM_Q8_0 ? TTQ_FMT_Q8_0 : (mode == GM_Q6K ? TTQ_FMT_Q6_K : TTQ_FMT_Q4_K); }
+
+template <int BM, int NSUB, int MODE>
 __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel(GemmParams p) {
+    constexpr bool PLAIN = MODE == GM_PLAIN;
     extern __shared__ uint8_t smem_raw[];
     using C = GemmCfg<BM, NSUB>;
     constexpr int STAGES = C::STAGES;
@@ -308,11 +317,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
-#ifdef TTQ_DIAG_NO_B
-            mbar_init(full_bar + 8 * s, C::DEQ_WARPS);
-#else
             mbar_init(full_bar + 8 * s, PLAIN ? 1 : (NSUB == 1 ? 8 : C::DEQ_WARPS) + 1);
-#endif
             mbar_init(empty_bar + 8 * s, 1);
         }
         for (int b = 0; b < 2; b++) {
@@ -439,6 +444,17 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
         __syncwarp();
     } else if (warp < GEMM_EPI_WARPS + C::DEQ_WARPS) {
         // ------------------------------------------------------------------ dequantize A
+        // A stage is 64 K values of the CTA's weight rows.  For every format it is a set of 512-byte chunks of the tiled
+        // layout, in which lane (g, t) holds, per register sl, four bytes of row g + 8 (sl & 1) and group
+        // u = (t >> 1) + 2 (sl >> 1) at positions 4 (t & 1) .. +3 of an 8-wide window:
+        //   Q4_K  stage s = window s of the 8 sub-blocks: one chunk; byte = {low nibble: sub-block 2u, high: 2u+1}
+        //   Q8_0  stage s = window s of the 8 blocks: chunk s (blocks 0..3 = group u) and chunk 4 + s (blocks 4..7)
+        //   Q6_K  stage (s', n) = window n of the sub-blocks of sets s' and s'+2: chunk 2s'+n of low nibbles
+        //         {low: sub-block 4s'+u, high: 4s'+8+u} and chunk n of the 2-bit planes (bit pair s of a byte = set s)
+        // Each register becomes runs of four fp16 values (k order 0 2 1 3) stored into 16-byte slot `j` of the row's
+        // 128-byte swizzled line; xh_prep_kernel lays the activations out with the same slot -> K mapping.
+        constexpr int FMT = gm_format(MODE);
+        constexpr int TB = tile_bytes(FMT);
         const int dwa = warp - GEMM_EPI_WARPS;  // dequant warp index
         constexpr bool PARITY = NSUB == 1;  // two groups of 8 warps alternate over the stages of the single sub-tile
         constexpr int STRIDE = PARITY ? 2 : 1;
@@ -448,7 +464,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
         const int g = lane >> 2, t = lane & 3;
         const int r = lane & 15, h = lane >> 4;
         const uint32_t my_hdr = hdr_u32 + dwa * 1280;
-        // byte offsets (inside a 128-row A sub-tile) of the 8 stores of this lane: slot sl, low | high nibble chunk
+        // byte offsets (inside a 128-row A sub-tile) of this lane's stores: register sl, slot pair
         const int u0 = t >> 1, u1 = 2 + (t >> 1);
         uint32_t dst_off[4][2], hdr_off[4];
 #pragma unroll
@@ -456,97 +472,150 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
             const int u = (sl >> 1) ? u1 : u0;
             const int row = dw * 16 + g + 8 * (sl & 1);
             const uint32_t key = (uint32_t)(row & 7);
-            dst_off[sl][0] = (uint32_t)row * 128 + ((((uint32_t)(2 * u)) ^ key) << 4) + (uint32_t)(t & 1) * 8;
-            dst_off[sl][1] = (uint32_t)row * 128 + ((((uint32_t)(2 * u + 1)) ^ key) << 4) + (uint32_t)(t & 1) * 8;
-            hdr_off[sl] = (uint32_t)((g + 8 * (sl & 1)) * 80 + 2 * u * 8);
+            // Q4_K, Q6_K: slots 2u (low nibbles) and 2u+1 (high nibbles).  Q8_0: slots u (first chunk) and 4 + u (second)
+            const uint32_t j0 = MODE == GM_Q8_0 ? (uint32_t)u : (uint32_t)(2 * u), j1 = MODE == GM_Q8_0 ? (uint32_t)(4 + u) : (uint32_t)(2 * u + 1);
+            dst_off[sl][0] = (uint32_t)row * 128 + ((j0 ^ key) << 4) + (uint32_t)(t & 1) * 8;
+            dst_off[sl][1] = (uint32_t)row * 128 + ((j1 ^ key) << 4) + (uint32_t)(t & 1) * 8;
+            // per-row scale records in the warp's header area (80-byte rows): Q4_K {scale2, offset2} per sub-block (8 B),
+            // Q8_0 scale2 per block (4 B), Q6_K scale2 per 16-wide sub-block (4 B)
+            hdr_off[sl] = (uint32_t)((g + 8 * (sl & 1)) * 80) + (MODE == GM_Q4K ? (uint32_t)(2 * u * 8) : (uint32_t)(u * 4));
         }
         bool alive = true;
         int git_base = 0;  // stage counter across tiles, at the start of the current tile
         const int64_t b_it_stride = (p.Mp >> 3) << 10;
-        // packed row tiles of this warp in a tile: sub s -> row tile (n_tile*NSUB + s)*8 + dw
-        auto tile_ptr = [&](int64_t tile, int sub, bool &have) {
-            const int64_t nt = (tile_n(tile / splits) * NSUB + my_sub + sub) * (GEMM_BN / TILE_ROWS) + dw;
+        // packed row tile of this warp in an output tile: (n_tile * NSUB + my_sub) * 8 + dw
+        auto tile_ptr = [&](int64_t tile, bool &have) {
+            const int64_t nt = (tile_n(tile / splits) * NSUB + my_sub) * (GEMM_BN / TILE_ROWS) + dw;
             have = tile < total_tiles && nt < p.NT;
             const uint8_t *wbase = p.tiles;
             if (grouped && have) wbase = p.group_tiles[p.mt_group[tile_m(tile / splits)]];
-            return wbase + ((have ? nt : 0) * p.SBp + (tile % splits) * sb_per_unit) * 2304;
+            return wbase + ((have ? nt : 0) * p.SBp + (tile % splits) * sb_per_unit) * TB;
+        };
+        struct Chunks {
+            uint4 a, b;  // b: second chunk of the stage (Q8_0: blocks 4..7, Q6_K: the 2-bit planes); unused for Q4_K
         };
         auto chunk_at = [&](const uint8_t *t0, bool ok, int it) {
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (ok) v = *reinterpret_cast<const uint4 *>(t0 + (int64_t)(it >> 2) * 2304 + (it & 3) * 512 + lane * 16);
-            return v;
+            Chunks c;
+            c.a = c.b = make_uint4(0, 0, 0, 0);
+            if (ok) {
+                const uint8_t *base = t0 + (int64_t)(it >> 2) * TB + lane * 16;
+                const int s = it & 3;
+                if constexpr (MODE == GM_Q4K) {
+                    c.a = *reinterpret_cast<const uint4 *>(base + s * 512);
+                } else if constexpr (MODE == GM_Q8_0) {
+                    c.a = *reinterpret_cast<const uint4 *>(base + s * 512);
+                    c.b = *reinterpret_cast<const uint4 *>(base + (4 + s) * 512);
+                } else {
+                    c.a = *reinterpret_cast<const uint4 *>(base + s * 512);  // chunk 2s' + n with s = 2s' + n
+                    c.b = *reinterpret_cast<const uint4 *>(base + 2048 + (s & 1) * 512);
+                }
+            }
+            return c;
         };
-        bool have[1];
-        const uint8_t *tile0[1];
-        uint4 next[1], next2[1];  // chunks of the next two stages stay in flight
-        uint4 hv_next[1];               // row header of the next super-block (loaded one super-block ahead)
+        bool have;
+        Chunks next, next2;  // chunks of the next two stages stay in flight
+        struct Header {
+            uint4 v;      // Q4_K: the row's 16 header bytes; Q8_0: its 8 fp16 block scales; Q6_K: its 16 int8 scales
+            uint32_t d;   // Q6_K: the row's fp16 super-block scale
+        };
+        Header hv_next;   // row header of the next super-block (loaded one super-block ahead)
         auto header_at = [&](const uint8_t *t0, bool ok, int sb) {
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (ok) v = *reinterpret_cast<const uint4 *>(t0 + (int64_t)sb * 2304 + 2048 + r * 16);
-            return v;
+            Header hd;
+            hd.v = make_uint4(0, 0, 0, 0);
+            hd.d = 0;
+            if (ok) {
+                const uint8_t *tb = t0 + (int64_t)sb * TB;
+                if constexpr (MODE == GM_Q4K) {
+                    hd.v = *reinterpret_cast<const uint4 *>(tb + 2048 + r * 16);
+                } else if constexpr (MODE == GM_Q8_0) {
+                    hd.v = *reinterpret_cast<const uint4 *>(tb + 4096 + r * 16);
+                } else {
+                    hd.v = *reinterpret_cast<const uint4 *>(tb + 3072 + r * 16);
+                    hd.d = *reinterpret_cast<const uint16_t *>(tb + 3328 + r * 2);
+                }
+            }
+            return hd;
         };
-#pragma unroll
-        for (int sub = 0; sub < 1; sub++) {
-            tile0[sub] = tile_ptr(blockIdx.x, sub, have[sub]);
-            next[sub] = chunk_at(tile0[sub], have[sub], grp);
-            next2[sub] = chunk_at(tile0[sub], have[sub] && grp + STRIDE < iters, grp + STRIDE);
-            hv_next[sub] = header_at(tile0[sub], have[sub], 0);
-        }
+        const uint8_t *tile0 = tile_ptr(blockIdx.x, have);
+        next = chunk_at(tile0, have, grp);
+        next2 = chunk_at(tile0, have && grp + STRIDE < iters, grp + STRIDE);
+        hv_next = header_at(tile0, have, 0);
         grid_dependency_wait();  // the first packed chunks and headers are in flight; activations come next
-        const __half2 k1032 = __float2half2_rn(1032.f), k1152 = __float2half2_rn(1152.f);
+        const __half2 k1032 = __float2half2_rn(1032.f), k1152 = __float2half2_rn(1152.f), k1056 = __float2half2_rn(1056.f);
+        // constants of the nibble expansion, kept in registers (see and_or)
+        uint32_t mask_lo = 0x000f000fu, mask_hi = 0x00f000f0u, mask_b = 0x00ff00ffu, k1024 = 0x64006400u;
+        asm volatile("" : "+r"(mask_lo), "+r"(mask_hi), "+r"(mask_b), "+r"(k1024));
         const bool trd = p.trace != nullptr && blockIdx.x == 0 && dwa == 0;
         unsigned long long t_empty = 0, t_conv = 0, t_begin = trd ? global_ns() : 0;
         for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-            bool have_n[1];
-            const uint8_t *tile0_n[1];
-#pragma unroll
-            for (int sub = 0; sub < 1; sub++) tile0_n[sub] = tile_ptr(tile + gridDim.x, sub, have_n[sub]);
+            bool have_n;
+            const uint8_t *tile0_n = tile_ptr(tile + gridDim.x, have_n);
             const int64_t m_tile_b = tile_m(tile / splits);
             const uint8_t *bsrc0 = reinterpret_cast<const uint8_t *>(p.xh) + ((tile_row0(m_tile_b) >> 3) << 10) +
                                    (tile % splits) * iters * b_it_stride;
             const uint32_t b_bytes = BM == 384 ? (uint32_t)tile_mh(m_tile_b) * (128u * 128u) : (uint32_t)C::B_BYTES;
             for (int it = grp; it < iters; it += STRIDE) {
-#ifdef TTQ_DIAG_MMA_ONLY
-                continue;
-#endif
                 const int git = git_base + it;  // iters is a multiple of 4: a warp group keeps its stage parity across tiles
                 const int sb = it >> 2;
                 const int stage = git % STAGES;
-                uint4 w[1];
-#pragma unroll
-                for (int sub = 0; sub < 1; sub++) {
-                    w[sub] = next[sub];
-                    next[sub] = next2[sub];
-                    if (it + 2 * STRIDE < iters) next2[sub] = chunk_at(tile0[sub], have[sub], it + 2 * STRIDE);
-                    else next2[sub] = chunk_at(tile0_n[sub], have_n[sub] && (it + 2 * STRIDE - iters) < iters, it + 2 * STRIDE - iters);
-                }
+                const Chunks w = next;
+                next = next2;
+                if (it + 2 * STRIDE < iters) next2 = chunk_at(tile0, have, it + 2 * STRIDE);
+                else next2 = chunk_at(tile0_n, have_n && (it + 2 * STRIDE - iters) < iters, it + 2 * STRIDE - iters);
                 if ((it & 3) == grp) {
-                    // first own stage of a super-block: headers of (row tile, super-block): lane (r, h) unpacks sub-blocks 4h..4h+3 of row r into
-                    // {scale, scale, offset, offset} halves: w = scale*(q-8) + offset (high nibbles arrive as 16*(q-8))
+                    // first own stage of a super-block: lane (r, h) unpacks half h of row r's scales into the header area
                     __syncwarp();
+                    {
+                        const Header hd = hv_next;
+                        if (sb + 1 < sb_per_unit) hv_next = header_at(tile0, have, sb + 1);
+                        else hv_next = header_at(tile0_n, have_n, 0);
+                        const uint4 hv = hd.v;
+                        if constexpr (MODE == GM_Q4K) {
+                            // sub-blocks 4h..4h+3: {scale, scale, offset, offset} halves, w = scale*(q-8) + offset (high
+                            // nibbles arrive as 16*(q-8))
+                            const __half2 dd = *reinterpret_cast<const __half2 *>(&hv.x);
+                            const float d = __low2float(dd), dmin = __high2float(dd);
+                            uint32_t scw, mw;
+                            if (h == 0) {
+                                scw = hv.y & 0x3f3f3f3fu;
+                                mw = hv.z & 0x3f3f3f3fu;
+                            } else {
+                                scw = (hv.w & 0x0f0f0f0fu) | ((hv.y >> 2) & 0x30303030u);
+                                mw = ((hv.w >> 4) & 0x0f0f0f0fu) | ((hv.z >> 2) & 0x30303030u);
+                            }
 #pragma unroll
-                    for (int sub = 0; sub < 1; sub++) {
-                        const uint4 hv = hv_next[sub];
-                        if (sb + 1 < sb_per_unit) hv_next[sub] = header_at(tile0[sub], have[sub], sb + 1);
-                        else hv_next[sub] = header_at(tile0_n[sub], have_n[sub], 0);
-                        const __half2 dd = *reinterpret_cast<const __half2 *>(&hv.x);
-                        const float d = __low2float(dd), dmin = __high2float(dd);
-                        uint32_t scw, mw;
-                        if (h == 0) {
-                            scw = hv.y & 0x3f3f3f3fu;
-                            mw = hv.z & 0x3f3f3f3fu;
+                            for (int i = 0; i < 4; i++) {
+                                const float sc = d * (float)((scw >> (8 * i)) & 0xff);
+                                const float off = fmaf(8.f, sc, -dmin * (float)((mw >> (8 * i)) & 0xff));
+                                const __half2 s2 = __float2half2_rn((i & 1) ? sc * 0.0625f : sc);
+                                const __half2 o2 = __float2half2_rn(off);
+                                asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(my_hdr + (uint32_t)(r * 80 + (4 * h + i) * 8)),
+                                             "r"(*reinterpret_cast<const uint32_t *>(&s2)), "r"(*reinterpret_cast<const uint32_t *>(&o2))
+                                             : "memory");
+                            }
+                        } else if constexpr (MODE == GM_Q8_0) {
+                            // blocks 4h..4h+3: the fp16 scale d, duplicated into both halves
+                            const uint32_t lo = h == 0 ? hv.x : hv.z, hi = h == 0 ? hv.y : hv.w;
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(my_hdr + (uint32_t)(r * 80 + h * 16)),
+                                         "r"(__byte_perm(lo, 0, 0x1010)), "r"(__byte_perm(lo, 0, 0x3232)), "r"(__byte_perm(hi, 0, 0x1010)),
+                                         "r"(__byte_perm(hi, 0, 0x3232))
+                                         : "memory");
                         } else {
-                            scw = (hv.w & 0x0f0f0f0fu) | ((hv.y >> 2) & 0x30303030u);
-                            mw = ((hv.w >> 4) & 0x0f0f0f0fu) | ((hv.z >> 2) & 0x30303030u);
-                        }
+                            // 16-wide sub-blocks 8h..8h+7: d * sc as fp16, duplicated into both halves
+                            const float d = __half2float(__ushort_as_half((unsigned short)hd.d));
+                            const uint32_t lo = h == 0 ? hv.x : hv.z, hi = h == 0 ? hv.y : hv.w;
+                            uint32_t sw[8];
 #pragma unroll
-                        for (int i = 0; i < 4; i++) {
-                            const float sc = d * (float)((scw >> (8 * i)) & 0xff);
-                            const float off = fmaf(8.f, sc, -dmin * (float)((mw >> (8 * i)) & 0xff));
-                            const __half2 s2 = __float2half2_rn((i & 1) ? sc * 0.0625f : sc);
-                            const __half2 o2 = __float2half2_rn(off);
-                            asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(my_hdr + (uint32_t)(r * 80 + (4 * h + i) * 8)),
-                                         "r"(*reinterpret_cast<const uint32_t *>(&s2)), "r"(*reinterpret_cast<const uint32_t *>(&o2))
+                            for (int i = 0; i < 8; i++) {
+                                const float sc = d * (float)(int)(int8_t)(((i < 4 ? lo : hi) >> (8 * (i & 3))) & 0xff);
+                                const __half2 s2 = __float2half2_rn(sc);
+                                sw[i] = *reinterpret_cast<const uint32_t *>(&s2);
+                            }
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(my_hdr + (uint32_t)(r * 80 + h * 32)), "r"(sw[0]),
+                                         "r"(sw[1]), "r"(sw[2]), "r"(sw[3])
+                                         : "memory");
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(my_hdr + (uint32_t)(r * 80 + h * 32 + 16)), "r"(sw[4]),
+                                         "r"(sw[5]), "r"(sw[6]), "r"(sw[7])
                                          : "memory");
                         }
                     }
@@ -561,43 +630,81 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
                     tw0 = global_ns();
                 }
                 const uint32_t a_stage = stages_u32 + stage * C::STAGE_BYTES;
-#ifndef TTQ_DIAG_NO_B
                 if (dw == 0 && my_sub == 0 && lane == 0) {
                     // the activation tile of this stage: one bulk copy, counted on the same full barrier
                     mbar_expect_tx(full_bar + 8 * stage, b_bytes);
                     bulk_g2s(a_stage + C::A_BYTES, bsrc0 + it * b_it_stride, b_bytes, full_bar + 8 * stage);
                 }
-#endif
-#ifdef TTQ_DIAG_NO_CONVERT
-                if (git < 0)
-#endif
-#pragma unroll
-                for (int sub = 0; sub < 1; sub++) {
-                    const uint32_t ww[4] = {w[sub].x, w[sub].y, w[sub].z, w[sub].w};
+                {
+                    const uint32_t wa[4] = {w.a.x, w.a.y, w.a.z, w.a.w};
                     const uint32_t a_sub = a_stage + my_sub * A_STAGE_BYTES;
                     // three phases (loads, arithmetic, stores) so that the shared-memory latencies overlap
-                    uint4 so[4];  // {scale2, offset2} of sub-blocks 2u (low nibbles) and 2u+1 (high nibbles) per slot
+                    __half2 res[4][4];  // per register: the two fp16 pairs of slot j0, then of slot j1
+                    if constexpr (MODE == GM_Q4K) {
+                        uint4 so[4];  // {scale2, offset2} of sub-blocks 2u (low nibbles) and 2u+1 (high nibbles) per slot
 #pragma unroll
-                    for (int sl = 0; sl < 4; sl++)
-                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                     : "=r"(so[sl].x), "=r"(so[sl].y), "=r"(so[sl].z), "=r"(so[sl].w)
-                                     : "r"(my_hdr + hdr_off[sl]));
-                    __half2 res[4][4];
+                        for (int sl = 0; sl < 4; sl++)
+                            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                         : "=r"(so[sl].x), "=r"(so[sl].y), "=r"(so[sl].z), "=r"(so[sl].w)
+                                         : "r"(my_hdr + hdr_off[sl]));
 #pragma unroll
-                    for (int sl = 0; sl < 4; sl++) {
-                        const __half2 sc_lo = *reinterpret_cast<const __half2 *>(&so[sl].x), of_lo = *reinterpret_cast<const __half2 *>(&so[sl].y);
-                        const __half2 sc_hi = *reinterpret_cast<const __half2 *>(&so[sl].z), of_hi = *reinterpret_cast<const __half2 *>(&so[sl].w);
-                        const uint32_t x = ww[sl], x8 = x >> 8;
-                        uint32_t v0 = (x & 0x000f000fu) | 0x64006400u, v1 = (x8 & 0x000f000fu) | 0x64006400u;  // 1024 + q
-                        uint32_t v2 = (x & 0x00f000f0u) | 0x64006400u, v3 = (x8 & 0x00f000f0u) | 0x64006400u;  // 1024 + 16 q
-                        res[sl][0] = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v0), k1032), sc_lo, of_lo);
-                        res[sl][1] = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v1), k1032), sc_lo, of_lo);
-                        res[sl][2] = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v2), k1152), sc_hi, of_hi);
-                        res[sl][3] = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v3), k1152), sc_hi, of_hi);
+                        for (int sl = 0; sl < 4; sl++) {
+                            const __half2 sc_lo = *reinterpret_cast<const __half2 *>(&so[sl].x), of_lo = *reinterpret_cast<const __half2 *>(&so[sl].y);
+                            const __half2 sc_hi = *reinterpret_cast<const __half2 *>(&so[sl].z), of_hi = *reinterpret_cast<const __half2 *>(&so[sl].w);
+                            const uint32_t x = wa[sl], x8 = x >> 8;
+                            uint32_t v0 = and_or(x, mask_lo, k1024), v1 = and_or(x8, mask_lo, k1024);  // 1024 + q
+                            uint32_t v2 = and_or(x, mask_hi, k1024), v3 = and_or(x8, mask_hi, k1024);  // 1024 + 16 q
+                            res[sl][0] = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v0), k1032), sc_lo, of_lo);
+                            res[sl][1] = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v1), k1032), sc_lo, of_lo);
+                            res[sl][2] = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v2), k1152), sc_hi, of_hi);
+                            res[sl][3] = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v3), k1152), sc_hi, of_hi);
+                        }
+                    } else if constexpr (MODE == GM_Q8_0) {
+                        const uint32_t wb[4] = {w.b.x, w.b.y, w.b.z, w.b.w};
+                        uint32_t sc0[4], sc1[4];  // scale2 of block u (first chunk) and block 4 + u (second chunk)
+#pragma unroll
+                        for (int sl = 0; sl < 4; sl++) {
+                            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sc0[sl]) : "r"(my_hdr + hdr_off[sl]));
+                            asm volatile("ld.shared.u32 %0, [%1+16];" : "=r"(sc1[sl]) : "r"(my_hdr + hdr_off[sl]));
+                        }
+#pragma unroll
+                        for (int sl = 0; sl < 4; sl++) {
+                            // int8 -> fp16: flip the sign bit (q + 128 in 0..255), OR into the mantissa of 1024, subtract 1152
+                            const uint32_t x = wa[sl] ^ 0x80808080u, y = wb[sl] ^ 0x80808080u;
+                            uint32_t v0 = and_or(x, mask_b, k1024), v1 = and_or(x >> 8, mask_b, k1024);
+                            uint32_t v2 = and_or(y, mask_b, k1024), v3 = and_or(y >> 8, mask_b, k1024);
+                            const __half2 s0 = *reinterpret_cast<const __half2 *>(&sc0[sl]), s1 = *reinterpret_cast<const __half2 *>(&sc1[sl]);
+                            res[sl][0] = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&v0), k1152), s0);
+                            res[sl][1] = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&v1), k1152), s0);
+                            res[sl][2] = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&v2), k1152), s1);
+                            res[sl][3] = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&v3), k1152), s1);
+                        }
+                    } else {
+                        const uint32_t wb[4] = {w.b.x, w.b.y, w.b.z, w.b.w};
+                        const int sp = (it & 3) >> 1;  // set s' of the low nibbles; the high nibbles are set s' + 2
+                        uint32_t sc0[4], sc1[4];       // scale2 of sub-blocks 4s'+u and 4s'+8+u
+#pragma unroll
+                        for (int sl = 0; sl < 4; sl++) {
+                            const uint32_t ha = my_hdr + hdr_off[sl] + (uint32_t)sp * 16;
+                            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sc0[sl]) : "r"(ha));
+                            asm volatile("ld.shared.u32 %0, [%1+32];" : "=r"(sc1[sl]) : "r"(ha));
+                        }
+#pragma unroll
+                        for (int sl = 0; sl < 4; sl++) {
+                            // 6-bit quant = nibble | (two plane bits << 4); OR-ed into the mantissa of 1024, minus 1024 + 32
+                            const uint32_t x = wa[sl], x8 = x >> 8;
+                            const uint32_t pl = wb[sl] >> (2 * sp), ph = wb[sl] >> (2 * sp + 4);  // plane bits of set s', s'+2 at bits 0..1 of each byte
+                            const uint32_t a02 = (pl << 4) & 0x00300030u, a13 = (pl >> 4) & 0x00300030u;
+                            const uint32_t b02 = (ph << 4) & 0x00300030u, b13 = (ph >> 4) & 0x00300030u;
+                            uint32_t v0 = and_or(x, mask_lo, k1024) | a02, v1 = and_or(x8, mask_lo, k1024) | a13;
+                            uint32_t v2 = and_or(x >> 4, mask_lo, k1024) | b02, v3 = and_or(x8 >> 4, mask_lo, k1024) | b13;
+                            const __half2 s0 = *reinterpret_cast<const __half2 *>(&sc0[sl]), s1 = *reinterpret_cast<const __half2 *>(&sc1[sl]);
+                            res[sl][0] = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&v0), k1056), s0);
+                            res[sl][1] = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&v1), k1056), s0);
+                            res[sl][2] = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&v2), k1056), s1);
+                            res[sl][3] = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&v3), k1056), s1);
+                        }
                     }
-#ifdef TTQ_DIAG_NO_STS
-                    if (p.Kp < 0)
-#endif
 #pragma unroll
                     for (int sl = 0; sl < 4; sl++) {
                         asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a_sub + dst_off[sl][0]),
@@ -608,18 +715,13 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
                                      : "memory");
                     }
                 }
-#ifndef TTQ_DIAG_NO_FENCE
                 fence_async_smem();
-#endif
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full_bar + 8 * stage);
                 if (trd) t_conv += global_ns() - tw0;
             }
-#pragma unroll
-            for (int sub = 0; sub < 1; sub++) {
-                tile0[sub] = tile0_n[sub];
-                have[sub] = have_n[sub];
-            }
+            tile0 = tile0_n;
+            have = have_n;
             git_base += iters;
         }
         if (trd && lane == 0) {
@@ -651,9 +753,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
                 for (int it = 0; it < iters; it++, git++) {
                     const int stage = git % STAGES;
                     if (tr) t0 = global_ns();
-#ifndef TTQ_DIAG_MMA_ONLY
                     if (alive) alive = mbar_wait_bounded(full_bar + 8 * stage, (uint32_t)((git / STAGES) & 1), p.status);
-#endif
                     if (tr) {
                         t_full += global_ns() - t0;
                         t0 = global_ns();
@@ -712,7 +812,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restr
     }
 }
 
-template <int BM, int NSUB, bool PLAIN = false>
+template <int BM, int NSUB, int MODE = GM_Q4K>
 cudaError_t launch_cfg(const GemmParams &p, int sms, cudaStream_t st) {
     using C = GemmCfg<BM, NSUB>;
     static bool configured[64] = {};  // per device: the shared-memory opt-in belongs to the device's copy of the function
@@ -721,18 +821,18 @@ cudaError_t launch_cfg(const GemmParams &p, int sms, cudaStream_t st) {
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (!configured[dev]) {
-        e = cudaFuncSetAttribute(gemm_q4k_kernel<BM, NSUB, PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL);
+        e = cudaFuncSetAttribute(gemm_q4k_kernel<BM, NSUB, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
     const int64_t tiles = ((p.N + GEMM_BN * NSUB - 1) / (GEMM_BN * NSUB)) * (p.group_tiles != nullptr ? p.mt_cap : p.Mp / BM) * p.splits;
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-    return launch_pdl(gemm_q4k_kernel<BM, NSUB, PLAIN>, dim3(grid), dim3(C::THREADS), (size_t)C::TOTAL, st, p);
+    return launch_pdl(gemm_q4k_kernel<BM, NSUB, MODE>, dim3(grid), dim3(C::THREADS), (size_t)C::TOTAL, st, p);
 }
 
 }  // namespace
 
-bool gemm_supported(int fmt) { return fmt == TTQ_FMT_Q4_K; }
+bool gemm_supported(int fmt) { return fmt == TTQ_FMT_Q4_K || fmt == TTQ_FMT_Q8_0 || fmt == TTQ_FMT_Q6_K; }
 
 // Rows of the fp16 weight images the plain mode reads: output features padded to whole 256-row tiles.
 int64_t gemm_wimg_rows(int64_t N) { return (N + 255) / 256 * 256; }
@@ -742,7 +842,8 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
                         unsigned long long *trace, cudaStream_t st, int *launches, const __half *wimg) {
     *launches = 0;
     const bool plain = wimg != nullptr;
-    if (!plain && fmt != TTQ_FMT_Q4_K) return cudaErrorNotSupported;
+    if (!plain && !gemm_supported(fmt)) return cudaErrorNotSupported;
+    const int kmap = (!plain && fmt == TTQ_FMT_Q6_K) ? 1 : 0;
     const int64_t Kp = a.SBp * TILE_K;
     const int BM = a.M <= 64 ? 64 : (a.M <= 128 ? 128 : 256);
     // two 128-row sub-tiles per CTA once there are enough tiles to keep every SM busy with them
@@ -757,7 +858,7 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
     const double cost1 = (double)((tiles1 + sms - 1) / sms), cost2 = 1.7 * (double)((tiles2 + sms - 1) / sms);
     int nsub = (a.N > 128 && cost2 < cost1) ? 2 : 1;
     if (force_nsub == 1 || force_nsub == 2) nsub = force_nsub;
-    if (plain) nsub = 2;  // no conversion work to balance: always the 256-row weight tile
+    if (plain || fmt != TTQ_FMT_Q4_K) nsub = 2;  // plain: no conversion work to balance; Q8_0 / Q6_K: one variant
     int64_t slab = (xh_capacity / Kp) / BM * BM;  // rows per pass
     if (slab < BM) return cudaErrorInvalidValue;
     const int esz_x = a.x_dt == TTQ_DT_F32 ? 4 : 2, esz_y = a.y_dt == TTQ_DT_F32 ? 4 : 2;
@@ -766,12 +867,12 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
         const int64_t m_tiles = (Ms + BM - 1) / BM, Mp = m_tiles * BM;
         const uint8_t *xs = reinterpret_cast<const uint8_t *>(a.x) + (size_t)m0 * a.ldx * esz_x;
         const int64_t chunks = Mp * (Kp / 8);
-        const unsigned grid = (unsigned)((chunks + 255) / 256 < 148 * 16 ? (chunks + 255) / 256 : 148 * 16);
+        const unsigned grid = (unsigned)((chunks + 255) / 256 < sms * 16 ? (chunks + 255) / 256 : sms * 16);
         const int *no_tab = nullptr;
         cudaError_t e = a.gated ? launch_pdl(xh_prep_kernel<true>, dim3(grid), dim3(256), 0, st, (const void *)xs, a.x_dt, Ms, Mp, a.K, Kp, a.ldx,
-                                             xh, no_tab, no_tab, 0)
+                                             xh, no_tab, no_tab, 0, kmap)
                                 : launch_pdl(xh_prep_kernel<false>, dim3(grid), dim3(256), 0, st, (const void *)xs, a.x_dt, Ms, Mp, a.K, Kp, a.ldx,
-                                             xh, no_tab, no_tab, 0);
+                                             xh, no_tab, no_tab, 0, kmap);
         if (e != cudaSuccess) return e;
         ++*launches;
         GemmParams p;
@@ -803,9 +904,19 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
             p.ws = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(xh) + ((xh_bytes + 255) & ~(size_t)255));
         }
         if (plain) {
-            if (BM == 64) e = launch_cfg<64, 2, true>(p, sms, st);
-            else if (BM == 128) e = launch_cfg<128, 2, true>(p, sms, st);
-            else e = launch_cfg<256, 2, true>(p, sms, st);
+            if (BM == 64) e = launch_cfg<64, 2, GM_PLAIN>(p, sms, st);
+            else if (BM == 128) e = launch_cfg<128, 2, GM_PLAIN>(p, sms, st);
+            else e = launch_cfg<256, 2, GM_PLAIN>(p, sms, st);
+        } else if (fmt == TTQ_FMT_Q8_0) {
+            // (these formats always take two sub-tiles: the single sub-tile variant pays off on the many small tiles of
+            // the grouped Q4_K GEMM, which they do not serve)
+            if (BM == 64) e = launch_cfg<64, 2, GM_Q8_0>(p, sms, st);
+            else if (BM == 128) e = launch_cfg<128, 2, GM_Q8_0>(p, sms, st);
+            else e = launch_cfg<256, 2, GM_Q8_0>(p, sms, st);
+        } else if (fmt == TTQ_FMT_Q6_K) {
+            if (BM == 64) e = launch_cfg<64, 2, GM_Q6K>(p, sms, st);
+            else if (BM == 128) e = launch_cfg<128, 2, GM_Q6K>(p, sms, st);
+            else e = launch_cfg<256, 2, GM_Q6K>(p, sms, st);
         } else if (nsub == 2) {
             if (BM == 64) e = launch_cfg<64, 2>(p, sms, st);
             else if (BM == 128) e = launch_cfg<128, 2>(p, sms, st);
@@ -819,7 +930,7 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
         ++*launches;
         if (splits > 1) {
             const int64_t total = Ms * a.N;
-            const unsigned rg = (unsigned)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+            const unsigned rg = (unsigned)((total + 255) / 256 < sms * 8 ? (total + 255) / 256 : sms * 8);
             e = launch_pdl(splitk_reduce_kernel, dim3(rg), dim3(256), 0, st, (const float *)p.ws, splits, Ms, Mp, a.N, a.bias, a.bias_dt, p.y,
                            a.y_dt, a.ldy);
             if (e != cudaSuccess) return e;
@@ -837,11 +948,11 @@ cudaError_t launch_gemm_grouped(const GroupedArgs &g, __half *xh, int sms, int *
     if (g.BM != 64 && g.BM != 128 && g.BM != 256 && g.BM != 384) return cudaErrorInvalidValue;
     if (g.Mp % 128 && g.Mp % g.BM) return cudaErrorInvalidValue;
     const int64_t chunks = g.Mp * (Kp / 8);
-    const unsigned grid = (unsigned)((chunks + 255) / 256 < 148 * 16 ? (chunks + 255) / 256 : 148 * 16);
+    const unsigned grid = (unsigned)((chunks + 255) / 256 < sms * 16 ? (chunks + 255) / 256 : sms * 16);
     cudaError_t e = g.gated ? launch_pdl(xh_prep_kernel<true>, dim3(grid), dim3(256), 0, st, g.x, g.x_dt, g.x_rows, g.Mp, g.K, Kp, g.ldx, xh,
-                                         g.row_src, g.rows_total, 1)
+                                         g.row_src, g.rows_total, 1, 0)
                             : launch_pdl(xh_prep_kernel<false>, dim3(grid), dim3(256), 0, st, g.x, g.x_dt, g.x_rows, g.Mp, g.K, Kp, g.ldx, xh,
-                                         g.row_src, g.rows_total, 1);
+                                         g.row_src, g.rows_total, 1, 0);
     if (e != cudaSuccess) return e;
     ++*launches;
     GemmParams p;

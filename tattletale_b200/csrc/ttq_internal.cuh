@@ -185,6 +185,19 @@ __device__ __forceinline__ void exchange_row_tile(const CommView &cm, int64_t rt
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Multiprocessor count of the current device (cached per device); grid caps are multiples of it.
+inline int device_sms() {
+    static int cache[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
+    if (cache[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 1;
+        cache[dev] = n;
+    }
+    return cache[dev];
+}
+
 inline bool env_flag(const char *name, bool dflt) {
     const char *v = getenv(name);
     if (!v || !*v) return dflt;
@@ -299,6 +312,14 @@ __device__ __forceinline__ void store_from_float(void *p, int dt, int64_t i, flo
     if (dt == TTQ_DT_BF16) reinterpret_cast<__nv_bfloat16 *>(p)[i] = __float2bfloat16_rn(v);
     else if (dt == TTQ_DT_F16) reinterpret_cast<__half *>(p)[i] = __float2half_rn(v);
     else reinterpret_cast<float *>(p)[i] = v;
+}
+
+// (a & b) | c in one instruction with both constants in registers (written with immediates the compiler emits
+// two instructions; hold b and c in variables made opaque by an empty asm statement).
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
 }
 
 // Q4_K: unpack the 6-bit scale (sc) and min (m) of sub-block j from the 12 packed bytes.

@@ -132,10 +132,10 @@ cudaError_t launch_moe_route(const MoeRouting &r, const int *topk_ids, int64_t T
     if (e != cudaSuccess) return e;
     e = cudaMemsetAsync(r.row_src, 0xff, sizeof(int) * (size_t)Mp, st);  // every row is padding until a pair claims it
     if (e != cudaSuccess) return e;
-    route_count_kernel<<<grid_of(pairs, 148 * 4), 256, 0, st>>>(topk_ids, pairs, E, r.counts);
+    route_count_kernel<<<grid_of(pairs, device_sms() * 4), 256, 0, st>>>(topk_ids, pairs, E, r.counts);
     route_plan_kernel<<<1, 1024, 2 * sizeof(int) * (size_t)(E + 1), st>>>(r.counts, E, BM, (int)mt_cap, r.row_start, r.cursor, r.mt_group,
                                                                           r.mt_row0, r.mt_mh, r.n_mt);
-    route_scatter_kernel<<<grid_of(pairs, 148 * 4), 256, 0, st>>>(topk_ids, pairs, top_k, E, Mp, r.row_start, r.cursor, r.slot_of,
+    route_scatter_kernel<<<grid_of(pairs, device_sms() * 4), 256, 0, st>>>(topk_ids, pairs, top_k, E, Mp, r.row_start, r.cursor, r.slot_of,
                                                                   r.row_src);
     *launches = 3;
     return cudaGetLastError();
@@ -143,7 +143,7 @@ cudaError_t launch_moe_route(const MoeRouting &r, const int *topk_ids, int64_t T
 
 cudaError_t launch_moe_combine(const MoeRouting &r, const void *o, int o_dt, int64_t ldo, const float *topk_w, int64_t T,
                                int top_k, int64_t H, void *y, int y_dt, int64_t ldy, cudaStream_t st) {
-    combine_kernel<<<grid_of(T * ((H + 7) / 8), 148 * 16), 256, 0, st>>>(o, o_dt, ldo, r.slot_of, topk_w, T, top_k, H, y, y_dt, ldy);
+    combine_kernel<<<grid_of(T * ((H + 7) / 8), device_sms() * 16), 256, 0, st>>>(o, o_dt, ldo, r.slot_of, topk_w, T, top_k, H, y, y_dt, ldy);
     return cudaGetLastError();
 }
 

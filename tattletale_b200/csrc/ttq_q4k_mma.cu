@@ -169,12 +169,6 @@ __device__ __forceinline__ uint32_t hadd2_u(uint32_t a, uint32_t b) {
 }
 constexpr uint32_t H2_1024 = 0x64006400u, H2_M1024 = 0xE400E400u, H2_16TH = 0x2C002C00u, H2_M64 = 0xD400D400u;
 
-// (a & b) | c in one instruction, with both constants in registers (as immediates the compiler emits two).
-__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t d;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
 // Expands one packed register (4 bytes = positions P..P+3 of a sub-block pair for one row) into the four
 // fp16x2 operands {lo nibbles of bytes 0,2 | lo of 1,3 | hi of 0,2 | hi of 1,3}, each = q * sc exactly.
 __device__ __forceinline__ void qm_expand(uint32_t w, uint32_t s_lo, uint32_t o_lo, uint32_t s_hi, uint32_t o_hi, uint32_t &l02, uint32_t &l13,

@@ -224,7 +224,7 @@ int grid_for(int64_t work_items, int per_block, int cap) {
 
 cudaError_t launch_repack(int fmt, const uint8_t *canon, uint8_t *tiled, int64_t N, int64_t K, int64_t NT,
                           int64_t SBp, cudaStream_t st) {
-    int grid = grid_for(NT * SBp, 1, 148 * 64);
+    int grid = grid_for(NT * SBp, 1, device_sms() * 64);
     if (fmt == TTQ_FMT_Q4_K) repack_kernel<TTQ_FMT_Q4_K><<<grid, 128, 0, st>>>(canon, tiled, N, K, NT, SBp);
     else if (fmt == TTQ_FMT_Q8_0) repack_kernel<TTQ_FMT_Q8_0><<<grid, 128, 0, st>>>(canon, tiled, N, K, NT, SBp);
     else repack_kernel<TTQ_FMT_Q6_K><<<grid, 128, 0, st>>>(canon, tiled, N, K, NT, SBp);
@@ -233,7 +233,7 @@ cudaError_t launch_repack(int fmt, const uint8_t *canon, uint8_t *tiled, int64_t
 
 cudaError_t launch_dequant(int fmt, const uint8_t *tiled, float *out, int64_t ld, int64_t N, int64_t K,
                            int64_t SBp, cudaStream_t st) {
-    int grid = grid_for(N * K, 256 * 8, 148 * 32);
+    int grid = grid_for(N * K, 256 * 8, device_sms() * 32);
     if (fmt == TTQ_FMT_Q4_K) dequant_kernel<TTQ_FMT_Q4_K><<<grid, 256, 0, st>>>(tiled, out, ld, N, K, SBp);
     else if (fmt == TTQ_FMT_Q8_0) dequant_kernel<TTQ_FMT_Q8_0><<<grid, 256, 0, st>>>(tiled, out, ld, N, K, SBp);
     else dequant_kernel<TTQ_FMT_Q6_K><<<grid, 256, 0, st>>>(tiled, out, ld, N, K, SBp);
@@ -242,7 +242,7 @@ cudaError_t launch_dequant(int fmt, const uint8_t *tiled, float *out, int64_t ld
 
 cudaError_t launch_wimg(int fmt, const uint8_t *tiled, int64_t N, int64_t K, int64_t SBp, __half *wimg, cudaStream_t st) {
     const int64_t Np = gemm_wimg_rows(N);
-    const int grid = grid_for(Np * (SBp * TILE_K / 8), 256, 148 * 32);
+    const int grid = grid_for(Np * (SBp * TILE_K / 8), 256, device_sms() * 32);
     if (fmt == TTQ_FMT_Q4_K) wimg_kernel<TTQ_FMT_Q4_K><<<grid, 256, 0, st>>>(tiled, N, Np, K, SBp, wimg);
     else if (fmt == TTQ_FMT_Q8_0) wimg_kernel<TTQ_FMT_Q8_0><<<grid, 256, 0, st>>>(tiled, N, Np, K, SBp, wimg);
     else wimg_kernel<TTQ_FMT_Q6_K><<<grid, 256, 0, st>>>(tiled, N, Np, K, SBp, wimg);
@@ -251,7 +251,7 @@ cudaError_t launch_wimg(int fmt, const uint8_t *tiled, int64_t N, int64_t K, int
 
 cudaError_t launch_silu_and_mul(const void *in, int dt, int64_t M, int64_t H, int64_t ld_in, void *out,
                                 int64_t ld_out, cudaStream_t st) {
-    int grid = grid_for(M * H, 256 * 4, 148 * 16);
+    int grid = grid_for(M * H, 256 * 4, device_sms() * 16);
     if (dt == TTQ_DT_BF16)
         return launch_pdl(silu_and_mul_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16 *)in, (__nv_bfloat16 *)out, M, H,
                           ld_in, ld_out);

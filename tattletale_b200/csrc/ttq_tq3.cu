@@ -208,19 +208,19 @@ unsigned grid_of(int64_t items, int per_block, int cap) {
 }  // namespace
 
 cudaError_t launch_tq3_decode(const uint8_t *packed, int64_t N, int64_t K, float *out, int64_t ld, cudaStream_t st) {
-    tq3_decode_kernel<false><<<grid_of(N * K, 256 * 4, 148 * 32), 256, 0, st>>>(packed, N, K, out, ld, 0, 0);
+    tq3_decode_kernel<false><<<grid_of(N * K, 256 * 4, device_sms() * 32), 256, 0, st>>>(packed, N, K, out, ld, 0, 0);
     return cudaGetLastError();
 }
 
 cudaError_t launch_tq3_wimg(const uint8_t *packed, int64_t N, int64_t K, __half *wimg, cudaStream_t st) {
     const int64_t Np = gemm_wimg_rows(N), Kp = (K + TILE_K - 1) / TILE_K * TILE_K;
-    tq3_decode_kernel<true><<<grid_of(Np * (Kp / 8), 256, 148 * 32), 256, 0, st>>>(packed, N, K, wimg, 0, Np, Kp);
+    tq3_decode_kernel<true><<<grid_of(Np * (Kp / 8), 256, device_sms() * 32), 256, 0, st>>>(packed, N, K, wimg, 0, Np, Kp);
     return cudaGetLastError();
 }
 
 cudaError_t launch_tq3_rotate(const void *in, int in_dt, int64_t M, int64_t C, int64_t ld_in, const uint8_t *sign, const __half *scale,
                               const void *bias, int bias_dt, void *out, int out_dt, int64_t ld_out, cudaStream_t st) {
-    return launch_pdl(tq3_rotate_kernel, dim3(grid_of(M * (C / 128), 8, 148 * 16)), dim3(256), 0, st, in, in_dt, M, C, ld_in, sign, scale, bias,
+    return launch_pdl(tq3_rotate_kernel, dim3(grid_of(M * (C / 128), 8, device_sms() * 16)), dim3(256), 0, st, in, in_dt, M, C, ld_in, sign, scale, bias,
                       bias_dt, out, out_dt, ld_out);
 }
 

@@ -16,8 +16,10 @@ type
   TtqCtx* {.importc: "ttq_ctx", header: "ttq.h", incompleteStruct.} = object
   TtqWeight* {.importc: "ttq_weight", header: "ttq.h", incompleteStruct.} = object
   TtqStatus* = cint
+  TtqComm* {.importc: "ttq_comm", header: "ttq.h", incompleteStruct.} = object
+  TtqMoe* {.importc: "ttq_moe", header: "ttq.h", incompleteStruct.} = object
   TtqFormat* {.size: sizeof(cint).} = enum
-    kQ8_0 = 0, kQ4_K = 1, kQ6_K = 2
+    kQ8_0 = 0, kQ4_K = 1, kQ6_K = 2, kTQ3 = 3
   TtqDtype* {.size: sizeof(cint).} = enum
     kTtqBF16 = 0, kTtqF16 = 1, kTtqF32 = 2
   TtqShard* {.importc: "ttq_shard", header: "ttq.h", bycopy.} = object
@@ -44,6 +46,48 @@ proc ttq_rope_kv_append(ctx: ptr TtqCtx, qkv: pointer, dt: TtqDtype, B, ldQkv: i
                         stream: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
 proc ttq_decode_attention(ctx: ptr TtqCtx, q, kCache, vCache: pointer, dt: TtqDtype, B: int64, hq, hkv, d: int32,
                           ctxLen, nCtx: int64, outp: pointer, stream: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
+
+# -- the rest of the C ABI (include/ttq.h), bound one to one ------------------------------------------------
+proc ttq_status_string(s: TtqStatus): cstring {.importc, cdecl, header: "ttq.h".}
+proc ttq_version(): cstring {.importc, cdecl, header: "ttq.h".}
+proc ttq_block_elems(fmt: TtqFormat): int64 {.importc, cdecl, header: "ttq.h".}
+proc ttq_block_bytes(fmt: TtqFormat): int64 {.importc, cdecl, header: "ttq.h".}
+proc ttq_packed_bytes(fmt: TtqFormat, N, K: int64): int64 {.importc, cdecl, header: "ttq.h".}
+proc ttq_weight_create_device(ctx: ptr TtqCtx, fmt: TtqFormat, N, K: int64, devBlocks: pointer, nbytes: csize_t,
+                              stream: pointer, w: ptr ptr TtqWeight): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_weight_info(w: ptr TtqWeight, fmt: ptr int32, N, K: ptr int64): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_weight_bytes(w: ptr TtqWeight): int64 {.importc, cdecl, header: "ttq.h".}
+proc ttq_dequantize(ctx: ptr TtqCtx, w: ptr TtqWeight, devOut: ptr cfloat, ld: int64,
+                    stream: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_linear_forward_host(ctx: ptr TtqCtx, w: ptr TtqWeight, xHost: pointer, xDt: TtqDtype, M, ldx: int64,
+                             biasHost: pointer, biasDt: TtqDtype, yHost: pointer, yDt: TtqDtype,
+                             ldy: int64): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_device_status(ctx: ptr TtqCtx, stream: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_linear_forward_static(w: ptr TtqWeight, x: pointer, xDt: TtqDtype, M, ldx: int64, bias: pointer,
+                               biasDt: TtqDtype, y: pointer, yDt: TtqDtype, ldy: int64, stream: pointer,
+                               errbuf: cstring, errbufLen: csize_t): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_static_status(stream: pointer, errbuf: cstring, errbufLen: csize_t): TtqStatus {.importc, cdecl, header: "ttq.h".}
+# tensor parallelism: exchange buffers and the row-parallel linear with the sum over ranks fused in
+proc ttq_comm_create(ctx: ptr TtqCtx, rank, world: cint, nCap: int64, mCap: cint, comm: ptr ptr TtqComm,
+                     ipcHandleOut: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_comm_connect(comm: ptr TtqComm, allHandles: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_comm_local_buffer(comm: ptr TtqComm, baseOut: ptr pointer, bytesOut: ptr csize_t): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_comm_connect_pointers(comm: ptr TtqComm, bases: ptr pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_comm_set_wait_limit(comm: ptr TtqComm, polls: int64): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_comm_destroy(comm: ptr TtqComm): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_linear_forward_allreduce(ctx: ptr TtqCtx, w: ptr TtqWeight, x: pointer, xDt: TtqDtype, M, ldx: int64,
+                                  bias: pointer, biasDt: TtqDtype, y: pointer, yDt: TtqDtype, ldy: int64,
+                                  comm: ptr TtqComm, stream: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
+# mixture-of-experts layer on the grouped Q4_K GEMM
+proc ttq_moe_create(ctx: ptr TtqCtx, nExperts: int32, gateUp, down: ptr ptr TtqWeight, maxTokens: int64, topK: int32,
+                    moe: ptr ptr TtqMoe): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_moe_destroy(moe: ptr TtqMoe): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_moe_forward(ctx: ptr TtqCtx, moe: ptr TtqMoe, x: pointer, xDt: TtqDtype, T, ldx: int64, topkIds: ptr int32,
+                     topkWeights: ptr cfloat, y: pointer, yDt: TtqDtype, ldy: int64,
+                     stream: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
+# introspection
+proc ttq_trace_read(ctx: ptr TtqCtx, outp: ptr uint64, maxEntries: int64, nEntries: ptr int64): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_launch_count(ctx: ptr TtqCtx): int64 {.importc, cdecl, header: "ttq.h".}
 
 template check(ctx: ptr TtqCtx, rc: TtqStatus) =
   ## Non-zero status -> ValueError, the exception style of the reference's own loaders

@@ -30,6 +30,20 @@ def test_binding_table_covers_header():
     assert sorted(_lib.SIGNATURES) == header_functions()
 
 
+def test_nim_binding_covers_header():
+    """The Nim side (uncompiled here: no Nim toolchain) imports every function the header declares."""
+    nim = open(os.path.join(ROOT, "tattletale_b200", "nim", "quant_linear.nim")).read()
+    bound = set(re.findall(r"proc (ttq_\w+)\(", nim))
+    assert sorted(bound) == header_functions()
+
+
+def test_new_entry_points_reject_null_handles():
+    lib = _lib.load()
+    assert lib.ttq_comm_local_buffer(None, None, None) == 1
+    assert lib.ttq_comm_connect_pointers(None, None) == 1
+    assert lib.ttq_comm_set_wait_limit(None, 10) == 1
+
+
 def test_format_facts():
     lib = _lib.load()
     for fmt in (_lib.FMT_Q8_0, _lib.FMT_Q4_K, _lib.FMT_Q6_K):

@@ -98,3 +98,13 @@ def test_argument_errors(ctx):
     h = torch.zeros(2, 100, device="cuda", dtype=torch.bfloat16)
     with pytest.raises(ttq.TtqError):
         ttq.add_rmsnorm(ctx, h, None, torch.ones(100, device="cuda", dtype=torch.bfloat16), 1e-5)  # H % 8
+    # a V cache that is an 8-byte-offset view of a larger buffer: refused on the host, before any launch (the kernel
+    # reads V rows as 16-byte vectors)
+    q = torch.zeros(1, 4, 128, device="cuda", dtype=torch.bfloat16)
+    kc = torch.zeros(1, 4, 16, 128, device="cuda", dtype=torch.bfloat16)
+    big = torch.zeros(4 * 16 * 128 + 8, device="cuda", dtype=torch.bfloat16)
+    v_off = big[4:4 + 4 * 16 * 128].view(1, 4, 16, 128)
+    assert v_off.data_ptr() % 16 == 8
+    with pytest.raises(ttq.TtqError) as ei:
+        ttq.decode_attention(ctx, q, kc, v_off, 8)
+    assert ei.value.status == 1  # TTQ_ERR_INVALID_ARG

@@ -1,4 +1,4 @@
-"""Tensor-core (tcgen05) dequant-GEMM for M > 16 against the CPU checker, through the C ABI.
+"""Tensor-core (tcgen05) dequant-GEMM (Q4_K beyond 16 rows, Q8_0 / Q6_K from 9) against the CPU checker, through the C ABI.
 
 Weights are expanded to fp16 before the MMA and activations are converted to fp16, so the expected
 relative L2 error is a few 1e-4 (bar: 1e-3, fp32 accumulation in tensor memory)."""
@@ -68,10 +68,10 @@ def test_same_rows_give_same_result_as_decode_path(ctx):
 
 
 @pytest.mark.parametrize("fmt", [ttq.FMT_Q8_0, ttq.FMT_Q6_K], ids=["q8_0", "q6_k"])
-@pytest.mark.parametrize("n,k,m", [(256, 512, 33), (130, 768, 200), (512, 1024, 300), (100, 256, 64)])
-def test_formats_without_fused_gemm_expand_then_multiply(ctx, fmt, n, k, m):
-    """Q8_0 and Q6_K batches beyond two decode passes: whole-weight expansion to fp16 images + the plain
-    tensor-core GEMM (both operands bulk-copied)."""
+@pytest.mark.parametrize("n,k,m", [(256, 512, 33), (130, 768, 200), (512, 1024, 300), (100, 256, 64), (272, 2304, 9), (4096, 1024, 40)])
+def test_q8_0_and_q6_k_fused_dequant_gemm(ctx, fmt, n, k, m):
+    """Q8_0 and Q6_K batches from 9 rows: the same tcgen05 kernel as Q4_K, its dequant warps expanding int8 values
+    (Q8_0) or nibble + 2-bit planes (Q6_K) to fp16 in shared memory; no whole-weight expansion."""
     from gpu_util import OFMT
 
     blocks = make_weight(fmt, n, k, seed=n + k + m + fmt)
@@ -81,7 +81,7 @@ def test_formats_without_fused_gemm_expand_then_multiply(ctx, fmt, n, k, m):
     c0 = ctx.launch_count
     y = lin.forward(x.cuda(), out_dtype=torch.float32)
     ctx.check_device_status()
-    assert ctx.launch_count - c0 <= 4  # expansion, activation images, GEMM (+ split-K sum)
+    assert ctx.launch_count - c0 <= 3  # activation images, GEMM (+ split-K sum)
     want = oracle.linear(OFMT[fmt], blocks, x_bits(x), oracle.BF16, bias.numpy())
     assert rel_l2(y.cpu().numpy(), want) < TOL
     lin.close()
