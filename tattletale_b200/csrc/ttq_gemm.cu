@@ -903,36 +903,96 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
             p.splits = splits;
             p.ws = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(xh) + ((xh_bytes + 255) & ~(size_t)255));
         }
-        if (plain) {
-            if (BM == 64) e = launch_cfg<64, 2, GM_PLAIN>(p, sms, st);
-            else if (BM == 128) e = launch_cfg<128, 2, GM_PLAIN>(p, sms, st);
-            else e = launch_cfg<256, 2, GM_PLAIN>(p, sms, st);
-        } else if (fmt == TTQ_FMT_Q8_0) {
-            // (these formats always take two sub-tiles: the single sub-tile variant pays off on the many small tiles of
-            // the grouped Q4_K GEMM, which they do not serve)
-            if (BM == 64) e = launch_cfg<64, 2, GM_Q8_0>(p, sms, st);
-            else if (BM == 128) e = launch_cfg<128, 2, GM_Q8_0>(p, sms, st);
-            else e = launch_cfg<256, 2, GM_Q8_0>(p, sms, st);
-        } else if (fmt == TTQ_FMT_Q6_K) {
-            if (BM == 64) e = launch_cfg<64, 2, GM_Q6K>(p, sms, st);
-            else if (BM == 128) e = launch_cfg<128, 2, GM_Q6K>(p, sms, st);
-            else e = launch_cfg<256, 2, GM_Q6K>(p, sms, st);
-        } else if (nsub == 2) {
-            if (BM == 64) e = launch_cfg<64, 2>(p, sms, st);
-            else if (BM == 128) e = launch_cfg<128, 2>(p, sms, st);
-            else e = launch_cfg<256, 2>(p, sms, st);
-        } else {
-            if (BM == 64) e = launch_cfg<64, 1>(p, sms, st);
-            else if (BM == 128) e = launch_cfg<128, 1>(p, sms, st);
-            else e = launch_cfg<256, 1>(p, sms, st);
+        auto run = [&](const GemmParams &q) -> cudaError_t {
+            if (plain) {
+                if (BM == 64) return launch_cfg<64, 2, GM_PLAIN>(q, sms, st);
+                if (BM == 128) return launch_cfg<128, 2, GM_PLAIN>(q, sms, st);
+                return launch_cfg<256, 2, GM_PLAIN>(q, sms, st);
+            }
+            if (fmt == TTQ_FMT_Q8_0) {
+                // (these formats always take two sub-tiles: the single sub-tile variant pays off on the many small tiles
+                // of the grouped Q4_K GEMM, which they do not serve)
+                if (BM == 64) return launch_cfg<64, 2, GM_Q8_0>(q, sms, st);
+                if (BM == 128) return launch_cfg<128, 2, GM_Q8_0>(q, sms, st);
+                return launch_cfg<256, 2, GM_Q8_0>(q, sms, st);
+            }
+            if (fmt == TTQ_FMT_Q6_K) {
+                if (BM == 64) return launch_cfg<64, 2, GM_Q6K>(q, sms, st);
+                if (BM == 128) return launch_cfg<128, 2, GM_Q6K>(q, sms, st);
+                return launch_cfg<256, 2, GM_Q6K>(q, sms, st);
+            }
+            if (nsub == 2) {
+                if (BM == 64) return launch_cfg<64, 2>(q, sms, st);
+                if (BM == 128) return launch_cfg<128, 2>(q, sms, st);
+                return launch_cfg<256, 2>(q, sms, st);
+            }
+            if (BM == 64) return launch_cfg<64, 1>(q, sms, st);
+            if (BM == 128) return launch_cfg<128, 1>(q, sms, st);
+            return launch_cfg<256, 1>(q, sms, st);
+        };
+        auto reduce = [&](const GemmParams &q) -> cudaError_t {
+            const int64_t total = Ms * q.N;
+            const unsigned rg = (unsigned)((total + 255) / 256 < sms * 8 ? (total + 255) / 256 : sms * 8);
+            return launch_pdl(splitk_reduce_kernel, dim3(rg), dim3(256), 0, st, (const float *)q.ws, q.splits, Ms, Mp, q.N, q.bias, q.bias_dt,
+                              (void *)q.y, q.y_dt, q.ldy);
+        };
+        // Ragged last round: with more output tiles than SMs, the tiles left over after the last full round keep a
+        // few SMs busy for a whole tile time.  The last weight-tile columns -- just enough of them that the rest fits
+        // one round less -- then go to a second launch of the same kernel with K cut into runs, spread over all SMs.
+        // Cost model in pipeline stages: a unit of iters/S stages also pays a fixed turnaround (accumulator drain +
+        // fp32 partial store, about 20 stages), the second launch a ramp of about 6, and the reduction pass reads
+        // every partial back.  Measured at 2048 rows: 4096 -> 28672 (896 tiles, 8 left over) gains a third of a tile
+        // time with 8 runs; 4096 -> 6144 (192 tiles, 44 left over) loses with any split and is left alone.
+        static const bool tail_on = env_flag("TTQ_GEMM_TAIL", true);
+        const int TN = 128 * nsub;
+        const int64_t n_tiles = (a.N + TN - 1) / TN, tiles = n_tiles * m_tiles;
+        int64_t tail_cols = 0;
+        int tail_splits = 1;
+        if (tail_on && !plain && splits == 1 && tiles > sms && tiles % sms != 0) {
+            const int64_t rounds = (tiles + sms - 1) / sms;
+            const int64_t cols = (tiles - (rounds - 1) * sms + m_tiles - 1) / m_tiles;  // columns that must leave the main launch
+            const double iters = (double)a.SBp * 4;
+            double best = 0.85 * (iters + 8.0);
+            const size_t xh_bytes = (size_t)Mp * Kp * sizeof(__half);
+            const size_t ws_cap = (size_t)xh_capacity * sizeof(__half) > xh_bytes ? (size_t)xh_capacity * sizeof(__half) - xh_bytes : 0;
+            for (int cand = 2; cand <= 16 && cols < n_tiles; cand++) {
+                if (a.SBp % cand || a.SBp / cand < 2) continue;
+                if ((size_t)cand * Mp * cols * TN * sizeof(float) > ws_cap) break;
+                const int64_t units = cols * m_tiles * cand;
+                const double cost = (double)((units + sms - 1) / sms) * (iters / cand + 20.0) + 6.0 + 0.08 * (double)units;
+                if (cost < best) {
+                    best = cost;
+                    tail_cols = cols;
+                    tail_splits = cand;
+                }
+            }
         }
+        if (tail_cols > 0) {
+            const int64_t n_main = (n_tiles - tail_cols) * TN;  // output features of the main launch
+            GemmParams q = p;
+            q.N = n_main; q.NT = n_main / TILE_ROWS;
+            e = run(q);
+            if (e != cudaSuccess) return e;
+            ++*launches;
+            q = p;
+            q.tiles = reinterpret_cast<const uint8_t *>(p.tiles) + (size_t)(n_main / TILE_ROWS) * a.SBp * tile_bytes(fmt);
+            q.N = a.N - n_main; q.NT = a.NT - n_main / TILE_ROWS;
+            if (a.bias != nullptr) q.bias = reinterpret_cast<const uint8_t *>(a.bias) + (size_t)n_main * (a.bias_dt == TTQ_DT_F32 ? 4 : 2);
+            q.y = reinterpret_cast<uint8_t *>(p.y) + (size_t)n_main * esz_y;
+            q.splits = tail_splits;
+            e = run(q);
+            if (e != cudaSuccess) return e;
+            ++*launches;
+            e = reduce(q);
+            if (e != cudaSuccess) return e;
+            ++*launches;
+            continue;
+        }
+        e = run(p);
         if (e != cudaSuccess) return e;
         ++*launches;
         if (splits > 1) {
-            const int64_t total = Ms * a.N;
-            const unsigned rg = (unsigned)((total + 255) / 256 < sms * 8 ? (total + 255) / 256 : sms * 8);
-            e = launch_pdl(splitk_reduce_kernel, dim3(rg), dim3(256), 0, st, (const float *)p.ws, splits, Ms, Mp, a.N, a.bias, a.bias_dt, p.y,
-                           a.y_dt, a.ldy);
+            e = reduce(p);
             if (e != cudaSuccess) return e;
             ++*launches;
         }

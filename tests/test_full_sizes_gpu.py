@@ -40,7 +40,10 @@ def test_q4k_llama_shapes_prefill_batches(ctx, idx):
     """Config 2 at M = 64 (all rows checked) and M = 2048 (64 sampled rows, all columns)."""
     k, n = LLAMA_SHAPES[idx]
     blocks = device_blocks(ttq.FMT_Q4_K, n, k, 2000 + idx)
-    lin = ttq.QuantLinear(ctx, ttq.FMT_Q4_K, blocks, k)
+    # a bias on the widest shape: at 2048 rows its last weight-tile column runs as a second, K-split launch whose
+    # bias, output and workspace offsets are checked this way
+    bias = torch.randn(n, generator=torch.Generator().manual_seed(2200 + idx)) * 0.5 if n == 28672 else None
+    lin = ttq.QuantLinear(ctx, ttq.FMT_Q4_K, blocks, k, bias=None if bias is None else bias.cuda())
     host = blocks.cpu().numpy()
     del blocks
     for m in (64, 2048):
@@ -50,6 +53,8 @@ def test_q4k_llama_shapes_prefill_batches(ctx, idx):
         assert torch.isfinite(y).all()
         rows = np.arange(m) if m <= 64 else np.sort(np.random.default_rng(m).choice(m, 64, replace=False))
         want = oracle.linear(oracle.Q4_K, host, x_bits(x[rows]), oracle.BF16)
+        if bias is not None:
+            want = want + bias.numpy()[None, :]
         assert rel_l2(y[rows].cpu().numpy(), want) < TOL, (k, n, m)
     lin.close()
 
