@@ -182,7 +182,7 @@ def workload_config(m: int, gpus: int):
         "workload": f"Llama-3-8B projection shapes, Q4_K, M={m} decode GEMV, {N_LAYERS} layers x 4 linears",
         "shapes_k_to_n": [[k, n] for _, k, n in SHAPES], "M": m, "layers": N_LAYERS,
         "parallelism": "single GPU" if gpus == 1 else f"tp{gpus} (column/row split; row-parallel sum fused into the GEMV "
-                       "over NVLink peer memory for M <= 4, NCCL all-reduce otherwise)",
+                       "over NVLink peer memory for M <= 16, NCCL all-reduce otherwise)",
         "l2": f"{N_LAYERS * 122683392 / 1e9:.2f} GB of weights per step, larger than L2: every step streams from HBM",
     }
 
@@ -330,6 +330,45 @@ def ours_arm(args):
         e2e = {"value": round(step_bytes / e2e_s / 1e9, 3), "unit": "GB/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_s * 1e3, 4), "steps": e2e_steps,
                "api": "ttq_linear_forward_host, one call per linear on pinned host buffers: the kernels read x and write y through the buffers' device mappings (no staging copy), failure flag in mapped host memory, one sync per call"}
+
+    if world > 1 and not args.no_e2e:
+        # every rank feeds its shard from pinned host memory and reads its result back: per linear one host -> device
+        # copy of the activations, the (row-parallel: fused-exchange) linear, one device -> host copy of the output;
+        # one synchronisation per step; wall clock, maximum over ranks
+        host = []
+        for entry in layers:
+            for name, lin, x, y in entry:
+                host.append((name, lin, x.cpu().pin_memory(), x, y, torch.empty(y.shape, dtype=y.dtype).pin_memory()))
+                h2d += x.numel() * x.element_size()
+                d2h += y.numel() * y.element_size()
+
+        def e2e_step():
+            for name, lin, xh, x, y, yh in host:
+                x.copy_(xh, non_blocking=True)
+                if name in ("o", "down"):
+                    if comm is not None:
+                        lin.forward_allreduce(x, comm, out=y)
+                    else:
+                        lin.forward(x, out=y)
+                        dist.all_reduce(y)
+                else:
+                    lin.forward(x, out=y)
+                yh.copy_(y, non_blocking=True)
+            torch.cuda.synchronize()
+
+        e2e_steps = max(3, min(args.steps, 50))
+        e2e_step()
+        dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        t = torch.tensor([(time.perf_counter() - t0) / e2e_steps], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+        e2e = {"value": round(step_bytes / e2e_s / 1e9, 3), "unit": "GB/s", "h2d_bytes_per_step": h2d * world,
+               "d2h_bytes_per_step": d2h * world, "ms_per_step": round(e2e_s * 1e3, 4), "steps": e2e_steps,
+               "api": "per rank and linear: pinned host -> device copy of x, QuantLinear.forward / forward_allreduce on the "
+                      "rank's shard, device -> pinned host copy of y; one sync per step; bytes summed over ranks"}
 
     # ---- per-shape breakdown (device-resident, cold L2: the 32 layers' copies are rotated)
     per_shape = {}

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libttq.so")
-SOURCES = ["ttq_api.cu", "ttq_repack.cu", "ttq_gemv.cu", "ttq_q4k_mma.cu", "ttq_gemm.cu", "ttq_moe.cu", "ttq_tq3.cu", "ttq_decode.cu"]
+SOURCES = ["ttq_api.cu", "ttq_repack.cu", "ttq_gemv.cu", "ttq_q4k_mma.cu", "ttq_q4k_umma.cu", "ttq_gemm.cu", "ttq_moe.cu", "ttq_tq3.cu", "ttq_decode.cu"]
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-I", os.path.join(ROOT, "include"),

@@ -538,6 +538,23 @@ static ttq_status linear_forward_impl(ttq_ctx *ctx, const ttq_weight *w, const v
         const char *v = getenv("TTQ_GEMM");
         return !(v && v[0] == '0');
     }();
+    // Q4_K, up to 8 rows: the integer tensor-memory kernel (TTQ_Q4K_UMMA=1; the maximum batch it takes is
+    // TTQ_Q4K_UMMA_MAX_M, default 8)
+    static const bool use_umma = env_flag("TTQ_Q4K_UMMA", false);
+    static const int64_t umma_max_m = []() -> int64_t {
+        const char *v = getenv("TTQ_Q4K_UMMA_MAX_M");
+        const int64_t n = v ? atoll(v) : 8;
+        return n < 0 ? 0 : (n > 8 ? 8 : n);
+    }();
+    if (w->fmt == TTQ_FMT_Q4_K && use_umma && M <= umma_max_m) {
+        a.x = x_dev; a.M = M; a.y = y_dev;
+        int launches = 0;
+        cudaError_t e = launch_q4k_umma(a, ctx->xq, ctx->xq_capacity_k, ctx->sms, ctx->dev_status, ctx->trace, ctx->split_ws,
+                                        ctx->split_ws_bytes, ctx->split_counters, ctx->split_counters_cap, st, &launches);
+        ctx->launches += launches;
+        if (e == cudaSuccess) return TTQ_OK;
+        if (e != cudaErrorNotSupported) return cuda_fail(ctx, e, "linear forward (Q4_K tensor-memory decode) launch");
+    }
     // Q4_K batches of 3 to 16 rows: one kernel (fp16 tensor-core instructions on exact integer operands, activations
     // converted inside the kernel).  Up to 2 rows the integer decode kernel below is faster, beyond 16 the tcgen05 path.
     // TTQ_Q4K_MMA=0 switches the kernel off.

@@ -56,9 +56,11 @@ struct XqRow {
     float *sum16;     // [Kp/16]
     float *sum32;     // [Kp/32]
     float *sx;        // [SBs]
+    // Order of the plane bytes inside each 32-wide sub-block: false = by K; true = position 16 h + 4 n + i holds
+    // K index 8 n + 4 h + i (n < 4, h < 2, i < 4), the order in which the tensor-memory decode kernel widens a packed
+    // tile into its operand rows.
+    bool interleaved = false;
 };
-
-__host__ __device__ constexpr int sx_stride(int64_t SBp) { return (int)((SBp + 3) & ~(int64_t)3); }
 
 // Raw 8 activations of one lane (loaded early so that several chunks' loads are in flight at once).
 struct RawChunk {
@@ -130,8 +132,17 @@ __device__ __forceinline__ void xprep_convert_vals(const float (&v)[8], int sb, 
                        d = __byte_perm(q[4 * i + 2] + 128, q[4 * i + 3] + 128, 0x0051);
         hiw[i] = __byte_perm(c, d, 0x5410);
     }
-    *reinterpret_cast<uint2 *>(dst.hi + k0) = make_uint2(hiw[0], hiw[1]);
-    *reinterpret_cast<uint2 *>(dst.lo + k0) = make_uint2(low[0], low[1]);
+    if (dst.interleaved) {
+        // this lane holds K indices 8 n .. 8 n + 7 of its sub-block, n = lane & 3: h = 0 for the first four, 1 for the rest
+        const int64_t seg = (int64_t)sb * TILE_K + 32 * (lane >> 2) + 4 * (lane & 3);
+        *reinterpret_cast<uint32_t *>(dst.hi + seg) = hiw[0];
+        *reinterpret_cast<uint32_t *>(dst.hi + seg + 16) = hiw[1];
+        *reinterpret_cast<uint32_t *>(dst.lo + seg) = low[0];
+        *reinterpret_cast<uint32_t *>(dst.lo + seg + 16) = low[1];
+    } else {
+        *reinterpret_cast<uint2 *>(dst.hi + k0) = make_uint2(hiw[0], hiw[1]);
+        *reinterpret_cast<uint2 *>(dst.lo + k0) = make_uint2(low[0], low[1]);
+    }
     const int s16 = s + __shfl_xor_sync(0xffffffffu, s, 1);
     const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);
     if ((lane & 1) == 0) dst.sum16[sb * 16 + (lane >> 1)] = (float)s16;
@@ -145,7 +156,7 @@ __device__ __forceinline__ void xprep_chunk(const void *xrow, int x_dt, int64_t 
 // Separate conversion pass: (Mpad x SBp) chunks, one warp each; rows >= M are written as zeros.
 __global__ void __launch_bounds__(GEMV_THREADS) xprep_kernel(const void *__restrict__ x, int x_dt, int64_t M,
                                                              int64_t Mpad, int64_t K, int64_t ldx, int64_t SBp,
-                                                             XqView xq, unsigned long long *trace, int gated) {
+                                                             XqView xq, unsigned long long *trace, int gated) {  // gated: bit 0 = gated activation, bit 1 = interleaved planes
     unsigned long long *te = trace_open(trace, 1);
     grid_launch_dependents();
     const int lane = threadIdx.x & 31;
@@ -157,7 +168,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) xprep_kernel(const void *__restr
     if (unit < M * SBp && x_dt != TTQ_DT_F32) {
         const int64_t pm = unit / SBp, psb = unit % SBp;
         const uint8_t *line = reinterpret_cast<const uint8_t *>(x) + (pm * ldx + psb * TILE_K) * 2 + (lane & 3) * 128;
-        if (lane < (gated ? 8 : 4) && psb * TILE_K + (lane & 3) * 64 < K)  // only lines that start inside the row
+        if (lane < ((gated & 1) ? 8 : 4) && psb * TILE_K + (lane & 3) * 64 < K)  // only lines that start inside the row
             asm volatile("prefetch.global.L2 [%0];" ::"l"(line + (lane >> 2) * K * 2));
     }
     grid_dependency_wait();  // the scratch planes may still be read by the preceding kernel
@@ -166,7 +177,8 @@ __global__ void __launch_bounds__(GEMV_THREADS) xprep_kernel(const void *__restr
     const int64_t m = unit / SBp;
     const int sb = (int)(unit % SBp);
     XqRow dst{xq.planes + (2 * m) * Kp, xq.planes + (2 * m + 1) * Kp, xq.sum16 + m * (Kp / 16),
-              xq.sum32 + m * (Kp / 32), xq.sx + m * sx_stride(SBp)};
+              xq.sum32 + m * (Kp / 32), xq.sx + m * sx_stride(SBp), (gated & 2) != 0};
+    gated &= 1;
     const void *xrow = nullptr;
     if (m < M) {
         const int esz = x_dt == TTQ_DT_F32 ? 4 : 2;
@@ -773,6 +785,14 @@ cudaError_t dispatch(GemvParams &p, int mode, int nw, int sms, cudaStream_t st) 
 
 }  // namespace
 
+// The separate activation pass: rows [0, M) of x become int8 planes, group sums and chunk scales in `xq`; rows
+// [M, Mpad) are written as zeros.
+cudaError_t launch_xprep(const LinearArgs &a, const XqView &xq, int64_t Mpad, unsigned long long *trace, cudaStream_t st, bool interleaved) {
+    const int64_t units = Mpad * a.SBp;
+    return launch_pdl(xprep_kernel, dim3((unsigned)((units + GEMV_WARPS - 1) / GEMV_WARPS)), dim3(GEMV_THREADS), 0, st, a.x, a.x_dt, a.M,
+                      Mpad, a.K, a.ldx, a.SBp, xq, trace, (a.gated ? 1 : 0) | (interleaved ? 2 : 0));
+}
+
 cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t xq_capacity_k, const uint8_t *zeros,
                         int sms, int *status, unsigned long long *trace, cudaStream_t st, int *launches, const CommView *comm) {
     GemvParams p{a, xq, zeros, 1, status, trace, {}};
@@ -796,10 +816,7 @@ cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t 
     const bool shared = mode != XSRC_GLOBAL;
     cudaError_t e = cudaSuccess;
     if (mode != XSRC_CONVERT) {
-        const int64_t Mpad = shared ? a.M : (a.M <= 4 ? 4 : (a.M <= 8 ? 8 : 16));
-        const int64_t units = Mpad * a.SBp;
-        e = launch_pdl(xprep_kernel, dim3((unsigned)((units + GEMV_WARPS - 1) / GEMV_WARPS)), dim3(GEMV_THREADS), 0, st, a.x,
-                       a.x_dt, a.M, Mpad, a.K, a.ldx, a.SBp, xq, trace, a.gated ? 1 : 0);
+        e = launch_xprep(a, xq, shared ? a.M : (a.M <= 4 ? 4 : (a.M <= 8 ? 8 : 16)), trace, st, false);
         if (e != cudaSuccess) return e;
         ++*launches;
     }

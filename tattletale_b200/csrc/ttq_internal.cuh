@@ -88,6 +88,9 @@ struct XqView {
     float *sx;        // [Mpad][SBp]
 };
 
+// row pitch (floats) of XqView::sx
+__host__ __device__ constexpr int sx_stride(int64_t SBp) { return (int)((SBp + 3) & ~(int64_t)3); }
+
 // Peer-memory exchange area of a row-parallel linear (tensor parallelism).  Passed by value to the decode
 // kernels; world <= 1 means "no exchange".  Every rank owns one buffer of 8-byte cells {value bits, epoch},
 //   cells [2][world][m_cap][n_cap]   partial outputs pushed by rank src, double-buffered by exchange parity,
@@ -281,6 +284,12 @@ cudaError_t launch_dequant(int fmt, const uint8_t *tiled, float *out, int64_t ld
 cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t xq_capacity_k, const uint8_t *zeros,
                         int sms, int *status, unsigned long long *trace, cudaStream_t st, int *launches,
                         const CommView *comm = nullptr);
+// (`interleaved`: plane bytes of a sub-block in the order of the tensor-memory decode kernel, see XqRow)
+cudaError_t launch_xprep(const LinearArgs &a, const XqView &xq, int64_t Mpad, unsigned long long *trace, cudaStream_t st, bool interleaved);
+// Q4_K decode linear on the integer tensor-memory path (tcgen05.mma kind::i8), M <= 8: the activation pass, then one
+// kernel (ttq_q4k_umma.cu).  `ws` / `counters` as for launch_q4k_mma.  cudaErrorNotSupported: take another path.
+cudaError_t launch_q4k_umma(const LinearArgs &a, const XqView &xq, int64_t xq_capacity_k, int sms, int *status, unsigned long long *trace,
+                            float *ws, size_t ws_bytes, unsigned *counters, int64_t counters_cap, cudaStream_t st, int *launches);
 // Q4_K decode linear on fp16 tensor-core instructions, M <= 16, activations converted inside the kernel
 // (ttq_q4k_mma.cu).  `ws` / `counters`: fp32 workspace and per-row-tile arrival counters (zero between launches)
 // for matrices whose K is split across CTAs.  cudaErrorNotSupported: the caller takes another path.
