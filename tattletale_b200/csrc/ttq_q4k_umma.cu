@@ -495,10 +495,10 @@ __global__ void __launch_bounds__(UM_THREADS, 1) q4k_umma_kernel(UmParams p) {
         if (tr) um_trace(p.trace, 2, t_begin, t_w0, t_w1, 0, n_items);
     } else {
         // ---------------------------------------------------------------- MMA issue
-        if (lane == 0) {
+        {
             bool alive = true;
             constexpr uint32_t idesc = um_idesc(NB);
-            const bool tr = p.trace != nullptr && blockIdx.x == 0;
+            const bool tr = p.trace != nullptr && blockIdx.x == 0 && lane == 0;
             unsigned long long t_begin = tr ? global_ns() : 0, t_w0 = 0, t_w1 = 0, t_w2 = 0, tt = 0, t_i = 0, t_c = 0;
             for (int li = 0; li < n_items; li++) {
                 const int slot = li % UM_SLOTS, bslot = li % UM_BSLOTS, accb = li % UM_NACC;
@@ -513,6 +513,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) q4k_umma_kernel(UmParams p) {
                 um_fence_after();
                 const uint32_t ab = a_u32 + (uint32_t)(slot * UM_A_BYTES), bs = b_u32 + (uint32_t)(bslot * L::B_BYTES);
                 const uint32_t td = tmem_base + (uint32_t)(accb * 8 * NB);
+                if (lane == 0) {
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
                     // sub-block j: K tile j >> 2, 32 bytes = 2 descriptor units along the swizzled row
@@ -524,6 +525,8 @@ __global__ void __launch_bounds__(UM_THREADS, 1) q4k_umma_kernel(UmParams p) {
                 um_commit(a_empty + 8 * slot);
                 um_commit(b_empty + 8 * bslot);
                 um_commit(acc_full + 8 * accb);
+                }
+                __syncwarp();
                 if (tr) t_c += (unsigned long long)clock64() - tt;
             }
             if (tr) um_trace(p.trace, 3, t_begin, t_w0, t_w1, t_w2, n_items);
