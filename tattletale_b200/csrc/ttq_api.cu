@@ -102,6 +102,7 @@ ttq_status cuda_fail(ttq_ctx *ctx, cudaError_t e, const char *what) {
 
 bool valid_fmt(int f) { return f == TTQ_FMT_Q8_0 || f == TTQ_FMT_Q4_K || f == TTQ_FMT_Q6_K || f == TTQ_FMT_TQ3; }
 constexpr int64_t TQ3_GEMV_MAX_M = 4;
+constexpr int64_t TQ3_MMA_MAX_M = 64;  // up to here the tensor-core decode kernel beats expansion + GEMM
 constexpr int64_t TQ3_SLAB = 512;  // rows of rotated activations / raw results the TQ3 scratch holds
 bool valid_dt(int d) { return d == TTQ_DT_BF16 || d == TTQ_DT_F16 || d == TTQ_DT_F32; }
 int dt_size(int d) { return d == TTQ_DT_F32 ? 4 : 2; }
@@ -181,7 +182,7 @@ ttq_status check_create_args(ttq_ctx *ctx, int fmt, int64_t N, int64_t K, const 
 }
 
 // y = out_scale * H_N(q . H_K(in_sign * x)) + bias in slabs of TQ3_SLAB rows: rotate in, multiply (decode kernel
-// for up to 32 rows, whole-weight expansion + plain tensor-core GEMM beyond), rotate out.
+// up to 4 rows, tensor-core decode kernel up to 64, whole-weight expansion + plain tensor-core GEMM beyond), rotate out.
 ttq_status tq3_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_dev, int x_dt, int64_t M, int64_t ldx, const void *bias_dev,
                        int bias_dt, void *y_dev, int y_dt, int64_t ldy, cudaStream_t st) {
     const int64_t N = w->N, K = w->K;
@@ -196,7 +197,11 @@ ttq_status tq3_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_dev, int
     }();
     // the decode-and-multiply kernel re-decodes every weight per 8 rows; beyond TQ3_GEMV_MAX_M rows one expansion
     // to fp16 and the tensor-core GEMM is cheaper
-    const bool gemm = M > TQ3_GEMV_MAX_M && use_gemm && ctx->wimg != nullptr &&
+    // 5 to TQ3_MMA_MAX_M rows: the tensor-core decode kernel (every weight decoded once, no expansion); TTQ_TQ3_MMA=0
+    // switches it off
+    static const bool use_mma = env_flag("TTQ_TQ3_MMA", true);
+    const bool mma = use_mma && M > TQ3_GEMV_MAX_M && M <= TQ3_MMA_MAX_M;
+    const bool gemm = !mma && M > TQ3_GEMV_MAX_M && use_gemm && ctx->wimg != nullptr &&
                       gemm_wimg_rows(N) * w->SBp * TILE_K <= ctx->wimg_capacity;
     cudaError_t e;
     if (gemm) {
@@ -208,7 +213,7 @@ ttq_status tq3_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_dev, int
         const int64_t Ms = (M - m0) < TQ3_SLAB ? (M - m0) : TQ3_SLAB;
         const uint8_t *xs = reinterpret_cast<const uint8_t *>(x_dev) + (size_t)m0 * ldx * dt_size(x_dt);
         uint8_t *ys = reinterpret_cast<uint8_t *>(y_dev) + (size_t)m0 * ldy * dt_size(y_dt);
-        e = launch_tq3_rotate(xs, x_dt, Ms, K, ldx, isign, nullptr, nullptr, TTQ_DT_F32, ctx->tq_x1, gemm ? TTQ_DT_F16 : TTQ_DT_F32, K, st);
+        e = launch_tq3_rotate(xs, x_dt, Ms, K, ldx, isign, nullptr, nullptr, TTQ_DT_F32, ctx->tq_x1, (gemm || mma) ? TTQ_DT_F16 : TTQ_DT_F32, K, st, mma);
         if (e != cudaSuccess) return cuda_fail(ctx, e, "input rotation launch");
         ctx->launches++;
         if (gemm) {
@@ -222,6 +227,10 @@ ttq_status tq3_forward(ttq_ctx *ctx, const ttq_weight *w, const void *x_dev, int
             e = launch_gemm(w->fmt, a, ctx->xh, ctx->xh_capacity, ctx->sms, ctx->dev_status, ctx->trace, st, &launches, ctx->wimg);
             ctx->launches += launches;
             if (e != cudaSuccess) return cuda_fail(ctx, e, "linear forward (plain GEMM) launch");
+        } else if (mma) {
+            e = launch_tq3_mma(packed, N, K, reinterpret_cast<const __half *>(ctx->tq_x1), (int)Ms, ctx->tq_y1, st);
+            if (e != cudaSuccess) return cuda_fail(ctx, e, "tensor-core decode-and-multiply launch");
+            ctx->launches++;
         } else {
             for (int64_t r0 = 0; r0 < Ms; r0 += TQ3_GEMV_MAX_M) {
                 const int rows = (int)((Ms - r0) < TQ3_GEMV_MAX_M ? (Ms - r0) : TQ3_GEMV_MAX_M);

@@ -250,8 +250,9 @@ inline int64_t tq3_packed_bytes(int64_t N, int64_t K) { return N * K * 3 / 8 + 2
 cudaError_t launch_tq3_decode(const uint8_t *packed, int64_t N, int64_t K, float *out, int64_t ld, cudaStream_t st);
 cudaError_t launch_tq3_wimg(const uint8_t *packed, int64_t N, int64_t K, __half *wimg, cudaStream_t st);
 cudaError_t launch_tq3_rotate(const void *in, int in_dt, int64_t M, int64_t C, int64_t ld_in, const uint8_t *sign, const __half *scale,
-                              const void *bias, int bias_dt, void *out, int out_dt, int64_t ld_out, cudaStream_t st);
+                              const void *bias, int bias_dt, void *out, int out_dt, int64_t ld_out, cudaStream_t st, bool fragments = false);
 cudaError_t launch_tq3_gemv(const uint8_t *packed, int64_t N, int64_t K, const float *x1, int rows, float *y1, cudaStream_t st);
+cudaError_t launch_tq3_mma(const uint8_t *packed, int64_t N, int64_t K, const __half *x1, int rows, float *y1, cudaStream_t st);
 
 // Decode-step kernels around the linears (ttq_decode.cu).
 cudaError_t launch_add_rmsnorm(void *h, const void *delta, const void *weight, int dt, int64_t M, int64_t H, int64_t ld_h, int64_t ld_delta,

@@ -12,6 +12,7 @@
 //   tq3_decode_kernel     q as fp32 [N][ld] (test hook, bit-exact) or as fp16 tile images for the plain GEMM
 //   tq3_rotate_kernel     Hadamard-128 of activation rows (signs in, fp32 | fp16 out) and of result rows
 //                         (scale and bias out); one warp per 128 block, four values per lane
+//   tq3_mma_kernel<NA>    5 <= M <= 64: decoded weights as the B operand of mma.sync m16n8k16, every weight decoded once
 //   tq3_gemv_kernel<MR>   M <= 4 rows per pass: one CTA per 16-row band, its 8 warps split K; a lane owns two
 //                         rows of a tile (32 weights = 3 words of the stream), decodes each weight with one
 //                         multiply and one byte-sum and accumulates in fp32
@@ -89,11 +90,13 @@ __global__ void __launch_bounds__(256) tq3_decode_kernel(const uint8_t *__restri
 
 // One warp per (row, block of 128): out = H128(in * sign) * scale + bias.
 //   in:  [M][ld_in] of in_dt;  sign: bit per column or nullptr;  scale: fp16 per column or nullptr;
-//   bias: per column of bias_dt or nullptr;  out: [M][ld_out] of out_dt.
+//   bias: per column of bias_dt or nullptr;  out: [M][ld_out] of out_dt, or (frag != 0, fp16, no scale / bias) the
+//   A-operand fragments of mma.sync m16n8k16 for tq3_mma_kernel: [group of 16 rows][K tile of 16][lane 4g + t][register]
+//   with register = (row >> 3 & 1) + 2 (k >> 3 & 1) holding columns 2t, 2t + 1 (+ 8) of row g (+ 8).
 __global__ void __launch_bounds__(256) tq3_rotate_kernel(const void *__restrict__ in, int in_dt, int64_t M, int64_t C, int64_t ld_in,
                                                          const uint8_t *__restrict__ sign, const __half *__restrict__ scale,
                                                          const void *__restrict__ bias, int bias_dt, void *__restrict__ out, int out_dt,
-                                                         int64_t ld_out) {
+                                                         int64_t ld_out, int frag) {
     grid_launch_dependents();
     grid_dependency_wait();
     const int lane = threadIdx.x & 31;
@@ -119,6 +122,14 @@ __global__ void __launch_bounds__(256) tq3_rotate_kernel(const void *__restrict_
                 const float o = __shfl_xor_sync(0xffffffffu, v[i], s);
                 v[i] = (lane & s) ? o - v[i] : v[i] + o;
             }
+        }
+        if (frag) {
+            const int64_t kt = c0 >> 4;
+            const int kk = (int)(c0 & 15), t0 = (kk & 7) >> 1, reg = (int)((m >> 3) & 1) + 2 * (kk >> 3);
+            __half2 *dst = reinterpret_cast<__half2 *>(out) + ((((m >> 4) * (C >> 4) + kt) * 32 + 4 * (m & 7) + t0) * 4 + reg);
+            dst[0] = __floats2half2_rn(v[0] * 0.08838834764831845f, v[1] * 0.08838834764831845f);
+            dst[4] = __floats2half2_rn(v[2] * 0.08838834764831845f, v[3] * 0.08838834764831845f);  // next lane of the fragment
+            continue;
         }
 #pragma unroll
         for (int i = 0; i < 4; i++) {
@@ -199,6 +210,101 @@ __global__ void __launch_bounds__(256) tq3_gemv_kernel(const uint8_t *__restrict
     }
 }
 
+// y1 [M][N] (fp32) = q . x1^T for M <= 16 NA rows of x1 [.][K] (fp16, already rotated) on tensor-core instructions
+// (mma.sync m16n8k16, fp32 accumulate): the decoded weights are the B operand, so a lane decodes exactly the four
+// weights of its fragment -- row g (first instruction) or g + 8 (second) of the tile, columns 2t, 2t+1, 2t+8,
+// 2t+9 -- from the 64 stream bits that start at the row (48 bits per row; the windows of the last columns reach
+// 13 bits into the next row, and past the end of the tile the stream is zero).  A decoded value is an exact
+// integer in [-510, 510]: the byte sum of two weights lands on the mantissas of a {1024, 1024} fp16 pair through
+// the dp4a accumulator, one HSUB2 removes 1024 + 510.  The activation rows are the A operand (16 rows per
+// instruction; the rotation kernel writes them in fragment order, so a lane needs one 16-byte load per K tile).
+// One CTA per 16-row band, its 8 warps split K; every weight is decoded once for all M rows.
+template <int NA>
+__global__ void __launch_bounds__(256) tq3_mma_kernel(const uint8_t *__restrict__ tiles, int64_t N, int64_t K, const __half *__restrict__ x1,
+                                                      int M, float *__restrict__ y1) {
+    __shared__ float red[8][NA * 16][16];  // [warp][activation row][weight row]
+    grid_launch_dependents();
+    grid_dependency_wait();  // the rotated activations come from the preceding kernel
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int64_t tk = K / 16, band = blockIdx.x;
+    const uint8_t *band_base = tiles + band * tk * TQ3_TILE_BYTES;
+    const int64_t t_begin = tk * warp / 8, t_end = tk * (warp + 1) / 8;
+    float c[NA][2][4];
+#pragma unroll
+    for (int a = 0; a < NA; a++)
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) c[a][h][i] = 0.f;
+    // row g starts at byte 6 g of the tile: word 6 g / 4 (rounded down), bit offset 0 or 16; rows g and g + 8 share it
+    const int sh = (g & 1) * 16;
+    const int w_lo = (6 * g) >> 2, w_hi = (6 * (g + 8)) >> 2;
+    const uint32_t k1534 = 0x65FE65FEu;  // {1534, 1534} as fp16
+    // activation fragments (written by the rotation kernel in fragment order): 16 bytes per lane and K tile; rows
+    // beyond M hold stale data and are masked off
+    const uint4 *xf[NA];
+    uint32_t keep[NA][2];
+#pragma unroll
+    for (int a = 0; a < NA; a++) {
+        xf[a] = reinterpret_cast<const uint4 *>(x1) + (int64_t)a * tk * 32 + lane;
+        keep[a][0] = 16 * a + g < M ? 0xffffffffu : 0u;
+        keep[a][1] = 16 * a + g + 8 < M ? 0xffffffffu : 0u;
+    }
+#pragma unroll 2
+    for (int64_t tile = t_begin; tile < t_end; tile++) {
+        const uint32_t *tw = reinterpret_cast<const uint32_t *>(band_base + tile * TQ3_TILE_BYTES);
+        uint32_t b[2][2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int w0 = h == 0 ? w_lo : w_hi;
+            const uint32_t q0 = __ldg(tw + w0), q1 = w0 + 1 < 24 ? __ldg(tw + w0 + 1) : 0u, q2 = w0 + 2 < 24 ? __ldg(tw + w0 + 2) : 0u;
+            // the row's 64 stream bits, then shifted so that this lane's first window starts at bit 0
+            uint32_t lo = __funnelshift_r(q0, q1, sh), hi = __funnelshift_r(q1, q2, sh);
+            const int o = 6 * t;
+            lo = __funnelshift_r(lo, hi, o);
+            hi >>= o;
+            const uint32_t s0 = lo & 0xffffu, s1 = (lo >> 3) & 0xffffu;
+            const uint32_t s2 = __funnelshift_r(lo, hi, 24) & 0xffffu, s3 = __funnelshift_r(lo, hi, 27) & 0xffffu;
+            const uint32_t p0 = __dp4a(s0 * 2654435761u, 0x01010101u, 0x64006400u), p1 = __dp4a(s1 * 2654435761u, 0x01010101u, 0u);
+            const uint32_t p2 = __dp4a(s2 * 2654435761u, 0x01010101u, 0x64006400u), p3 = __dp4a(s3 * 2654435761u, 0x01010101u, 0u);
+            const uint32_t v0 = p0 + (p1 << 16), v1 = p2 + (p3 << 16);
+            const __half2 d0 = __hsub2(*reinterpret_cast<const __half2 *>(&v0), *reinterpret_cast<const __half2 *>(&k1534));
+            const __half2 d1 = __hsub2(*reinterpret_cast<const __half2 *>(&v1), *reinterpret_cast<const __half2 *>(&k1534));
+            b[h][0] = *reinterpret_cast<const uint32_t *>(&d0);
+            b[h][1] = *reinterpret_cast<const uint32_t *>(&d1);
+        }
+#pragma unroll
+        for (int a = 0; a < NA; a++) {
+            const uint4 xa = __ldg(xf[a] + tile * 32);
+            const uint32_t a0 = xa.x & keep[a][0], a1 = xa.y & keep[a][1], a2 = xa.z & keep[a][0], a3 = xa.w & keep[a][1];
+#pragma unroll
+            for (int h = 0; h < 2; h++)
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                             : "+f"(c[a][h][0]), "+f"(c[a][h][1]), "+f"(c[a][h][2]), "+f"(c[a][h][3])
+                             : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b[h][0]), "r"(b[h][1]));
+        }
+    }
+    // c[a][h]: activation rows 16 a + g (values 0, 1) and + 8 (values 2, 3), weight rows 8 h + 2 t, + 1
+#pragma unroll
+    for (int a = 0; a < NA; a++)
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            red[warp][16 * a + g][8 * h + 2 * t] = c[a][h][0];
+            red[warp][16 * a + g][8 * h + 2 * t + 1] = c[a][h][1];
+            red[warp][16 * a + g + 8][8 * h + 2 * t] = c[a][h][2];
+            red[warp][16 * a + g + 8][8 * h + 2 * t + 1] = c[a][h][3];
+        }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 16 * M; i += blockDim.x) {
+        const int m = i >> 4, r = i & 15;
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; w++) s += red[w][m][r];
+        y1[(int64_t)m * N + band * 16 + r] = s * TQ3_UNIT;
+    }
+}
+
 unsigned grid_of(int64_t items, int per_block, int cap) {
     int64_t b = (items + per_block - 1) / per_block;
     if (b < 1) b = 1;
@@ -219,9 +325,9 @@ cudaError_t launch_tq3_wimg(const uint8_t *packed, int64_t N, int64_t K, __half 
 }
 
 cudaError_t launch_tq3_rotate(const void *in, int in_dt, int64_t M, int64_t C, int64_t ld_in, const uint8_t *sign, const __half *scale,
-                              const void *bias, int bias_dt, void *out, int out_dt, int64_t ld_out, cudaStream_t st) {
+                              const void *bias, int bias_dt, void *out, int out_dt, int64_t ld_out, cudaStream_t st, bool fragments) {
     return launch_pdl(tq3_rotate_kernel, dim3(grid_of(M * (C / 128), 8, device_sms() * 16)), dim3(256), 0, st, in, in_dt, M, C, ld_in, sign, scale, bias,
-                      bias_dt, out, out_dt, ld_out);
+                      bias_dt, out, out_dt, ld_out, fragments ? 1 : 0);
 }
 
 // `rows` (1..4) rows of x1 [.][K] -> y1 [.][N]
@@ -235,6 +341,16 @@ cudaError_t launch_tq3_gemv(const uint8_t *packed, int64_t N, int64_t K, const f
         case 4: return launch_pdl(tq3_gemv_kernel<4>, dim3(grid), blk, 0, st, packed, N, K, x1, y1);
         default: return cudaErrorInvalidValue;
     }
+}
+
+// `rows` (1..64) rows of x1 [.][K] (fp16) -> y1 [.][N] on the tensor-core decode kernel
+cudaError_t launch_tq3_mma(const uint8_t *packed, int64_t N, int64_t K, const __half *x1, int rows, float *y1, cudaStream_t st) {
+    const unsigned grid = (unsigned)(N / 16);
+    const dim3 blk(256);
+    if (rows <= 16) return launch_pdl(tq3_mma_kernel<1>, dim3(grid), blk, 0, st, packed, N, K, x1, rows, y1);
+    if (rows <= 32) return launch_pdl(tq3_mma_kernel<2>, dim3(grid), blk, 0, st, packed, N, K, x1, rows, y1);
+    if (rows <= 64) return launch_pdl(tq3_mma_kernel<4>, dim3(grid), blk, 0, st, packed, N, K, x1, rows, y1);
+    return cudaErrorInvalidValue;
 }
 
 }  // namespace ttq

@@ -58,8 +58,10 @@ def test_decode_and_multiply_rows(ctx, m):
     lin.close()
 
 
-@pytest.mark.parametrize("m", [5, 8, 16, 33, 100, 300, 700])
-def test_expansion_and_tensor_core_gemm(ctx, m):
+@pytest.mark.parametrize("m", [5, 8, 16, 17, 33, 64, 65, 100, 300, 700])
+def test_tensor_core_paths(ctx, m):
+    """5..64 rows: decoded weights as the B operand of mma.sync (every weight decoded once, activations in fragment
+    order); beyond: whole-weight expansion + plain tcgen05 GEMM."""
     n, k = 384, 640
     packed = random_packed(n, k, seed=60 + m)
     bias = torch.from_numpy(np.random.default_rng(m).normal(0, 0.1, n).astype(np.float32))
