@@ -125,8 +125,8 @@ ttq_status alloc_weight(ttq_ctx *ctx, int fmt, int64_t N, int64_t K, ttq_weight 
         return cuda_fail(ctx, e, "cudaMalloc(tiled weight)");
     }
     if (!gemm_supported(fmt)) {
-        // larger batches of this format run as expansion to fp16 + plain tensor-core GEMM: make sure the
-        // context's expansion scratch holds this matrix (load time; forward never allocates)
+        // (the trellis format) batches beyond the decode kernels run as expansion to fp16 + plain tensor-core GEMM:
+        // make sure the context's expansion scratch holds this matrix (load time; forward never allocates)
         const int64_t need = gemm_wimg_rows(N) * w->SBp * TILE_K;
         if (need > ctx->wimg_capacity) {
             cudaDeviceSynchronize();
@@ -595,21 +595,6 @@ static ttq_status linear_forward_impl(ttq_ctx *ctx, const ttq_weight *w, const v
         cudaError_t e = launch_gemm(w->fmt, a, ctx->xh, ctx->xh_capacity, ctx->sms, ctx->dev_status, ctx->trace, st, &launches);
         ctx->launches += launches;
         if (e != cudaSuccess) return cuda_fail(ctx, e, "linear forward (GEMM) launch");
-        return TTQ_OK;
-    }
-    // formats without a fused dequant GEMM: beyond two decode passes, expand the weight to fp16 once and run
-    // the plain tensor-core GEMM on it
-    constexpr int64_t PLAIN_MIN_M = 2 * MAX_GEMV_M + 1;
-    if (M >= PLAIN_MIN_M && use_gemm && !gemm_supported(w->fmt) && ctx->wimg != nullptr &&
-        gemm_wimg_rows(w->N) * w->SBp * TILE_K <= ctx->wimg_capacity) {
-        cudaError_t e = launch_wimg(w->fmt, w->tiles, w->N, w->K, w->SBp, ctx->wimg, st);
-        if (e != cudaSuccess) return cuda_fail(ctx, e, "weight expansion launch");
-        ctx->launches++;
-        a.x = x_dev; a.M = M; a.y = y_dev;
-        int launches = 0;
-        e = launch_gemm(w->fmt, a, ctx->xh, ctx->xh_capacity, ctx->sms, ctx->dev_status, ctx->trace, st, &launches, ctx->wimg);
-        ctx->launches += launches;
-        if (e != cudaSuccess) return cuda_fail(ctx, e, "linear forward (plain GEMM) launch");
         return TTQ_OK;
     }
     // decode path; more rows than one pass holds are processed in groups of MAX_GEMV_M

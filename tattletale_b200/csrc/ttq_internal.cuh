@@ -300,13 +300,12 @@ cudaError_t launch_q4k_mma(const LinearArgs &a, int sms, int *status, unsigned l
 constexpr int TTQ_TRACE_ENTRIES = 8192;
 // tcgen05 dequant-GEMM for M > MAX_GEMV_M (formats for which gemm_supported() is true)
 bool gemm_supported(int fmt);
-// `wimg` != nullptr selects the plain mode: weights of any format, expanded beforehand by launch_wimg.
+// `wimg` != nullptr selects the plain mode: both operands are fp16 tile images (the trellis format's expansion).
 cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_capacity, int sms, int *status,
                         unsigned long long *trace, cudaStream_t st, int *launches, const __half *wimg = nullptr);
-// fp16 tile images of a whole weight matrix (any format) for the plain GEMM mode: [Kp / 64][Np / 8][1024 B],
-// Np = gemm_wimg_rows(N); rows >= N and columns >= K are zero.
+// rows of the fp16 tile images the plain GEMM mode reads: [Kp / 64][Np / 8][1024 B], Np = gemm_wimg_rows(N); rows >= N
+// and columns >= K are zero (written by launch_tq3_wimg)
 int64_t gemm_wimg_rows(int64_t N);
-cudaError_t launch_wimg(int fmt, const uint8_t *tiled, int64_t N, int64_t K, int64_t SBp, __half *wimg, cudaStream_t st);
 cudaError_t launch_silu_and_mul(const void *in, int dt, int64_t M, int64_t H, int64_t ld_in, void *out,
                                 int64_t ld_out, cudaStream_t st);
 

@@ -171,35 +171,6 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t *__restrict_
     }
 }
 
-// Expansion of a packed matrix into the fp16 tile images the tensor-core GEMM reads in its plain mode: the same
-// [stage][row atom][1024 B] layout, 128-byte swizzle and in-chunk K order as the activation images, so that
-// one stage of 256 output rows is a single contiguous 32 KB run.  Values are dequant_elem's fp32 results
-// rounded to fp16.
-template <int FMT>
-__global__ void __launch_bounds__(256) wimg_kernel(const uint8_t *__restrict__ tiled, int64_t N, int64_t Np, int64_t K, int64_t SBp,
-                                                   __half *__restrict__ wimg) {
-    constexpr int TB = tile_bytes(FMT);
-    const int64_t total = Np * (SBp * TILE_K / 8);
-    for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < total; c += (int64_t)gridDim.x * blockDim.x) {
-        const int j = (int)(c & 7);
-        const int64_t n = (c >> 3) % Np, it = (c >> 3) / Np;
-        const int64_t sb = it >> 2;
-        const int s = (int)(it & 3);
-        const int kk0 = 32 * j + 8 * s;  // inside the 256-wide K tile
-        __half out[8];
-#pragma unroll
-        for (int q = 0; q < 8; q++) {
-            const int i = (q & 4) + ((q & 1) << 1) + ((q & 2) >> 1);  // K order inside a chunk: 0 2 1 3 | 4 6 5 7
-            float v = 0.f;
-            if (n < N && sb * TILE_K + kk0 + i < K)
-                v = dequant_elem<FMT>(tiled + ((n / TILE_ROWS) * SBp + sb) * TB, (int)(n % TILE_ROWS), kk0 + i);
-            out[q] = __float2half_rn(v);
-        }
-        const int64_t dst = ((it * (Np >> 3) + (n >> 3)) << 10) + ((n & 7) << 7) + ((int64_t)(j ^ (int)(n & 7)) << 4);
-        *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(wimg) + dst) = *reinterpret_cast<const uint4 *>(out);
-    }
-}
-
 template <typename T>
 __global__ void __launch_bounds__(256) silu_and_mul_kernel(const T *__restrict__ in, T *__restrict__ out,
                                                            int64_t M, int64_t H, int64_t ld_in, int64_t ld_out) {
@@ -237,15 +208,6 @@ cudaError_t launch_dequant(int fmt, const uint8_t *tiled, float *out, int64_t ld
     if (fmt == TTQ_FMT_Q4_K) dequant_kernel<TTQ_FMT_Q4_K><<<grid, 256, 0, st>>>(tiled, out, ld, N, K, SBp);
     else if (fmt == TTQ_FMT_Q8_0) dequant_kernel<TTQ_FMT_Q8_0><<<grid, 256, 0, st>>>(tiled, out, ld, N, K, SBp);
     else dequant_kernel<TTQ_FMT_Q6_K><<<grid, 256, 0, st>>>(tiled, out, ld, N, K, SBp);
-    return cudaGetLastError();
-}
-
-cudaError_t launch_wimg(int fmt, const uint8_t *tiled, int64_t N, int64_t K, int64_t SBp, __half *wimg, cudaStream_t st) {
-    const int64_t Np = gemm_wimg_rows(N);
-    const int grid = grid_for(Np * (SBp * TILE_K / 8), 256, device_sms() * 32);
-    if (fmt == TTQ_FMT_Q4_K) wimg_kernel<TTQ_FMT_Q4_K><<<grid, 256, 0, st>>>(tiled, N, Np, K, SBp, wimg);
-    else if (fmt == TTQ_FMT_Q8_0) wimg_kernel<TTQ_FMT_Q8_0><<<grid, 256, 0, st>>>(tiled, N, Np, K, SBp, wimg);
-    else wimg_kernel<TTQ_FMT_Q6_K><<<grid, 256, 0, st>>>(tiled, N, Np, K, SBp, wimg);
     return cudaGetLastError();
 }
 
