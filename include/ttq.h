@@ -256,6 +256,24 @@ TTQ_API ttq_status ttq_add_rmsnorm(ttq_ctx *ctx, void *h_dev, const void *delta_
                                    int64_t M, int64_t H, int64_t ld_h, int64_t ld_delta, float eps, void *out_dev,
                                    int64_t ld_out, void *stream);
 
+/* The same step, which in addition converts the M <= 2 output rows into the context's activation scratch in the form
+ * the decode kernel reads, so that the linear consuming `out` can be called as ttq_linear_forward_prepared and skip
+ * its own conversion pass (one launch and one dependent hand-over less per linear in a decode layer: RmsNorm.forward
+ * followed by Linear.forward, transformer.nim:122-156).  H a multiple of 256, at most 8192.  The prepared rows stay
+ * valid until the next ttq_linear_forward* / ttq_linear_forward_allreduce call on the context that is not the
+ * prepared form (those rewrite the scratch); several prepared linears may consume the same rows.  No reference
+ * counterpart: the reference has no quantized activations. */
+TTQ_API ttq_status ttq_add_rmsnorm_prepare(ttq_ctx *ctx, void *h_dev, const void *delta_dev, const void *weight_dev, ttq_dtype dt,
+                                           int64_t M, int64_t H, int64_t ld_h, int64_t ld_delta, float eps, void *out_dev,
+                                           int64_t ld_out, void *stream);
+
+/* Linear.forward (linear.nim:45-57) on the rows the last ttq_add_rmsnorm_prepare on `ctx` left in the scratch:
+ * y [M][ldy] = x . W^T + bias with x = that call's `out`.  Block formats only; M and K must match the prepared rows
+ * (TTQ_ERR_SHAPE otherwise, TTQ_ERR_INVALID_ARG when nothing is prepared).  Must run on the same stream, after the
+ * prepare call.  Results are bit-identical to ttq_linear_forward on `out`. */
+TTQ_API ttq_status ttq_linear_forward_prepared(ttq_ctx *ctx, const ttq_weight *w, int64_t M, const void *bias_dev, ttq_dtype bias_dt,
+                                               void *y_dev, ttq_dtype y_dt, int64_t ldy, void *stream);
+
 /* Rotary embedding in the rotate-half form (workspace/transformers/src/layers/rope.nim:29-92) of the q and k heads
  * of fused qkv rows [B][ld_qkv] = [hq q heads | hkv k heads | hkv v heads] x d, for ONE position `pos` whose
  * cos / sin vectors [d] the caller supplies; q goes to q_out [B][hq][d], k and v into the caches

@@ -60,6 +60,8 @@ SIGNATURES = {
     "ttq_moe_destroy": (_ci, [_vp]),
     "ttq_moe_forward": (_ci, [_vp, _vp, _vp, _ci, _i64, _i64, _vp, _vp, _vp, _ci, _i64, _vp]),
     "ttq_add_rmsnorm": (_ci, [_vp, _vp, _vp, _vp, _ci, _i64, _i64, _i64, _i64, ctypes.c_float, _vp, _i64, _vp]),
+    "ttq_add_rmsnorm_prepare": (_ci, [_vp, _vp, _vp, _vp, _ci, _i64, _i64, _i64, _i64, ctypes.c_float, _vp, _i64, _vp]),
+    "ttq_linear_forward_prepared": (_ci, [_vp, _vp, _i64, _vp, _ci, _vp, _ci, _i64, _vp]),
     "ttq_rope_kv_append": (_ci, [_vp, _vp, _ci, _i64, _i64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, _vp, _vp, _vp, _vp, _vp,
                                  _i64, _i64, _vp]),
     "ttq_decode_attention": (_ci, [_vp, _vp, _vp, _vp, _ci, _i64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, _i64, _i64, _vp, _vp]),

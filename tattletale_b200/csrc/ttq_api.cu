@@ -21,6 +21,7 @@ struct ttq_ctx {
     XqView xq;
     int64_t xq_capacity_k;
     void *xq_base;
+    int64_t prepared_m, prepared_k;  // rows and row length of the planes ttq_add_rmsnorm_prepare left in `xq` (0: none)
     int sms;          // multiprocessor count of the device
     int *dev_status;  // device word the kernels OR failure bits into (bit 0: a bounded wait gave up)
     int *host_status; // pinned, device-mapped host words: [0] raised by a failing kernel (see report_failure), [1] copy of the status word
@@ -519,6 +520,7 @@ static ttq_status linear_forward_impl(ttq_ctx *ctx, const ttq_weight *w, const v
                               int64_t ldx, const void *bias_dev, ttq_dtype bias_dt, void *y_dev, ttq_dtype y_dt,
                               int64_t ldy, void *stream, bool gated) {
     if (!ctx) return TTQ_ERR_INVALID_ARG;
+    ctx->prepared_m = 0;  // the activation scratch may be rewritten below
     if (!w) return fail(ctx, TTQ_ERR_INVALID_ARG, "weight is NULL");
     if (w->ctx != ctx) return fail(ctx, TTQ_ERR_INVALID_ARG, "weight belongs to another context");
     if (M < 0) return fail(ctx, TTQ_ERR_SHAPE, "M=%lld is negative", (long long)M);
@@ -801,6 +803,7 @@ ttq_status ttq_linear_forward_allreduce(ttq_ctx *ctx, const ttq_weight *w, const
                                         const void *bias_dev, ttq_dtype bias_dt, void *y_dev, ttq_dtype y_dt, int64_t ldy,
                                         ttq_comm *comm, void *stream) {
     if (!ctx) return TTQ_ERR_INVALID_ARG;
+    ctx->prepared_m = 0;  // the activation scratch may be rewritten below
     if (!w || !comm) return fail(ctx, TTQ_ERR_INVALID_ARG, "weight or communicator is NULL");
     if (w->ctx != ctx || comm->ctx != ctx) return fail(ctx, TTQ_ERR_INVALID_ARG, "weight or communicator belongs to another context");
     if (comm->view.cells[comm->view.world - 1] == nullptr) return fail(ctx, TTQ_ERR_INVALID_ARG, "communicator is not connected");
@@ -1026,6 +1029,56 @@ ttq_status ttq_add_rmsnorm(ttq_ctx *ctx, void *h_dev, const void *delta_dev, con
     cudaError_t e = launch_add_rmsnorm(h_dev, delta_dev, weight_dev, dt, M, H, ld_h, ld_delta, eps, out_dev, ld_out, (cudaStream_t)stream);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "add_rmsnorm launch");
     ctx->launches++;
+    return TTQ_OK;
+}
+
+ttq_status ttq_add_rmsnorm_prepare(ttq_ctx *ctx, void *h_dev, const void *delta_dev, const void *weight_dev, ttq_dtype dt, int64_t M,
+                                   int64_t H, int64_t ld_h, int64_t ld_delta, float eps, void *out_dev, int64_t ld_out, void *stream) {
+    if (!ctx) return TTQ_ERR_INVALID_ARG;
+    ctx->prepared_m = ctx->prepared_k = 0;
+    if (M < 1 || M > 2) return fail(ctx, TTQ_ERR_LIMIT, "M=%lld: the prepared form serves 1 or 2 rows", (long long)M);
+    if (H <= 0 || H % TILE_K || H > 8192 || H > ctx->xq_capacity_k)
+        return fail(ctx, TTQ_ERR_SHAPE, "H=%lld: the prepared form needs a multiple of 256, at most 8192 and within the activation scratch", (long long)H);
+    if (!h_dev || !weight_dev || !out_dev) return fail(ctx, TTQ_ERR_INVALID_ARG, "a device pointer is NULL");
+    if (dt != TTQ_DT_BF16 && dt != TTQ_DT_F16) return fail(ctx, TTQ_ERR_INVALID_ARG, "dtype must be bf16 or f16");
+    if (ld_h % 8 || ld_out % 8 || (delta_dev && ld_delta % 8) || ld_h < H || ld_out < H || (delta_dev && ld_delta < H))
+        return fail(ctx, TTQ_ERR_SHAPE, "the leading dimensions must be multiples of 8 and at least H");
+    if (((uintptr_t)h_dev | (uintptr_t)weight_dev | (uintptr_t)out_dev | (uintptr_t)delta_dev) & 15)
+        return fail(ctx, TTQ_ERR_INVALID_ARG, "pointers must be 16-byte aligned");
+    cudaError_t e = launch_add_rmsnorm(h_dev, delta_dev, weight_dev, dt, M, H, ld_h, ld_delta, eps, out_dev, ld_out, (cudaStream_t)stream, &ctx->xq);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "add_rmsnorm (prepared) launch");
+    ctx->launches++;
+    ctx->prepared_m = M;
+    ctx->prepared_k = H;
+    return TTQ_OK;
+}
+
+ttq_status ttq_linear_forward_prepared(ttq_ctx *ctx, const ttq_weight *w, int64_t M, const void *bias_dev, ttq_dtype bias_dt, void *y_dev,
+                                       ttq_dtype y_dt, int64_t ldy, void *stream) {
+    if (!ctx) return TTQ_ERR_INVALID_ARG;
+    if (!w) return fail(ctx, TTQ_ERR_INVALID_ARG, "weight is NULL");
+    if (w->ctx != ctx) return fail(ctx, TTQ_ERR_INVALID_ARG, "weight belongs to another context");
+    if (w->fmt == TTQ_FMT_TQ3) return fail(ctx, TTQ_ERR_UNSUPPORTED, "the prepared form serves the block formats");
+    if (ctx->prepared_m == 0) return fail(ctx, TTQ_ERR_INVALID_ARG, "no prepared activations: call ttq_add_rmsnorm_prepare first");
+    if (M != ctx->prepared_m || w->K != ctx->prepared_k)
+        return fail(ctx, TTQ_ERR_SHAPE, "prepared activations are [%lld][%lld], the call wants [%lld][%lld]", (long long)ctx->prepared_m,
+                    (long long)ctx->prepared_k, (long long)M, (long long)w->K);
+    if (!y_dev) return fail(ctx, TTQ_ERR_INVALID_ARG, "y pointer is NULL");
+    if (!valid_dt(y_dt) || (bias_dev && !valid_dt(bias_dt))) return fail(ctx, TTQ_ERR_INVALID_ARG, "unknown dtype");
+    if (ldy < w->N) return fail(ctx, TTQ_ERR_SHAPE, "ldy=%lld is smaller than N=%lld", (long long)ldy, (long long)w->N);
+    LinearArgs a;
+    a.tiles = w->tiles;
+    a.N = w->N; a.K = w->K; a.NT = w->NT; a.SBp = w->SBp;
+    a.x = nullptr; a.x_dt = TTQ_DT_BF16; a.M = M; a.ldx = w->K;
+    a.bias = bias_dev; a.bias_dt = bias_dt;
+    a.y = y_dev; a.y_dt = y_dt; a.ldy = ldy;
+    a.gated = false;
+    int launches = 0;
+    cudaError_t e = launch_gemv(w->fmt, a, ctx->xq, ctx->xq_capacity_k, reinterpret_cast<const uint8_t *>(ctx->dev_status) + 256, ctx->sms,
+                                ctx->dev_status, ctx->trace, (cudaStream_t)stream, &launches, nullptr, true);
+    ctx->launches += launches;
+    if (e == cudaErrorNotSupported) return fail(ctx, TTQ_ERR_UNSUPPORTED, "this shape does not fit the copying mode of the decode kernel");
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "linear forward (prepared) launch");
     return TTQ_OK;
 }
 

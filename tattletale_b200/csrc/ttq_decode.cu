@@ -16,6 +16,7 @@
 //                             slice (V read coalesced); partial (max, sum, output) per slice
 //   decode_attn_merge_kernel  one CTA per (sequence, query head): merges the slices
 #include "ttq_internal.cuh"
+#include "ttq_xprep.cuh"
 
 namespace ttq {
 namespace {
@@ -64,9 +65,12 @@ __device__ __forceinline__ float block_sum(float v, float *red) {
     return s;
 }
 // H % 8 == 0, rows 16-byte aligned (checked by the launcher).
+// `xq.planes` != nullptr (H a multiple of 256, H <= 8192): the normalised row, as rounded for `out`, is also converted
+// to the fixed-point planes a decode linear reads (thread t holds the 8 values lane t & 31 of chunk t >> 5 converts in
+// the activation pass), so that the linear that consumes `out` can skip its own conversion pass.
 __global__ void __launch_bounds__(256) add_rmsnorm_kernel(void *__restrict__ h, const void *__restrict__ delta, const void *__restrict__ weight,
                                                           int dt, int64_t H, int64_t ld_h, int64_t ld_delta, float eps,
-                                                          void *__restrict__ out, int64_t ld_out) {
+                                                          void *__restrict__ out, int64_t ld_out, XqView xq) {
     __shared__ float red[8];
     grid_launch_dependents();
     grid_dependency_wait();
@@ -119,7 +123,16 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(void *__restrict__ h, 
                 unpack8(wv[i], dt, w);
 #pragma unroll
                 for (int q = 0; q < 8; q++) v[q] = v[q] * inv * w[q];
-                *reinterpret_cast<uint4 *>(orow + c * 16) = pack8(v, dt);
+                const uint4 packed = pack8(v, dt);
+                *reinterpret_cast<uint4 *>(orow + c * 16) = packed;
+                if (xq.planes != nullptr) {
+                    // (whole warps pass here: H / 8 is a multiple of 32)
+                    const int64_t SBp = H / TILE_K, Kp = H;
+                    unpack8(packed, dt, v);
+                    const XqRow dst{xq.planes + (2 * m) * Kp, xq.planes + (2 * m + 1) * Kp, xq.sum16 + m * (Kp / 16), xq.sum32 + m * (Kp / 32),
+                                    xq.sx + m * sx_stride(SBp)};
+                    xprep_convert_vals(v, (int)(c >> 5), (int)(threadIdx.x & 31), dst);
+                }
             }
         }
         return;
@@ -186,8 +199,8 @@ __global__ void rope_kv_kernel(const void *__restrict__ qkv, int dt, int64_t ld_
 // a warp's 32 positions in flight together), partial dots are folded over the 16 lanes.  Output: thread (pg, dg)
 // accumulates dimensions 8 dg .. 8 dg + 7 over positions pg, pg + 8, ... with 16-byte V loads, the 8 position
 // groups are summed through shared memory.
-// PREFETCH: the first half of a thread's V rows is requested before the softmax statistics (helps while the grid
-// leaves SMs under-occupied, costs registers and therefore occupancy on large grids).
+// PREFETCH: every K and V row of the thread is requested before anything else (helps while the grid leaves SMs
+// under-occupied, costs registers and therefore occupancy on large grids).
 template <int G, bool PREFETCH>
 __global__ void __launch_bounds__(ATT_SLICE) decode_attn_kernel(const void *__restrict__ q, const void *__restrict__ k_cache,
                                                                 const void *__restrict__ v_cache, int dt, int hq, int hkv, int64_t ctx_len,
@@ -200,54 +213,61 @@ __global__ void __launch_bounds__(ATT_SLICE) decode_attn_kernel(const void *__re
     const int slice = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, t = threadIdx.x;
     const int warp = t >> 5, lane = t & 31;
     const int slices = gridDim.x;
-    for (int i = t; i < G * ATT_D; i += ATT_SLICE)
-        q_s[i / ATT_D][i % ATT_D] = load_as_float(q, dt, ((int64_t)b * hq + (int64_t)kvh * G + i / ATT_D) * ATT_D + i % ATT_D) * scale;
-    __syncthreads();
     const int64_t p0 = (int64_t)slice * ATT_SLICE;
     const int64_t n_here = n_ctx - p0 < ATT_SLICE ? n_ctx - p0 : ATT_SLICE;
     const uint8_t *kbase = reinterpret_cast<const uint8_t *>(k_cache) + ((((int64_t)b * hkv + kvh) * ctx_len + p0) * ATT_D) * 2;
     const uint8_t *vbase = reinterpret_cast<const uint8_t *>(v_cache) + ((((int64_t)b * hkv + kvh) * ctx_len + p0) * ATT_D) * 2;
-    {
-        const int hw = lane >> 4, c = lane & 15;
-#pragma unroll 1
-        for (int half = 0; half < 2; half++) {
-        uint4 raw[8];
+    const int hw = lane >> 4, c = lane & 15;
+    const int pg = t >> 4, dg = t & 15;
+    // PREFETCH (small grids, about one CTA per SM: latency is everything and registers are free): every K and V row of
+    // the thread is requested before anything else, the query loads and all arithmetic run under those loads.
+    constexpr int NK = PREFETCH ? 16 : 8, NV = PREFETCH ? 16 : 1;
+    uint4 kraw[NK], vraw[NV];
+    auto load_k = [&](int first, int count, uint4 *dst) {
 #pragma unroll
-        for (int i8 = 0; i8 < 8; i8++) {
-            const int j = 32 * warp + 2 * (8 * half + i8) + hw;
-            raw[i8] = j < n_here ? *reinterpret_cast<const uint4 *>(kbase + (int64_t)j * (ATT_D * 2) + 16 * c) : make_uint4(0u, 0u, 0u, 0u);
-        }
-#pragma unroll
-        for (int i8 = 0; i8 < 8; i8++) {
-            const int it = 8 * half + i8;
-            float kv[8];
-            unpack8(raw[i8], dt, kv);
-            float s[G];
-#pragma unroll
-            for (int g = 0; g < G; g++) {
-                float a = 0.f;
-#pragma unroll
-                for (int i = 0; i < 8; i++) a = fmaf(kv[i], q_s[g][8 * c + i], a);
-#pragma unroll
-                for (int o = 8; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-                s[g] = a;
-            }
-            if (c == 0) {
-                const int j = 32 * warp + 2 * it + hw;
-#pragma unroll
-                for (int g = 0; g < G; g++) p_s[g][j] = s[g];
+        for (int i = 0; i < 16; i++) {
+            if (i < count) {
+                const int j = 32 * warp + 2 * (first + i) + hw;
+                dst[i] = j < n_here ? *reinterpret_cast<const uint4 *>(kbase + (int64_t)j * (ATT_D * 2) + 16 * c) : make_uint4(0u, 0u, 0u, 0u);
             }
         }
+    };
+    if constexpr (PREFETCH) {
+        load_k(0, 16, kraw);
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const int j = pg + 8 * i;
+            vraw[i] = j < n_here ? *reinterpret_cast<const uint4 *>(vbase + (int64_t)j * (ATT_D * 2) + 16 * dg) : make_uint4(0u, 0u, 0u, 0u);
         }
     }
-    // first half of this thread's V rows: in flight while the softmax statistics are computed
-    const int pg = t >> 4, dg = t & 15;
-    uint4 vraw[PREFETCH ? 8 : 1];
-    if (PREFETCH) {
+    for (int i = t; i < G * ATT_D; i += ATT_SLICE)
+        q_s[i / ATT_D][i % ATT_D] = load_as_float(q, dt, ((int64_t)b * hq + (int64_t)kvh * G + i / ATT_D) * ATT_D + i % ATT_D) * scale;
+    __syncthreads();
+    {
+#pragma unroll 1
+        for (int half = 0; half < (PREFETCH ? 1 : 2); half++) {
+            if constexpr (!PREFETCH) load_k(8 * half, 8, kraw);
 #pragma unroll
-        for (int i8 = 0; i8 < (PREFETCH ? 8 : 1); i8++) {
-            const int j = pg + 8 * i8;
-            vraw[i8] = j < n_here ? *reinterpret_cast<const uint4 *>(vbase + (int64_t)j * (ATT_D * 2) + 16 * dg) : make_uint4(0u, 0u, 0u, 0u);
+            for (int i8 = 0; i8 < NK; i8++) {
+                const int it = 8 * half + i8;
+                float kv[8];
+                unpack8(kraw[i8], dt, kv);
+                float sg[G];
+#pragma unroll
+                for (int g = 0; g < G; g++) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) a = fmaf(kv[i], q_s[g][8 * c + i], a);
+#pragma unroll
+                    for (int o = 8; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+                    sg[g] = a;
+                }
+                if (c == 0) {
+                    const int j = 32 * warp + 2 * it + hw;
+#pragma unroll
+                    for (int g = 0; g < G; g++) p_s[g][j] = sg[g];
+                }
+            }
         }
     }
     __syncthreads();
@@ -289,7 +309,7 @@ __global__ void __launch_bounds__(ATT_SLICE) decode_attn_kernel(const void *__re
 #pragma unroll
         for (int i8 = 0; i8 < 8; i8++) {
             const int j = pg + 8 * (8 * half + i8);
-            if (PREFETCH && half == 0) raw[i8] = vraw[PREFETCH ? i8 : 0];
+            if constexpr (PREFETCH) raw[i8] = half == 0 ? vraw[i8] : vraw[8 + i8];
             else raw[i8] = j < n_here ? *reinterpret_cast<const uint4 *>(vbase + (int64_t)j * (ATT_D * 2) + 16 * dg) : make_uint4(0u, 0u, 0u, 0u);
         }
 #pragma unroll
@@ -320,21 +340,50 @@ __global__ void __launch_bounds__(ATT_SLICE) decode_attn_kernel(const void *__re
     }
 }
 
-// grid (hq, B), 128 threads
+// grid (hq, B), 128 threads.  The slices' statistics are read by one thread each and their weights exp(max_s - max)
+// shared through shared memory, so that the loads of a merge are in flight together instead of one L2 round trip per
+// slice (a decode step at batch 1 is a chain of such latencies).
+constexpr int ATT_MERGE_SLICES = 512;  // slices whose weights fit the shared array (context 65536); beyond: recomputed
 __global__ void __launch_bounds__(ATT_D) decode_attn_merge_kernel(const float *__restrict__ part, int hq, int hkv, int G, int slices,
                                                                   void *__restrict__ out, int dt) {
+    __shared__ float w_s[ATT_MERGE_SLICES];
+    __shared__ float red[2][ATT_D / 32];
     grid_launch_dependents();
     grid_dependency_wait();
-    const int h = blockIdx.x, b = blockIdx.y, t = threadIdx.x;
+    const int h = blockIdx.x, b = blockIdx.y, t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int kvh = h / G, g = h % G;
     const float *base = part + (((int64_t)b * hkv + kvh) * slices * G + g) * (2 + ATT_D);
     const int64_t stride = (int64_t)G * (2 + ATT_D);
+    // this thread's slices: t, t + 128, ...
     float mx = -INFINITY;
-    for (int s = 0; s < slices; s++) mx = fmaxf(mx, base[s * stride]);
-    float den = 0.f, num = 0.f;
-    for (int s = 0; s < slices; s++) {
+    for (int s = t; s < slices; s += ATT_D) mx = fmaxf(mx, base[s * stride]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) red[0][warp] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(red[0][0], red[0][1]), fmaxf(red[0][2], red[0][3]));
+    float den = 0.f;
+    for (int s = t; s < slices; s += ATT_D) {
         const float w = __expf(base[s * stride] - mx);
+        if (s < ATT_MERGE_SLICES) w_s[s] = w;
         den = fmaf(w, base[s * stride + 1], den);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+    if (lane == 0) red[1][warp] = den;
+    __syncthreads();
+    den = (red[1][0] + red[1][1]) + (red[1][2] + red[1][3]);
+    float num = 0.f;
+    int s = 0;
+    for (; s + 8 <= slices && s + 8 <= ATT_MERGE_SLICES; s += 8) {
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = base[(s + i) * stride + 2 + t];
+#pragma unroll
+        for (int i = 0; i < 8; i++) num = fmaf(w_s[s + i], v[i], num);
+    }
+    for (; s < slices; s++) {
+        const float w = s < ATT_MERGE_SLICES ? w_s[s] : __expf(base[s * stride] - mx);
         num = fmaf(w, base[s * stride + 2 + t], num);
     }
     store_from_float(out, dt, ((int64_t)b * hq + h) * ATT_D + t, num / den);
@@ -343,8 +392,13 @@ __global__ void __launch_bounds__(ATT_D) decode_attn_merge_kernel(const float *_
 }  // namespace
 
 cudaError_t launch_add_rmsnorm(void *h, const void *delta, const void *weight, int dt, int64_t M, int64_t H, int64_t ld_h, int64_t ld_delta,
-                               float eps, void *out, int64_t ld_out, cudaStream_t st) {
-    return launch_pdl(add_rmsnorm_kernel, dim3((unsigned)M), dim3(256), 0, st, h, delta, weight, dt, H, ld_h, ld_delta, eps, out, ld_out);
+                               float eps, void *out, int64_t ld_out, cudaStream_t st, const XqView *xq) {
+    XqView v{nullptr, nullptr, nullptr, nullptr};
+    if (xq != nullptr) {
+        if (H % TILE_K || H > 8192) return cudaErrorInvalidValue;  // whole 256-wide chunks, row kept in registers
+        v = *xq;
+    }
+    return launch_pdl(add_rmsnorm_kernel, dim3((unsigned)M), dim3(256), 0, st, h, delta, weight, dt, H, ld_h, ld_delta, eps, out, ld_out, v);
 }
 
 cudaError_t launch_rope_kv(const void *qkv, int dt, int64_t B, int64_t ld_qkv, int hq, int hkv, int d, const void *cosv, const void *sinv,
@@ -367,7 +421,7 @@ cudaError_t launch_decode_attention(const void *q, const void *k_cache, const vo
     const dim3 grid((unsigned)slices, (unsigned)hkv, (unsigned)B);
     cudaError_t e;
     const dim3 blk(ATT_SLICE);
-    const bool pre = (int64_t)slices * hkv * B <= 2048;  // up to about two waves of CTAs
+    const bool pre = (int64_t)slices * hkv * B <= 2 * (int64_t)device_sms();  // at most two CTAs per SM: registers are free, latency is not
 #define TTQ_ATT_LAUNCH(GG)                                                                                                          \
     e = pre ? launch_pdl(decode_attn_kernel<GG, true>, grid, blk, 0, st, q, k_cache, v_cache, dt, hq, hkv, ctx_len, n_ctx, scale, part) \
             : launch_pdl(decode_attn_kernel<GG, false>, grid, blk, 0, st, q, k_cache, v_cache, dt, hq, hkv, ctx_len, n_ctx, scale, part)

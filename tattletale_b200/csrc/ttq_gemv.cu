@@ -24,6 +24,7 @@
 #include <cstdlib>
 
 #include "ttq_devutil.cuh"
+#include "ttq_xprep.cuh"
 
 namespace ttq {
 
@@ -49,19 +50,7 @@ __device__ __forceinline__ void mma_k32_s8s8(int (&c)[4], uint32_t a0, uint32_t 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// ---- activation conversion -------------------------------------------------------------------
-// Destination of one activation row's planes and side sums (shared memory or global scratch).
-struct XqRow {
-    int8_t *hi, *lo;  // [Kp]
-    float *sum16;     // [Kp/16]
-    float *sum32;     // [Kp/32]
-    float *sx;        // [SBs]
-    // Order of the plane bytes inside each 32-wide sub-block: false = by K; true = position 16 h + 4 n + i holds
-    // K index 8 n + 4 h + i (n < 4, h < 2, i < 4), the order in which the tensor-memory decode kernel widens a packed
-    // tile into its operand rows.
-    bool interleaved = false;
-};
-
+// ---- activation conversion (XqRow and xprep_convert_vals: ttq_xprep.cuh) --------------------------
 // Raw 8 activations of one lane (loaded early so that several chunks' loads are in flight at once).
 struct RawChunk {
     uint4 raw;
@@ -79,7 +68,6 @@ __device__ __forceinline__ RawChunk xprep_load(const void *xrow, int x_dt, int64
 
 // One warp converts the 256-wide chunk `sb` of activation row `xrow` (nullptr = emit zeros):
 // xq = round(x * 32639 / amax) in [-32639, 32639], stored as two int8 planes with xq = 256*hi + lo.
-__device__ __forceinline__ void xprep_convert_vals(const float (&v)[8], int sb, int lane, const XqRow &dst);
 __device__ __forceinline__ void xprep_convert(const RawChunk &rc, const void *xrow, int x_dt, int64_t K, int sb, int lane,
                                               const XqRow &dst) {
     const int64_t k0 = (int64_t)sb * TILE_K + 8 * lane;
@@ -105,49 +93,6 @@ __device__ __forceinline__ void xprep_convert(const RawChunk &rc, const void *xr
             if (k0 + i < K) v[i] = load_as_float(xrow, x_dt, k0 + i);
     }
     xprep_convert_vals(v, sb, lane, dst);
-}
-// the 8 values of this lane (k0 = 256 sb + 8 lane, zero beyond K) -> planes, group sums, chunk scale
-__device__ __forceinline__ void xprep_convert_vals(const float (&v)[8], int sb, int lane, const XqRow &dst) {
-    const int64_t k0 = (int64_t)sb * TILE_K + 8 * lane;
-    float amax = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    // amax * inv <= 32639 * (1 + 2^-22): rounds to at most 32639, no clamp needed
-    const float inv = amax > 1e-20f ? (float)XQ_MAX * __frcp_rn(amax) : 0.f;
-    int q[8], s = 0;
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        q[i] = __float2int_rn(v[i] * inv);
-        s += q[i];
-    }
-    // low plane = low byte of q (as int8); high plane = byte 1 of q + 128 (carry when the low byte is negative)
-    uint32_t low[2], hiw[2];
-#pragma unroll
-    for (int i = 0; i < 2; i++) {
-        const uint32_t a = __byte_perm(q[4 * i], q[4 * i + 1], 0x0040), b = __byte_perm(q[4 * i + 2], q[4 * i + 3], 0x0040);
-        low[i] = __byte_perm(a, b, 0x5410);
-        const uint32_t c = __byte_perm(q[4 * i] + 128, q[4 * i + 1] + 128, 0x0051),
-                       d = __byte_perm(q[4 * i + 2] + 128, q[4 * i + 3] + 128, 0x0051);
-        hiw[i] = __byte_perm(c, d, 0x5410);
-    }
-    if (dst.interleaved) {
-        // this lane holds K indices 8 n .. 8 n + 7 of its sub-block, n = lane & 3: h = 0 for the first four, 1 for the rest
-        const int64_t seg = (int64_t)sb * TILE_K + 32 * (lane >> 2) + 4 * (lane & 3);
-        *reinterpret_cast<uint32_t *>(dst.hi + seg) = hiw[0];
-        *reinterpret_cast<uint32_t *>(dst.hi + seg + 16) = hiw[1];
-        *reinterpret_cast<uint32_t *>(dst.lo + seg) = low[0];
-        *reinterpret_cast<uint32_t *>(dst.lo + seg + 16) = low[1];
-    } else {
-        *reinterpret_cast<uint2 *>(dst.hi + k0) = make_uint2(hiw[0], hiw[1]);
-        *reinterpret_cast<uint2 *>(dst.lo + k0) = make_uint2(low[0], low[1]);
-    }
-    const int s16 = s + __shfl_xor_sync(0xffffffffu, s, 1);
-    const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);
-    if ((lane & 1) == 0) dst.sum16[sb * 16 + (lane >> 1)] = (float)s16;
-    if ((lane & 3) == 0) dst.sum32[sb * 8 + (lane >> 2)] = (float)s32;
-    if (lane == 0) dst.sx[sb] = amax > 1e-20f ? amax * (1.0f / (float)XQ_MAX) : 0.f;
 }
 __device__ __forceinline__ void xprep_chunk(const void *xrow, int x_dt, int64_t K, int sb, int lane, const XqRow &dst) {
     xprep_convert(xprep_load(xrow, x_dt, K, sb, lane), xrow, x_dt, K, sb, lane, dst);
@@ -794,7 +739,8 @@ cudaError_t launch_xprep(const LinearArgs &a, const XqView &xq, int64_t Mpad, un
 }
 
 cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t xq_capacity_k, const uint8_t *zeros,
-                        int sms, int *status, unsigned long long *trace, cudaStream_t st, int *launches, const CommView *comm) {
+                        int sms, int *status, unsigned long long *trace, cudaStream_t st, int *launches, const CommView *comm,
+                        bool prepared) {
     GemvParams p{a, xq, zeros, 1, status, trace, {}};
     if (comm != nullptr) p.comm = *comm;
     else p.comm.world = 0;
@@ -811,11 +757,16 @@ cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t 
     }();
     int mode = pref;
     if (a.gated && mode == XSRC_CONVERT) mode = XSRC_COPY;  // the gated activation lives in the separate pass
+    if (prepared) {
+        // planes written in the layout of a.M rows by the producer of the activations: only the copying mode reads that
+        if (a.gated || a.M > 4 || pick_nw(fmt, XSRC_COPY, a.M, a.SBp) == 0) return cudaErrorNotSupported;
+        mode = XSRC_COPY;
+    }
     const int nw = (a.M <= 4 && mode != XSRC_GLOBAL) ? pick_nw(fmt, mode, a.M, a.SBp) : 0;
     if (nw == 0) mode = XSRC_GLOBAL;
     const bool shared = mode != XSRC_GLOBAL;
     cudaError_t e = cudaSuccess;
-    if (mode != XSRC_CONVERT) {
+    if (mode != XSRC_CONVERT && !prepared) {
         e = launch_xprep(a, xq, shared ? a.M : (a.M <= 4 ? 4 : (a.M <= 8 ? 8 : 16)), trace, st, false);
         if (e != cudaSuccess) return e;
         ++*launches;

@@ -255,8 +255,9 @@ cudaError_t launch_tq3_gemv(const uint8_t *packed, int64_t N, int64_t K, const f
 cudaError_t launch_tq3_mma(const uint8_t *packed, int64_t N, int64_t K, const __half *x1, int rows, float *y1, cudaStream_t st);
 
 // Decode-step kernels around the linears (ttq_decode.cu).
+// (`xq` != nullptr: also convert the output rows into the activation planes of a decode linear)
 cudaError_t launch_add_rmsnorm(void *h, const void *delta, const void *weight, int dt, int64_t M, int64_t H, int64_t ld_h, int64_t ld_delta,
-                               float eps, void *out, int64_t ld_out, cudaStream_t st);
+                               float eps, void *out, int64_t ld_out, cudaStream_t st, const XqView *xq = nullptr);
 cudaError_t launch_rope_kv(const void *qkv, int dt, int64_t B, int64_t ld_qkv, int hq, int hkv, int d, const void *cosv, const void *sinv,
                            void *q_out, void *k_cache, void *v_cache, int64_t ctx_len, int64_t pos, cudaStream_t st);
 int64_t decode_attention_scratch_floats(int64_t B, int hq, int64_t n_ctx);
@@ -282,9 +283,11 @@ cudaError_t launch_repack(int fmt, const uint8_t *canon, uint8_t *tiled, int64_t
 cudaError_t launch_dequant(int fmt, const uint8_t *tiled, float *out, int64_t ld, int64_t N, int64_t K,
                            int64_t SBp, cudaStream_t st);
 // GEMV for M <= MAX_GEMV_M.  `xq` is scratch for the separate x-prep pass (used when M > fused limit).
+// `prepared`: the planes of a.M rows are already in `xq` (written by the kernel that produced the activations): no
+// activation pass is launched, a.x is not read.
 cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t xq_capacity_k, const uint8_t *zeros,
                         int sms, int *status, unsigned long long *trace, cudaStream_t st, int *launches,
-                        const CommView *comm = nullptr);
+                        const CommView *comm = nullptr, bool prepared = false);
 // (`interleaved`: plane bytes of a sub-block in the order of the tensor-memory decode kernel, see XqRow)
 cudaError_t launch_xprep(const LinearArgs &a, const XqView &xq, int64_t Mpad, unsigned long long *trace, cudaStream_t st, bool interleaved);
 // Q4_K decode linear on the integer tensor-memory path (tcgen05.mma kind::i8), M <= 8: the activation pass, then one

@@ -113,14 +113,17 @@ class DecoderStack:
         cfg, B, d, ctx = self.cfg, token_ids.shape[0], self.cfg.head_dim, self.ctx  # any batch up to the one the caches hold
         h = self.emb_rows[token_ids].contiguous()
         delta = None
+        # up to two rows the linears run the integer decode kernel, whose activation planes the norm kernel can write
+        # itself: one launch and one dependent hand-over less for the QKV and gate|up projections
+        prep = B <= 2 and cfg.hidden % 256 == 0 and cfg.hidden <= 8192
         for L in self.layers:
-            x = add_rmsnorm(ctx, h, delta, L["attn_norm"], cfg.rms_eps)
-            qkv = L["qkv"].forward(x)
+            x = add_rmsnorm(ctx, h, delta, L["attn_norm"], cfg.rms_eps, prepare=prep)
+            qkv = L["qkv"].forward_prepared(B, x.dtype) if prep else L["qkv"].forward(x)
             q = rope_kv_append(ctx, qkv, self.hq, self.hkv, d, self.cos, self.sin, L["k"], L["v"], self.pos)
             att = decode_attention(ctx, q, L["k"], L["v"], cfg.context)
             o = self._row_parallel(L["o"], att.view(B, self.hq * d))
-            x = add_rmsnorm(ctx, h, o, L["mlp_norm"], cfg.rms_eps)
-            gu = L["gate_up"].forward(x)
+            x = add_rmsnorm(ctx, h, o, L["mlp_norm"], cfg.rms_eps, prepare=prep)
+            gu = L["gate_up"].forward_prepared(B, x.dtype) if prep else L["gate_up"].forward(x)
             if self.world == 1:
                 delta = L["down"].forward_gated(gu)  # silu(gate) * up folded into the projection's input conversion
             else:

@@ -152,6 +152,20 @@ class QuantLinear:
 
     __call__ = forward
 
+    def forward_prepared(self, m: int, out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None,
+                         use_bias: bool = True) -> torch.Tensor:
+        """``forward`` on the ``m`` rows the last ``add_rmsnorm(..., prepare=True)`` left in the context (same stream);
+        bit-identical to ``forward`` on that call's result, without the conversion pass."""
+        if out is None:
+            out = torch.empty((m, self.out_features), dtype=out_dtype, device=self.ctx.device)
+        y2 = out.reshape(-1, self.out_features)
+        b = self.bias if use_bias else None
+        st = self.ctx._lib.ttq_linear_forward_prepared(
+            self.ctx.handle, self.handle, m, None if b is None else b.data_ptr(), _lib.DT_F32 if b is None else _dt(b.dtype),
+            y2.data_ptr(), _dt(y2.dtype), y2.stride(0) if m > 1 else self.out_features, _stream_ptr(self.ctx.device))
+        check(self.ctx.handle, st)
+        return out
+
     def forward_gated(self, gate_up: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``forward(silu(gate) * up)`` for ``gate_up = [gate | up]`` of ``2 * in_features`` columns: the activation
@@ -342,15 +356,20 @@ class MoELayer:
 
 
 def add_rmsnorm(ctx: Context, h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
-                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out: Optional[torch.Tensor] = None, prepare: bool = False) -> torch.Tensor:
     """``h += delta`` in place (skipped when ``delta`` is None), returns ``rmsnorm(h) * weight``
-    (norm.nim:23-38, ``forward_with_residual`` fused).  2-D contiguous 16-bit tensors."""
+    (norm.nim:23-38, ``forward_with_residual`` fused).  2-D contiguous 16-bit tensors.
+
+    ``prepare=True`` (1 or 2 rows, hidden size a multiple of 256) also leaves the rows in the context in the form
+    the decode kernel reads: the linear that consumes the result may then be called as
+    ``QuantLinear.forward_prepared`` and skips its own conversion pass."""
     m, hid = h.shape
     if out is None:
         out = torch.empty_like(h)
-    st = ctx._lib.ttq_add_rmsnorm(ctx.handle, h.data_ptr(), None if delta is None else delta.data_ptr(), weight.data_ptr(),
-                                  _dt(h.dtype), m, hid, h.stride(0), hid if delta is None else delta.stride(0), eps,
-                                  out.data_ptr(), out.stride(0), _stream_ptr(h.device))
+    fn = ctx._lib.ttq_add_rmsnorm_prepare if prepare else ctx._lib.ttq_add_rmsnorm
+    st = fn(ctx.handle, h.data_ptr(), None if delta is None else delta.data_ptr(), weight.data_ptr(),
+            _dt(h.dtype), m, hid, h.stride(0), hid if delta is None else delta.stride(0), eps,
+            out.data_ptr(), out.stride(0), _stream_ptr(h.device))
     check(ctx.handle, st)
     return out
 

@@ -41,6 +41,10 @@ proc ttq_linear_forward_gated(ctx: ptr TtqCtx, w: ptr TtqWeight, gateUp: pointer
                               stream: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
 proc ttq_add_rmsnorm(ctx: ptr TtqCtx, h, delta, weight: pointer, dt: TtqDtype, M, H, ldH, ldDelta: int64,
                      eps: cfloat, outp: pointer, ldOut: int64, stream: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_add_rmsnorm_prepare(ctx: ptr TtqCtx, h, delta, weight: pointer, dt: TtqDtype, M, H, ldH, ldDelta: int64,
+                             eps: cfloat, outp: pointer, ldOut: int64, stream: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_linear_forward_prepared(ctx: ptr TtqCtx, w: ptr TtqWeight, M: int64, bias: pointer, biasDt: TtqDtype, y: pointer,
+                                 yDt: TtqDtype, ldy: int64, stream: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
 proc ttq_rope_kv_append(ctx: ptr TtqCtx, qkv: pointer, dt: TtqDtype, B, ldQkv: int64, hq, hkv, d: int32,
                         cosv, sinv, qOut, kCache, vCache: pointer, ctxLen, pos: int64,
                         stream: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}

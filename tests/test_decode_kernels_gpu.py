@@ -108,3 +108,50 @@ def test_argument_errors(ctx):
     with pytest.raises(ttq.TtqError) as ei:
         ttq.decode_attention(ctx, q, kc, v_off, 8)
     assert ei.value.status == 1  # TTQ_ERR_INVALID_ARG
+
+
+@pytest.mark.parametrize("fmt", [ttq.FMT_Q4_K, ttq.FMT_Q6_K, ttq.FMT_Q8_0])
+@pytest.mark.parametrize("m", [1, 2])
+def test_norm_prepares_the_linear_input(ctx, fmt, m):
+    """add_rmsnorm(prepare=True) + forward_prepared gives, bit for bit, what add_rmsnorm + forward gives: the norm
+    kernel writes the same fixed-point planes the linear's own conversion pass would make of its (rounded) output."""
+    from tattletale_b200 import quantize as Q
+
+    hid, n = 4096, 1536
+    g = torch.Generator(device="cuda").manual_seed(31 + m)
+    lin = ttq.QuantLinear(ctx, fmt, Q.quantize(fmt, torch.randn(n, hid, generator=g, device="cuda") * 0.02), hid,
+                          bias=torch.randn(n, generator=g, device="cuda"))
+    w = (1 + 0.1 * torch.randn(hid, generator=g, device="cuda")).to(torch.bfloat16)
+    h0 = torch.randn(m, hid, generator=g, device="cuda").to(torch.bfloat16)
+    delta = torch.randn(m, hid, generator=g, device="cuda").to(torch.bfloat16)
+    h1, h2 = h0.clone(), h0.clone()
+    x1 = ttq.add_rmsnorm(ctx, h1, delta, w, 1e-5)
+    y1 = lin.forward(x1, out_dtype=torch.float32)
+    x2 = ttq.add_rmsnorm(ctx, h2, delta, w, 1e-5, prepare=True)
+    y2 = lin.forward_prepared(m, torch.float32)
+    y2b = lin.forward_prepared(m, torch.float32)  # the prepared rows may be consumed more than once
+    ctx.check_device_status()
+    assert torch.equal(x1, x2) and torch.equal(h1, h2) and torch.equal(y2, y2b)
+    assert torch.equal(y1, y2)
+    lin.close()
+
+
+def test_prepared_form_errors(ctx):
+    from tattletale_b200 import quantize as Q
+
+    hid = 512
+    lin = ttq.QuantLinear(ctx, ttq.FMT_Q4_K, Q.quantize(ttq.FMT_Q4_K, torch.randn(64, hid, device="cuda") * 0.02), hid)
+    w = torch.ones(hid, dtype=torch.bfloat16, device="cuda")
+    h = torch.randn(2, hid, device="cuda").to(torch.bfloat16)
+    x = ttq.add_rmsnorm(ctx, h, None, w, 1e-5, prepare=True)
+    with pytest.raises(ttq.TtqError):  # row count differs from the prepared rows
+        lin.forward_prepared(1)
+    lin.forward(x)  # rewrites the scratch: the prepared rows are gone
+    with pytest.raises(ttq.TtqError):
+        lin.forward_prepared(2)
+    with pytest.raises(ttq.TtqError):  # hidden size not a multiple of 256
+        ttq.add_rmsnorm(ctx, torch.zeros(1, 384, dtype=torch.bfloat16, device="cuda"), None,
+                        torch.ones(384, dtype=torch.bfloat16, device="cuda"), 1e-5, prepare=True)
+    with pytest.raises(ttq.TtqError):  # more rows than the prepared form serves
+        ttq.add_rmsnorm(ctx, torch.zeros(3, hid, dtype=torch.bfloat16, device="cuda"), None, w, 1e-5, prepare=True)
+    lin.close()
