@@ -570,8 +570,10 @@ static ttq_status linear_forward_impl(ttq_ctx *ctx, const ttq_weight *w, const v
     // converted inside the kernel).  Up to 2 rows the integer decode kernel below is faster, beyond 16 the tcgen05 path.
     // TTQ_Q4K_MMA=0 switches the kernel off.
     static const bool use_mma = env_flag("TTQ_Q4K_MMA", true);
+    // (two rows of a long K -- 8192 and more -- also go there: their planes leave room for one small CTA per SM only in
+    // the integer kernel; measured 17.3 against 21.1 us on 14336 -> 4096)
     constexpr int64_t MMA_MIN_M = 3, MMA_MAX_M = 16;
-    if (w->fmt == TTQ_FMT_Q4_K && use_mma && M >= MMA_MIN_M && M <= MMA_MAX_M) {
+    if (w->fmt == TTQ_FMT_Q4_K && use_mma && (M >= MMA_MIN_M || (M == 2 && w->SBp >= 32)) && M <= MMA_MAX_M) {
         a.x = x_dev; a.M = M; a.y = y_dev;
         int launches = 0;
         cudaError_t e = launch_q4k_mma(a, ctx->sms, ctx->dev_status, ctx->trace, ctx->split_ws, ctx->split_ws_bytes, ctx->split_counters,
