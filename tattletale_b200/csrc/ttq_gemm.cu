@@ -797,6 +797,421 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
     }
 }
 
+// ================================================================================================================
+// Two-CTA form (cta_group::2): a pair of CTAs on neighbouring SMs shares one 256 x 256 output tile.  Each CTA expands
+// only HALF of the tile's weight rows (128) per stage and holds half of its activation rows (128); one
+// tcgen05.mma.cta_group::2 instruction (M = 256, N = 256, issued by the pair's first CTA) reads both halves of both
+// operands, and each CTA's tensor memory receives the 128 activation rows it holds x all 256 columns.  Per SM the
+// conversion work per multiplied element is half that of the one-CTA kernel, which is bound by exactly that work, and
+// two accumulator sets fit (2 x 256 columns), so the epilogue overlaps the next tile.
+//
+// Hand-shakes: `full[stage]` lives in the first CTA and counts its own conversion warps, its activation copy and ONE
+// arrival for the second CTA, whose conversion warps and activation copy meet on a local barrier that its otherwise
+// idle MMA warp forwards (mapa + mbarrier.arrive.release.cluster); `empty[stage]` and `acc_full[set]` exist in both
+// CTAs at the same offsets and are signalled by ONE tcgen05.commit with cluster multicast (an arrive, not a load);
+// `acc_empty[set]` lives in the first CTA and counts the epilogue warps of both.  No TMA or bulk load uses multicast.
+// Dense Q4_K only, no K split; every wait is bounded.
+// ================================================================================================================
+constexpr int GP_STAGE_W = 128 * 128;   // 128 expanded weight rows x 64 fp16
+constexpr int GP_STAGE_X = 2 * 128 * 128;   // two blocks of 128 activation rows x 64 fp16
+constexpr int GP_STAGE = GP_STAGE_W + GP_STAGE_X;
+constexpr int GP_STAGES = 4;
+constexpr int GP_HDR = 16 * 1280;
+constexpr int GP_BARS = 256;  // full, empty, act [GP_STAGES]; acc_full, acc_empty [2]; tensor-memory address word
+constexpr int GP_TOTAL = 1024 + GP_STAGES * GP_STAGE + GP_HDR + GP_BARS;
+constexpr int GP_EPI_WARPS = 8;  // two per tensor-memory lane quarter
+constexpr int GP_WARPS = GP_EPI_WARPS + 16 + 1, GP_THREADS = GP_WARPS * 32;
+static_assert(GP_TOTAL <= 227 * 1024, "shared memory over the limit");
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive on the barrier at the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(bar), "r"(rank));
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
+// bounded wait with cluster-scope acquire: the arrivals it observes come from both CTAs of the pair
+__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t parity, int *status) {
+    for (int i = 0; i < GEMM_WAIT_LIMIT; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    report_failure(status, 2);
+    return false;
+}
+// instruction descriptor, kind::f16, pair form: D = f32, A = B = f16, both K-major, M = 256 over the pair, N = n
+__host__ __device__ constexpr uint32_t idesc_f16_pair(int n) { return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((256u >> 4) << 24); }
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+// completion of all MMAs issued so far arrives on the barrier at this offset in both CTAs of the pair
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"((uint16_t)3)
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(GP_THREADS, 1) gemm_q4k_pair_kernel(GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    constexpr int STAGES = GP_STAGES;
+    constexpr int TB = tile_bytes(TTQ_FMT_Q4_K);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();  // 0: issues the MMAs and owns the counting barriers
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t stages_u32 = base, hdr_u32 = base + STAGES * GP_STAGE, bars_u32 = hdr_u32 + GP_HDR;
+    const uint32_t full_bar = bars_u32, empty_bar = full_bar + 8 * STAGES, act_bar = empty_bar + 8 * STAGES;
+    const uint32_t accf_bar = act_bar + 8 * STAGES, acce_bar = accf_bar + 16;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + STAGES * GP_STAGE + GP_HDR + 24 * STAGES + 32);
+    grid_launch_dependents();
+    // Output tiles: 256 weight rows x 512 activation rows; a last block of 256 activation rows makes half tiles.  All full
+    // tiles come first (weight-tile column major, so that pairs running side by side share weights), the half tiles
+    // after them: dealt round-robin, every pair then gets its share of both kinds.
+    const int64_t m_full = p.Mp / 512, m_half = (p.Mp % 512) ? 1 : 0, n_tiles = (p.N + 255) / 256;
+    const int64_t n_full = n_tiles * m_full, n_otiles = n_full + n_tiles * m_half;
+    auto tile_at = [&](int64_t tile, int64_t &n_tile, int64_t &m_tile) -> int {  // returns the tile's 256-row blocks
+        if (tile < n_full) {
+            n_tile = tile / m_full;
+            m_tile = tile % m_full;
+            return 2;
+        }
+        n_tile = tile - n_full;
+        m_tile = m_full;
+        return 1;
+    };
+    const int64_t pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int iters = (int)p.SBp * 4;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            // first CTA: its 8 conversion warps of the stage, its activation copy, one forwarded arrival for the second CTA;
+            // second CTA: its 8 conversion warps and its activation copy meet on `act`, which its MMA warp forwards
+            mbar_init(full_bar + 8 * s, 8 + 1 + 1);
+            mbar_init(empty_bar + 8 * s, 1);
+            mbar_init(act_bar + 8 * s, 8 + 1);
+        }
+        mbar_init(accf_bar, 1);
+        mbar_init(acce_bar, 2 * GP_EPI_WARPS);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+    }
+    if (warp == GP_WARPS - 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // both CTAs' barriers and tensor memory exist before anything arrives remotely
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < GP_EPI_WARPS) {
+        // ------------------------------------------------------------------ epilogue: this CTA's 128 activation rows
+        grid_dependency_wait();
+        bool alive = true;
+        int tcount = 0;
+        const int esz = p.y_dt == TTQ_DT_F32 ? 4 : 2;
+        for (int64_t tile = pair; tile < n_otiles; tile += n_pairs, tcount++) {
+            int64_t n_tile, m_tile;
+            const int mh = tile_at(tile, n_tile, m_tile);
+            if (alive) alive = mbar_wait_warp(accf_bar, (uint32_t)(tcount & 1), p.status, lane);
+            tc_fence_after();
+            // a warp reads the 32 tensor-memory lanes of its quarter; the two warps of a quarter split the columns
+            const int quad = warp & 3, part = warp >> 2, c_len = mh * 128;
+#pragma unroll 1
+            for (int c = part * c_len; c < (part + 1) * c_len; c += 16) {
+                // columns [256 hb, 256 hb + 256) hold activation rows 256 hb + 128 rank + lane of the tile
+                const int hb = c >> 8, c0 = c & 255;
+                const int64_t m = m_tile * 512 + hb * 256 + (int64_t)rank * 128 + quad * 32 + lane;
+                const bool row_ok = m < p.M;
+                uint32_t v[16];
+                tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c, v);
+                const int64_t n0 = n_tile * 256 + c0;
+                if (!row_ok || n0 >= p.N) continue;
+                float f[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) f[i] = __uint_as_float(v[i]);
+                if (p.bias != nullptr) {
+#pragma unroll
+                    for (int i = 0; i < 16; i++)
+                        if (n0 + i < p.N) f[i] += load_as_float(p.bias, p.bias_dt, n0 + i);
+                }
+                uint8_t *dst = reinterpret_cast<uint8_t *>(p.y) + (size_t)(m * p.ldy + n0) * esz;
+                if (n0 + 16 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                    if (p.y_dt == TTQ_DT_F32) {
+#pragma unroll
+                        for (int q = 0; q < 4; q++)
+                            reinterpret_cast<float4 *>(dst)[q] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+                    } else {
+                        uint32_t w[8];
+#pragma unroll
+                        for (int q = 0; q < 8; q++) {
+                            if (p.y_dt == TTQ_DT_BF16) {
+                                const __nv_bfloat162 t2 = __floats2bfloat162_rn(f[2 * q], f[2 * q + 1]);
+                                w[q] = *reinterpret_cast<const uint32_t *>(&t2);
+                            } else {
+                                const __half2 t2 = __floats2half2_rn(f[2 * q], f[2 * q + 1]);
+                                w[q] = *reinterpret_cast<const uint32_t *>(&t2);
+                            }
+                        }
+                        reinterpret_cast<uint4 *>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                        reinterpret_cast<uint4 *>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; i++)
+                        if (n0 + i < p.N) store_from_float(p.y, p.y_dt, m * p.ldy + n0 + i, f[i]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acce_bar, 0);
+        }
+    } else if (warp < GP_EPI_WARPS + 16) {
+        // ------------------------------------------------------------------ conversion: this CTA's 128 weight rows
+        // two groups of 8 warps take the even and the odd stages; warp dw of a group expands packed row tile dw
+        const int dwa = warp - GP_EPI_WARPS, dw = dwa & 7, grp = dwa >> 3;
+        const int g = lane >> 2, t = lane & 3, r = lane & 15, h = lane >> 4;
+        const uint32_t my_hdr = hdr_u32 + dwa * 1280;
+        const int u0 = t >> 1, u1 = 2 + (t >> 1);
+        uint32_t dst_off[4][2], hdr_off[4];
+#pragma unroll
+        for (int sl = 0; sl < 4; sl++) {
+            const int u = (sl >> 1) ? u1 : u0;
+            const int row = dw * 16 + g + 8 * (sl & 1);
+            const uint32_t key = (uint32_t)(row & 7);
+            dst_off[sl][0] = (uint32_t)row * 128 + (((uint32_t)(2 * u) ^ key) << 4) + (uint32_t)(t & 1) * 8;
+            dst_off[sl][1] = (uint32_t)row * 128 + (((uint32_t)(2 * u + 1) ^ key) << 4) + (uint32_t)(t & 1) * 8;
+            hdr_off[sl] = (uint32_t)((g + 8 * (sl & 1)) * 80) + (uint32_t)(2 * u * 8);
+        }
+        auto tile_ptr = [&](int64_t tile, bool &have) {
+            int64_t n_tile = 0, m_tile = 0;
+            if (tile < n_otiles) tile_at(tile, n_tile, m_tile);
+            const int64_t nt = (n_tile * 2 + rank) * 8 + dw;
+            have = tile < n_otiles && nt < p.NT;
+            return p.tiles + (have ? nt : 0) * p.SBp * TB;
+        };
+        auto chunk_at = [&](const uint8_t *t0, bool ok, int it) {
+            uint4 c = make_uint4(0, 0, 0, 0);
+            if (ok) c = *reinterpret_cast<const uint4 *>(t0 + (int64_t)(it >> 2) * TB + lane * 16 + (it & 3) * 512);
+            return c;
+        };
+        auto header_at = [&](const uint8_t *t0, bool ok, int sb) {
+            uint4 hd = make_uint4(0, 0, 0, 0);
+            if (ok) hd = *reinterpret_cast<const uint4 *>(t0 + (int64_t)sb * TB + 2048 + r * 16);
+            return hd;
+        };
+        bool have;
+        const uint8_t *tile0 = tile_ptr(pair, have);
+        uint4 next = chunk_at(tile0, have, grp), next2 = chunk_at(tile0, have && grp + 2 < iters, grp + 2);
+        uint4 hv_next = header_at(tile0, have, 0);
+        grid_dependency_wait();
+        const __half2 k1032 = __float2half2_rn(1032.f), k1152 = __float2half2_rn(1152.f);
+        uint32_t mask_lo = 0x000f000fu, mask_hi = 0x00f000f0u, k1024 = 0x64006400u;
+        asm volatile("" : "+r"(mask_lo), "+r"(mask_hi), "+r"(k1024));
+        bool alive = true;
+        int git_base = 0;
+        const int64_t b_it_stride = (p.Mp >> 3) << 10;
+        const bool trd = p.trace != nullptr && pair == 0 && dwa == 0;
+        unsigned long long t_empty = 0, t_conv = 0, t_begin = trd ? global_ns() : 0;
+        for (int64_t tile = pair; tile < n_otiles; tile += n_pairs) {
+            bool have_n;
+            const uint8_t *tile0_n = tile_ptr(tile + n_pairs, have_n);
+            // this CTA's activation rows of a stage: 128 of each 256-row block of the tile, a contiguous 16 KB run each
+            int64_t n_tile_c, m_tile_c;
+            const int mh = tile_at(tile, n_tile_c, m_tile_c);
+            const int64_t m_row0 = m_tile_c * 512;
+            const uint8_t *bsrc0 = reinterpret_cast<const uint8_t *>(p.xh) + (((m_row0 + (int64_t)rank * 128) >> 3) << 10);
+            for (int it = grp; it < iters; it += 2) {
+                const int git = git_base + it, sb = it >> 2, stage = git % STAGES;
+                const uint4 w = next;
+                next = next2;
+                if (it + 4 < iters) next2 = chunk_at(tile0, have, it + 4);
+                else next2 = chunk_at(tile0_n, have_n && (it + 4 - iters) < iters, it + 4 - iters);
+                if ((it & 3) == grp) {
+                    // first own stage of a super-block: lane (r, h) unpacks half h of row r's scales into the header area
+                    __syncwarp();
+                    const uint4 hv = hv_next;
+                    if (sb + 1 < (int)p.SBp) hv_next = header_at(tile0, have, sb + 1);
+                    else hv_next = header_at(tile0_n, have_n, 0);
+                    const __half2 dd = *reinterpret_cast<const __half2 *>(&hv.x);
+                    const float d = __low2float(dd), dmin = __high2float(dd);
+                    uint32_t scw, mw;
+                    if (h == 0) {
+                        scw = hv.y & 0x3f3f3f3fu;
+                        mw = hv.z & 0x3f3f3f3fu;
+                    } else {
+                        scw = (hv.w & 0x0f0f0f0fu) | ((hv.y >> 2) & 0x30303030u);
+                        mw = ((hv.w >> 4) & 0x0f0f0f0fu) | ((hv.z >> 2) & 0x30303030u);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float sc = d * (float)((scw >> (8 * i)) & 0xff);
+                        const float off = fmaf(8.f, sc, -dmin * (float)((mw >> (8 * i)) & 0xff));
+                        const __half2 s2 = __float2half2_rn((i & 1) ? sc * 0.0625f : sc);
+                        const __half2 o2 = __float2half2_rn(off);
+                        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(my_hdr + (uint32_t)(r * 80 + (4 * h + i) * 8)),
+                                     "r"(*reinterpret_cast<const uint32_t *>(&s2)), "r"(*reinterpret_cast<const uint32_t *>(&o2))
+                                     : "memory");
+                    }
+                    __syncwarp();
+                }
+                unsigned long long tw0 = trd ? global_ns() : 0;
+                if (git >= STAGES && alive) alive = mbar_wait_warp(empty_bar + 8 * stage, (uint32_t)(((git / STAGES) - 1) & 1), p.status, lane);
+                if (trd) {
+                    t_empty += global_ns() - tw0;
+                    tw0 = global_ns();
+                }
+                const uint32_t w_stage = stages_u32 + stage * GP_STAGE;
+                if (dw == 0 && lane == 0) {
+                    // the first CTA's copy is counted on `full` itself, the second CTA's on its local barrier (forwarded below)
+                    const uint32_t bar = (rank == 0 ? full_bar : act_bar) + 8 * stage;
+                    mbar_expect_tx(bar, (uint32_t)mh * 16384u);
+                    for (int hb = 0; hb < mh; hb++)
+                        bulk_g2s(w_stage + GP_STAGE_W + hb * 16384, bsrc0 + it * b_it_stride + (int64_t)hb * (32 << 10), 16384u, bar);
+                }
+                {
+                    const uint32_t wa[4] = {w.x, w.y, w.z, w.w};
+                    uint4 so[4];
+                    __half2 res[4][4];
+#pragma unroll
+                    for (int sl = 0; sl < 4; sl++)
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(so[sl].x), "=r"(so[sl].y), "=r"(so[sl].z), "=r"(so[sl].w)
+                                     : "r"(my_hdr + hdr_off[sl]));
+#pragma unroll
+                    for (int sl = 0; sl < 4; sl++) {
+                        const __half2 sc_lo = *reinterpret_cast<const __half2 *>(&so[sl].x), of_lo = *reinterpret_cast<const __half2 *>(&so[sl].y);
+                        const __half2 sc_hi = *reinterpret_cast<const __half2 *>(&so[sl].z), of_hi = *reinterpret_cast<const __half2 *>(&so[sl].w);
+                        const uint32_t x = wa[sl], x8 = x >> 8;
+                        uint32_t v0 = and_or(x, mask_lo, k1024), v1 = and_or(x8, mask_lo, k1024);
+                        uint32_t v2 = and_or(x, mask_hi, k1024), v3 = and_or(x8, mask_hi, k1024);
+                        res[sl][0] = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v0), k1032), sc_lo, of_lo);
+                        res[sl][1] = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v1), k1032), sc_lo, of_lo);
+                        res[sl][2] = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v2), k1152), sc_hi, of_hi);
+                        res[sl][3] = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&v3), k1152), sc_hi, of_hi);
+                    }
+#pragma unroll
+                    for (int sl = 0; sl < 4; sl++) {
+                        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(w_stage + dst_off[sl][0]),
+                                     "r"(*reinterpret_cast<const uint32_t *>(&res[sl][0])), "r"(*reinterpret_cast<const uint32_t *>(&res[sl][1]))
+                                     : "memory");
+                        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(w_stage + dst_off[sl][1]),
+                                     "r"(*reinterpret_cast<const uint32_t *>(&res[sl][2])), "r"(*reinterpret_cast<const uint32_t *>(&res[sl][3]))
+                                     : "memory");
+                    }
+                }
+                fence_async_smem();  // (both CTAs' tensor cores read these rows; the release at cluster scope below orders them)
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive((rank == 0 ? full_bar : act_bar) + 8 * stage);
+                }
+                if (trd) t_conv += global_ns() - tw0;
+            }
+            tile0 = tile0_n;
+            have = have_n;
+            git_base += iters;
+        }
+        if (trd && lane == 0) {
+            // timeline entry of kind 4: conversion warp 0 of either CTA of the first pair
+            const unsigned long long slot = atomicAdd(p.trace, 1ull);
+            if (slot < 8192) {
+                unsigned long long *e = p.trace + 8 + slot * 8;
+                e[0] = 4; e[1] = t_begin; e[2] = t_empty; e[3] = t_conv; e[4] = (unsigned long long)git_base; e[5] = global_ns();
+                e[6] = gridDim.x; e[7] = (unsigned long long)p.N;
+            }
+        }
+    } else if (rank == 0) {
+        // ------------------------------------------------------------------ MMA issue (first CTA of the pair)
+        if (lane == 0) {
+            bool alive = true;
+            constexpr uint32_t idesc = idesc_f16_pair(256);
+            int git = 0, tcount = 0;
+            const bool tr = p.trace != nullptr && pair == 0;
+            unsigned long long t_start = tr ? global_ns() : 0, t_full = 0, t_acc = 0, t_issue = 0;
+            for (int64_t tile = pair; tile < n_otiles; tile += n_pairs, tcount++) {
+                // both CTAs' epilogue warps have drained the accumulators of the previous tile
+                unsigned long long t0 = tr ? global_ns() : 0;
+                if (tcount >= 1 && alive) alive = mbar_wait_bounded_cluster(acce_bar, (uint32_t)((tcount - 1) & 1), p.status);
+                if (tr) t_acc += global_ns() - t0;
+                tc_fence_after();
+                int64_t n_tile_c, m_tile_c;
+                const int mh = tile_at(tile, n_tile_c, m_tile_c);
+                for (int it = 0; it < iters; it++, git++) {
+                    const int stage = git % STAGES;
+                    if (tr) t0 = global_ns();
+                    if (alive) alive = mbar_wait_bounded(full_bar + 8 * stage, (uint32_t)((git / STAGES) & 1), p.status);
+                    if (tr) {
+                        t_full += global_ns() - t0;
+                        t0 = global_ns();
+                    }
+                    tc_fence_after();
+                    const uint32_t w_stage = stages_u32 + stage * GP_STAGE;
+                    const uint64_t wdesc = smem_desc_sw128(w_stage);
+                    for (int hb = 0; hb < mh; hb++) {
+                        const uint64_t xdesc = smem_desc_sw128(w_stage + GP_STAGE_W + hb * 16384);
+#pragma unroll
+                        for (int kk = 0; kk < 4; kk++)
+                            umma_f16_pair(tmem_base + (uint32_t)(hb * 256), xdesc + (uint64_t)(2 * kk), wdesc + (uint64_t)(2 * kk), idesc, (it > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    umma_commit_pair(empty_bar + 8 * stage);
+                    if (tr) t_issue += global_ns() - t0;
+                }
+                umma_commit_pair(accf_bar);
+            }
+            if (tr) {
+                // timeline entry of kind 3, as in the one-CTA kernel
+                const unsigned long long slot = atomicAdd(p.trace, 1ull);
+                if (slot < 8192) {
+                    unsigned long long *e = p.trace + 8 + slot * 8;
+                    e[0] = 3; e[1] = t_start; e[2] = t_full; e[3] = t_acc; e[4] = (unsigned long long)git; e[5] = global_ns();
+                    e[6] = t_issue; e[7] = (unsigned long long)p.N;
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ second CTA: forward the activation copies
+        if (lane == 0) {
+            bool alive = true;
+            int git = 0;
+            for (int64_t tile = pair; tile < n_otiles; tile += n_pairs) {
+                for (int it = 0; it < iters; it++, git++) {
+                    const int stage = git % STAGES;
+                    if (alive) alive = mbar_wait_bounded(act_bar + 8 * stage, (uint32_t)((git / STAGES) & 1), p.status);
+                    mbar_arrive_cluster(full_bar + 8 * stage, 0);
+                }
+            }
+        }
+        __syncwarp();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // nothing of the pair is in flight any more: barriers, shared and tensor memory may go
+    if (warp == GP_WARPS - 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
 // Sum of the split-K partials (+ bias) into y.
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ ws, int splits, int64_t M, int64_t Mp, int64_t N,
                                                             const void *bias, int bias_dt, void *y, int y_dt, int64_t ldy) {
@@ -828,6 +1243,38 @@ cudaError_t launch_cfg(const GemmParams &p, int sms, cudaStream_t st) {
     const int64_t tiles = ((p.N + GEMM_BN * NSUB - 1) / (GEMM_BN * NSUB)) * (p.group_tiles != nullptr ? p.mt_cap : p.Mp / BM) * p.splits;
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
     return launch_pdl(gemm_q4k_kernel<BM, NSUB, MODE>, dim3(grid), dim3(C::THREADS), (size_t)C::TOTAL, st, p);
+}
+
+// pairs of CTAs (cluster of 2) over the output tiles; programmatic stream serialization like every other launch
+cudaError_t launch_pair(const GemmParams &p, int sms, cudaStream_t st) {
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!configured[dev]) {
+        e = cudaFuncSetAttribute(gemm_q4k_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GP_TOTAL);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    const int64_t tiles = ((p.N + 255) / 256) * ((p.Mp + 511) / 512);
+    const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
+    static const bool pdl = env_flag("TTQ_PDL", true);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * pairs));
+    cfg.blockDim = dim3(GP_THREADS);
+    cfg.dynamicSmemBytes = GP_TOTAL;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, gemm_q4k_pair_kernel, p);
 }
 
 }  // namespace
@@ -903,7 +1350,8 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
             p.splits = splits;
             p.ws = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(xh) + ((xh_bytes + 255) & ~(size_t)255));
         }
-        auto run = [&](const GemmParams &q) -> cudaError_t {
+        auto run = [&](const GemmParams &q, bool pair) -> cudaError_t {
+            if (pair) return launch_pair(q, sms, st);
             if (plain) {
                 if (BM == 64) return launch_cfg<64, 2, GM_PLAIN>(q, sms, st);
                 if (BM == 128) return launch_cfg<128, 2, GM_PLAIN>(q, sms, st);
@@ -938,40 +1386,92 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
         };
         // Ragged last round: with more output tiles than SMs, the tiles left over after the last full round keep a
         // few SMs busy for a whole tile time.  The last weight-tile columns -- just enough of them that the rest fits
-        // one round less -- then go to a second launch of the same kernel with K cut into runs, spread over all SMs.
-        // Cost model in pipeline stages: a unit of iters/S stages also pays a fixed turnaround (accumulator drain +
-        // fp32 partial store, about 20 stages), the second launch a ramp of about 6, and the reduction pass reads
-        // every partial back.  Measured at 2048 rows: 4096 -> 28672 (896 tiles, 8 left over) gains a third of a tile
-        // time with 8 runs; 4096 -> 6144 (192 tiles, 44 left over) loses with any split and is left alone.
+        // one round less -- then go to a second launch of the one-CTA kernel with K cut into runs, spread over all SMs.
+        // Cost model in pipeline stages of the one-CTA kernel: a unit of iters/S stages also pays a fixed turnaround
+        // (accumulator drain + fp32 partial store, about 20 stages), the second launch a ramp of about 6, and the
+        // reduction pass reads every partial back.  Measured at 2048 rows: 4096 -> 28672 (896 tiles, 8 left over) gains
+        // a third of a tile time with 8 runs; 4096 -> 6144 (192 tiles, 44 left over) loses with any split and is left alone.
         static const bool tail_on = env_flag("TTQ_GEMM_TAIL", true);
         const int TN = 128 * nsub;
         const int64_t n_tiles = (a.N + TN - 1) / TN, tiles = n_tiles * m_tiles;
+        const double iters = (double)a.SBp * 4;
+        const size_t xh_bytes = (size_t)Mp * Kp * sizeof(__half);
+        const size_t ws_cap = (size_t)xh_capacity * sizeof(__half) > xh_bytes ? (size_t)xh_capacity * sizeof(__half) - xh_bytes : 0;
+        auto tail_cost = [&](int64_t cols, int min_runs, int &runs) -> double {
+            double best = 1e30;
+            runs = 0;
+            for (int cand = min_runs; cand <= 16; cand++) {
+                if (a.SBp % cand || (cand > 1 && a.SBp / cand < 2)) continue;
+                if (cand > 1 && (size_t)cand * Mp * cols * TN * sizeof(float) > ws_cap) break;
+                const int64_t units = cols * m_tiles * cand;
+                const double cost = cand > 1 ? (double)((units + sms - 1) / sms) * (iters / cand + 20.0) + 6.0 + 0.08 * (double)units
+                                             : (double)((units + sms - 1) / sms) * (iters + 8.0) + 6.0;
+                if (cost < best) {
+                    best = cost;
+                    runs = cand;
+                }
+            }
+            return best;
+        };
         int64_t tail_cols = 0;
         int tail_splits = 1;
+        double cost_one = (double)((tiles + sms - 1) / sms) * (iters + 8.0);
         if (tail_on && !plain && splits == 1 && tiles > sms && tiles % sms != 0) {
             const int64_t rounds = (tiles + sms - 1) / sms;
             const int64_t cols = (tiles - (rounds - 1) * sms + m_tiles - 1) / m_tiles;  // columns that must leave the main launch
-            const double iters = (double)a.SBp * 4;
-            double best = 0.85 * (iters + 8.0);
-            const size_t xh_bytes = (size_t)Mp * Kp * sizeof(__half);
-            const size_t ws_cap = (size_t)xh_capacity * sizeof(__half) > xh_bytes ? (size_t)xh_capacity * sizeof(__half) - xh_bytes : 0;
-            for (int cand = 2; cand <= 16 && cols < n_tiles; cand++) {
-                if (a.SBp % cand || a.SBp / cand < 2) continue;
-                if ((size_t)cand * Mp * cols * TN * sizeof(float) > ws_cap) break;
-                const int64_t units = cols * m_tiles * cand;
-                const double cost = (double)((units + sms - 1) / sms) * (iters / cand + 20.0) + 6.0 + 0.08 * (double)units;
-                if (cost < best) {
-                    best = cost;
-                    tail_cols = cols;
-                    tail_splits = cand;
+            int runs = 0;
+            const double c = cols < n_tiles ? tail_cost(cols, 2, runs) : 1e30;
+            if (runs > 0 && c < 0.85 * (iters + 8.0)) {
+                tail_cols = cols;
+                tail_splits = runs;
+                cost_one = (double)(rounds - 1) * (iters + 8.0) + c;
+            }
+        }
+        // The two-CTA kernel (dense Q4_K, more than 128 rows, no K split): a pair's tile is 256 weight rows x 512
+        // activation rows, and a stage of it takes about 0.85 of the one-CTA kernel's stage for twice the work (measured
+        // at 4096 -> 28672, 2048 rows); a half tile (256 rows) about 0.6.  With 74 slots the rounds are coarser, so the
+        // model prices both kernels, each with its best tail, and takes the cheaper.  The pair's load is that of the
+        // first pair: tiles are dealt round-robin, full tiles first.
+        // TTQ_GEMM_PAIR: 0 never, 1 (default) where the model prefers it, 2 wherever it applies
+        static const int pair_mode = []() {
+            const char *v = getenv("TTQ_GEMM_PAIR");
+            return v ? atoi(v) : 1;
+        }();
+        bool use_pair = false;
+        if (pair_mode > 0 && !plain && fmt == TTQ_FMT_Q4_K && BM == 256 && nsub == 2 && splits == 1) {
+            const int64_t slots = sms / 2, m_full = Mp / 512, m_half = (Mp % 512) ? 1 : 0;
+            const double c_full = 0.85 * iters + 8.0, c_half = 0.6 * iters + 6.0;
+            auto makespan = [&](int64_t cols) {
+                const int64_t nf = cols * m_full, nt = nf + cols * m_half;
+                double t = 0;
+                for (int64_t k = 0; k < nt; k += slots) t += k < nf ? c_full : c_half;
+                return t;
+            };
+            double best = makespan(n_tiles);
+            int64_t best_cols = 0;
+            int best_runs = 1;
+            for (int64_t cols = 1; tail_on && cols <= 16 && cols < n_tiles; cols++) {
+                int runs = 0;
+                const double t = tail_cost(cols, 1, runs);
+                if (runs == 0) continue;
+                const double total = makespan(n_tiles - cols) + t;
+                if (total < 0.97 * best) {
+                    best = total;
+                    best_cols = cols;
+                    best_runs = runs;
                 }
+            }
+            if (slots > 0 && (best < cost_one || pair_mode >= 2)) {
+                use_pair = true;
+                tail_cols = best_cols;
+                tail_splits = best_runs;
             }
         }
         if (tail_cols > 0) {
             const int64_t n_main = (n_tiles - tail_cols) * TN;  // output features of the main launch
             GemmParams q = p;
             q.N = n_main; q.NT = n_main / TILE_ROWS;
-            e = run(q);
+            e = run(q, use_pair);
             if (e != cudaSuccess) return e;
             ++*launches;
             q = p;
@@ -980,15 +1480,17 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
             if (a.bias != nullptr) q.bias = reinterpret_cast<const uint8_t *>(a.bias) + (size_t)n_main * (a.bias_dt == TTQ_DT_F32 ? 4 : 2);
             q.y = reinterpret_cast<uint8_t *>(p.y) + (size_t)n_main * esz_y;
             q.splits = tail_splits;
-            e = run(q);
+            e = run(q, false);
             if (e != cudaSuccess) return e;
             ++*launches;
-            e = reduce(q);
-            if (e != cudaSuccess) return e;
-            ++*launches;
+            if (tail_splits > 1) {
+                e = reduce(q);
+                if (e != cudaSuccess) return e;
+                ++*launches;
+            }
             continue;
         }
-        e = run(p);
+        e = run(p, use_pair);
         if (e != cudaSuccess) return e;
         ++*launches;
         if (splits > 1) {
