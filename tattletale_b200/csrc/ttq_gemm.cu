@@ -126,6 +126,23 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         : "r"(taddr));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// The same load without the wait, and the wait: the registers pass through the wait statement so that no use of them
+// is scheduled before it.
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&v)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]),
+                   "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+                 :
+                 : "memory");
+}
 
 // ---- activation pass: x [M][K] (bf16 | f16) -> fp16 tile images ------------------------------------
 // Output layout: [stage it = 4*sb + s][row atom m/8][1024 bytes]: the 8 rows x 128 bytes of one
@@ -466,19 +483,24 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
         const uint32_t my_hdr = hdr_u32 + dwa * 1280;
         // byte offsets (inside a 128-row A sub-tile) of this lane's stores: register sl, slot pair
         const int u0 = t >> 1, u1 = 2 + (t >> 1);
+        // Q4_K: lanes with t >= 2 take their four packed words in the order 2, 3, 0, 1.  A store instruction of 8 bytes per
+        // lane is served half a warp at a time, and the 16 lanes of a half (rows g = 0..3) then write eight different
+        // 16-byte columns of the swizzled rows instead of four, twice each: half the shared-memory wavefronts.
+        const bool swp = MODE == GM_Q4K && (t & 2) != 0;
         uint32_t dst_off[4][2], hdr_off[4];
 #pragma unroll
-        for (int sl = 0; sl < 4; sl++) {
+        for (int slp = 0; slp < 4; slp++) {
+            const int sl = swp ? (slp ^ 2) : slp;
             const int u = (sl >> 1) ? u1 : u0;
             const int row = dw * 16 + g + 8 * (sl & 1);
             const uint32_t key = (uint32_t)(row & 7);
             // Q4_K, Q6_K: slots 2u (low nibbles) and 2u+1 (high nibbles).  Q8_0: slots u (first chunk) and 4 + u (second)
             const uint32_t j0 = MODE == GM_Q8_0 ? (uint32_t)u : (uint32_t)(2 * u), j1 = MODE == GM_Q8_0 ? (uint32_t)(4 + u) : (uint32_t)(2 * u + 1);
-            dst_off[sl][0] = (uint32_t)row * 128 + ((j0 ^ key) << 4) + (uint32_t)(t & 1) * 8;
-            dst_off[sl][1] = (uint32_t)row * 128 + ((j1 ^ key) << 4) + (uint32_t)(t & 1) * 8;
+            dst_off[slp][0] = (uint32_t)row * 128 + ((j0 ^ key) << 4) + (uint32_t)(t & 1) * 8;
+            dst_off[slp][1] = (uint32_t)row * 128 + ((j1 ^ key) << 4) + (uint32_t)(t & 1) * 8;
             // per-row scale records in the warp's header area (80-byte rows): Q4_K {scale2, offset2} per sub-block (8 B),
             // Q8_0 scale2 per block (4 B), Q6_K scale2 per 16-wide sub-block (4 B)
-            hdr_off[sl] = (uint32_t)((g + 8 * (sl & 1)) * 80) + (MODE == GM_Q4K ? (uint32_t)(2 * u * 8) : (uint32_t)(u * 4));
+            hdr_off[slp] = (uint32_t)((g + 8 * (sl & 1)) * 80) + (MODE == GM_Q4K ? (uint32_t)(2 * u * 8) : (uint32_t)(u * 4));
         }
         bool alive = true;
         int git_base = 0;  // stage counter across tiles, at the start of the current tile
@@ -636,7 +658,7 @@ __global__ void __launch_bounds__(GemmCfg<BM, NSUB>::THREADS, 1) gemm_q4k_kernel
                     bulk_g2s(a_stage + C::A_BYTES, bsrc0 + it * b_it_stride, b_bytes, full_bar + 8 * stage);
                 }
                 {
-                    const uint32_t wa[4] = {w.a.x, w.a.y, w.a.z, w.a.w};
+                    const uint32_t wa[4] = {swp ? w.a.z : w.a.x, swp ? w.a.w : w.a.y, swp ? w.a.x : w.a.z, swp ? w.a.y : w.a.w};
                     const uint32_t a_sub = a_stage + my_sub * A_STAGE_BYTES;
                     // three phases (loads, arithmetic, stores) so that the shared-memory latencies overlap
                     __half2 res[4][4];  // per register: the two fp16 pairs of slot j0, then of slot j1
@@ -819,7 +841,7 @@ constexpr int GP_STAGES = 4;
 constexpr int GP_HDR = 16 * 1280;
 constexpr int GP_BARS = 256;  // full, empty, act [GP_STAGES]; acc_full, acc_empty [2]; tensor-memory address word
 constexpr int GP_TOTAL = 1024 + GP_STAGES * GP_STAGE + GP_HDR + GP_BARS;
-constexpr int GP_EPI_WARPS = 8;  // two per tensor-memory lane quarter
+constexpr int GP_EPI_WARPS = 4;  // one per tensor-memory lane quarter (21 warps leave 80 registers a thread)
 constexpr int GP_WARPS = GP_EPI_WARPS + 16 + 1, GP_THREADS = GP_WARPS * 32;
 static_assert(GP_TOTAL <= 227 * 1024, "shared memory over the limit");
 
@@ -934,18 +956,14 @@ __global__ void __launch_bounds__(GP_THREADS, 1) gemm_q4k_pair_kernel(GemmParams
             const int mh = tile_at(tile, n_tile, m_tile);
             if (alive) alive = mbar_wait_warp(accf_bar, (uint32_t)(tcount & 1), p.status, lane);
             tc_fence_after();
-            // a warp reads the 32 tensor-memory lanes of its quarter; the two warps of a quarter split the columns
-            const int quad = warp & 3, part = warp >> 2, c_len = mh * 128;
-#pragma unroll 1
-            for (int c = part * c_len; c < (part + 1) * c_len; c += 16) {
+            const int quad = warp & 3;  // a warp reads the 32 tensor-memory lanes of its quarter
+            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16);
+            auto emit = [&](const uint32_t (&v)[16], int c) {
                 // columns [256 hb, 256 hb + 256) hold activation rows 256 hb + 128 rank + lane of the tile
                 const int hb = c >> 8, c0 = c & 255;
                 const int64_t m = m_tile * 512 + hb * 256 + (int64_t)rank * 128 + quad * 32 + lane;
-                const bool row_ok = m < p.M;
-                uint32_t v[16];
-                tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c, v);
                 const int64_t n0 = n_tile * 256 + c0;
-                if (!row_ok || n0 >= p.N) continue;
+                if (m >= p.M || n0 >= p.N) return;
                 float f[16];
 #pragma unroll
                 for (int i = 0; i < 16; i++) f[i] = __uint_as_float(v[i]);
@@ -980,6 +998,19 @@ __global__ void __launch_bounds__(GP_THREADS, 1) gemm_q4k_pair_kernel(GemmParams
                     for (int i = 0; i < 16; i++)
                         if (n0 + i < p.N) store_from_float(p.y, p.y_dt, m * p.ldy + n0 + i, f[i]);
                 }
+            };
+            // two register sets: the next 16 columns are on their way from tensor memory while these are stored
+            uint32_t va[16], vb[16];
+            const int c_begin = 0, c_end = mh * 256;
+            tmem_ld16_issue(t_row + (uint32_t)c_begin, va);
+#pragma unroll 1
+            for (int c = c_begin; c < c_end; c += 32) {
+                tmem_ld_wait(va);
+                tmem_ld16_issue(t_row + (uint32_t)(c + 16), vb);
+                emit(va, c);
+                tmem_ld_wait(vb);
+                if (c + 32 < c_end) tmem_ld16_issue(t_row + (uint32_t)(c + 32), va);
+                emit(vb, c + 16);
             }
             tc_fence_before();
             __syncwarp();
@@ -992,15 +1023,20 @@ __global__ void __launch_bounds__(GP_THREADS, 1) gemm_q4k_pair_kernel(GemmParams
         const int g = lane >> 2, t = lane & 3, r = lane & 15, h = lane >> 4;
         const uint32_t my_hdr = hdr_u32 + dwa * 1280;
         const int u0 = t >> 1, u1 = 2 + (t >> 1);
+        // Lanes with t >= 2 take their four packed words in the order 2, 3, 0, 1: a store instruction of 8 bytes per lane
+        // is served half a warp at a time, and the 16 lanes of a half (rows g = 0..3) then write eight different
+        // 16-byte columns of the swizzled rows instead of four, twice each.
+        const bool swp = (t & 2) != 0;
         uint32_t dst_off[4][2], hdr_off[4];
 #pragma unroll
-        for (int sl = 0; sl < 4; sl++) {
+        for (int slp = 0; slp < 4; slp++) {
+            const int sl = swp ? (slp ^ 2) : slp;
             const int u = (sl >> 1) ? u1 : u0;
             const int row = dw * 16 + g + 8 * (sl & 1);
             const uint32_t key = (uint32_t)(row & 7);
-            dst_off[sl][0] = (uint32_t)row * 128 + (((uint32_t)(2 * u) ^ key) << 4) + (uint32_t)(t & 1) * 8;
-            dst_off[sl][1] = (uint32_t)row * 128 + (((uint32_t)(2 * u + 1) ^ key) << 4) + (uint32_t)(t & 1) * 8;
-            hdr_off[sl] = (uint32_t)((g + 8 * (sl & 1)) * 80) + (uint32_t)(2 * u * 8);
+            dst_off[slp][0] = (uint32_t)row * 128 + (((uint32_t)(2 * u) ^ key) << 4) + (uint32_t)(t & 1) * 8;
+            dst_off[slp][1] = (uint32_t)row * 128 + (((uint32_t)(2 * u + 1) ^ key) << 4) + (uint32_t)(t & 1) * 8;
+            hdr_off[slp] = (uint32_t)((g + 8 * (sl & 1)) * 80) + (uint32_t)(2 * u * 8);
         }
         auto tile_ptr = [&](int64_t tile, bool &have) {
             int64_t n_tile = 0, m_tile = 0;
@@ -1089,7 +1125,7 @@ __global__ void __launch_bounds__(GP_THREADS, 1) gemm_q4k_pair_kernel(GemmParams
                         bulk_g2s(w_stage + GP_STAGE_W + hb * 16384, bsrc0 + it * b_it_stride + (int64_t)hb * (32 << 10), 16384u, bar);
                 }
                 {
-                    const uint32_t wa[4] = {w.x, w.y, w.z, w.w};
+                    const uint32_t wa[4] = {swp ? w.z : w.x, swp ? w.w : w.y, swp ? w.x : w.z, swp ? w.y : w.w};
                     uint4 so[4];
                     __half2 res[4][4];
 #pragma unroll
