@@ -441,7 +441,7 @@ def ours_arm(args):
         "traffic": _measured_traffic("gemv_q4k_m1_llama8b_per_launch") if (m == 1 and world == 1) else None,
         "traffic_source": "ncu capture of a 2-layer case, mean over one layer's four launches" if (m == 1 and world == 1) else None,
         "peak_source": peak_kind,
-        "kernel": "xprep_kernel + gemv_kernel<Q4_K> (activation planes bulk-copied from scratch)",
+        "kernel": _linear_kernel_name(m),
         "avg_launch_us": round(ms_step * 1e3 / gemv_launches, 3),
         "algorithmic_bytes_per_launch": step_bytes // gemv_launches,
         "frac_of_nominal_8TBs": round(value / world / 8000.0, 4),
@@ -470,11 +470,20 @@ def ours_arm(args):
         tpeak = float(peaks.get("bf16_tflops", 1590.0))
         line["sweep"] = sweep
         line["roofline_gemm"] = {"bound": "tensor", "achieved": best, "peak": tpeak, "unit": "TFLOP/s",
-                                 "frac": round(best / tpeak, 4), "kernel": "gemm_q4k_kernel (tcgen05, fp16 operands, fp32 accumulate)",
+                                 "frac": round(best / tpeak, 4), "kernel": "gemm_q4k_pair_kernel (tcgen05 cta_group::2) or gemm_q4k_kernel, chosen per call by the library's cost model; fp16 operands, fp32 accumulate",
                                  "workload": "best of the four Q4_K shapes at M=2048 (graph replay over 4 layers' weights, includes the activation pass)",
                                  "peak_source": "MEASURED_PEAKS.json bf16_tflops (burst)" if "bf16_tflops" in peaks else "fallback 1590"}
     print(json.dumps(line), flush=True)
     _finish_distributed(dist, world)
+
+
+def _linear_kernel_name(m: int) -> str:
+    """The kernels a Q4_K linear of `m` rows runs (the library's dispatch by row count)."""
+    if m <= 2:
+        return "xprep_kernel + gemv_kernel<Q4_K> (activation planes bulk-copied from scratch)"
+    if m <= 16:
+        return "q4k_decode_kernel (one launch, integer-exact fp16 mma.sync)"
+    return "xh_prep_kernel + gemm_q4k_kernel / gemm_q4k_pair_kernel (tcgen05, tensor memory)"
 
 
 def _time_graph(step, reps: int = 4, warm: int = 2) -> float:
