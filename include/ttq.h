@@ -43,6 +43,7 @@ typedef struct ttq_ctx ttq_ctx;
 typedef struct ttq_weight ttq_weight;
 typedef struct ttq_comm ttq_comm;
 typedef struct ttq_moe ttq_moe;
+typedef struct ttq_host_batch ttq_host_batch;
 
 typedef enum ttq_status {
     TTQ_OK = 0,
@@ -152,12 +153,51 @@ TTQ_API ttq_status ttq_linear_forward(ttq_ctx *ctx, const ttq_weight *w, const v
                               int64_t M, int64_t ldx, const void *bias_dev, ttq_dtype bias_dt,
                               void *y_dev, ttq_dtype y_dt, int64_t ldy, void *stream);
 
-/* Host-buffer form of the same call: copies x (and bias) to the device through the context's pinned
- * staging area, runs forward, copies y back and synchronises.  x/y limited to the staging capacity
- * (TTQ_ERR_LIMIT beyond it). */
+/* Host-buffer form of the same call, synchronous like the reference's `Linear.forward`
+ * (workspace/libtorch/src/workspace/layers/module.nim:8-24 on CPU tensors).  Page-locked buffers of up to 1 MiB in
+ * total (decode sizes) are read and written in place through their device mappings; pageable or larger buffers go
+ * through the context's pinned staging area (TTQ_ERR_LIMIT beyond its capacity).  Runs on the context's own host
+ * stream, waits for it and reports a kernel that gave up a bounded wait (TTQ_ERR_TIMEOUT). */
 TTQ_API ttq_status ttq_linear_forward_host(ttq_ctx *ctx, const ttq_weight *w, const void *x_host, ttq_dtype x_dt,
                                    int64_t M, int64_t ldx, const void *bias_host, ttq_dtype bias_dt,
                                    void *y_host, ttq_dtype y_dt, int64_t ldy);
+
+/* The same call without the wait (no counterpart in the reference, whose forward is synchronous): it only enqueues
+ * the work on the context's host stream, so that a caller with several linears to run pays one wait per batch
+ * of calls instead of one per call.  x, bias and y must be page-locked and at most 1 MiB in total
+ * (TTQ_ERR_INVALID_ARG for pageable memory, TTQ_ERR_LIMIT for size); they must stay valid, and y unread, until
+ * ttq_host_sync returns.  Calls execute in the order they were made. */
+TTQ_API ttq_status ttq_linear_forward_host_async(ttq_ctx *ctx, const ttq_weight *w, const void *x_host, ttq_dtype x_dt,
+                                         int64_t M, int64_t ldx, const void *bias_host, ttq_dtype bias_dt,
+                                         void *y_host, ttq_dtype y_dt, int64_t ldy);
+
+/* One host-buffer linear of a recorded batch: the arguments of ttq_linear_forward_host. */
+typedef struct ttq_host_linear {
+    const ttq_weight *w;
+    const void *x_host;
+    int32_t x_dt;
+    int64_t M, ldx;
+    const void *bias_host; /* may be NULL */
+    int32_t bias_dt;
+    void *y_host;
+    int32_t y_dt;
+    int64_t ldy;
+} ttq_host_linear;
+
+/* Records `n` host-buffer linears (a decode step's worth) once, as a CUDA graph on the context's host stream, for
+ * callers that run the same linears on the same page-locked buffers step after step (no counterpart in the
+ * reference).  Same limits per linear as ttq_linear_forward_host_async.  The linears run once during the call
+ * (every kernel is configured before the recording starts).  Weights and buffers must outlive the batch; create
+ * every weight of the context before recording (see ttq_linear_forward on scratch that may move). */
+TTQ_API ttq_status ttq_host_batch_create(ttq_ctx *ctx, const ttq_host_linear *linears, int n, ttq_host_batch **out);
+/* Runs the recorded linears in order, waits, and reports a kernel that gave up a bounded wait (TTQ_ERR_TIMEOUT):
+ * when it returns TTQ_OK every y of the batch is in host memory. */
+TTQ_API ttq_status ttq_host_batch_run(ttq_host_batch *batch);
+TTQ_API ttq_status ttq_host_batch_destroy(ttq_host_batch *batch);
+
+/* Waits for everything the host entry points have enqueued on this context; TTQ_ERR_TIMEOUT if a kernel of those
+ * calls gave up a bounded wait (the results of the batch are invalid then; the flag is cleared). */
+TTQ_API ttq_status ttq_host_sync(ttq_ctx *ctx);
 
 /* Synchronises `stream` and reports whether any kernel launched through this context since the last
  * check gave up a bounded device-side wait (TTQ_ERR_TIMEOUT; the flag is cleared).  The *_host entry

@@ -12,13 +12,13 @@ streams.  Importing this package does not need a GPU; creating a :class:`Context
 """
 from ._lib import (DT_BF16, DT_F16, DT_F32, FMT_Q4_K, FMT_Q6_K, FMT_Q8_0, FMT_TQ3, SHARD_COLUMN,
                    SHARD_COLUMN_GATED, SHARD_NONE, SHARD_ROW, TtqError)
-from .layers import (ActivationKind, Context, GatedMLP, MoELayer, QuantLinear, add_rmsnorm, decode_attention,
+from .layers import (ActivationKind, Context, GatedMLP, HostBatch, MoELayer, QuantLinear, add_rmsnorm, decode_attention,
                      rope_kv_append, silu_and_mul)
 from .formats import BLOCK_BYTES, BLOCK_ELEMS, FORMAT_NAMES, packed_bytes
 from . import tp
 
 __all__ = [
-    "Context", "QuantLinear", "GatedMLP", "MoELayer", "add_rmsnorm", "rope_kv_append", "decode_attention", "ActivationKind", "silu_and_mul", "TtqError",
+    "Context", "QuantLinear", "HostBatch", "GatedMLP", "MoELayer", "add_rmsnorm", "rope_kv_append", "decode_attention", "ActivationKind", "silu_and_mul", "TtqError",
     "FMT_Q8_0", "FMT_Q4_K", "FMT_Q6_K", "FMT_TQ3", "DT_BF16", "DT_F16", "DT_F32",
     "SHARD_NONE", "SHARD_COLUMN", "SHARD_COLUMN_GATED", "SHARD_ROW",
     "BLOCK_BYTES", "BLOCK_ELEMS", "FORMAT_NAMES", "packed_bytes",

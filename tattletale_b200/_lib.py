@@ -28,6 +28,13 @@ class Shard(ctypes.Structure):
     _fields_ = [("kind", ctypes.c_int32), ("rank", ctypes.c_int32), ("world", ctypes.c_int32)]
 
 
+class HostLinear(ctypes.Structure):
+    """``ttq_host_linear``: one host-buffer linear of a recorded batch."""
+    _fields_ = [("w", ctypes.c_void_p), ("x_host", ctypes.c_void_p), ("x_dt", ctypes.c_int32), ("M", ctypes.c_int64),
+                ("ldx", ctypes.c_int64), ("bias_host", ctypes.c_void_p), ("bias_dt", ctypes.c_int32), ("y_host", ctypes.c_void_p),
+                ("y_dt", ctypes.c_int32), ("ldy", ctypes.c_int64)]
+
+
 SIGNATURES = {
     "ttq_init": (_ci, [_ci, _pp]),
     "ttq_destroy": (_ci, [_vp]),
@@ -45,6 +52,11 @@ SIGNATURES = {
     "ttq_dequantize": (_ci, [_vp, _vp, _vp, _i64, _vp]),
     "ttq_linear_forward": (_ci, [_vp, _vp, _vp, _ci, _i64, _i64, _vp, _ci, _vp, _ci, _i64, _vp]),
     "ttq_linear_forward_host": (_ci, [_vp, _vp, _vp, _ci, _i64, _i64, _vp, _ci, _vp, _ci, _i64]),
+    "ttq_linear_forward_host_async": (_ci, [_vp, _vp, _vp, _ci, _i64, _i64, _vp, _ci, _vp, _ci, _i64]),
+    "ttq_host_sync": (_ci, [_vp]),
+    "ttq_host_batch_create": (_ci, [_vp, ctypes.POINTER(HostLinear), _ci, _pp]),
+    "ttq_host_batch_run": (_ci, [_vp]),
+    "ttq_host_batch_destroy": (_ci, [_vp]),
     "ttq_linear_forward_static": (_ci, [_vp, _vp, _ci, _i64, _i64, _vp, _ci, _vp, _ci, _i64, _vp, ctypes.c_char_p, _sz]),
     "ttq_static_status": (_ci, [_vp, ctypes.c_char_p, _sz]),
     "ttq_linear_forward_gated": (_ci, [_vp, _vp, _vp, _ci, _i64, _i64, _vp, _ci, _vp, _ci, _i64, _vp]),

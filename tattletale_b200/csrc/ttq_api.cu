@@ -26,8 +26,7 @@ struct ttq_ctx {
     int *dev_status;  // device word the kernels OR failure bits into (bit 0: a bounded wait gave up)
     int *host_status; // pinned, device-mapped host words: [0] raised by a failing kernel (see report_failure), [1] copy of the status word
     // device mappings of the page-locked host buffers most recently passed to the host entry points
-    struct { const void *host; void *dev; } map_cache[8];
-    int map_next;
+    struct { const void *host; void *dev; } map_cache[1024];  // direct-mapped by address bits
     unsigned long long *trace;  // device timeline buffer, allocated only when TTQ_TRACE=1 is set at init
     float *tq_x1, *tq_y1;       // TQ3: rotated activations [TQ3_SLAB][K] and raw results [TQ3_SLAB][N] (fp32; x1 also
     int64_t tq_x1_cap, tq_y1_cap;  //   holds the fp16 form for the GEMM); capacities in floats, grown at weight creation
@@ -626,9 +625,45 @@ ttq_status ttq_linear_forward_gated(ttq_ctx *ctx, const ttq_weight *w, const voi
     return linear_forward_impl(ctx, w, gate_up_dev, x_dt, M, ld_gate_up, bias_dev, bias_dt, y_dev, y_dt, ldy, stream, true);
 }
 
-ttq_status ttq_linear_forward_host(ttq_ctx *ctx, const ttq_weight *w, const void *x_host, ttq_dtype x_dt, int64_t M,
-                                   int64_t ldx, const void *bias_host, ttq_dtype bias_dt, void *y_host, ttq_dtype y_dt,
-                                   int64_t ldy) {
+namespace {
+
+// Device mappings of page-locked host buffers (nullptr for pageable memory).  The driver query costs about a
+// microsecond per pointer: buffers that come back call after call are remembered.
+void *host_mapping(ttq_ctx *ctx, const void *p) {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    auto &slot = ctx->map_cache[((a >> 6) ^ (a >> 16)) & 1023];
+    if (slot.host == p) return slot.dev;
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    if (at.type != cudaMemoryTypeHost) return nullptr;
+    slot = {p, at.devicePointer};
+    return at.devicePointer;
+}
+
+// Waits for the context's host stream; a kernel that gave up a bounded wait has raised the mapped host flag by then.
+ttq_status host_stream_sync(ttq_ctx *ctx) {
+    cudaStream_t st = ctx->host_stream;
+    TTQ_CUDA(ctx, cudaStreamSynchronize(st));
+    if (*reinterpret_cast<volatile int *>(ctx->host_status) != 0) {
+        ctx->host_status[0] = 0;
+        TTQ_CUDA(ctx, cudaMemcpyAsync(ctx->host_status + 1, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, st));
+        TTQ_CUDA(ctx, cudaStreamSynchronize(st));
+        const int seen = ctx->host_status[1];
+        cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), st);
+        cudaMemsetAsync(ctx->split_counters, 0, (size_t)ctx->split_counters_cap * sizeof(unsigned), st);
+        return fail(ctx, TTQ_ERR_TIMEOUT, "a kernel gave up a bounded wait (status word 0x%x); results of that call are invalid", seen);
+    }
+    return TTQ_OK;
+}
+
+// Shared body of the host-buffer entry points.  `wait`: synchronise before returning (pageable buffers are allowed
+// then and go through the staging copies); without it the buffers must be page-locked and small enough to be read
+// and written in place over the host link.
+ttq_status forward_host_impl(ttq_ctx *ctx, const ttq_weight *w, const void *x_host, ttq_dtype x_dt, int64_t M, int64_t ldx,
+                             const void *bias_host, ttq_dtype bias_dt, void *y_host, ttq_dtype y_dt, int64_t ldy, bool wait) {
     if (!ctx) return TTQ_ERR_INVALID_ARG;
     if (!w) return fail(ctx, TTQ_ERR_INVALID_ARG, "weight is NULL");
     if (M < 0) return fail(ctx, TTQ_ERR_SHAPE, "M=%lld is negative", (long long)M);
@@ -649,25 +684,14 @@ ttq_status ttq_linear_forward_host(ttq_ctx *ctx, const ttq_weight *w, const void
     void *y_map = nullptr;
     bool direct = xb + yb + bbytes <= (1u << 20);
     if (direct) {
-        // the driver query costs about a microsecond per pointer: buffers that come back call after call are remembered
-        auto mapped = [ctx](const void *p) -> void * {
-            for (auto &c : ctx->map_cache)
-                if (c.host == p) return c.dev;
-            cudaPointerAttributes at;
-            if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
-                cudaGetLastError();
-                return nullptr;
-            }
-            if (at.type != cudaMemoryTypeHost) return nullptr;
-            ctx->map_cache[ctx->map_next] = {p, at.devicePointer};
-            ctx->map_next = (ctx->map_next + 1) % 8;
-            return at.devicePointer;
-        };
-        x_map = mapped(x_host);
-        y_map = mapped(y_host);
-        if (bias_host) b_map = mapped(bias_host);
+        x_map = host_mapping(ctx, x_host);
+        y_map = host_mapping(ctx, y_host);
+        if (bias_host) b_map = host_mapping(ctx, bias_host);
         direct = x_map && y_map && (!bias_host || b_map);
     }
+    if (!wait && !direct)
+        return fail(ctx, xb + yb + bbytes <= (1u << 20) ? TTQ_ERR_INVALID_ARG : TTQ_ERR_LIMIT,
+                    "the asynchronous host entry needs page-locked buffers of at most 1 MiB in total (x %zu B, y %zu B)", xb, yb);
     ttq_status s;
     if (direct) {
         s = ttq_linear_forward(ctx, w, x_map, x_dt, M, ldx, b_map, bias_dt, y_map, y_dt, ldy, st);
@@ -680,18 +704,97 @@ ttq_status ttq_linear_forward_host(ttq_ctx *ctx, const ttq_weight *w, const void
         if (s != TTQ_OK) return s;
         TTQ_CUDA(ctx, cudaMemcpyAsync(y_host, ctx->stage_y, yb, cudaMemcpyDeviceToHost, st));
     }
-    // one synchronisation per call; a kernel that gave up a wait has raised the mapped host flag by then
-    TTQ_CUDA(ctx, cudaStreamSynchronize(st));
-    if (*reinterpret_cast<volatile int *>(ctx->host_status) != 0) {
-        ctx->host_status[0] = 0;
-        TTQ_CUDA(ctx, cudaMemcpyAsync(ctx->host_status + 1, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, st));
-        TTQ_CUDA(ctx, cudaStreamSynchronize(st));
-        const int seen = ctx->host_status[1];
-        cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), st);
-        cudaMemsetAsync(ctx->split_counters, 0, (size_t)ctx->split_counters_cap * sizeof(unsigned), st);
-        return fail(ctx, TTQ_ERR_TIMEOUT, "a kernel gave up a bounded wait (status word 0x%x); results of that call are invalid", seen);
+    return wait ? host_stream_sync(ctx) : TTQ_OK;
+}
+
+}  // namespace
+
+ttq_status ttq_linear_forward_host(ttq_ctx *ctx, const ttq_weight *w, const void *x_host, ttq_dtype x_dt, int64_t M,
+                                   int64_t ldx, const void *bias_host, ttq_dtype bias_dt, void *y_host, ttq_dtype y_dt,
+                                   int64_t ldy) {
+    return forward_host_impl(ctx, w, x_host, x_dt, M, ldx, bias_host, bias_dt, y_host, y_dt, ldy, true);
+}
+
+ttq_status ttq_linear_forward_host_async(ttq_ctx *ctx, const ttq_weight *w, const void *x_host, ttq_dtype x_dt, int64_t M,
+                                         int64_t ldx, const void *bias_host, ttq_dtype bias_dt, void *y_host, ttq_dtype y_dt,
+                                         int64_t ldy) {
+    return forward_host_impl(ctx, w, x_host, x_dt, M, ldx, bias_host, bias_dt, y_host, y_dt, ldy, false);
+}
+
+struct ttq_host_batch {
+    ttq_ctx *ctx;
+    cudaGraph_t graph;
+    cudaGraphExec_t exec;
+};
+
+ttq_status ttq_host_batch_create(ttq_ctx *ctx, const ttq_host_linear *linears, int n, ttq_host_batch **out) {
+    if (!ctx) return TTQ_ERR_INVALID_ARG;
+    if (!out) return fail(ctx, TTQ_ERR_INVALID_ARG, "output pointer is NULL");
+    *out = nullptr;
+    if (!linears || n <= 0) return fail(ctx, TTQ_ERR_INVALID_ARG, "empty batch");
+    TTQ_CUDA(ctx, cudaSetDevice(ctx->device));
+    auto enqueue = [&]() -> ttq_status {
+        for (int i = 0; i < n; i++) {
+            const ttq_host_linear &l = linears[i];
+            ttq_status s = forward_host_impl(ctx, l.w, l.x_host, (ttq_dtype)l.x_dt, l.M, l.ldx, l.bias_host, (ttq_dtype)l.bias_dt, l.y_host,
+                                             (ttq_dtype)l.y_dt, l.ldy, false);
+            if (s != TTQ_OK) return s;
+        }
+        return TTQ_OK;
+    };
+    // first pass outside the recording: argument errors surface here, and every kernel's attributes are set
+    ttq_status s = enqueue();
+    if (s != TTQ_OK) return s;
+    s = host_stream_sync(ctx);
+    if (s != TTQ_OK) return s;
+    ttq_host_batch *b = new (std::nothrow) ttq_host_batch();
+    if (!b) return fail(ctx, TTQ_ERR_OOM, "out of host memory");
+    b->ctx = ctx;
+    cudaError_t e = cudaStreamBeginCapture(ctx->host_stream, cudaStreamCaptureModeThreadLocal);
+    if (e != cudaSuccess) {
+        delete b;
+        return fail(ctx, TTQ_ERR_CUDA, "cudaStreamBeginCapture: %s", cudaGetErrorString(e));
     }
+    s = enqueue();
+    e = cudaStreamEndCapture(ctx->host_stream, &b->graph);  // always ends the recording, also after an error
+    if (s != TTQ_OK || e != cudaSuccess) {
+        if (e == cudaSuccess && b->graph) cudaGraphDestroy(b->graph);
+        delete b;
+        cudaGetLastError();
+        return s != TTQ_OK ? s : fail(ctx, TTQ_ERR_CUDA, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
+    }
+    e = cudaGraphInstantiate(&b->exec, b->graph, 0);
+    if (e != cudaSuccess) {
+        cudaGraphDestroy(b->graph);
+        delete b;
+        return fail(ctx, TTQ_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
+    }
+    *out = b;
     return TTQ_OK;
+}
+
+ttq_status ttq_host_batch_run(ttq_host_batch *batch) {
+    if (!batch) return TTQ_ERR_INVALID_ARG;
+    ttq_ctx *ctx = batch->ctx;
+    TTQ_CUDA(ctx, cudaSetDevice(ctx->device));
+    TTQ_CUDA(ctx, cudaGraphLaunch(batch->exec, ctx->host_stream));
+    return host_stream_sync(ctx);
+}
+
+ttq_status ttq_host_batch_destroy(ttq_host_batch *batch) {
+    if (!batch) return TTQ_OK;
+    cudaSetDevice(batch->ctx->device);
+    cudaStreamSynchronize(batch->ctx->host_stream);
+    cudaGraphExecDestroy(batch->exec);
+    cudaGraphDestroy(batch->graph);
+    delete batch;
+    return TTQ_OK;
+}
+
+ttq_status ttq_host_sync(ttq_ctx *ctx) {
+    if (!ctx) return TTQ_ERR_INVALID_ARG;
+    TTQ_CUDA(ctx, cudaSetDevice(ctx->device));
+    return host_stream_sync(ctx);
 }
 
 ttq_status ttq_device_status(ttq_ctx *ctx, void *stream) {

@@ -49,6 +49,10 @@ class Context:
         except Exception:
             pass
 
+    def host_sync(self) -> None:
+        """Waits for the calls enqueued with ``forward_host(..., wait=False)``; raises if one of their kernels gave up a wait."""
+        check(self.handle, self._lib.ttq_host_sync(self.handle))
+
     def check_device_status(self) -> None:
         """Synchronises the current stream; raises TtqError(TIMEOUT) if a kernel gave up a bounded wait."""
         check(self.handle, self._lib.ttq_device_status(self.handle, _stream_ptr(self.device)))
@@ -63,6 +67,42 @@ class Context:
     @property
     def launch_count(self) -> int:
         return int(self._lib.ttq_launch_count(self.handle))
+
+
+class HostBatch:
+    """A decode step's host-buffer linears, recorded once (``ttq_host_batch_create``) and run with one foreign call and
+    one wait per step.  ``items``: (QuantLinear, x, y) with x and y pinned, contiguous CPU tensors of decode size.
+    After ``run()`` returns every y holds its linear's result.  No bias: these are the plain projections of a step."""
+
+    def __init__(self, ctx: "Context", items):
+        self.ctx = ctx
+        self._keep = list(items)
+        arr = (_lib.HostLinear * len(self._keep))()
+        for slot, (lin, x, y) in zip(arr, self._keep):
+            x2 = x.reshape(-1, lin.in_features)
+            y2 = y.reshape(-1, lin.out_features)
+            if x2.data_ptr() != x.data_ptr() or y2.data_ptr() != y.data_ptr() or not x2.is_contiguous() or not y2.is_contiguous():
+                raise TtqError(1, "x and y must be contiguous host tensors")
+            slot.w, slot.x_host, slot.x_dt, slot.M, slot.ldx = lin.handle, x2.data_ptr(), _dt(x2.dtype), x2.shape[0], lin.in_features
+            slot.bias_host, slot.bias_dt = None, _lib.DT_F32
+            slot.y_host, slot.y_dt, slot.ldy = y2.data_ptr(), _dt(y2.dtype), lin.out_features
+        handle = ctypes.c_void_p()
+        check(ctx.handle, ctx._lib.ttq_host_batch_create(ctx.handle, arr, len(self._keep), ctypes.byref(handle)))
+        self.handle = handle
+
+    def run(self) -> None:
+        check(self.ctx.handle, self.ctx._lib.ttq_host_batch_run(self.handle))
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self.ctx._lib.ttq_host_batch_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class QuantLinear:
@@ -224,16 +264,39 @@ class QuantLinear:
         out.reshape(part.shape).copy_(part)
         return out.reshape(*x.shape[:-1], self.out_features)
 
-    def forward_host(self, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
-        """Host-buffer call: x and y are CPU tensors (pinned for speed); copies are part of the call."""
+    def forward_host(self, x: torch.Tensor, y: torch.Tensor, wait: bool = True) -> torch.Tensor:
+        """Host-buffer call: x and y are CPU tensors (pinned for speed); copies are part of the call.
+
+        ``wait=False`` only enqueues the call (pinned buffers of decode size required); ``Context.host_sync()`` then
+        waits for all enqueued calls at once, and y must not be read before it returns."""
         x2 = x.reshape(-1, self.in_features)
         y2 = y.reshape(-1, self.out_features)
         m = x2.shape[0]
-        st = self.ctx._lib.ttq_linear_forward_host(
+        fn = self.ctx._lib.ttq_linear_forward_host if wait else self.ctx._lib.ttq_linear_forward_host_async
+        st = fn(
             self.ctx.handle, self.handle, x2.data_ptr(), _dt(x2.dtype), m, self.in_features, None, _lib.DT_F32,
             y2.data_ptr(), _dt(y2.dtype), self.out_features)
         check(self.ctx.handle, st)
         return y
+
+    def host_call(self, x: torch.Tensor, y: torch.Tensor, wait: bool = True):
+        """A zero-argument callable that runs ``forward_host(x, y, wait)`` on these very buffers with every argument
+        bound ahead (a decode loop reuses its buffers: this leaves one foreign call per linear and step).  The
+        callable keeps x and y alive; it raises like ``forward_host``."""
+        x2 = x.reshape(-1, self.in_features)
+        y2 = y.reshape(-1, self.out_features)
+        if x2.data_ptr() != x.data_ptr() or y2.data_ptr() != y.data_ptr():
+            raise TtqError(1, "x and y must be contiguous host tensors")
+        fn = self.ctx._lib.ttq_linear_forward_host if wait else self.ctx._lib.ttq_linear_forward_host_async
+        args = (self.ctx.handle, self.handle, x2.data_ptr(), _dt(x2.dtype), x2.shape[0], self.in_features, None, _lib.DT_F32,
+                y2.data_ptr(), _dt(y2.dtype), self.out_features)
+        ctx_handle = self.ctx.handle
+
+        def call(_keep=(x, y, self)):
+            st = fn(*args)
+            if st != 0:
+                check(ctx_handle, st)
+        return call
 
     def close(self) -> None:
         if getattr(self, "handle", None):

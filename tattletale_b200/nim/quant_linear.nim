@@ -24,6 +24,17 @@ type
     kTtqBF16 = 0, kTtqF16 = 1, kTtqF32 = 2
   TtqShard* {.importc: "ttq_shard", header: "ttq.h", bycopy.} = object
     kind*, rank*, world*: int32
+  TtqHostBatch* {.importc: "ttq_host_batch", header: "ttq.h", incompleteStruct.} = object
+  TtqHostLinear* {.importc: "ttq_host_linear", header: "ttq.h", bycopy.} = object
+    w*: ptr TtqWeight
+    x_host*: pointer
+    x_dt*: int32
+    M*, ldx*: int64
+    bias_host*: pointer
+    bias_dt*: int32
+    y_host*: pointer
+    y_dt*: int32
+    ldy*: int64
 
 proc ttq_init(device: cint, ctx: ptr ptr TtqCtx): TtqStatus {.importc, cdecl, header: "ttq.h".}
 proc ttq_destroy(ctx: ptr TtqCtx): TtqStatus {.importc, cdecl, header: "ttq.h".}
@@ -66,6 +77,14 @@ proc ttq_dequantize(ctx: ptr TtqCtx, w: ptr TtqWeight, devOut: ptr cfloat, ld: i
 proc ttq_linear_forward_host(ctx: ptr TtqCtx, w: ptr TtqWeight, xHost: pointer, xDt: TtqDtype, M, ldx: int64,
                              biasHost: pointer, biasDt: TtqDtype, yHost: pointer, yDt: TtqDtype,
                              ldy: int64): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_linear_forward_host_async(ctx: ptr TtqCtx, w: ptr TtqWeight, xHost: pointer, xDt: TtqDtype, M, ldx: int64,
+                                   biasHost: pointer, biasDt: TtqDtype, yHost: pointer, yDt: TtqDtype,
+                                   ldy: int64): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_host_sync(ctx: ptr TtqCtx): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_host_batch_create(ctx: ptr TtqCtx, linears: ptr TtqHostLinear, n: cint,
+                            batch: ptr ptr TtqHostBatch): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_host_batch_run(batch: ptr TtqHostBatch): TtqStatus {.importc, cdecl, header: "ttq.h".}
+proc ttq_host_batch_destroy(batch: ptr TtqHostBatch): TtqStatus {.importc, cdecl, header: "ttq.h".}
 proc ttq_device_status(ctx: ptr TtqCtx, stream: pointer): TtqStatus {.importc, cdecl, header: "ttq.h".}
 proc ttq_linear_forward_static(w: ptr TtqWeight, x: pointer, xDt: TtqDtype, M, ldx: int64, bias: pointer,
                                biasDt: TtqDtype, y: pointer, yDt: TtqDtype, ldy: int64, stream: pointer,

@@ -146,6 +146,68 @@ def test_host_entry_point(ctx):
     lin.close()
 
 
+def test_host_entry_point_enqueue_then_wait(ctx):
+    """Several host-buffer calls enqueued without a wait, one ttq_host_sync: results as from the synchronous call; pageable
+    buffers are refused (they would need the one staging area per call)."""
+    fmt = ttq.FMT_Q4_K
+    lins, xs, ys, wants = [], [], [], []
+    for i, (n, k) in enumerate([(64, 512), (48, 256), (4096, 4096)]):
+        blocks = make_weight(fmt, n, k, seed=40 + i)
+        lin = ttq.QuantLinear(ctx, fmt, torch.from_numpy(blocks), k)
+        x = make_x(1 + i, k, 50 + i).pin_memory()
+        lins.append(lin)
+        xs.append(x)
+        ys.append(torch.zeros(1 + i, n, dtype=torch.float32).pin_memory())
+        wants.append(oracle.linear(oracle.Q4_K, blocks, x_bits(x), oracle.BF16))
+    for _ in range(2):
+        for lin, x, y in zip(lins, xs, ys):
+            lin.forward_host(x, y, wait=False)
+        ctx.host_sync()
+        for y, want in zip(ys, wants):
+            assert rel_l2(y.numpy(), want) < TOL
+            y.zero_()
+    calls = [lin.host_call(x, y, wait=False) for lin, x, y in zip(lins, xs, ys)]  # the pre-bound form
+    for call in calls:
+        call()
+    ctx.host_sync()
+    for y, want in zip(ys, wants):
+        assert rel_l2(y.numpy(), want) < TOL
+    with pytest.raises(ttq.TtqError):
+        lins[0].forward_host(make_x(1, 512, 3), torch.zeros(1, 64), wait=False)
+    ctx.host_sync()
+    for lin in lins:
+        lin.close()
+
+
+def test_recorded_host_batch(ctx):
+    """ttq_host_batch_*: three linears recorded once, run three times on refreshed inputs; every y as from the checker.
+    A pageable buffer is refused at creation."""
+    fmt = ttq.FMT_Q4_K
+    items, blocks_of = [], []
+    for i, (n, k) in enumerate([(64, 512), (4096, 4096), (48, 256)]):
+        blocks = make_weight(fmt, n, k, seed=60 + i)
+        lin = ttq.QuantLinear(ctx, fmt, torch.from_numpy(blocks), k)
+        items.append((lin, make_x(1 + (i % 2), k, 70 + i).pin_memory(), torch.zeros(1 + (i % 2), n, dtype=torch.float32).pin_memory()))
+        blocks_of.append(blocks)
+    batch = ttq.HostBatch(ctx, items)
+    for rep in range(3):
+        for i, (lin, x, y) in enumerate(items):
+            x.copy_(make_x(x.shape[0], x.shape[1], 80 + 7 * rep + i))  # same buffers, new activations
+            y.zero_()
+        batch.run()
+        for (lin, x, y), blocks in zip(items, blocks_of):
+            assert rel_l2(y.numpy(), oracle.linear(oracle.Q4_K, blocks, x_bits(x), oracle.BF16)) < TOL
+    batch.close()
+    with pytest.raises(ttq.TtqError):
+        ttq.HostBatch(ctx, [(items[0][0], make_x(1, 512, 3), torch.zeros(1, 64))])
+    ctx.host_sync()
+    lin = items[0][0]
+    y = lin.forward(items[0][1].cuda(), out_dtype=torch.float32)  # the context is still usable
+    assert torch.isfinite(y).all()
+    for lin, _, _ in items:
+        lin.close()
+
+
 def test_config1_q8_0_decode(ctx):
     """Single Q8_0 linear, M=1, K=N=4096, fp16 activations, fp32 output."""
     rng = np.random.default_rng(1001)
