@@ -725,48 +725,110 @@ struct ttq_host_batch {
     ttq_ctx *ctx;
     cudaGraph_t graph;
     cudaGraphExec_t exec;
+    void *stage;  // device copies of the batch's activations, filled by the first node of the graph
+    void *table;  // device array of HostGatherItem
 };
+
+namespace {
+
+struct HostGatherItem {
+    const void *src;  // device mapping of a page-locked host buffer
+    void *dst;        // its place in the batch's staging area
+    unsigned long long bytes;
+};
+
+// grid (pieces, items): the activations of all linears of a recorded batch come over the host link in one kernel, with
+// every read in flight at once, instead of one dependent round trip at the start of each linear's activation pass.
+__global__ void __launch_bounds__(256) host_gather_kernel(const HostGatherItem *__restrict__ items) {
+    const HostGatherItem it = items[blockIdx.y];
+    const bool vec = ((reinterpret_cast<uintptr_t>(it.src) | reinterpret_cast<uintptr_t>(it.dst) | it.bytes) & 15) == 0;
+    if (vec) {
+        const unsigned long long n16 = it.bytes / 16;
+        for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (unsigned long long)gridDim.x * blockDim.x)
+            reinterpret_cast<uint4 *>(it.dst)[i] = reinterpret_cast<const uint4 *>(it.src)[i];
+    } else {
+        for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < it.bytes; i += (unsigned long long)gridDim.x * blockDim.x)
+            reinterpret_cast<uint8_t *>(it.dst)[i] = reinterpret_cast<const uint8_t *>(it.src)[i];
+    }
+}
+
+void host_batch_free(ttq_host_batch *b) {
+    if (b->exec) cudaGraphExecDestroy(b->exec);
+    if (b->graph) cudaGraphDestroy(b->graph);
+    cudaFree(b->stage);
+    cudaFree(b->table);
+    delete b;
+}
+
+}  // namespace
 
 ttq_status ttq_host_batch_create(ttq_ctx *ctx, const ttq_host_linear *linears, int n, ttq_host_batch **out) {
     if (!ctx) return TTQ_ERR_INVALID_ARG;
     if (!out) return fail(ctx, TTQ_ERR_INVALID_ARG, "output pointer is NULL");
     *out = nullptr;
-    if (!linears || n <= 0) return fail(ctx, TTQ_ERR_INVALID_ARG, "empty batch");
+    if (!linears || n <= 0 || n > 65535) return fail(ctx, TTQ_ERR_INVALID_ARG, "a batch holds 1 to 65535 linears");
     TTQ_CUDA(ctx, cudaSetDevice(ctx->device));
-    auto enqueue = [&]() -> ttq_status {
-        for (int i = 0; i < n; i++) {
-            const ttq_host_linear &l = linears[i];
-            ttq_status s = forward_host_impl(ctx, l.w, l.x_host, (ttq_dtype)l.x_dt, l.M, l.ldx, l.bias_host, (ttq_dtype)l.bias_dt, l.y_host,
-                                             (ttq_dtype)l.y_dt, l.ldy, false);
-            if (s != TTQ_OK) return s;
-        }
-        return TTQ_OK;
-    };
-    // first pass outside the recording: argument errors surface here, and every kernel's attributes are set
-    ttq_status s = enqueue();
-    if (s != TTQ_OK) return s;
-    s = host_stream_sync(ctx);
+    // first pass outside the recording, straight on the host buffers: argument errors surface here, every kernel's
+    // attributes are set, and every buffer's device mapping is known afterwards
+    for (int i = 0; i < n; i++) {
+        const ttq_host_linear &l = linears[i];
+        ttq_status s = forward_host_impl(ctx, l.w, l.x_host, (ttq_dtype)l.x_dt, l.M, l.ldx, l.bias_host, (ttq_dtype)l.bias_dt, l.y_host,
+                                         (ttq_dtype)l.y_dt, l.ldy, false);
+        if (s != TTQ_OK) return s;
+    }
+    ttq_status s = host_stream_sync(ctx);
     if (s != TTQ_OK) return s;
     ttq_host_batch *b = new (std::nothrow) ttq_host_batch();
     if (!b) return fail(ctx, TTQ_ERR_OOM, "out of host memory");
     b->ctx = ctx;
-    cudaError_t e = cudaStreamBeginCapture(ctx->host_stream, cudaStreamCaptureModeThreadLocal);
+    // the staging area of the activations and the table of the gather kernel
+    std::vector<HostGatherItem> items((size_t)n);
+    std::vector<size_t> offs((size_t)n);
+    size_t total = 0, longest = 0;
+    for (int i = 0; i < n; i++) {
+        const ttq_host_linear &l = linears[i];
+        const size_t xb = (size_t)l.M * l.ldx * dt_size((ttq_dtype)l.x_dt);
+        offs[i] = total;
+        total += (xb + 255) & ~(size_t)255;
+        longest = xb > longest ? xb : longest;
+    }
+    cudaError_t e = cudaMalloc(&b->stage, total ? total : 256);
+    if (e == cudaSuccess) e = cudaMalloc(&b->table, (size_t)n * sizeof(HostGatherItem));
+    for (int i = 0; e == cudaSuccess && i < n; i++) {
+        const ttq_host_linear &l = linears[i];
+        items[i].src = host_mapping(ctx, l.x_host);
+        items[i].dst = reinterpret_cast<uint8_t *>(b->stage) + offs[i];
+        items[i].bytes = (unsigned long long)l.M * l.ldx * dt_size((ttq_dtype)l.x_dt);
+        if (items[i].src == nullptr) e = cudaErrorInvalidValue;  // (the first pass has already refused pageable buffers)
+    }
+    if (e == cudaSuccess) e = cudaMemcpy(b->table, items.data(), (size_t)n * sizeof(HostGatherItem), cudaMemcpyHostToDevice);
     if (e != cudaSuccess) {
-        delete b;
+        host_batch_free(b);
+        return cuda_fail(ctx, e, "host batch staging");
+    }
+    e = cudaStreamBeginCapture(ctx->host_stream, cudaStreamCaptureModeThreadLocal);
+    if (e != cudaSuccess) {
+        host_batch_free(b);
         return fail(ctx, TTQ_ERR_CUDA, "cudaStreamBeginCapture: %s", cudaGetErrorString(e));
     }
-    s = enqueue();
+    const unsigned pieces = (unsigned)((longest / 16 + 255) / 256 > 0 ? (longest / 16 + 255) / 256 : 1);
+    host_gather_kernel<<<dim3(pieces < 64 ? pieces : 64, (unsigned)n), 256, 0, ctx->host_stream>>>(reinterpret_cast<const HostGatherItem *>(b->table));
+    s = TTQ_OK;
+    for (int i = 0; s == TTQ_OK && i < n; i++) {
+        const ttq_host_linear &l = linears[i];
+        s = ttq_linear_forward(ctx, l.w, items[i].dst, (ttq_dtype)l.x_dt, l.M, l.ldx, l.bias_host ? host_mapping(ctx, l.bias_host) : nullptr,
+                               (ttq_dtype)l.bias_dt, host_mapping(ctx, l.y_host), (ttq_dtype)l.y_dt, l.ldy, ctx->host_stream);
+    }
     e = cudaStreamEndCapture(ctx->host_stream, &b->graph);  // always ends the recording, also after an error
     if (s != TTQ_OK || e != cudaSuccess) {
-        if (e == cudaSuccess && b->graph) cudaGraphDestroy(b->graph);
-        delete b;
+        host_batch_free(b);
         cudaGetLastError();
         return s != TTQ_OK ? s : fail(ctx, TTQ_ERR_CUDA, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
     }
     e = cudaGraphInstantiate(&b->exec, b->graph, 0);
     if (e != cudaSuccess) {
-        cudaGraphDestroy(b->graph);
-        delete b;
+        b->exec = nullptr;
+        host_batch_free(b);
         return fail(ctx, TTQ_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
     }
     *out = b;
@@ -785,9 +847,7 @@ ttq_status ttq_host_batch_destroy(ttq_host_batch *batch) {
     if (!batch) return TTQ_OK;
     cudaSetDevice(batch->ctx->device);
     cudaStreamSynchronize(batch->ctx->host_stream);
-    cudaGraphExecDestroy(batch->exec);
-    cudaGraphDestroy(batch->graph);
-    delete batch;
+    host_batch_free(batch);
     return TTQ_OK;
 }
 
