@@ -347,7 +347,7 @@ def ours_arm(args):
         batch.close()
         e2e = {"value": round(step_bytes / e2e_s / 1e9, 3), "unit": "GB/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_s * 1e3, 4), "steps": e2e_steps,
-               "api": "ttq_host_batch_run: the step's 128 host-buffer linears recorded once (ttq_host_batch_create) on pinned buffers; every step one kernel gathers all x over the host link, the linears write y through the buffers' device mappings, and the call returns when all results are in host memory; failure flag in mapped host memory",
+               "api": "ttq_host_batch_run: the step's 128 host-buffer linears recorded once (ttq_host_batch_create) on pinned buffers; every step one kernel converts the activations of all linears straight from the host buffers (batched activation pass), the linears write y through the buffers' device mappings, and the call returns when all results are in host memory; failure flag in mapped host memory",
                "enqueue_then_wait": {"value": round(step_bytes / enqueue_s / 1e9, 3), "ms_per_step": round(enqueue_s * 1e3, 4),
                                      "api": "ttq_linear_forward_host_async per linear + one ttq_host_sync per step"},
                "wait_per_call": {"value": round(step_bytes / per_call_s / 1e9, 3), "ms_per_step": round(per_call_s * 1e3, 4),

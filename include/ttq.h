@@ -187,9 +187,12 @@ typedef struct ttq_host_linear {
 /* Records `n` host-buffer linears (a decode step's worth) once, as a CUDA graph on the context's host stream, for
  * callers that run the same linears on the same page-locked buffers step after step (no counterpart in the
  * reference).  Same limits per linear as ttq_linear_forward_host_async.  The linears run once during the call
- * (every kernel is configured before the recording starts).  Allocates: a device copy of the batch's activations,
- * which the first node of the graph fills from the host buffers in one kernel (all reads over the host link in
- * flight together); the results are written to the host buffers by the linears themselves.  Weights and buffers must outlive the batch; create
+ * (every kernel is configured before the recording starts).  The activations of ALL decode-size linears
+ * of the batch (one row; two rows below K = 8192; block formats) are converted by one launch at the head of the
+ * graph, straight from the host buffers, so those linears run without an activation pass of their own; the
+ * activations of the other linears are copied to the device by one gather launch.  Either way all reads over the host
+ * link are in flight together.  Allocates the device storage for both; the results are written to the host buffers
+ * by the linears themselves.  Weights and buffers must outlive the batch; create
  * every weight of the context before recording (see ttq_linear_forward on scratch that may move). */
 TTQ_API ttq_status ttq_host_batch_create(ttq_ctx *ctx, const ttq_host_linear *linears, int n, ttq_host_batch **out);
 /* Runs the recorded linears in order, waits, and reports a kernel that gave up a bounded wait (TTQ_ERR_TIMEOUT):

@@ -725,8 +725,10 @@ struct ttq_host_batch {
     ttq_ctx *ctx;
     cudaGraph_t graph;
     cudaGraphExec_t exec;
-    void *stage;  // device copies of the batch's activations, filled by the first node of the graph
-    void *table;  // device array of HostGatherItem
+    void *stage;   // device copies of the activations of the linears that run their own activation pass (gather kernel)
+    void *table;   // device array of HostGatherItem
+    void *planes;  // converted activations of the decode-size linears (batched activation pass)
+    void *xitems;  // device array of XprepBatchItem
 };
 
 namespace {
@@ -757,6 +759,8 @@ void host_batch_free(ttq_host_batch *b) {
     if (b->graph) cudaGraphDestroy(b->graph);
     cudaFree(b->stage);
     cudaFree(b->table);
+    cudaFree(b->planes);
+    cudaFree(b->xitems);
     delete b;
 }
 
@@ -781,27 +785,67 @@ ttq_status ttq_host_batch_create(ttq_ctx *ctx, const ttq_host_linear *linears, i
     ttq_host_batch *b = new (std::nothrow) ttq_host_batch();
     if (!b) return fail(ctx, TTQ_ERR_OOM, "out of host memory");
     b->ctx = ctx;
-    // the staging area of the activations and the table of the gather kernel
-    std::vector<HostGatherItem> items((size_t)n);
-    std::vector<size_t> offs((size_t)n);
-    size_t total = 0, longest = 0;
+    // Decode-size linears of the block formats (the ones ttq_linear_forward serves with the GEMV) get their activations
+    // converted by ONE launch for the whole batch, straight from the host buffers; the others get theirs copied to a
+    // staging area by one gather launch and run their own activation pass.
+    std::vector<HostGatherItem> items;
+    std::vector<XprepBatchItem> xitems;
+    std::vector<int> slot((size_t)n);  // index into xitems (>= 0) or -1 - index into items
+    std::vector<size_t> offs;
+    size_t stage_total = 0, longest = 0, planes_total = 0;
+    int total_units = 0;
+    auto take = [](size_t &total, size_t bytes) {
+        const size_t at = total;
+        total += (bytes + 255) & ~(size_t)255;
+        return at;
+    };
     for (int i = 0; i < n; i++) {
         const ttq_host_linear &l = linears[i];
+        const void *x_map = host_mapping(ctx, l.x_host);  // (the first pass has already refused pageable buffers)
         const size_t xb = (size_t)l.M * l.ldx * dt_size((ttq_dtype)l.x_dt);
-        offs[i] = total;
-        total += (xb + 255) & ~(size_t)255;
-        longest = xb > longest ? xb : longest;
+        const bool decode = (l.M == 1 || (l.M == 2 && l.w->SBp < 32)) && gemv_prepared_supported(l.w->fmt, l.M, l.w->SBp);
+        if (decode) {
+            const int64_t Kp = l.w->SBp * TILE_K;
+            XprepBatchItem it;
+            it.x = x_map; it.x_dt = l.x_dt; it.M = (int)l.M; it.K = l.w->K; it.ldx = l.ldx; it.SBp = l.w->SBp;
+            // (offsets for now; turned into pointers once the buffer exists)
+            it.xq.planes = reinterpret_cast<int8_t *>(take(planes_total, (size_t)2 * l.M * Kp));
+            it.xq.sum16 = reinterpret_cast<float *>(take(planes_total, (size_t)l.M * (Kp / 16) * sizeof(float)));
+            it.xq.sum32 = reinterpret_cast<float *>(take(planes_total, (size_t)l.M * (Kp / 32) * sizeof(float)));
+            it.xq.sx = reinterpret_cast<float *>(take(planes_total, (size_t)l.M * sx_stride(l.w->SBp) * sizeof(float)));
+            it.unit0 = total_units;
+            total_units += (int)(l.M * l.w->SBp);
+            slot[i] = (int)xitems.size();
+            xitems.push_back(it);
+        } else {
+            HostGatherItem it;
+            it.src = x_map;
+            it.dst = reinterpret_cast<void *>(take(stage_total, xb));
+            it.bytes = xb;
+            longest = xb > longest ? xb : longest;
+            slot[i] = -1 - (int)items.size();
+            items.push_back(it);
+        }
     }
-    cudaError_t e = cudaMalloc(&b->stage, total ? total : 256);
-    if (e == cudaSuccess) e = cudaMalloc(&b->table, (size_t)n * sizeof(HostGatherItem));
-    for (int i = 0; e == cudaSuccess && i < n; i++) {
-        const ttq_host_linear &l = linears[i];
-        items[i].src = host_mapping(ctx, l.x_host);
-        items[i].dst = reinterpret_cast<uint8_t *>(b->stage) + offs[i];
-        items[i].bytes = (unsigned long long)l.M * l.ldx * dt_size((ttq_dtype)l.x_dt);
-        if (items[i].src == nullptr) e = cudaErrorInvalidValue;  // (the first pass has already refused pageable buffers)
+    cudaError_t e = cudaSuccess;
+    if (!items.empty()) {
+        e = cudaMalloc(&b->stage, stage_total);
+        if (e == cudaSuccess) e = cudaMalloc(&b->table, items.size() * sizeof(HostGatherItem));
+        for (auto &it : items) it.dst = reinterpret_cast<uint8_t *>(b->stage) + reinterpret_cast<uintptr_t>(it.dst);
+        if (e == cudaSuccess) e = cudaMemcpy(b->table, items.data(), items.size() * sizeof(HostGatherItem), cudaMemcpyHostToDevice);
     }
-    if (e == cudaSuccess) e = cudaMemcpy(b->table, items.data(), (size_t)n * sizeof(HostGatherItem), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess && !xitems.empty()) {
+        e = cudaMalloc(&b->planes, planes_total);
+        if (e == cudaSuccess) e = cudaMalloc(&b->xitems, xitems.size() * sizeof(XprepBatchItem));
+        uint8_t *base = reinterpret_cast<uint8_t *>(b->planes);
+        for (auto &it : xitems) {
+            it.xq.planes = reinterpret_cast<int8_t *>(base + reinterpret_cast<uintptr_t>(it.xq.planes));
+            it.xq.sum16 = reinterpret_cast<float *>(base + reinterpret_cast<uintptr_t>(it.xq.sum16));
+            it.xq.sum32 = reinterpret_cast<float *>(base + reinterpret_cast<uintptr_t>(it.xq.sum32));
+            it.xq.sx = reinterpret_cast<float *>(base + reinterpret_cast<uintptr_t>(it.xq.sx));
+        }
+        if (e == cudaSuccess) e = cudaMemcpy(b->xitems, xitems.data(), xitems.size() * sizeof(XprepBatchItem), cudaMemcpyHostToDevice);
+    }
     if (e != cudaSuccess) {
         host_batch_free(b);
         return cuda_fail(ctx, e, "host batch staging");
@@ -811,13 +855,37 @@ ttq_status ttq_host_batch_create(ttq_ctx *ctx, const ttq_host_linear *linears, i
         host_batch_free(b);
         return fail(ctx, TTQ_ERR_CUDA, "cudaStreamBeginCapture: %s", cudaGetErrorString(e));
     }
-    const unsigned pieces = (unsigned)((longest / 16 + 255) / 256 > 0 ? (longest / 16 + 255) / 256 : 1);
-    host_gather_kernel<<<dim3(pieces < 64 ? pieces : 64, (unsigned)n), 256, 0, ctx->host_stream>>>(reinterpret_cast<const HostGatherItem *>(b->table));
     s = TTQ_OK;
+    if (!items.empty()) {
+        const unsigned pieces = (unsigned)((longest / 16 + 255) / 256 > 0 ? (longest / 16 + 255) / 256 : 1);
+        host_gather_kernel<<<dim3(pieces < 64 ? pieces : 64, (unsigned)items.size()), 256, 0, ctx->host_stream>>>(
+            reinterpret_cast<const HostGatherItem *>(b->table));
+    }
+    if (!xitems.empty()) {
+        e = launch_xprep_batch(reinterpret_cast<const XprepBatchItem *>(b->xitems), (int)xitems.size(), total_units, ctx->host_stream);
+        if (e != cudaSuccess) s = cuda_fail(ctx, e, "batched activation pass launch");
+    }
     for (int i = 0; s == TTQ_OK && i < n; i++) {
         const ttq_host_linear &l = linears[i];
-        s = ttq_linear_forward(ctx, l.w, items[i].dst, (ttq_dtype)l.x_dt, l.M, l.ldx, l.bias_host ? host_mapping(ctx, l.bias_host) : nullptr,
-                               (ttq_dtype)l.bias_dt, host_mapping(ctx, l.y_host), (ttq_dtype)l.y_dt, l.ldy, ctx->host_stream);
+        const void *b_map = l.bias_host ? host_mapping(ctx, l.bias_host) : nullptr;
+        void *y_map = host_mapping(ctx, l.y_host);
+        if (slot[i] >= 0) {
+            const XprepBatchItem &it = xitems[(size_t)slot[i]];
+            LinearArgs a;
+            a.tiles = l.w->tiles;
+            a.N = l.w->N; a.K = l.w->K; a.NT = l.w->NT; a.SBp = l.w->SBp;
+            a.x = nullptr; a.x_dt = TTQ_DT_BF16; a.M = l.M; a.ldx = l.w->K;
+            a.bias = b_map; a.bias_dt = l.bias_dt;
+            a.y = y_map; a.y_dt = l.y_dt; a.ldy = l.ldy;
+            a.gated = false;
+            int launches = 0;
+            e = launch_gemv(l.w->fmt, a, it.xq, l.w->SBp * TILE_K, reinterpret_cast<const uint8_t *>(ctx->dev_status) + 256, ctx->sms,
+                            ctx->dev_status, nullptr, ctx->host_stream, &launches, nullptr, true);
+            if (e != cudaSuccess) s = cuda_fail(ctx, e, "linear forward (batched activations) launch");
+        } else {
+            s = ttq_linear_forward(ctx, l.w, items[(size_t)(-1 - slot[i])].dst, (ttq_dtype)l.x_dt, l.M, l.ldx, b_map, (ttq_dtype)l.bias_dt, y_map,
+                                   (ttq_dtype)l.y_dt, l.ldy, ctx->host_stream);
+        }
     }
     e = cudaStreamEndCapture(ctx->host_stream, &b->graph);  // always ends the recording, also after an error
     if (s != TTQ_OK || e != cudaSuccess) {

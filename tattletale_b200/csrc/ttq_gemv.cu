@@ -152,6 +152,31 @@ __global__ void __launch_bounds__(GEMV_THREADS) xprep_kernel(const void *__restr
     }
 }
 
+// The activation pass of many independent linears in one launch (a recorded batch of host-buffer linears): warp u of
+// the grid converts chunk u - unit0 of the item whose range holds u.  The rows may live in mapped host memory: all reads
+// over the host link are in flight together, and no linear of the batch has an activation pass of its own left.
+__global__ void __launch_bounds__(GEMV_THREADS) xprep_batch_kernel(const XprepBatchItem *__restrict__ items, int n, int total_units) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int lane = threadIdx.x & 31;
+    const int u = (int)blockIdx.x * GEMV_WARPS + (threadIdx.x >> 5);
+    if (u >= total_units) return;
+    int lo = 0, hi = n - 1;  // last item with unit0 <= u
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (items[mid].unit0 <= u) lo = mid;
+        else hi = mid - 1;
+    }
+    const XprepBatchItem it = items[lo];
+    const int local = u - it.unit0, SBp = (int)it.SBp;
+    const int m = local / SBp, sb = local - m * SBp;
+    const int64_t Kp = it.SBp * TILE_K;
+    XqRow dst{it.xq.planes + (2 * m) * Kp, it.xq.planes + (2 * m + 1) * Kp, it.xq.sum16 + m * (Kp / 16), it.xq.sum32 + m * (Kp / 32),
+              it.xq.sx + m * sx_stride(it.SBp), false};
+    const int esz = it.x_dt == TTQ_DT_F32 ? 4 : 2;
+    xprep_chunk(reinterpret_cast<const uint8_t *>(it.x) + (int64_t)m * it.ldx * esz, it.x_dt, it.K, sb, lane, dst);
+}
+
 // ---- the GEMV --------------------------------------------------------------------------------
 struct GemvParams {
     LinearArgs a;
@@ -736,6 +761,16 @@ cudaError_t launch_xprep(const LinearArgs &a, const XqView &xq, int64_t Mpad, un
     const int64_t units = Mpad * a.SBp;
     return launch_pdl(xprep_kernel, dim3((unsigned)((units + GEMV_WARPS - 1) / GEMV_WARPS)), dim3(GEMV_THREADS), 0, st, a.x, a.x_dt, a.M,
                       Mpad, a.K, a.ldx, a.SBp, xq, trace, (a.gated ? 1 : 0) | (interleaved ? 2 : 0));
+}
+
+cudaError_t launch_xprep_batch(const XprepBatchItem *items_dev, int n, int total_units, cudaStream_t st) {
+    return launch_pdl(xprep_batch_kernel, dim3((unsigned)((total_units + GEMV_WARPS - 1) / GEMV_WARPS)), dim3(GEMV_THREADS), 0, st, items_dev, n,
+                      total_units);
+}
+
+// whether launch_gemv serves a linear of M rows from activation planes somebody else prepared
+bool gemv_prepared_supported(int fmt, int64_t M, int64_t SBp) {
+    return (fmt == TTQ_FMT_Q4_K || fmt == TTQ_FMT_Q8_0 || fmt == TTQ_FMT_Q6_K) && M >= 1 && M <= 4 && pick_nw(fmt, XSRC_COPY, M, SBp) != 0;
 }
 
 cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t xq_capacity_k, const uint8_t *zeros,

@@ -88,6 +88,16 @@ struct XqView {
     float *sx;        // [Mpad][SBp]
 };
 
+// One linear's activations in a batched activation pass (xprep_batch_kernel): M rows of K values at x, converted into xq;
+// unit0 = first (row, chunk) unit of the item in the batch's numbering, ascending over the items.
+struct XprepBatchItem {
+    const void *x;
+    int x_dt, M;
+    int64_t K, ldx, SBp;
+    XqView xq;
+    int unit0;
+};
+
 // row pitch (floats) of XqView::sx
 __host__ __device__ constexpr int sx_stride(int64_t SBp) { return (int)((SBp + 3) & ~(int64_t)3); }
 
@@ -285,6 +295,8 @@ cudaError_t launch_dequant(int fmt, const uint8_t *tiled, float *out, int64_t ld
 // GEMV for M <= MAX_GEMV_M.  `xq` is scratch for the separate x-prep pass (used when M > fused limit).
 // `prepared`: the planes of a.M rows are already in `xq` (written by the kernel that produced the activations): no
 // activation pass is launched, a.x is not read.
+cudaError_t launch_xprep_batch(const XprepBatchItem *items_dev, int n, int total_units, cudaStream_t st);
+bool gemv_prepared_supported(int fmt, int64_t M, int64_t SBp);
 cudaError_t launch_gemv(int fmt, const LinearArgs &a, const XqView &xq, int64_t xq_capacity_k, const uint8_t *zeros,
                         int sms, int *status, unsigned long long *trace, cudaStream_t st, int *launches,
                         const CommView *comm = nullptr, bool prepared = false);
