@@ -865,6 +865,29 @@ ttq_status ttq_host_batch_create(ttq_ctx *ctx, const ttq_host_linear *linears, i
         e = launch_xprep_batch(reinterpret_cast<const XprepBatchItem *>(b->xitems), (int)xitems.size(), total_units, ctx->host_stream);
         if (e != cudaSuccess) s = cuda_fail(ctx, e, "batched activation pass launch");
     }
+    // The decode-size linears depend on the batched activation pass only, not on each other (their planes and outputs are
+    // their own): they are recorded round-robin on a few side streams that fork from the head of the graph, so that the
+    // last CTAs of one linear and the first of the next run side by side instead of a dependent launch apart.
+    // TTQ_HOST_BATCH_STREAMS (default 4, 1 = one chain).  The other linears share the context's scratch and stay in line.
+    static const int n_side_env = []() {
+        const char *v = getenv("TTQ_HOST_BATCH_STREAMS");
+        return v ? atoi(v) : 4;
+    }();
+    constexpr int MAX_SIDE = 8;
+    const int n_side = xitems.size() < 2 ? 1 : (n_side_env < 1 ? 1 : (n_side_env > MAX_SIDE ? MAX_SIDE : n_side_env));
+    cudaStream_t side[MAX_SIDE] = {};
+    cudaEvent_t fork_ev = nullptr, join_ev[MAX_SIDE] = {};
+    if (n_side > 1) {
+        e = cudaEventCreateWithFlags(&fork_ev, cudaEventDisableTiming);
+        for (int k = 0; e == cudaSuccess && k < n_side; k++) {
+            e = cudaStreamCreateWithFlags(&side[k], cudaStreamNonBlocking);
+            if (e == cudaSuccess) e = cudaEventCreateWithFlags(&join_ev[k], cudaEventDisableTiming);
+        }
+        if (e == cudaSuccess) e = cudaEventRecord(fork_ev, ctx->host_stream);
+        for (int k = 0; e == cudaSuccess && k < n_side; k++) e = cudaStreamWaitEvent(side[k], fork_ev, 0);
+        if (e != cudaSuccess) s = cuda_fail(ctx, e, "host batch side streams");
+    }
+    int next_side = 0;
     for (int i = 0; s == TTQ_OK && i < n; i++) {
         const ttq_host_linear &l = linears[i];
         const void *b_map = l.bias_host ? host_mapping(ctx, l.bias_host) : nullptr;
@@ -879,15 +902,31 @@ ttq_status ttq_host_batch_create(ttq_ctx *ctx, const ttq_host_linear *linears, i
             a.y = y_map; a.y_dt = l.y_dt; a.ldy = l.ldy;
             a.gated = false;
             int launches = 0;
+            cudaStream_t lst = n_side > 1 ? side[next_side++ % n_side] : ctx->host_stream;
             e = launch_gemv(l.w->fmt, a, it.xq, l.w->SBp * TILE_K, reinterpret_cast<const uint8_t *>(ctx->dev_status) + 256, ctx->sms,
-                            ctx->dev_status, nullptr, ctx->host_stream, &launches, nullptr, true);
+                            ctx->dev_status, nullptr, lst, &launches, nullptr, true);
             if (e != cudaSuccess) s = cuda_fail(ctx, e, "linear forward (batched activations) launch");
         } else {
             s = ttq_linear_forward(ctx, l.w, items[(size_t)(-1 - slot[i])].dst, (ttq_dtype)l.x_dt, l.M, l.ldx, b_map, (ttq_dtype)l.bias_dt, y_map,
                                    (ttq_dtype)l.y_dt, l.ldy, ctx->host_stream);
         }
     }
+    if (n_side > 1) {
+        // join: the recording ends on the host stream with every side chain merged back (also after an error, so that the
+        // recording can end)
+        for (int k = 0; k < n_side; k++) {
+            if (side[k] == nullptr || join_ev[k] == nullptr) continue;
+            cudaError_t je = cudaEventRecord(join_ev[k], side[k]);
+            if (je == cudaSuccess) je = cudaStreamWaitEvent(ctx->host_stream, join_ev[k], 0);
+            if (je != cudaSuccess && s == TTQ_OK) s = cuda_fail(ctx, je, "host batch join");
+        }
+    }
     e = cudaStreamEndCapture(ctx->host_stream, &b->graph);  // always ends the recording, also after an error
+    for (int k = 0; k < MAX_SIDE; k++) {
+        if (join_ev[k]) cudaEventDestroy(join_ev[k]);
+        if (side[k]) cudaStreamDestroy(side[k]);
+    }
+    if (fork_ev) cudaEventDestroy(fork_ev);
     if (s != TTQ_OK || e != cudaSuccess) {
         host_batch_free(b);
         cudaGetLastError();
