@@ -627,7 +627,8 @@ ttq_status ttq_linear_forward_gated(ttq_ctx *ctx, const ttq_weight *w, const voi
 
 namespace {
 
-// Device mappings of page-locked host buffers (nullptr for pageable memory).  The driver query costs about a
+// Device-side addresses of the buffers of the host entry points: the mapping of a page-locked host buffer, a device
+// pointer as it is (nullptr for pageable memory).  The driver query costs about a
 // microsecond per pointer: buffers that come back call after call are remembered.
 void *host_mapping(ttq_ctx *ctx, const void *p) {
     const uintptr_t a = reinterpret_cast<uintptr_t>(p);
@@ -638,7 +639,8 @@ void *host_mapping(ttq_ctx *ctx, const void *p) {
         cudaGetLastError();
         return nullptr;
     }
-    if (at.type != cudaMemoryTypeHost) return nullptr;
+    // page-locked host memory through its device mapping; device (or managed) memory as it is
+    if (at.type != cudaMemoryTypeHost && at.type != cudaMemoryTypeDevice && at.type != cudaMemoryTypeManaged) return nullptr;
     slot = {p, at.devicePointer};
     return at.devicePointer;
 }

@@ -70,9 +70,11 @@ class Context:
 
 
 class HostBatch:
-    """A decode step's host-buffer linears, recorded once (``ttq_host_batch_create``) and run with one foreign call and
-    one wait per step.  ``items``: (QuantLinear, x, y) with x and y pinned, contiguous CPU tensors of decode size.
-    After ``run()`` returns every y holds its linear's result.  No bias: these are the plain projections of a step."""
+    """Independent linears recorded once (``ttq_host_batch_create``) and run with one foreign call and one wait per
+    step.  ``items``: (QuantLinear, x, y) with x and y contiguous tensors of decode size, either pinned CPU tensors or
+    tensors on the context's device.  The linears must not depend on each other (no y is another's x): the activations
+    of all decode-size linears are converted by one launch and those linears run side by side.  After ``run()`` returns
+    every y holds its linear's result.  No bias: these are the plain projections of a step."""
 
     def __init__(self, ctx: "Context", items):
         self.ctx = ctx
