@@ -187,7 +187,9 @@ typedef struct ttq_host_linear {
 /* Records `n` host-buffer linears (a decode step's worth) once, as a CUDA graph on the context's host stream, for
  * callers that run the same linears on the same buffers step after step (no counterpart in the reference).  The
  * buffers are page-locked host memory or device memory; the linears of a batch must not depend on each other (no y
- * of one is the x of another): the decode-size ones run side by side.  Same limits per linear as ttq_linear_forward_host_async.  The linears run once during the call
+ * of one is the x of another): the decode-size ones run side by side.  The batch runs on the context's own host
+ * stream: device buffers must have been written (their producing stream synchronised) before ttq_host_batch_run, and
+ * may be read once it has returned.  Same limits per linear as ttq_linear_forward_host_async.  The linears run once during the call
  * (every kernel is configured before the recording starts).  The activations of ALL decode-size linears
  * of the batch (one row; two rows below K = 8192; block formats) are converted by one launch at the head of the
  * graph, straight from the host buffers, so those linears run without an activation pass of their own; the

@@ -74,7 +74,8 @@ class HostBatch:
     step.  ``items``: (QuantLinear, x, y) with x and y contiguous tensors of decode size, either pinned CPU tensors or
     tensors on the context's device.  The linears must not depend on each other (no y is another's x): the activations
     of all decode-size linears are converted by one launch and those linears run side by side.  After ``run()`` returns
-    every y holds its linear's result.  No bias: these are the plain projections of a step."""
+    every y holds its linear's result.  The batch runs on the context's own stream: synchronise the stream that wrote
+    device inputs before ``run()``.  No bias: these are the plain projections of a step."""
 
     def __init__(self, ctx: "Context", items):
         self.ctx = ctx
