@@ -377,14 +377,27 @@ def ours_arm(args):
         # copy of the activations, the (row-parallel: fused-exchange) linear, one device -> host copy of the output;
         # one synchronisation per step; wall clock, maximum over ranks
         host = []
+        in_place = comm is not None
         for entry in layers:
             for name, lin, x, y in entry:
-                host.append((name, lin, x.cpu().pin_memory(), x, y, torch.empty(y.shape, dtype=y.dtype).pin_memory()))
+                xh, yh = x.cpu().pin_memory(), torch.empty(y.shape, dtype=y.dtype).pin_memory()
+                xa = ya = None
+                if in_place:
+                    # the kernels read x and write y in the pinned buffers themselves, through their device addresses
+                    xa, ya = _device_alias(xh, dev), _device_alias(yh, dev)
+                    in_place = xa is not None and ya is not None
+                host.append((name, lin, xh, x, y, yh, xa, ya))
                 h2d += x.numel() * x.element_size()
                 d2h += y.numel() * y.element_size()
 
         def e2e_step():
-            for name, lin, xh, x, y, yh in host:
+            for name, lin, xh, x, y, yh, xa, ya in host:
+                if in_place:
+                    if name in ("o", "down"):
+                        lin.forward_allreduce(xa, comm, out=ya)
+                    else:
+                        lin.forward(xa, out=ya)
+                    continue
                 x.copy_(xh, non_blocking=True)
                 if name in ("o", "down"):
                     if comm is not None:
@@ -408,8 +421,11 @@ def ours_arm(args):
         e2e_s = float(t.item())
         e2e = {"value": round(step_bytes / e2e_s / 1e9, 3), "unit": "GB/s", "h2d_bytes_per_step": h2d * world,
                "d2h_bytes_per_step": d2h * world, "ms_per_step": round(e2e_s * 1e3, 4), "steps": e2e_steps,
-               "api": "per rank and linear: pinned host -> device copy of x, QuantLinear.forward / forward_allreduce on the "
-                      "rank's shard, device -> pinned host copy of y; one sync per step; bytes summed over ranks"}
+               "api": ("per rank and linear: QuantLinear.forward / forward_allreduce on the rank's shard with x and y in pinned host "
+                       "memory (the kernels read and write them in place over the host link); one sync per step; bytes summed over ranks")
+                      if in_place else
+                      ("per rank and linear: pinned host -> device copy of x, QuantLinear.forward / forward_allreduce on the "
+                       "rank's shard, device -> pinned host copy of y; one sync per step; bytes summed over ranks")}
 
     # ---- per-shape breakdown (device-resident, cold L2: the 32 layers' copies are rotated)
     per_shape = {}
@@ -522,6 +538,27 @@ def ours_arm(args):
                                  "peak_source": "MEASURED_PEAKS.json bf16_tflops (burst)" if "bf16_tflops" in peaks else "fallback 1590"}
     print(json.dumps(line), flush=True)
     _finish_distributed(dist, world)
+
+
+class _PinnedView:
+    """The CUDA array interface of a pinned host tensor's bytes (16-bit elements)."""
+
+    def __init__(self, t):
+        self.keep = t
+        self.__cuda_array_interface__ = {"data": (t.data_ptr(), False), "shape": tuple(t.shape), "typestr": "<i2", "version": 2,
+                                         "strides": None}
+
+
+def _device_alias(t, dev):
+    """A CUDA tensor over the memory of pinned host tensor `t` (unified addressing: the device address of page-locked
+    memory allocated by the runtime is its host address), or None when that cannot be had."""
+    if t.element_size() != 2 or not t.is_pinned() or not t.is_contiguous():
+        return None
+    try:
+        alias = torch.as_tensor(_PinnedView(t), device=dev).view(t.dtype)
+        return alias if alias.data_ptr() == t.data_ptr() else None
+    except Exception:
+        return None
 
 
 def _linear_kernel_name(m: int) -> str:
