@@ -465,6 +465,26 @@ def ours_arm(args):
                 sweep[f"M{ms}_{k}x{n}"] = {"us": round(us, 2), "tflops": round(2.0 * ms * n * k / us / 1e6, 1),
                                             "gbs": round(algorithmic_bytes(ms, k, n) / us / 1e3, 1)}
                 del xs, ys
+        # the decode-batch sizes again as recorded batches of independent linears (ttq_host_batch_* on the device buffers):
+        # per shape the same 32 weights, wall clock around the synchronous run call
+        for ms in (2, 4, 8, 16):
+            for idx, (name, k, n) in enumerate(SHAPES):
+                lins = [layers[l][idx][1] for l in range(N_LAYERS)]
+                g = torch.Generator(device=dev).manual_seed(2100 + ms)
+                xs = torch.randn(ms, k, generator=g, device=dev).to(torch.bfloat16)
+                ybuf = [torch.empty(ms, n, dtype=torch.bfloat16, device=dev) for _ in lins]
+                torch.cuda.synchronize()
+                batch = ttq.HostBatch(ctx, [(lin, xs, y) for lin, y in zip(lins, ybuf)])
+                for _ in range(2):
+                    batch.run()
+                t0 = time.perf_counter()
+                for _ in range(4):
+                    batch.run()
+                us = (time.perf_counter() - t0) / 4 / len(lins) * 1e6
+                batch.close()
+                sweep[f"M{ms}_{k}x{n}"]["batched_us"] = round(us, 2)
+                sweep[f"M{ms}_{k}x{n}"]["batched_gbs"] = round(algorithmic_bytes(ms, k, n) / us / 1e3, 1)
+                del xs, ybuf
         ctx.check_device_status()
 
     # ---- the other half of the metric: decode tokens/s of the full decoder stack (one GPU)

@@ -193,7 +193,8 @@ typedef struct ttq_host_linear {
  * (every kernel is configured before the recording starts).  The activations of ALL decode-size linears
  * of the batch (one row; two rows below K = 8192; block formats) are converted by one launch at the head of the
  * graph, straight from the host buffers, so those linears run without an activation pass of their own; the
- * activations of the other linears are copied to the device by one gather launch.  Either way all reads over the host
+ * activations of the other linears are copied to the device by one gather launch (Q4_K linears of up to 16 rows then
+ * run side by side as well, each forked stream with a K-split workspace of its own; larger ones run in order).  Either way all reads over the host
  * link are in flight together.  Allocates the device storage for both; the results are written to the host buffers
  * by the linears themselves.  Weights and buffers must outlive the batch; create
  * every weight of the context before recording (see ttq_linear_forward on scratch that may move). */

@@ -731,6 +731,8 @@ struct ttq_host_batch {
     void *table;   // device array of HostGatherItem
     void *planes;  // converted activations of the decode-size linears (batched activation pass)
     void *xitems;  // device array of XprepBatchItem
+    void *side_ws;        // per side stream: K-split partial sums of the one-launch Q4_K decode kernel ...
+    void *side_counters;  // ... and its arrival counters (zero between launches)
 };
 
 namespace {
@@ -763,6 +765,8 @@ void host_batch_free(ttq_host_batch *b) {
     cudaFree(b->table);
     cudaFree(b->planes);
     cudaFree(b->xitems);
+    cudaFree(b->side_ws);
+    cudaFree(b->side_counters);
     delete b;
 }
 
@@ -793,6 +797,7 @@ ttq_status ttq_host_batch_create(ttq_ctx *ctx, const ttq_host_linear *linears, i
     std::vector<HostGatherItem> items;
     std::vector<XprepBatchItem> xitems;
     std::vector<int> slot((size_t)n);  // index into xitems (>= 0) or -1 - index into items
+    std::vector<char> one_launch((size_t)n, 0);  // Q4_K batches of the one-launch decode kernel: staged x, side stream
     std::vector<size_t> offs;
     size_t stage_total = 0, longest = 0, planes_total = 0;
     int total_units = 0;
@@ -827,8 +832,11 @@ ttq_status ttq_host_batch_create(ttq_ctx *ctx, const ttq_host_linear *linears, i
             longest = xb > longest ? xb : longest;
             slot[i] = -1 - (int)items.size();
             items.push_back(it);
+            one_launch[i] = l.w->fmt == TTQ_FMT_Q4_K && l.M <= 16 && (l.M >= 3 || (l.M == 2 && l.w->SBp >= 32));
         }
     }
+    bool any_one_launch = false;
+    for (int i = 0; i < n; i++) any_one_launch = any_one_launch || one_launch[i];
     cudaError_t e = cudaSuccess;
     if (!items.empty()) {
         e = cudaMalloc(&b->stage, stage_total);
@@ -852,6 +860,27 @@ ttq_status ttq_host_batch_create(ttq_ctx *ctx, const ttq_host_linear *linears, i
         host_batch_free(b);
         return cuda_fail(ctx, e, "host batch staging");
     }
+    // side streams of the recording (see below) and what they need, settled before the recording starts
+    static const int n_side_env = []() {
+        const char *v = getenv("TTQ_HOST_BATCH_STREAMS");
+        return v ? atoi(v) : 4;
+    }();
+    constexpr int MAX_SIDE = 8;
+    int side_work = (int)xitems.size();
+    for (int i = 0; i < n; i++) side_work += one_launch[i];
+    const int n_side = side_work < 2 ? 1 : (n_side_env < 1 ? 1 : (n_side_env > MAX_SIDE ? MAX_SIDE : n_side_env));
+    if (any_one_launch && n_side > 1) {
+        // the one-launch decode kernel sums K-split partials through a workspace: one per side stream (the linears of a
+        // stream run in order)
+        e = cudaMalloc(&b->side_ws, (size_t)n_side * SPLIT_WS_BYTES);
+        if (e == cudaSuccess) e = cudaMalloc(&b->side_counters, (size_t)n_side * SPLIT_COUNTERS * sizeof(unsigned));
+        if (e == cudaSuccess) e = cudaMemsetAsync(b->side_counters, 0, (size_t)n_side * SPLIT_COUNTERS * sizeof(unsigned), nullptr);
+        if (e == cudaSuccess) e = cudaDeviceSynchronize();
+        if (e != cudaSuccess) {
+            host_batch_free(b);
+            return cuda_fail(ctx, e, "host batch workspaces");
+        }
+    }
     e = cudaStreamBeginCapture(ctx->host_stream, cudaStreamCaptureModeThreadLocal);
     if (e != cudaSuccess) {
         host_batch_free(b);
@@ -871,12 +900,6 @@ ttq_status ttq_host_batch_create(ttq_ctx *ctx, const ttq_host_linear *linears, i
     // their own): they are recorded round-robin on a few side streams that fork from the head of the graph, so that the
     // last CTAs of one linear and the first of the next run side by side instead of a dependent launch apart.
     // TTQ_HOST_BATCH_STREAMS (default 4, 1 = one chain).  The other linears share the context's scratch and stay in line.
-    static const int n_side_env = []() {
-        const char *v = getenv("TTQ_HOST_BATCH_STREAMS");
-        return v ? atoi(v) : 4;
-    }();
-    constexpr int MAX_SIDE = 8;
-    const int n_side = xitems.size() < 2 ? 1 : (n_side_env < 1 ? 1 : (n_side_env > MAX_SIDE ? MAX_SIDE : n_side_env));
     cudaStream_t side[MAX_SIDE] = {};
     cudaEvent_t fork_ev = nullptr, join_ev[MAX_SIDE] = {};
     if (n_side > 1) {
@@ -909,8 +932,27 @@ ttq_status ttq_host_batch_create(ttq_ctx *ctx, const ttq_host_linear *linears, i
                             ctx->dev_status, nullptr, lst, &launches, nullptr, true);
             if (e != cudaSuccess) s = cuda_fail(ctx, e, "linear forward (batched activations) launch");
         } else {
-            s = ttq_linear_forward(ctx, l.w, items[(size_t)(-1 - slot[i])].dst, (ttq_dtype)l.x_dt, l.M, l.ldx, b_map, (ttq_dtype)l.bias_dt, y_map,
-                                   (ttq_dtype)l.y_dt, l.ldy, ctx->host_stream);
+            const void *xs = items[(size_t)(-1 - slot[i])].dst;
+            bool done = false;
+            if (one_launch[i] && n_side > 1 && b->side_ws != nullptr) {
+                const int k = next_side++ % n_side;
+                LinearArgs a;
+                a.tiles = l.w->tiles;
+                a.N = l.w->N; a.K = l.w->K; a.NT = l.w->NT; a.SBp = l.w->SBp;
+                a.x = xs; a.x_dt = l.x_dt; a.M = l.M; a.ldx = l.ldx;
+                a.bias = b_map; a.bias_dt = l.bias_dt;
+                a.y = y_map; a.y_dt = l.y_dt; a.ldy = l.ldy;
+                a.gated = false;
+                int launches = 0;
+                e = launch_q4k_mma(a, ctx->sms, ctx->dev_status, nullptr, reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(b->side_ws) + (size_t)k * SPLIT_WS_BYTES),
+                                   SPLIT_WS_BYTES, reinterpret_cast<unsigned *>(b->side_counters) + (size_t)k * SPLIT_COUNTERS, SPLIT_COUNTERS, side[k],
+                                   &launches);
+                if (e == cudaSuccess) done = true;
+                else if (e != cudaErrorNotSupported) s = cuda_fail(ctx, e, "linear forward (batched, one-launch decode) launch");
+            }
+            if (!done && s == TTQ_OK)
+                s = ttq_linear_forward(ctx, l.w, xs, (ttq_dtype)l.x_dt, l.M, l.ldx, b_map, (ttq_dtype)l.bias_dt, y_map, (ttq_dtype)l.y_dt, l.ldy,
+                                       ctx->host_stream);
         }
     }
     if (n_side > 1) {
