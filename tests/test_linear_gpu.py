@@ -208,6 +208,35 @@ def test_recorded_host_batch(ctx):
         lin.close()
 
 
+@pytest.mark.parametrize("m", [2, 5, 16, 17])
+def test_recorded_batch_on_device_buffers(ctx, m):
+    """A recorded batch of Q4_K linears of several rows on device buffers: the linears of up to 16 rows run on the forked
+    streams (two rows of a long K and 3-16 rows: the one-launch decode kernel with a workspace per stream), 17 rows stay in
+    line; every y is bit-identical to the stand-alone forward on the same input, run after run."""
+    fmt = ttq.FMT_Q4_K
+    lins = [ttq.QuantLinear(ctx, fmt, torch.from_numpy(make_weight(fmt, n, k, seed=90 + i)), k)
+            for i, (n, k) in enumerate([(512, 1024), (256, 8192), (1000, 512)])]
+    items = []
+    for i, lin in enumerate(lins * 2):
+        x = make_x(m, lin.in_features, 200 + i).cuda()
+        items.append((lin, x, torch.zeros(m, lin.out_features, dtype=torch.bfloat16, device="cuda")))
+    torch.cuda.synchronize()
+    batch = ttq.HostBatch(ctx, items)
+    for rep in range(2):
+        for _, _, y in items:
+            y.zero_()
+        torch.cuda.synchronize()
+        batch.run()
+        for lin, x, y in items:
+            want = lin.forward(x)
+            torch.cuda.synchronize()
+            assert torch.equal(want, y)
+    batch.close()
+    ctx.check_device_status()
+    for lin in lins:
+        lin.close()
+
+
 def test_config1_q8_0_decode(ctx):
     """Single Q8_0 linear, M=1, K=N=4096, fp16 activations, fp32 output."""
     rng = np.random.default_rng(1001)
