@@ -75,7 +75,7 @@ class HostBatch:
     tensors on the context's device.  The linears must not depend on each other (no y is another's x): the activations
     of all decode-size linears are converted by one launch and those linears run side by side.  After ``run()`` returns
     every y holds its linear's result.  The batch runs on the context's own stream: synchronise the stream that wrote
-    device inputs before ``run()``.  No bias: these are the plain projections of a step."""
+    device inputs before ``run()``.  A linear's bias (a device tensor) is added as in ``forward``."""
 
     def __init__(self, ctx: "Context", items):
         self.ctx = ctx
@@ -87,7 +87,10 @@ class HostBatch:
             if x2.data_ptr() != x.data_ptr() or y2.data_ptr() != y.data_ptr() or not x2.is_contiguous() or not y2.is_contiguous():
                 raise TtqError(1, "x and y must be contiguous host tensors")
             slot.w, slot.x_host, slot.x_dt, slot.M, slot.ldx = lin.handle, x2.data_ptr(), _dt(x2.dtype), x2.shape[0], lin.in_features
-            slot.bias_host, slot.bias_dt = None, _lib.DT_F32
+            if lin.bias is not None:
+                slot.bias_host, slot.bias_dt = lin.bias.data_ptr(), _dt(lin.bias.dtype)
+            else:
+                slot.bias_host, slot.bias_dt = None, _lib.DT_F32
             slot.y_host, slot.y_dt, slot.ldy = y2.data_ptr(), _dt(y2.dtype), lin.out_features
         handle = ctypes.c_void_p()
         check(ctx.handle, ctx._lib.ttq_host_batch_create(ctx.handle, arr, len(self._keep), ctypes.byref(handle)))

@@ -214,7 +214,8 @@ def test_recorded_batch_on_device_buffers(ctx, m):
     streams (two rows of a long K and 3-16 rows: the one-launch decode kernel with a workspace per stream), 17 rows stay in
     line; every y is bit-identical to the stand-alone forward on the same input, run after run."""
     fmt = ttq.FMT_Q4_K
-    lins = [ttq.QuantLinear(ctx, fmt, torch.from_numpy(make_weight(fmt, n, k, seed=90 + i)), k)
+    lins = [ttq.QuantLinear(ctx, fmt, torch.from_numpy(make_weight(fmt, n, k, seed=90 + i)), k,
+                            bias=(torch.randn(n, generator=torch.Generator().manual_seed(i)) * 0.1).cuda() if i == 0 else None)
             for i, (n, k) in enumerate([(512, 1024), (256, 8192), (1000, 512)])]
     items = []
     for i, lin in enumerate(lins * 2):
