@@ -810,7 +810,12 @@ ttq_status ttq_host_batch_create(ttq_ctx *ctx, const ttq_host_linear *linears, i
         const ttq_host_linear &l = linears[i];
         const void *x_map = host_mapping(ctx, l.x_host);  // (the first pass has already refused pageable buffers)
         const size_t xb = (size_t)l.M * l.ldx * dt_size((ttq_dtype)l.x_dt);
-        const bool decode = (l.M == 1 || (l.M == 2 && l.w->SBp < 32)) && gemv_prepared_supported(l.w->fmt, l.M, l.w->SBp);
+        // one row always; two rows below K = 8192 (as in ttq_linear_forward); three and four rows only for weights of up to
+        // 24 MB, where the small GEMV CTAs of neighbouring launches share the SMs (measured in batches: 4096 -> 4096 at four
+        // rows 5.7 against 8.9 us with the one-launch kernel, 4096 -> 28672 27.8 against 22.5)
+        const size_t packed = l.w->tiled_bytes;
+        const bool decode = (l.M == 1 || (l.M == 2 && l.w->SBp < 32) || (l.M <= 4 && l.w->SBp < 32 && packed <= (24u << 20))) &&
+                            gemv_prepared_supported(l.w->fmt, l.M, l.w->SBp);
         if (decode) {
             const int64_t Kp = l.w->SBp * TILE_K;
             XprepBatchItem it;

@@ -208,11 +208,12 @@ def test_recorded_host_batch(ctx):
         lin.close()
 
 
-@pytest.mark.parametrize("m", [2, 5, 16, 17])
+@pytest.mark.parametrize("m", [2, 4, 5, 16, 17])
 def test_recorded_batch_on_device_buffers(ctx, m):
     """A recorded batch of Q4_K linears of several rows on device buffers: the linears of up to 16 rows run on the forked
     streams (two rows of a long K and 3-16 rows: the one-launch decode kernel with a workspace per stream), 17 rows stay in
-    line; every y is bit-identical to the stand-alone forward on the same input, run after run."""
+    line; every y is bit-identical to the stand-alone forward on the same input, run after run (within bf16 rounding at 3-4
+    rows, where a batch serves small weights with another kernel than the stand-alone call)."""
     fmt = ttq.FMT_Q4_K
     lins = [ttq.QuantLinear(ctx, fmt, torch.from_numpy(make_weight(fmt, n, k, seed=90 + i)), k,
                             bias=(torch.randn(n, generator=torch.Generator().manual_seed(i)) * 0.1).cuda() if i == 0 else None)
@@ -231,7 +232,11 @@ def test_recorded_batch_on_device_buffers(ctx, m):
         for lin, x, y in items:
             want = lin.forward(x)
             torch.cuda.synchronize()
-            assert torch.equal(want, y)
+            if m in (3, 4):
+                # small weights at 3-4 rows take the integer GEMV inside a batch, the one-launch fp16 kernel stand-alone
+                assert rel_l2(y.float().cpu().numpy(), want.float().cpu().numpy()) < 6e-3
+            else:
+                assert torch.equal(want, y)
     batch.close()
     ctx.check_device_status()
     for lin in lins:
