@@ -1281,20 +1281,42 @@ cudaError_t launch_cfg(const GemmParams &p, int sms, cudaStream_t st) {
     return launch_pdl(gemm_q4k_kernel<BM, NSUB, MODE>, dim3(grid), dim3(C::THREADS), (size_t)C::TOTAL, st, p);
 }
 
+// Pairs of CTAs the current device runs at once: the shared-memory opt-in is set on first use, and the driver is asked
+// how many clusters of two fit (SM counts per GPC may leave an SM without a partner).  0: the kernel cannot run here.
+int pair_slots(int sms) {
+    static int slots[64] = {};
+    static bool known[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    if (!known[dev]) {
+        known[dev] = true;
+        slots[dev] = 0;
+        if (cudaFuncSetAttribute(gemm_q4k_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GP_TOTAL) == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)(sms / 2 * 2));
+            cfg.blockDim = dim3(GP_THREADS);
+            cfg.dynamicSmemBytes = GP_TOTAL;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 2;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, gemm_q4k_pair_kernel, &cfg) == cudaSuccess) slots[dev] = n < sms / 2 ? n : sms / 2;
+        }
+        cudaGetLastError();
+    }
+    return slots[dev];
+}
+
 // pairs of CTAs (cluster of 2) over the output tiles; programmatic stream serialization like every other launch
 cudaError_t launch_pair(const GemmParams &p, int sms, cudaStream_t st) {
-    static bool configured[64] = {};
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return e;
-    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-    if (!configured[dev]) {
-        e = cudaFuncSetAttribute(gemm_q4k_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GP_TOTAL);
-        if (e != cudaSuccess) return e;
-        configured[dev] = true;
-    }
+    const int slots = pair_slots(sms);
+    if (slots < 1) return cudaErrorNotSupported;
     const int64_t tiles = ((p.N + 255) / 256) * ((p.Mp + 511) / 512);
-    const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
+    const int64_t pairs = tiles < slots ? tiles : slots;
     static const bool pdl = env_flag("TTQ_PDL", true);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(2 * pairs));
@@ -1475,12 +1497,12 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
         }();
         bool use_pair = false;
         if (pair_mode > 0 && !plain && fmt == TTQ_FMT_Q4_K && BM == 256 && nsub == 2 && splits == 1) {
-            const int64_t slots = sms / 2, m_full = Mp / 512, m_half = (Mp % 512) ? 1 : 0;
+            const int64_t slots = pair_slots(sms), m_full = Mp / 512, m_half = (Mp % 512) ? 1 : 0;
             const double c_full = 0.85 * iters + 8.0, c_half = 0.6 * iters + 6.0;
             auto makespan = [&](int64_t cols) {
                 const int64_t nf = cols * m_full, nt = nf + cols * m_half;
                 double t = 0;
-                for (int64_t k = 0; k < nt; k += slots) t += k < nf ? c_full : c_half;
+                for (int64_t k = 0; slots > 0 && k < nt; k += slots) t += k < nf ? c_full : c_half;
                 return t;
             };
             double best = makespan(n_tiles);
