@@ -187,7 +187,8 @@ def test_recorded_host_batch(ctx):
     for i, (n, k) in enumerate([(64, 512), (4096, 4096), (48, 256)]):
         blocks = make_weight(fmt, n, k, seed=60 + i)
         lin = ttq.QuantLinear(ctx, fmt, torch.from_numpy(blocks), k)
-        items.append((lin, make_x(1 + (i % 2), k, 70 + i).pin_memory(), torch.zeros(1 + (i % 2), n, dtype=torch.float32).pin_memory()))
+        rows = (1, 2, 5)[i]  # batched activation pass twice, gathered activations + one-launch kernel once
+        items.append((lin, make_x(rows, k, 70 + i).pin_memory(), torch.zeros(rows, n, dtype=torch.float32).pin_memory()))
         blocks_of.append(blocks)
     batch = ttq.HostBatch(ctx, items)
     for rep in range(3):
