@@ -1356,11 +1356,12 @@ cudaError_t launch_gemm(int fmt, const LinearArgs &a, __half *xh, int64_t xh_cap
         const char *v = getenv("TTQ_GEMM_NSUB");
         return v ? atoi(v) : 0;
     }();
-    // a CTA with two sub-tiles does twice the work per activation stage in about 1.7x the time of one (measured; the
-    // single sub-tile is expanded by two warp groups on alternating stages)
+    // a CTA with two sub-tiles does twice the work per activation stage in about 1.65x the time of one (measured: five
+    // rounds of one sub-tile against three of two on 4096 -> 28672 at 768 rows take 221 against 203 us; the single
+    // sub-tile is expanded by two warp groups on alternating stages)
     const int64_t mt = (a.M + BM - 1) / BM;
     const int64_t tiles1 = ((a.N + 127) / 128) * mt, tiles2 = ((a.N + 255) / 256) * mt;
-    const double cost1 = (double)((tiles1 + sms - 1) / sms), cost2 = 1.7 * (double)((tiles2 + sms - 1) / sms);
+    const double cost1 = (double)((tiles1 + sms - 1) / sms), cost2 = 1.65 * (double)((tiles2 + sms - 1) / sms);
     int nsub = (a.N > 128 && cost2 < cost1) ? 2 : 1;
     if (force_nsub == 1 || force_nsub == 2) nsub = force_nsub;
     if (plain || fmt != TTQ_FMT_Q4_K) nsub = 2;  // plain: no conversion work to balance; Q8_0 / Q6_K: one variant
